@@ -216,7 +216,8 @@ LexResult lex(const char* s, size_t n) {
                     q++;
                 }
                 if (closed) { p = q + 2; continue; }
-                r.errors.push_back({T_ERROR, (uint32_t)p, (uint32_t)n});   // unterminated comment
+                // unterminated comment: reported at the end of the input (the span of a lex error is unpinned)
+                r.errors.push_back({T_ERROR, (uint32_t)n, (uint32_t)n});
                 p = n;
                 continue;
             }
