@@ -1,0 +1,142 @@
+// Sequential host backend for the front-end pipeline.  TEST INFRASTRUCTURE: it runs the product's own step bodies
+// (zluda_b200/csrc/ptxfe_pipeline.h) one index at a time on the CPU so that the lexer, the unit speculation, the
+// decoders and the record format can be checked against the oracle on a machine without a GPU.  It is not linked
+// into the product library and is never a fallback for it.
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <math.h>
+#include <string>
+#include <vector>
+
+#define PTX_HD
+#define PTX_TABLE static const
+#include "../../zluda_b200/csrc/ptx_dump.h"
+
+struct HostBackend {
+    std::vector<void*> blocks;
+    ~HostBackend() { for (void* p : blocks) free(p); }
+    void* alloc(size_t bytes) {
+        void* p = calloc(bytes + 64, 1);
+        blocks.push_back(p);
+        return p;
+    }
+    void zero(void* p, size_t bytes) { memset(p, 0, bytes); }
+    void download(void* host, const void* dev, size_t bytes) { memcpy(host, dev, bytes); }
+    template <class F> void pf(size_t n, F f) {
+        for (size_t i = 0; i < n; i++) f(i);
+    }
+    template <class T, class Ld, class St, class Op> void scan(size_t n, Ld ld, St st, Op op, T identity) {
+        T acc = identity;
+        for (size_t i = 0; i < n; i++) {
+            acc = op(acc, ld(i));
+            st(i, acc);
+        }
+    }
+};
+
+extern "C" {
+
+// Parse n modules; returns the dumps concatenated with '\0' separators (malloc'ed).  stats: tokens, units, words,
+// errors, modules that took the sequential path.
+char* emu_parse(const char* const* texts, const uint64_t* lens, uint32_t n, uint32_t mode, uint64_t* out_len, uint64_t* stats) {
+    HostBackend bk;
+    PtxWork w;
+    std::vector<PtxModuleLayout> layout(n);
+    std::vector<uint32_t> mcb(n + 1);
+    uint64_t off = 0;
+    uint32_t chunks = 0;
+    for (uint32_t m = 0; m < n; m++) {
+        layout[m].text_off = off;
+        layout[m].text_len = lens[m];
+        layout[m].chunk_begin = chunks;
+        layout[m].pad = 0;
+        mcb[m] = chunks;
+        uint32_t c = (uint32_t)((lens[m] + PTX_CHUNK - 1) / PTX_CHUNK);
+        chunks += c;
+        off += (uint64_t)c * PTX_CHUNK;
+    }
+    mcb[n] = chunks;
+    uint8_t* text = (uint8_t*)bk.alloc(off + 64);
+    for (uint32_t m = 0; m < n; m++) memcpy(text + layout[m].text_off, texts[m], lens[m]);
+    w.text = text;
+    w.n_modules = n;
+    w.n_chunks = chunks;
+    w.layout = layout.data();
+    w.mod_chunk_begin = mcb.data();
+    w.results = (PtxModuleResult*)bk.alloc(sizeof(PtxModuleResult) * (n + 1));
+    w.counters = (PtxCounters*)bk.alloc(sizeof(PtxCounters));
+    PtxCounters hc;
+    memset(&hc, 0, sizeof hc);
+    ptx_stage_lex(bk, w, hc);
+    ptx_stage_structure(bk, w, hc, mode);
+    ptx_stage_decode(bk, w, hc);
+    PtxBatchView v;
+    v.n_modules = n;
+    v.mode = mode;
+    v.layout = w.layout;
+    v.results = w.results;
+    v.words = w.words;
+    v.errs = w.errs;
+    v.lexerrs = w.lexerrs;
+    v.texts = texts;
+    std::string all;
+    uint64_t seq = 0;
+    for (uint32_t m = 0; m < n; m++) {
+        int st;
+        all += ptxdump::dump_module(v, m, &st);
+        all.push_back('\0');
+        seq += w.results[m].sequential;
+    }
+    if (stats) {
+        stats[0] = hc.n_tokens;
+        stats[1] = hc.n_units;
+        stats[2] = hc.n_words;
+        stats[3] = hc.n_errs;
+        stats[4] = seq;
+    }
+    char* r = (char*)malloc(all.size() + 1);
+    memcpy(r, all.data(), all.size());
+    *out_len = all.size();
+    return r;
+}
+
+// Tokens of one module: triples (kind, start, len), then lex errors (start, len).
+uint32_t* emu_lex(const char* text, uint64_t len, uint64_t* n_tokens, uint64_t* n_errors) {
+    HostBackend bk;
+    PtxWork w;
+    PtxModuleLayout layout;
+    layout.text_off = 0;
+    layout.text_len = len;
+    layout.chunk_begin = 0;
+    layout.pad = 0;
+    uint32_t mcb[2] = {0, (uint32_t)((len + PTX_CHUNK - 1) / PTX_CHUNK)};
+    uint8_t* t = (uint8_t*)bk.alloc(len + 256);
+    memcpy(t, text, len);
+    w.text = t;
+    w.n_modules = 1;
+    w.n_chunks = mcb[1];
+    w.layout = &layout;
+    w.mod_chunk_begin = mcb;
+    w.results = (PtxModuleResult*)bk.alloc(sizeof(PtxModuleResult) * 2);
+    w.counters = (PtxCounters*)bk.alloc(sizeof(PtxCounters));
+    PtxCounters hc;
+    memset(&hc, 0, sizeof hc);
+    ptx_stage_lex(bk, w, hc);
+    uint32_t* r = (uint32_t*)malloc(((size_t)hc.n_tokens * 3 + (size_t)hc.n_lexerrs * 2 + 1) * 4);
+    size_t k = 0;
+    for (uint32_t i = 0; i < hc.n_tokens; i++) {
+        r[k++] = w.tokens[i].kind;
+        r[k++] = w.tokens[i].start;
+        r[k++] = ptx_token_len(t, w.tokens[i], len);
+    }
+    for (uint32_t i = 0; i < hc.n_lexerrs; i++) { r[k++] = w.lexerrs[2 * i]; r[k++] = w.lexerrs[2 * i + 1]; }
+    *n_tokens = hc.n_tokens;
+    *n_errors = hc.n_lexerrs;
+    return r;
+}
+
+uint64_t emu_parse_f64(const char* s, uint32_t len) { return ptx_parse_f64((const uint8_t*)s, len); }
+void emu_free(void* p) { free(p); }
+}

@@ -1,0 +1,335 @@
+// Byte-parallel PTX lexer: per-thread pieces (host/device), used by the kernels in ptxfe.cu.
+//
+// Replaces the logos-generated lexer that ptx_parser drives in parse_module_checked
+// (ptx_parser/src/lib.rs:431-446; token set at lib.rs:1930-2030 plus one literal per opcode and modifier).
+//
+// The text of a batch is one device buffer; every module starts on a CHUNK boundary.  Lexing is split so that
+// no thread depends on its left neighbour:
+//   1. comment/string context is a 6-state automaton over raw bytes.  Each chunk computes its transition vector
+//      (all 6 start states at once, 4 bits each, packed in one 32-bit word); an exclusive scan with function
+//      composition gives every chunk its incoming state.
+//   2. inside code, every byte outside [A-Za-z0-9_$%.:+-] ends a token unconditionally, so a thread finds the
+//      first token boundary of its chunk by walking back over at most one run of those "soft" bytes and
+//      re-lexing that run; it then owns every token that starts inside its chunk (a token may run past the end).
+#pragma once
+#include "gen/ptx_tables.h"
+
+#define PTX_CHUNK 128u
+
+enum { CX_CODE = 0, CX_SLASH = 1, CX_LINE = 2, CX_BLOCK = 3, CX_STAR = 4, CX_STR = 5, CX_STATES = 6 };
+#define CX_IDENTITY 0x543210u
+
+// one token: byte offset in the batch text, length (0xFFFF = longer; re-lex to get it), kind (PtxTok)
+struct PtxToken {
+    uint32_t start;
+    uint16_t len;
+    uint16_t kind;
+};
+
+PTX_HD inline int cx_step(int s, unsigned c) {
+    switch (s) {
+    case CX_CODE: return c == '/' ? CX_SLASH : c == '"' ? CX_STR : CX_CODE;
+    case CX_SLASH: return c == '/' ? CX_LINE : c == '*' ? CX_BLOCK : c == '"' ? CX_STR : CX_CODE;
+    case CX_LINE: return (c == '\n' || c == '\r') ? CX_CODE : CX_LINE;
+    case CX_BLOCK: return c == '*' ? CX_STAR : CX_BLOCK;
+    case CX_STAR: return c == '/' ? CX_CODE : c == '*' ? CX_STAR : CX_BLOCK;
+    default: return c == '"' ? CX_CODE : CX_STR;
+    }
+}
+
+// transition vector of one byte: nibble i = state reached from state i
+PTX_HD inline uint32_t cx_byte_vector(unsigned c) {
+    switch (c) {
+    case '/': return (CX_SLASH) | (CX_LINE << 4) | (CX_LINE << 8) | (CX_BLOCK << 12) | (CX_CODE << 16) | (CX_STR << 20);
+    case '*': return (CX_CODE) | (CX_BLOCK << 4) | (CX_LINE << 8) | (CX_STAR << 12) | (CX_STAR << 16) | (CX_STR << 20);
+    case '"': return (CX_STR) | (CX_STR << 4) | (CX_LINE << 8) | (CX_BLOCK << 12) | (CX_BLOCK << 16) | (CX_CODE << 20);
+    case '\n': case '\r':
+        return (CX_CODE) | (CX_CODE << 4) | (CX_CODE << 8) | (CX_BLOCK << 12) | (CX_BLOCK << 16) | (CX_STR << 20);
+    default: return (CX_CODE) | (CX_CODE << 4) | (CX_LINE << 8) | (CX_BLOCK << 12) | (CX_BLOCK << 16) | (CX_STR << 20);
+    }
+}
+
+// (f then g): result[i] = g[f[i]]
+PTX_HD inline uint32_t cx_compose(uint32_t f, uint32_t g) {
+    uint32_t r = 0;
+#pragma unroll
+    for (int i = 0; i < CX_STATES; i++) {
+        uint32_t mid = (f >> (4 * i)) & 7u;
+        r |= ((g >> (4 * mid)) & 7u) << (4 * i);
+    }
+    return r;
+}
+// a vector that ignores its input and always yields the state reached from CX_CODE (first chunk of a module)
+PTX_HD inline uint32_t cx_restart(uint32_t f) { return (f & 7u) * 0x111111u; }
+
+// transition vector of text[begin, end)
+PTX_HD inline uint32_t cx_chunk_vector(const uint8_t* text, uint64_t begin, uint64_t end) {
+    // only '/', '*', '"', newline and the byte after '/' or '*' can change the vector; track the six states directly
+    int s0 = 0, s1 = 1, s2 = 2, s3 = 3, s4 = 4, s5 = 5;
+    for (uint64_t p = begin; p < end; p++) {
+        unsigned c = text[p];
+        s0 = cx_step(s0, c); s1 = cx_step(s1, c); s2 = cx_step(s2, c);
+        s3 = cx_step(s3, c); s4 = cx_step(s4, c); s5 = cx_step(s5, c);
+    }
+    return s0 | (s1 << 4) | (s2 << 8) | (s3 << 12) | (s4 << 16) | (s5 << 20);
+}
+
+// ------------------------------------------------------------------------------------------------ character classes
+PTX_HD inline bool lx_alpha(unsigned c) { return ((c | 32u) - 'a') < 26u; }
+PTX_HD inline bool lx_digit(unsigned c) { return (c - '0') < 10u; }
+PTX_HD inline bool lx_alnum(unsigned c) { return lx_alpha(c) || lx_digit(c); }
+PTX_HD inline bool lx_identc(unsigned c) { return lx_alnum(c) || c == '_' || c == '$'; }
+PTX_HD inline bool lx_sigil(unsigned c) { return c == '_' || c == '$' || c == '%'; }
+PTX_HD inline bool lx_ws(unsigned c) { return c == ' ' || (c - 9u) < 5u; }
+// bytes that can continue or join tokens; every other byte is an unconditional token boundary in code
+PTX_HD inline bool lx_soft(unsigned c) { return lx_identc(c) || c == '%' || c == '.' || c == ':' || c == '+' || c == '-'; }
+
+// ------------------------------------------------------------------------------------------------ keyword lookup
+PTX_HD inline uint16_t lx_keyword(const uint8_t* s, uint32_t len) {
+    if (len > PTX_KW_MAXLEN) return T_ERROR;
+    uint32_t h = 2166136261u;
+    for (uint32_t i = 0; i < len; i++) h = (h ^ s[i]) * PTX_KW_MULT;
+    h = (h ^ (h >> 15)) & (PTX_KW_SIZE - 1);
+    for (;;) {
+        PtxKwEntry e = ptx_kw_table[h];
+        if (e.kind == 0xFFFF) return T_ERROR;
+        if (e.len == len) {
+            bool same = true;
+            for (uint32_t i = 0; i < len; i++)
+                if ((uint8_t)ptx_kw_pool[e.off + i] != s[i]) { same = false; break; }
+            if (same) return e.kind;
+        }
+        h = (h + 1) & (PTX_KW_SIZE - 1);
+    }
+}
+
+// ".L1::" ".L2::" ".param::" ".shared::" literals: `p` is at the '.', `q` at the first ':' ; returns the literal's
+// length and kind when the text continues with one of the known suffixes (longest match beats the DotIdent prefix)
+PTX_HD inline uint32_t lx_colon_literal(const uint8_t* s, uint64_t p, uint64_t q, uint64_t n, uint16_t* kind) {
+    uint64_t r = q + 2;
+    if (r >= n) return 0;
+    uint64_t e = r;
+    while (e < n && e < r + 16 && lx_identc(s[e])) e++;
+    // try every prefix length of the suffix run, longest first: the literal is a prefix of the text
+    for (uint64_t end = e; end > r; end--) {
+        uint16_t k = lx_keyword(s + p, (uint32_t)(end - p));
+        if (k != T_ERROR) { *kind = k; return (uint32_t)(end - p); }
+    }
+    return 0;
+}
+
+// Longest token at p (p < n; text[p] is not whitespace, '/', or '"').  Returns its kind; *len = its length.
+// T_ERROR: no rule matches here (*len = 1).
+PTX_HD inline uint16_t lx_one(const uint8_t* s, uint64_t p, uint64_t n, uint32_t* len) {
+    unsigned c = s[p];
+    switch (c) {
+    case ',': *len = 1; return T_COMMA;
+    case ':': *len = 1; return T_COLON;
+    case ';': *len = 1; return T_SEMI;
+    case '@': *len = 1; return T_AT;
+    case '|': *len = 1; return T_PIPE;
+    case '!': *len = 1; return T_EXCL;
+    case '(': *len = 1; return T_LPAREN;
+    case ')': *len = 1; return T_RPAREN;
+    case '[': *len = 1; return T_LBRACKET;
+    case ']': *len = 1; return T_RBRACKET;
+    case '{': *len = 1; return T_LBRACE;
+    case '}': *len = 1; return T_RBRACE;
+    case '<': *len = 1; return T_LT;
+    case '>': *len = 1; return T_GT;
+    case '-': *len = 1; return T_MINUS;
+    case '+': *len = 1; return T_PLUS;
+    case '=': *len = 1; return T_EQ;
+    default: break;
+    }
+    if (lx_alpha(c) || lx_sigil(c)) {
+        uint64_t q = p + 1;
+        while (q < n && lx_identc(s[q])) q++;
+        if (lx_sigil(c) && q == p + 1) { *len = 1; return T_ERROR; }
+        *len = (uint32_t)(q - p);
+        if (lx_alpha(c)) {
+            uint16_t k = lx_keyword(s + p, (uint32_t)(q - p));
+            if (k != T_ERROR) return k;
+        }
+        return T_IDENT;
+    }
+    if (c == '.') {
+        unsigned d = p + 1 < n ? s[p + 1] : 0;
+        if (lx_alpha(d) || lx_sigil(d)) {
+            uint64_t q = p + 2;
+            while (q < n && lx_identc(s[q])) q++;
+            if (lx_sigil(d) && q == p + 2) { *len = 1; return T_DOT; }
+            if (q + 1 < n && s[q] == ':' && s[q + 1] == ':') {
+                uint16_t k;
+                uint32_t l = lx_colon_literal(s, p, q, n, &k);
+                if (l) { *len = l; return k; }
+            }
+            *len = (uint32_t)(q - p);
+            uint16_t k = lx_keyword(s + p, (uint32_t)(q - p));
+            return k != T_ERROR ? k : (uint16_t)T_DOTIDENT;
+        }
+        if (lx_digit(d)) {
+            if ((d == '1' || d == '2' || d == '3') && p + 2 < n && s[p + 2] == 'd') {
+                *len = 3;
+                return lx_keyword(s + p, 3);
+            }
+            uint64_t q = p + 1;
+            while (q < n && lx_digit(s[q])) q++;
+            if (q < n && (s[q] | 32u) == 'e') {
+                uint64_t r = q + 1;
+                if (r < n && (s[r] == '-' || s[r] == '+')) r++;
+                if (r < n && lx_digit(s[r])) {
+                    while (r < n && lx_digit(s[r])) r++;
+                    q = r;
+                }
+            }
+            *len = (uint32_t)(q - p);
+            return T_F64;
+        }
+        *len = 1;
+        return T_DOT;
+    }
+    if (lx_digit(c)) {
+        if (c == '0' && p + 1 < n) {
+            unsigned d = s[p + 1] | 32u;
+            if (d == 'x') {
+                uint64_t q = p + 2;
+                while (q < n && lx_alnum(s[q])) q++;
+                if (q > p + 2) { *len = (uint32_t)(q - p); return T_HEX; }
+            } else if (d == 'f' || d == 'd') {
+                uint64_t need = d == 'f' ? 8 : 16;
+                uint64_t q = p + 2;
+                while (q < n && q < p + 2 + need && lx_alnum(s[q])) q++;
+                if (q == p + 2 + need) { *len = (uint32_t)(q - p); return d == 'f' ? T_F32HEX : T_F64HEX; }
+            }
+        }
+        uint64_t q = p + 1;
+        while (q < n && lx_digit(s[q])) q++;
+        if (q + 1 < n && s[q] == '.' && lx_digit(s[q + 1])) {
+            uint64_t r = q + 1;
+            while (r < n && lx_digit(s[r])) r++;
+            if (r < n && (s[r] | 32u) == 'e') {
+                uint64_t e = r + 1;
+                if (e < n && (s[e] == '-' || s[e] == '+')) e++;
+                if (e < n && lx_digit(s[e])) {
+                    while (e < n && lx_digit(s[e])) e++;
+                    r = e;
+                }
+            }
+            *len = (uint32_t)(r - p);
+            return T_F64;
+        }
+        if (q < n && s[q] == 'U') q++;
+        *len = (uint32_t)(q - p);
+        return T_DECIMAL;
+    }
+    *len = 1;
+    return T_ERROR;
+}
+
+// ------------------------------------------------------------------------------------------------ chunk lexing
+// Sink concept: void token(uint64_t start, uint32_t len, uint16_t kind); void error(uint64_t start, uint32_t len);
+struct LexCountSink {
+    uint32_t n_tokens = 0, n_errors = 0;
+    PTX_HD void token(uint64_t, uint32_t, uint16_t) { n_tokens++; }
+    PTX_HD void error(uint64_t, uint32_t) { n_errors++; }
+};
+struct LexWriteSink {
+    PtxToken* tokens;      // already offset to this chunk's first slot
+    uint32_t* errors;      // pairs (start, len), already offset
+    uint32_t n_tokens = 0, n_errors = 0;
+    PTX_HD void token(uint64_t start, uint32_t len, uint16_t kind) {
+        PtxToken t;
+        t.start = (uint32_t)start;
+        t.len = len >= 0xFFFFu ? (uint16_t)0xFFFF : (uint16_t)len;
+        t.kind = kind;
+        tokens[n_tokens++] = t;
+    }
+    PTX_HD void error(uint64_t start, uint32_t len) {
+        errors[2 * n_errors] = (uint32_t)start;
+        errors[2 * n_errors + 1] = len;
+        n_errors++;
+    }
+};
+
+// Lex the tokens that START in [cs, ce) of a module occupying [ms, me).  `state` is the context at cs.
+template <class Sink>
+PTX_HD inline void lx_chunk(const uint8_t* s, uint64_t ms, uint64_t me, uint64_t cs, uint64_t ce, int state, Sink& out) {
+    if (ce > me) ce = me;
+    uint64_t p = cs;
+    if (state == CX_CODE && cs > ms && lx_soft(s[cs - 1]) && cs < me && lx_soft(s[cs])) {
+        // cs may be inside a token: re-lex the run of soft bytes that reaches into this chunk
+        uint64_t q = cs - 1;
+        while (q > ms && lx_soft(s[q - 1])) q--;
+        while (q < cs) {
+            uint32_t l;
+            lx_one(s, q, me, &l);
+            q += l;
+        }
+        p = q;
+    }
+    while (p < ce) {
+        unsigned c = s[p];
+        switch (state) {
+        case CX_CODE:
+            if (lx_ws(c)) { p++; break; }
+            if (c == '/') {
+                unsigned d = p + 1 < me ? s[p + 1] : 0;
+                if (d == '/') { state = CX_LINE; p += 2; }
+                else if (d == '*') { state = CX_BLOCK; p += 2; }
+                else { out.error(p, 1); p++; }
+                break;
+            }
+            if (c == '"') {
+                uint64_t q = p + 1;
+                while (q < me && s[q] != '"') q++;
+                if (q >= me) { out.error(p, (uint32_t)(me - p)); p = me; }
+                else { out.token(p, (uint32_t)(q + 1 - p), T_STRING); p = q + 1; }
+                break;
+            }
+            {
+                uint32_t l;
+                uint16_t k = lx_one(s, p, me, &l);
+                if (k == T_ERROR) out.error(p, l);
+                else out.token(p, l, k);
+                p += l;
+            }
+            break;
+        case CX_SLASH:   // the '/' is the last byte of the previous chunk; its owner already classified it
+            if (c == '/') { state = CX_LINE; p++; }
+            else if (c == '*') { state = CX_BLOCK; p++; }
+            else state = CX_CODE;
+            break;
+        case CX_LINE:
+            while (p < ce && s[p] != '\n' && s[p] != '\r') p++;
+            if (p < ce) state = CX_CODE;
+            break;
+        case CX_BLOCK:
+        case CX_STAR:
+            while (p < ce) {
+                unsigned b = s[p++];
+                if (state == CX_STAR && b == '/') { state = CX_CODE; break; }
+                state = b == '*' ? CX_STAR : CX_BLOCK;
+            }
+            break;
+        default:   // CX_STR: the string's owner emitted the token; skip to the closing quote
+            while (p < ce && s[p] != '"') p++;
+            if (p < ce) { p++; state = CX_CODE; }
+            break;
+        }
+    }
+    // an unterminated block comment is reported at the end of the module by the owner of its last byte
+    if (ce == me && p >= me && cs < me && (state == CX_BLOCK || state == CX_STAR)) out.error(me, 0);
+}
+
+PTX_HD inline uint32_t ptx_token_len(const uint8_t* s, const PtxToken& t, uint64_t me) {
+    if (t.len != 0xFFFF) return t.len;
+    if (t.kind == T_STRING) {
+        uint64_t q = (uint64_t)t.start + 1;
+        while (q < me && s[q] != '"') q++;
+        return (uint32_t)(q + 1 - t.start);
+    }
+    uint32_t l;
+    lx_one(s, t.start, me, &l);
+    return l;
+}

@@ -1,0 +1,495 @@
+// The front-end pipeline as a sequence of data-parallel steps (parallel-for over chunks, tokens or units) and prefix
+// scans, written once against a small backend interface.  The CUDA backend (ptxfe.cu) runs every step as a kernel on
+// the context's stream; the test suite has a sequential backend that runs the same step bodies on the host to check
+// the logic where no GPU is present.  No step reads another thread's work of the same step.
+//
+//   text -> [context vectors | scan] -> [count tokens | scan | emit tokens]
+//        -> [brace / paren classification | segmented scan] -> [unit starts | scan | compact]
+//        -> [decode units: count] -> [chain check per module] -> [scan sizes] -> [function table] -> [decode units: emit]
+#pragma once
+#include "ptx_units.h"
+
+struct PtxModuleLayout {
+    uint64_t text_off;    // byte offset in the batch text buffer (multiple of PTX_CHUNK)
+    uint64_t text_len;
+    uint32_t chunk_begin; // first chunk index
+    uint32_t pad;
+};
+
+// per-module results, copied to the host
+struct PtxModuleResult {
+    uint32_t tok_begin, tok_end;
+    uint32_t lexerr_begin, lexerr_end;
+    uint32_t unit_begin, unit_end;
+    uint32_t word_begin, word_end;
+    uint32_t err_begin, err_end;
+    uint32_t sequential;   // 1 = parsed by the sequential path
+    uint32_t status;       // PtxUnitStatus of the sequential path
+};
+
+struct PtxDepth {
+    int32_t scope, paren;
+};
+struct PtxSeg3 {
+    int32_t scope, paren, flag;
+};
+
+// token classification bits
+enum { TF_MODULE_FIRST = 1, TF_SCOPE_OPEN = 2, TF_SCOPE_CLOSE = 4, TF_UNIT_START = 8 };
+
+struct PtxCounters {
+    uint32_t n_tokens, n_lexerrs, n_units, n_words, n_errs, n_funcs, any_sequential, pad;
+};
+
+PTX_HD inline uint32_t ptx_upper_bound_u32(const uint32_t* a, uint32_t n, uint32_t x) {
+    // number of entries <= x
+    uint32_t lo = 0, hi = n;
+    while (lo < hi) {
+        uint32_t mid = (lo + hi) >> 1;
+        if (a[mid] <= x) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+
+// Device-resident working set of one batch.  Pointers are owned by the backend's arena.
+struct PtxWork {
+    const uint8_t* text = nullptr;
+    uint32_t n_modules = 0, n_chunks = 0;
+    PtxModuleLayout* layout = nullptr;     // [n_modules]
+    uint32_t* mod_chunk_begin = nullptr;   // [n_modules + 1]
+    uint32_t* chunk_vec = nullptr;         // [n_chunks] transition vectors, then inclusive prefix
+    PtxPair* chunk_cnt = nullptr;          // [n_chunks + 1] tokens/errors per chunk, then exclusive prefix
+    PtxToken* tokens = nullptr;            // [n_tokens]
+    uint32_t* lexerrs = nullptr;           // [2 * n_lexerrs]
+    uint32_t* mod_tok_begin = nullptr;     // [n_modules + 1]
+    uint8_t* tflags = nullptr;             // [n_tokens]
+    PtxDepth* depth = nullptr;             // [n_tokens] inclusive segmented scan of scope/paren deltas
+    uint32_t* unit_of_tok = nullptr;       // [n_tokens + 1] exclusive scan of unit-start flags
+    uint32_t* unit_start = nullptr;        // [n_units + 1]
+    uint32_t* unit_depth = nullptr;        // [n_units]  scope depth in front of the unit | module-first << 31
+    uint32_t* unit_end = nullptr;          // [n_units]
+    uint32_t* unit_dir = nullptr;          // [n_units]  inclusive scan of top-level flags
+    PtxPair* unit_size = nullptr;          // [n_units + 1] words/errors per unit, then exclusive prefix
+    uint8_t* unit_status = nullptr;        // [n_units]
+    uint32_t* mod_unit_begin = nullptr;    // [n_modules + 1]
+    uint32_t* mod_bad = nullptr;           // [n_modules]
+    uint32_t* mod_skip = nullptr;          // [n_modules] not parsed: lex errors (checked/unchecked mode) or no tokens
+    PtxPair* mod_seq_size = nullptr;       // [n_modules]
+    uint32_t* mod_seq_status = nullptr;    // [n_modules]
+    PtxFnEntry* fn_entries = nullptr;      // [n_funcs]
+    uint32_t* fn_slots = nullptr;          // [fn_mask + 1]
+    uint32_t fn_mask = 0;
+    uint32_t* words = nullptr;             // [n_words]
+    PtxErrRec* errs = nullptr;             // [n_errs]
+    PtxModuleResult* results = nullptr;    // [n_modules]
+    PtxCounters* counters = nullptr;       // device copy
+};
+
+struct ComposeOp {
+    PTX_HD uint32_t operator()(uint32_t a, uint32_t b) const { return cx_compose(a, b); }
+};
+struct PairAddOp {
+    PTX_HD PtxPair operator()(PtxPair x, PtxPair y) const { PtxPair r; r.a = x.a + y.a; r.b = x.b + y.b; return r; }
+};
+struct AddOp {
+    PTX_HD uint32_t operator()(uint32_t a, uint32_t b) const { return a + b; }
+};
+struct SegDepthOp {
+    PTX_HD PtxSeg3 operator()(PtxSeg3 x, PtxSeg3 y) const {
+        if (y.flag) return y;
+        PtxSeg3 r;
+        r.scope = x.scope + y.scope;
+        r.paren = x.paren + y.paren;
+        r.flag = x.flag;
+        return r;
+    }
+};
+
+// Backend concept:
+//   template <class F> void pf(size_t n, F f);                                  f(i) for i in [0, n)
+//   template <class T, class Op, class Ld, class St> void scan(size_t n, Ld ld, St st, Op op, T identity);
+//        inclusive scan: st(i, op(ld(0), ..., ld(i)))
+//   void* alloc(size_t bytes); void zero(void* p, size_t bytes);
+//   void download(void* host, const void* dev, size_t bytes);   (synchronises the stream)
+// The pipeline allocates through the backend and never frees: the backend's arena is reset per batch.
+
+// ------------------------------------------------------------------------------------------------ stage A: lexer
+template <class BK>
+inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
+    const uint8_t* text = w.text;
+    const PtxModuleLayout* layout = w.layout;
+    const uint32_t* mcb = w.mod_chunk_begin;
+    const uint32_t n_modules = w.n_modules, n_chunks = w.n_chunks;
+    uint32_t* vec = w.chunk_vec = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_chunks + 1));
+    PtxPair* cnt = w.chunk_cnt = (PtxPair*)bk.alloc(sizeof(PtxPair) * (n_chunks + 2));
+    w.mod_tok_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 2));
+    uint32_t* mod_lexerr_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 2));
+    PtxCounters* counters = w.counters;
+
+    // A1: transition vector of every chunk
+    bk.pf(n_chunks, [=] PTX_HD(size_t c) {
+        uint32_t m = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)c) - 1;
+        uint64_t cs = layout[m].text_off + (uint64_t)(c - mcb[m]) * PTX_CHUNK;
+        uint64_t me = layout[m].text_off + layout[m].text_len;
+        uint64_t ce = cs + PTX_CHUNK < me ? cs + PTX_CHUNK : me;
+        uint32_t v = cx_chunk_vector(text, cs, ce);
+        vec[c] = (c == mcb[m]) ? cx_restart(v) : v;
+    });
+    // A2: inclusive scan with composition; chunk c starts in state (prefix[c-1])[CODE]
+    bk.template scan<uint32_t>(n_chunks, [=] PTX_HD(size_t i) { return vec[i]; }, [=] PTX_HD(size_t i, uint32_t v) { vec[i] = v; },
+                               ComposeOp(), CX_IDENTITY);
+    // A3: count the tokens that start in every chunk
+    bk.pf(n_chunks, [=] PTX_HD(size_t c) {
+        uint32_t m = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)c) - 1;
+        uint64_t ms = layout[m].text_off, me = ms + layout[m].text_len;
+        uint64_t cs = ms + (uint64_t)(c - mcb[m]) * PTX_CHUNK;
+        int state = (c == mcb[m]) ? CX_CODE : (int)(vec[c - 1] & 7u);
+        LexCountSink sink;
+        lx_chunk(text, ms, me, cs, cs + PTX_CHUNK, state, sink);
+        PtxPair p;
+        p.a = sink.n_tokens;
+        p.b = sink.n_errors;
+        cnt[c + 1] = p;
+        if (c == 0) { PtxPair z; z.a = z.b = 0; cnt[0] = z; }
+    });
+    // A4: exclusive offsets (cnt[c] = tokens before chunk c; cnt[n_chunks] = total)
+    bk.template scan<PtxPair>(n_chunks + 1, [=] PTX_HD(size_t i) { return cnt[i]; }, [=] PTX_HD(size_t i, PtxPair v) { cnt[i] = v; },
+                              PairAddOp(), PtxPair{0, 0});
+    bk.pf(1, [=] PTX_HD(size_t) {
+        counters->n_tokens = n_chunks ? cnt[n_chunks].a : 0;
+        counters->n_lexerrs = n_chunks ? cnt[n_chunks].b : 0;
+    });
+    bk.download(&host_counters, counters, sizeof(PtxCounters));
+    const uint32_t n_tokens = host_counters.n_tokens, n_lexerrs = host_counters.n_lexerrs;
+    PtxToken* tokens = w.tokens = (PtxToken*)bk.alloc(sizeof(PtxToken) * (size_t)(n_tokens + 1));
+    uint32_t* lexerrs = w.lexerrs = (uint32_t*)bk.alloc(sizeof(uint32_t) * 2 * (size_t)(n_lexerrs + 1));
+    // A5: emit
+    bk.pf(n_chunks, [=] PTX_HD(size_t c) {
+        uint32_t m = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)c) - 1;
+        uint64_t ms = layout[m].text_off, me = ms + layout[m].text_len;
+        uint64_t cs = ms + (uint64_t)(c - mcb[m]) * PTX_CHUNK;
+        int state = (c == mcb[m]) ? CX_CODE : (int)(vec[c - 1] & 7u);
+        LexWriteSink sink;
+        sink.tokens = tokens + cnt[c].a;
+        sink.errors = lexerrs + 2 * (size_t)cnt[c].b;
+        lx_chunk(text, ms, me, cs, cs + PTX_CHUNK, state, sink);
+    });
+    uint32_t* mtb = w.mod_tok_begin;
+    bk.pf(n_modules + 1, [=] PTX_HD(size_t m) {
+        uint32_t c = mcb[m];   // mod_chunk_begin[n_modules] = n_chunks
+        mtb[m] = n_chunks ? cnt[c].a : 0;
+        mod_lexerr_begin[m] = n_chunks ? cnt[c].b : 0;
+    });
+    PtxModuleResult* results = w.results;
+    bk.pf(n_modules, [=] PTX_HD(size_t m) {
+        PtxModuleResult r;
+        r.tok_begin = mtb[m];
+        r.tok_end = mtb[m + 1];
+        r.lexerr_begin = mod_lexerr_begin[m];
+        r.lexerr_end = mod_lexerr_begin[m + 1];
+        r.unit_begin = r.unit_end = r.word_begin = r.word_end = r.err_begin = r.err_end = 0;
+        r.sequential = r.status = 0;
+        results[m] = r;
+    });
+}
+
+// ------------------------------------------------------------------------------------------------ stage B: structure
+PTX_HD inline bool ptx_opens_operand(uint16_t prev) {
+    // a '{' after one of these starts a vector operand or an initialiser, not a scope
+    return prev == T_COMMA || prev == T_EQ || prev == T_LPAREN || (prev >= T_OP_FIRST && prev < T_COUNT);
+}
+PTX_HD inline bool ptx_is_directive_start(uint16_t k) {
+    return k == T_DOT_EXTERN || k == T_DOT_VISIBLE || k == T_MOD_weak || k == T_DOT_FUNC || k == T_DOT_ENTRY ||
+           k == T_MOD_global || k == T_MOD_const || k == T_MOD_shared || k == T_DOT_FILE || k == T_DOT_SECTION;
+}
+
+template <class BK>
+inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, uint32_t mode) {
+    const uint32_t n_tokens = host_counters.n_tokens, n_modules = w.n_modules;
+    const PtxToken* tokens = w.tokens;
+    const uint32_t* mtb = w.mod_tok_begin;
+    const PtxModuleResult* results = w.results;
+    uint8_t* tflags = w.tflags = (uint8_t*)bk.alloc((size_t)n_tokens + 16);
+    PtxDepth* depth = w.depth = (PtxDepth*)bk.alloc(sizeof(PtxDepth) * ((size_t)n_tokens + 1));
+    uint32_t* uot = w.unit_of_tok = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_tokens + 2));
+    w.mod_unit_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 2));
+    PtxCounters* counters = w.counters;
+    uint32_t* mod_skip = w.mod_skip = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 1));
+    bk.zero(tflags, (size_t)n_tokens + 16);
+    // B0: mark the first token of every module.  A module with a lex error is not parsed unless only its errors
+    // are wanted (lib.rs:392-411 vs 447-449, 487-489)
+    bk.pf(n_modules, [=] PTX_HD(size_t m) {
+        if (mtb[m] < mtb[m + 1]) tflags[mtb[m]] = TF_MODULE_FIRST;
+        bool lexerr = results[m].lexerr_end > results[m].lexerr_begin;
+        mod_skip[m] = (mtb[m] == mtb[m + 1] || (lexerr && mode != 2)) ? 1u : 0u;
+    });
+    // B1: classify braces from their left neighbours
+    bk.pf(n_tokens, [=] PTX_HD(size_t i) {
+        uint16_t k = tokens[i].kind;
+        uint8_t f = tflags[i];
+        bool first = (f & TF_MODULE_FIRST) != 0;
+        uint16_t prev = first ? (uint16_t)0xFFFE : tokens[i - 1].kind;
+        if (k == T_LBRACE) {
+            bool section = false;
+            if (!first && i >= 2 && !(tflags[i - 1] & TF_MODULE_FIRST)) section = tokens[i - 2].kind == T_DOT_SECTION;
+            if (!ptx_opens_operand(prev) && !section) f |= TF_SCOPE_OPEN;
+        } else if (k == T_RBRACE) {
+            if (prev == T_SEMI || prev == T_COLON || prev == T_LBRACE || prev == T_RBRACE) f |= TF_SCOPE_CLOSE;
+        }
+        tflags[i] = f;
+    });
+    // B2: scope and paren depth, restarting at every module (inclusive)
+    bk.template scan<PtxSeg3>(
+        n_tokens,
+        [=] PTX_HD(size_t i) {
+            PtxSeg3 v;
+            uint8_t f = tflags[i];
+            uint16_t k = tokens[i].kind;
+            v.scope = (f & TF_SCOPE_OPEN) ? 1 : (f & TF_SCOPE_CLOSE) ? -1 : 0;
+            v.paren = k == T_LPAREN ? 1 : k == T_RPAREN ? -1 : 0;
+            v.flag = (f & TF_MODULE_FIRST) ? 1 : 0;
+            return v;
+        },
+        [=] PTX_HD(size_t i, PtxSeg3 v) {
+            PtxDepth d;
+            d.scope = v.scope;
+            d.paren = v.paren;
+            depth[i] = d;
+        },
+        SegDepthOp(), PtxSeg3{0, 0, 0});
+    // B3: speculate unit starts
+    bk.pf(n_tokens, [=] PTX_HD(size_t i) {
+        uint8_t f = tflags[i];
+        bool first = (f & TF_MODULE_FIRST) != 0;
+        bool start = first;
+        if (!first) {
+            int32_t sd = depth[i - 1].scope, pd = depth[i - 1].paren;
+            uint16_t k = tokens[i].kind;
+            uint8_t pf_ = tflags[i - 1];
+            uint16_t prev = tokens[i - 1].kind;
+            if (sd <= 0) {
+                // top level: a directive keyword outside parentheses that does not continue a run of linking keywords
+                start = sd == 0 && pd == 0 && ptx_is_directive_start(k) &&
+                        !(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak);
+                // the token after a function's closing brace or after a directive's terminator is not a start by
+                // itself: a well-formed module continues with a directive keyword there
+            } else {
+                start = (f & (TF_SCOPE_OPEN | TF_SCOPE_CLOSE)) != 0 || (pf_ & (TF_SCOPE_OPEN | TF_SCOPE_CLOSE)) != 0 ||
+                        prev == T_SEMI || prev == T_COLON;
+            }
+        }
+        if (start) tflags[i] = f | TF_UNIT_START;
+        uot[i + 1] = start ? 1u : 0u;
+        if (i == 0) uot[0] = 0;
+    });
+    bk.template scan<uint32_t>((size_t)n_tokens + 1, [=] PTX_HD(size_t i) { return uot[i]; },
+                               [=] PTX_HD(size_t i, uint32_t v) { uot[i] = v; }, AddOp(), 0u);
+    bk.pf(1, [=] PTX_HD(size_t) { counters->n_units = n_tokens ? uot[n_tokens] : 0; });
+    bk.download(&host_counters, counters, sizeof(PtxCounters));
+    const uint32_t n_units = host_counters.n_units;
+    uint32_t* ustart = w.unit_start = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 2));
+    uint32_t* udepth = w.unit_depth = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    // B5: compact
+    bk.pf(n_tokens, [=] PTX_HD(size_t i) {
+        uint8_t f = tflags[i];
+        if (!(f & TF_UNIT_START)) return;
+        uint32_t u = uot[i];
+        ustart[u] = (uint32_t)i;
+        bool first = (f & TF_MODULE_FIRST) != 0;
+        int32_t sd = first ? 0 : depth[i - 1].scope;
+        udepth[u] = (uint32_t)(sd < 0 ? 0 : sd) | (first ? 0x80000000u : 0u);
+    });
+    uint32_t* mub = w.mod_unit_begin;
+    bk.pf(n_modules + 1, [=] PTX_HD(size_t m) { mub[m] = n_tokens ? uot[mtb[m]] : 0; });
+}
+
+// ------------------------------------------------------------------------------------------------ stage C: decode
+template <class BK>
+inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
+    const uint32_t n_tokens = host_counters.n_tokens, n_units = host_counters.n_units, n_modules = w.n_modules;
+    const uint8_t* text = w.text;
+    const PtxToken* tokens = w.tokens;
+    const PtxModuleLayout* layout = w.layout;
+    const uint32_t* mtb = w.mod_tok_begin;
+    const uint32_t* mub = w.mod_unit_begin;
+    const uint32_t* ustart = w.unit_start;
+    const uint32_t* udepth = w.unit_depth;
+    const PtxDepth* depth = w.depth;
+    const uint32_t* mod_skip = w.mod_skip;
+    PtxModuleResult* results = w.results;
+    PtxCounters* counters = w.counters;
+    uint32_t* uend = w.unit_end = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    uint32_t* udir = w.unit_dir = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    PtxPair* usize = w.unit_size = (PtxPair*)bk.alloc(sizeof(PtxPair) * ((size_t)n_units + 2));
+    uint8_t* ustatus = w.unit_status = (uint8_t*)bk.alloc((size_t)n_units + 16);
+    uint32_t* mod_bad = w.mod_bad = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 1));
+    PtxPair* mod_seq = w.mod_seq_size = (PtxPair*)bk.alloc(sizeof(PtxPair) * (n_modules + 1));
+    uint32_t* mod_seq_status = w.mod_seq_status = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 1));
+    // worst case one function per top-level unit; sized after the top-level scan below
+    bk.zero(mod_bad, sizeof(uint32_t) * (n_modules + 1));
+    bk.zero(mod_seq, sizeof(PtxPair) * (n_modules + 1));
+    bk.zero(mod_seq_status, sizeof(uint32_t) * (n_modules + 1));
+
+    // C0: ordinal of the enclosing top-level unit
+    bk.template scan<uint32_t>(n_units, [=] PTX_HD(size_t u) { return (udepth[u] & 0x7FFFFFFFu) == 0 ? 1u : 0u; },
+                               [=] PTX_HD(size_t u, uint32_t v) { udir[u] = v; }, AddOp(), 0u);
+    bk.pf(1, [=] PTX_HD(size_t) {
+        counters->n_funcs = 0;
+        counters->any_sequential = 0;
+        counters->pad = n_units ? udir[n_units - 1] : 0;   // number of top-level units: bound for the function table
+    });
+    bk.download(&host_counters, counters, sizeof(PtxCounters));
+    const uint32_t max_funcs = host_counters.pad;
+    PtxFnEntry* fn_entries = w.fn_entries = (PtxFnEntry*)bk.alloc(sizeof(PtxFnEntry) * ((size_t)max_funcs + 1));
+
+    // C1: decode every unit, counting only
+    bk.pf(n_units, [=] PTX_HD(size_t u) {
+        uint32_t start = ustart[u];
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        // modules without units share their begin with the next one: take the last module that starts at or before u
+        if (u == 0) { PtxPair z; z.a = z.b = 0; usize[0] = z; }
+        if (mod_skip[m]) {
+            PtxPair z;
+            z.a = z.b = 0;
+            usize[u + 1] = z;
+            uend[u] = 0;
+            ustatus[u] = US_OK;
+            return;
+        }
+        DecCountSink sink;
+        PtxHashResolver res;
+        res.entries = nullptr; res.slots = nullptr; res.mask = 0; res.unit_off = nullptr; res.module = m; res.my_dir_ord = 0;
+        PtxDecoder<DecCountSink, PtxHashResolver> d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
+        uint32_t dp = udepth[u];
+        PtxUnitResult r = ptx_decode_unit(d, start, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
+        uend[u] = r.end;
+        ustatus[u] = (uint8_t)r.status;
+        PtxPair sz;
+        sz.a = sink.nw;
+        sz.b = sink.ne;
+        usize[u + 1] = sz;
+        if (r.status == US_OK && r.kind == U_FUNC) {
+#ifdef __CUDA_ARCH__
+            uint32_t slot = atomicAdd(&counters->n_funcs, 1u);
+#else
+            uint32_t slot = counters->n_funcs++;
+#endif
+            PtxFnEntry e;
+            e.unit = (uint32_t)u;
+            e.dir_ord = udir[u];
+            e.name_off = tokens[r.name_tok].start;
+            e.name_len = ptx_token_len(text, tokens[r.name_tok], layout[m].text_off + layout[m].text_len);
+            e.n_rets = r.n_rets;
+            e.n_inputs = r.n_inputs;
+            e.module = m;
+            e.pad = 0;
+            fn_entries[slot] = e;
+        }
+    });
+    // C2: do consecutive units meet, and does every module return to depth 0?
+    bk.pf(n_units, [=] PTX_HD(size_t u) {
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        if (mod_skip[m]) return;
+        uint32_t next = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        bool ok = ustatus[u] == US_OK && uend[u] == next;
+        if (u + 1 == mub[m + 1]) ok = ok && depth[mtb[m + 1] - 1].scope == 0;
+        if (!ok) mod_bad[m] = 1;
+    });
+    // C3: modules whose units do not meet are parsed sequentially by one thread each (count)
+    bk.pf(n_modules, [=] PTX_HD(size_t m) {
+        if (!mod_bad[m]) return;
+        counters->any_sequential = 1;
+        DecCountSink sink;
+        PtxChainResolver res;
+        res.words = nullptr;
+        res.last_func = PTX_ABSENT;
+        PtxDecoder<DecCountSink, PtxChainResolver> d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
+        int st = ptx_decode_module_sequential(d, mtb[m], 0);
+        PtxPair sz;
+        sz.a = sink.nw;
+        sz.b = sink.ne;
+        mod_seq[m] = sz;
+        mod_seq_status[m] = (uint32_t)st;
+    });
+    // C4: sizes of sequential modules replace those of their units
+    bk.pf(n_units, [=] PTX_HD(size_t u) {
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        if (!mod_bad[m]) return;
+        PtxPair z;
+        z.a = z.b = 0;
+        usize[u + 1] = (u == mub[m]) ? mod_seq[m] : z;
+    });
+    bk.template scan<PtxPair>((size_t)n_units + 1, [=] PTX_HD(size_t i) { return usize[i]; },
+                              [=] PTX_HD(size_t i, PtxPair v) { usize[i] = v; }, PairAddOp(), PtxPair{0, 0});
+    bk.pf(1, [=] PTX_HD(size_t) {
+        counters->n_words = n_units ? usize[n_units].a : 0;
+        counters->n_errs = n_units ? usize[n_units].b : 0;
+    });
+    bk.download(&host_counters, counters, sizeof(PtxCounters));
+    const uint32_t n_words = host_counters.n_words, n_errs = host_counters.n_errs, n_funcs = host_counters.n_funcs;
+    uint32_t* words = w.words = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_words + 4));
+    PtxErrRec* errs = w.errs = (PtxErrRec*)bk.alloc(sizeof(PtxErrRec) * ((size_t)n_errs + 1));
+    // C5: function table for `call`
+    uint32_t mask = 1;
+    while (mask < 2 * n_funcs + 2) mask <<= 1;
+    mask -= 1;
+    uint32_t* slots = w.fn_slots = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)mask + 1));
+    w.fn_mask = mask;
+    bk.pf((size_t)mask + 1, [=] PTX_HD(size_t i) { slots[i] = PTX_ABSENT; });
+    bk.pf(n_funcs, [=] PTX_HD(size_t i) {
+        const PtxFnEntry e = fn_entries[i];
+        uint32_t h = ptx_name_hash(text, e.name_off, e.name_len, e.module) & mask;
+        for (;;) {
+#ifdef __CUDA_ARCH__
+            uint32_t old = atomicCAS(&slots[h], PTX_ABSENT, (uint32_t)i);
+#else
+            uint32_t old = slots[h];
+            if (old == PTX_ABSENT) slots[h] = (uint32_t)i;
+#endif
+            if (old == PTX_ABSENT) break;
+            h = (h + 1) & mask;
+        }
+    });
+    // C6: decode again, writing
+    bk.pf(n_units, [=] PTX_HD(size_t u) {
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        DecWriteSink sink;
+        sink.words = words + usize[u].a;
+        sink.errs = errs + usize[u].b;
+        uint64_t text_end = layout[m].text_off + layout[m].text_len;
+        if (mod_skip[m]) return;
+        if (mod_bad[m]) {
+            if (u != mub[m]) return;
+            PtxChainResolver res;
+            res.words = words;
+            res.last_func = PTX_ABSENT;
+            PtxDecoder<DecWriteSink, PtxChainResolver> d(text, tokens, mtb[m + 1], text_end, sink, res);
+            ptx_decode_module_sequential(d, mtb[m], usize[u].a);
+            return;
+        }
+        PtxHashResolver res;
+        res.entries = fn_entries;
+        res.slots = slots;
+        res.mask = mask;
+        res.unit_off = usize;
+        res.module = m;
+        res.my_dir_ord = udir[u];
+        PtxDecoder<DecWriteSink, PtxHashResolver> d(text, tokens, mtb[m + 1], text_end, sink, res);
+        uint32_t dp = udepth[u];
+        ptx_decode_unit(d, ustart[u], dp & 0x7FFFFFFFu, (dp >> 31) != 0);
+    });
+    bk.pf(n_modules, [=] PTX_HD(size_t m) {
+        PtxModuleResult r = results[m];
+        r.unit_begin = mub[m];
+        r.unit_end = mub[m + 1];
+        r.word_begin = n_units ? usize[mub[m]].a : 0;
+        r.word_end = n_units ? usize[mub[m + 1]].a : 0;
+        r.err_begin = n_units ? usize[mub[m]].b : 0;
+        r.err_end = n_units ? usize[mub[m + 1]].b : 0;
+        r.sequential = mod_bad[m];
+        r.status = mod_seq_status[m];
+        results[m] = r;
+    });
+    (void)n_tokens;
+}
