@@ -1,0 +1,286 @@
+#!/usr/bin/env python3
+"""Benchmark of the PTX front end (lex + parse to records) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--modules M] [--bytes B]
+
+A step is one pass of the whole front end over one batch of synthetic PTX modules: the fatbin-scale configuration
+(4,096 independent modules, ~1 GiB of text, log-normal sizes, mixed sm_80/86/90 targets, 10 % tensor-core tile
+statements).  With N > 1 (torchrun, one rank per GPU) the global module list of N x 4,096 modules is split by
+byte-balanced greedy partitioning; ranks exchange nothing on the data path (weak scaling).
+
+Printed JSON line (rank 0):
+  value      front-end GB/s of input text with the text already resident in HBM (all kernels, CUDA-event timed on the
+             library's stream, max over ranks)
+  e2e        the same through ptxfe_parse_batch with pinned host text: H2D of the text and D2H of all result
+             records inside the timed region
+  roofline   the dominant kernel: algorithmic bytes / its CUDA-event time, against the measured HBM copy peak
+  cpu_baseline  the CPU restatement of ptx_parser (the oracle) on all host cores, on a bounded sample of the workload
+--impl reference times that CPU implementation as the main line (the Rust crate itself cannot be built here).
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "ptx_front_end_throughput"
+UNIT = "GB/s"
+
+
+def measured_hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        return float(json.load(open(p))["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+
+    def run(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
+                                     stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, timeout=5).stdout.strip()
+                f = [x.strip() for x in out.split(",")]
+                self.samples.append(float(f[0]))
+                self.max_mhz = float(f[1])
+                for n, v in zip(names, f[2:]):
+                    if v.lower().startswith("active"):
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.2)
+
+    def summary(self):
+        return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+def make_workload(rank, world, n_modules, total_bytes, seed=1001):
+    """The rank's share of world x n_modules modules (byte-balanced greedy partition of the global list)."""
+    from zluda_b200 import corpus
+    if world == 1:
+        return corpus.config1(seed=seed, n_modules=n_modules, total_bytes=total_bytes)
+    sizes = corpus.config1_sizes(seed, n_modules * world, total_bytes * world)
+    mine = corpus.greedy_partition(sizes, world)[rank]
+    return corpus.config1(seed=seed, n_modules=n_modules * world, total_bytes=total_bytes * world, indices=mine)
+
+
+def cpu_parse_all_cores(mods, seconds_budget=20.0):
+    """Oracle (CPU restatement of ptx_parser) over `mods` with one thread per core; returns (GB/s, cores, bytes)."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+    o = oracle_lib.load()
+    cores = os.cpu_count() or 1
+    # calibrate on a few modules, then size the sample to the time budget
+    t0 = time.perf_counter()
+    nb = 0
+    for m in mods[:4]:
+        o.lib.oracle_parse_only(m, len(m), None, None)
+        nb += len(m)
+    rate1 = nb / max(1e-6, time.perf_counter() - t0)
+    budget_bytes = rate1 * cores * seconds_budget * 0.6
+    sample, total = [], 0
+    for m in mods:
+        if total > budget_bytes and len(sample) >= cores:
+            break
+        sample.append(m)
+        total += len(m)
+    idx = [0]
+    lock = threading.Lock()
+    bad = [0]
+
+    def worker():
+        while True:
+            with lock:
+                i = idx[0]
+                idx[0] += 1
+            if i >= len(sample):
+                return
+            if o.lib.oracle_parse_only(sample[i], len(sample[i]), None, None) != 0:
+                bad[0] += 1
+
+    t0 = time.perf_counter()
+    threads = [threading.Thread(target=worker) for _ in range(cores)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    dt = time.perf_counter() - t0
+    assert bad[0] == 0, "the oracle rejected a generated module"
+    return total / dt / 1e9, cores, total, len(sample)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--modules", type=int, default=4096)
+    ap.add_argument("--bytes", type=int, default=1 << 30)
+    a = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    workload = "fatbin-scale batch: %d modules/GPU, ~%.2f GiB/GPU, config-0 grammar + 10%% mma/ld.shared.v4 tiles" % (
+        a.modules, a.bytes / 2**30)
+    config = {"workload": workload, "modules_per_gpu": a.modules, "parallelism": "modules sharded by byte-balanced greedy partition, no collective",
+              "l2": "inputs (%.0f MiB/GPU) larger than the 126 MB L2" % (a.bytes / 2**20)}
+
+    if a.impl == "reference":
+        if rank != 0:
+            return
+        mods = make_workload(0, 1, a.modules, a.bytes)
+        vals = []
+        for _ in range(a.warmup + a.steps):
+            gbs, cores, nbytes, nmods = cpu_parse_all_cores(mods, seconds_budget=max(4.0, 60.0 / (a.warmup + a.steps)))
+            vals.append(gbs)
+        v = float(np.mean(vals[a.warmup:]))
+        sample = "%d modules (%.1f MB) of the workload per step" % (nmods, nbytes / 1e6)
+        print(json.dumps({
+            "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": nbytes / 1e9 / v * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+            "data": "synthetic", "impl": "reference", "config": config,
+            "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "CPU restatement of ptx_parser (oracle/), one module per task over all host cores; the Rust crate cannot be built here"}))
+        return
+
+    import torch
+    import torch.distributed as dist
+    import zluda_b200
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    os.environ.setdefault("PTXFE_PROFILE", "1")
+    mods = make_workload(rank, world, a.modules, a.bytes)
+    nbytes = sum(len(m) for m in mods)
+    # pinned host copy of the text: the e2e leg reads it from there
+    blob = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+    view = blob.numpy()
+    spans, off = [], 0
+    for m in mods:
+        view[off:off + len(m)] = np.frombuffer(m, dtype=np.uint8)
+        spans.append((blob.data_ptr() + off, len(m)))
+        off += len(m)
+    ctx = zluda_b200.Context(local_rank)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- kernels only, text resident in HBM
+    ctx.stage(spans)
+    for _ in range(a.warmup):
+        ctx.run()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    kernel_ms, prof = 0.0, {}
+    t_wall = time.perf_counter()
+    for _ in range(a.steps):
+        ctx.run()
+        st = ctx.stats()
+        kernel_ms += st["kernel_ms"]
+        for k, v in ctx.profile().items():
+            prof[k] = prof.get(k, 0.0) + v
+    barrier()
+    wall_ms = (time.perf_counter() - t_wall) * 1e3
+    stats = ctx.stats()
+    # ---- end to end through the public call: pinned host text in, records out
+    for _ in range(min(2, a.warmup)):
+        ctx.parse_batch(spans).free()
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(a.steps):
+        b = ctx.parse_batch(spans)
+        nerr = b.error_count(0)
+        b.free()
+    barrier()
+    e2e_ms = (time.perf_counter() - t0) * 1e3
+    e2e_stats = ctx.stats()
+    sampler.stop_flag = True
+    sampler.join()
+
+    times = torch.tensor([kernel_ms, e2e_ms, float(nbytes)], dtype=torch.float64, device="cuda")
+    if world > 1:
+        tmax = times.clone()
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        tsum = times.clone()
+        dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
+        kernel_ms, e2e_ms, total_bytes = float(tmax[0]), float(tmax[1]), float(tsum[2])
+    else:
+        total_bytes = float(nbytes)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    value = total_bytes * a.steps / (kernel_ms / 1e3) / 1e9
+    e2e = total_bytes * a.steps / (e2e_ms / 1e3) / 1e9
+    # ---- roofline of the dominant kernel
+    peak, peak_kind = measured_hbm_peak()
+    T, W, N = stats["n_tokens"], stats["n_result_words"], nbytes
+    algo = {   # algorithmic bytes per launch: text read once, tokens / records read or written once
+        "lex_context_vectors": N, "lex_count_tokens": N, "lex_emit_tokens": N + 8 * T,
+        "classify_braces": 8 * T + T, "speculate_unit_starts": 8 * T + 8 * T + T, "scan_depth": 9 * T + 8 * T,
+        "decode_count": N + 8 * T, "decode_emit": N + 8 * T + 4 * W,
+    }
+    top = max(prof, key=prof.get) if prof else None
+    roof = None
+    if top:
+        ms = prof[top] / a.steps
+        ab = algo.get(top)
+        ach = ab / (ms / 1e3) / 1e9 if ab else None
+        roof = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
+                "frac": ach / peak if ach else None, "traffic": None, "ms_per_launch": ms, "algorithmic_bytes": ab,
+                "lexer_segmenter": None}
+        lex_ms = sum(prof.get(k, 0.0) for k in ("lex_context_vectors", "scan_context", "lex_count_tokens", "scan_token_counts",
+                                                  "lex_emit_tokens", "classify_braces", "scan_depth", "speculate_unit_starts",
+                                                  "scan_unit_index", "compact_unit_starts")) / a.steps
+        if lex_ms > 0:
+            a_lex = N + 8 * T
+            roof["lexer_segmenter"] = {"ms": lex_ms, "algorithmic_bytes": a_lex, "achieved": a_lex / (lex_ms / 1e3) / 1e9,
+                                       "frac": a_lex / (lex_ms / 1e3) / 1e9 / peak}
+    cpu_gbs, cores, cpu_bytes, cpu_mods = cpu_parse_all_cores(mods, seconds_budget=15.0)
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": kernel_ms / a.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "u8",
+        "data": "synthetic", "config": config,
+        "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": e2e_ms / a.steps, "h2d_bytes_per_step": int(e2e_stats["h2d_bytes"]),
+                "d2h_bytes_per_step": int(e2e_stats["d2h_bytes"]), "h2d_ms": e2e_stats["h2d_ms"], "kernel_ms": e2e_stats["kernel_ms"],
+                "d2h_ms": e2e_stats["d2h_ms"]},
+        "gpu_launches": int(stats["n_kernel_launches"]) * a.steps,
+        "roofline": roof,
+        "cpu_baseline": {"value": cpu_gbs, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": "%d modules (%.1f MB) of the same workload" % (cpu_mods, cpu_bytes / 1e6)},
+        "clocks": sampler.summary(),
+        "stages_ms": {"lex": stats["lex_ms"], "structure": stats["structure_ms"], "decode": stats["decode_ms"]},
+        "kernels_ms": {k: v / a.steps for k, v in sorted(prof.items(), key=lambda kv: -kv[1])},
+        "counts": {"text_bytes": nbytes, "tokens": int(T), "units": int(stats["n_units"]), "result_words": int(W),
+                   "sequential_modules": int(e2e_stats["n_sequential"]), "errors_module0": int(nerr)},
+        "wall_ms_kernel_loop": wall_ms,
+    }
+    print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

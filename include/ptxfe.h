@@ -1,0 +1,108 @@
+/* ptxfe - a GPU-resident PTX front end (text -> directive / instruction records).  C ABI.
+ *
+ * Drop-in boundary for the three public entry points of ZLUDA's ptx_parser crate.  Those are plain Rust functions
+ * (no FFI layer exists in the reference); a binding crate would declare the functions below `extern "C"` and
+ * rebuild `ast::Module` from the records.
+ *
+ *   reference (ptx_parser/src/lib.rs)                                  here
+ *   parse_module_checked(text)   -> Result<Module, Vec<PtxError>>      ptxfe_parse_batch(.., PTXFE_CHECKED, ..)     lib.rs:428-468
+ *   parse_module_unchecked(text) -> Module                             ptxfe_parse_batch(.., PTXFE_UNCHECKED, ..)   lib.rs:470-501
+ *   parse_for_errors(text)       -> Vec<PtxError>                      ptxfe_parse_batch(.., PTXFE_ERRORS_ONLY, ..) lib.rs:392-411
+ *
+ * The reference parses one module per call on one CPU thread; its only batch caller (zluda_precompile/src/main.rs:57-64)
+ * fans modules out over a thread pool.  Here a call takes a whole batch of independent modules and processes it on one
+ * GPU.  All work happens on the device; there is no CPU parsing path, and every function fails with PTXFE_ERR_CUDA when
+ * no device is usable.
+ *
+ * Ownership: the caller keeps `texts` alive until the batch is freed - identifiers in the records are (offset, length)
+ * references into it, as the reference's AST borrows from its input (`&'input str`).  A batch stays valid until the
+ * next ptxfe_parse_batch / ptxfe_run on the same context or until ptxfe_batch_free; a context serves one thread at a time.
+ */
+#ifndef PTXFE_H
+#define PTXFE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct ptxfe_ctx ptxfe_ctx;
+typedef struct ptxfe_batch ptxfe_batch;
+
+enum { PTXFE_CHECKED = 0, PTXFE_UNCHECKED = 1, PTXFE_ERRORS_ONLY = 2 };
+
+enum {
+    PTXFE_OK = 0,
+    PTXFE_ERR_BAD_ARG = 1,
+    PTXFE_ERR_CUDA = 2,      /* a CUDA call failed; ptxfe_last_error(ctx) has the text */
+    PTXFE_ERR_TOO_LARGE = 3, /* batch text (with per-module padding) exceeds 4 GiB - 1, or a result table exceeds 2^32 entries */
+    PTXFE_ERR_OOM = 4
+};
+
+/* per-module verdict, mirroring the three reference return shapes */
+enum {
+    PTXFE_MODULE_OK = 0,        /* checked: Ok(module); unchecked: a module was returned */
+    PTXFE_MODULE_ERR = 1,       /* checked: Err(errors); unchecked: Module::empty() (ptx_parser/src/ast.rs:2008-2016) */
+    PTXFE_MODULE_REF_PANICS = 2 /* input on which the reference unwraps an empty slice (lib.rs:939) */
+};
+
+typedef struct ptxfe_stats {
+    uint64_t text_bytes;      /* sum of module lengths */
+    uint64_t n_modules, n_tokens, n_units, n_result_words, n_errors, n_lex_errors;
+    uint64_t n_sequential;    /* modules re-parsed by the single-thread recovery path */
+    uint64_t n_kernel_launches;
+    uint64_t h2d_bytes, d2h_bytes;
+    float h2d_ms, kernel_ms, d2h_ms;   /* CUDA-event times of the three phases of the last call */
+    float lex_ms, structure_ms, decode_ms;   /* kernel_ms split by stage */
+} ptxfe_stats;
+
+/* Create a context on CUDA device `device` (one stream, reusable device arenas, pinned result buffers). */
+int ptxfe_create(int device, ptxfe_ctx** out);
+void ptxfe_destroy(ptxfe_ctx* ctx);
+const char* ptxfe_last_error(const ptxfe_ctx* ctx);
+const char* ptxfe_status_str(int status);
+
+/* Whole path: copy `n` module texts to the device, parse them, copy the records back.  `texts[i]` need not be
+ * NUL-terminated.  Host buffers may be pageable or pinned. */
+int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, uint32_t n, uint32_t mode,
+                      ptxfe_batch** out);
+
+/* The same in three steps, for callers that keep text resident in device memory across calls or overlap transfers:
+ *   ptxfe_stage : host text -> device (module i starts at a 128-byte boundary of the batch buffer)
+ *   ptxfe_run   : all kernels; results stay on the device
+ *   ptxfe_fetch : device -> host records, returns the batch */
+int ptxfe_stage(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, uint32_t n);
+int ptxfe_run(ptxfe_ctx* ctx, uint32_t mode);
+int ptxfe_fetch(ptxfe_ctx* ctx, ptxfe_batch** out);
+
+void ptxfe_batch_free(ptxfe_batch* batch);
+uint32_t ptxfe_batch_size(const ptxfe_batch* batch);
+int ptxfe_module_status(const ptxfe_batch* batch, uint32_t i);
+uint32_t ptxfe_module_error_count(const ptxfe_batch* batch, uint32_t i);
+void ptxfe_get_stats(const ptxfe_ctx* ctx, ptxfe_stats* out);
+/* When the environment variable PTXFE_PROFILE=1 was set at ptxfe_create: one line "step_name milliseconds" per pipeline
+ * step of the last ptxfe_run (CUDA-event time on the context's stream).  Empty otherwise. */
+const char* ptxfe_profile(const ptxfe_ctx* ctx);
+
+/* Raw record views of module i (layout: zluda_b200/csrc/ptx_decode.h).  Offsets inside records index the batch text
+ * buffer; subtract *text_base to index texts[i]. */
+int ptxfe_module_records(const ptxfe_batch* batch, uint32_t i, const uint32_t** words, uint64_t* n_words,
+                         uint64_t* text_base);
+
+/* Canonical text dump of module i: the tree printed as if every ptx_parser AST type derived Debug (floats as bit
+ * patterns), followed by the ordered error list.  malloc'ed; release with ptxfe_free. */
+int ptxfe_module_dump(const ptxfe_batch* batch, uint32_t i, char** out, uint64_t* out_len);
+/* 64-bit FNV-1a of the same dump, without materialising it beyond one module at a time. */
+int ptxfe_module_dump_hash(const ptxfe_batch* batch, uint32_t i, uint64_t* out_hash);
+void ptxfe_free(void* p);
+
+/* Token table of module i of the staged batch (lexer only; for tests): triples (kind, start, length) relative to the
+ * module text, then error spans (start, length).  malloc'ed. */
+int ptxfe_lex_module(ptxfe_ctx* ctx, const char* text, uint64_t len, uint32_t** out, uint64_t* n_tokens, uint64_t* n_errors);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,81 @@
+"""Edge-case inputs shared by the CPU (emulated pipeline) and GPU parity tests.  Each is a complete module text."""
+HEADER = ".version 6.5\n.target sm_30\n.address_size 64\n"
+DECLS = ".reg .b32 %r<10>; .reg .b64 %rd<10>; .reg .f32 %f<10>; .reg .f64 %fd<4>; .reg .pred %p<4>;"
+
+
+def body(stmts):
+    return HEADER + ".visible .entry k()\n{\n" + DECLS + "\n" + stmts + "\nret;\n}\n"
+
+
+LITERALS = ["10", "18446744073709551615", "18446744073709551616", "10U", "-10U", "-9223372036854775808",
+            "-9223372036854775809", "010", "09", "0", "0x1F", "0X1f", "0xFFFFFFFFFFFFFFFF", "0xFFU", "0xU", "0xZZ",
+            "0f3F800000", "0fGGGGGGGG", "0d3FF0000000000000", "1.5", ".5", "1.5e-3", "0.1", "1.7976931348623157e308",
+            "4.9e-324", "1.0e400", "WARP_SZ", "2.4703282292062327e-324", "2.4703282292062328e-324",
+            "9007199254740993.0", "9007199254740992.9999999999999999999999", "8.98846567431158e307"]
+
+STATEMENTS = [
+    "mov.f64 %fd1, -1.5;", "mov.f32 %f1, -0f3F800000;", "mov.f32 %f1, 0f3F8000;", "mov.f64 %fd1, 2.E5;", "mov.f64 %fd1, 2.;",
+    "bra add;", ".reg .b32 %z<0>;", ".reg .b32 %a, %b<4>;", "ld.u32.v2 {%r1,%r2}, [%rd1];", "add.s32.s32 %r1, %r2, %r3;",
+    "shf.l.wrap.b32 %r1, %r2.r, %r3, %r4;", "cvt.f32.u32 %f1, %r1;", "setp.lt.ftz.u32 %p1, %r1, %r2;",
+    "setp.ltu.u32 %p1, %r1, %r2;", "add:\n", ".reg .b32 %q<99999999999>;", "mov.u32 %r1, %v.q;",
+    "ld.global.u32 %r1, [%rd1+2147483648];", "mov.u32 foo, {} {};", "ret }", "{ add.s32 %r1,%r2,%r3; { ret } }",
+    "{ { foo bar } ret; } ret;", "mov.b32 %r1, %envreg3;", ".loc 1 2 3\n}", "@%p1 bra L1; L1:",
+    "@!%p1 add.s32 %r1,%r2,%r3;", "foo: bar: ret;", ".pragma \"nounroll\";",
+    "unknown_op1.asdf foobar;\nadd.u64 %rd1,%rd2,1;\nunknown_op2 t, u;",
+    "ld.global.nc.ca.L1::evict_last.u32 %r1, [%rd1];", "ld.global.L2::cache_hint.u32 %r1, [%rd1], %rd2;",
+    "cp.async.ca.shared.global [%rd1], [%rd2], 16;", "cp.async.ca.shared.global [%rd1], [%rd2], 5, 4;",
+    "createpolicy.fractional.L2::evict_last.b64 %rd1, 0.5;", "createpolicy.fractional.L2::evict_last.b64 %rd1;",
+    "bar.red.and.pred %p1, 0, !%p2;", "bar.red.or.pred %p1, 0, 32, %p2;", "barrier.sync.aligned 0, 32;",
+    "shfl.sync.bfly.b32 %r1|%p1, %r2, 1, 31, -1;", "shfl.bfly.b32 %r1, %r2, 1, 31;",
+    "vote.sync.ballot.b32 %r1, !%p1, -1;", "vote.ballot.b32 %r1, %p1;", "vshr.u32.u32.u32.clamp.add %r1, %r2, %r3, %r4;",
+    "tex.2d.v4.f32.f32 {%f1,%f2,%f3,%f4}, [tex, {%f5,%f6}];", "atom.global.add.u32 %r1, [%rd1], 1;",
+    "atom.acq_rel.gpu.global.cas.b32 %r1, [%rd1], %r2, %r3;", "atom.global.add.noftz.f16x2 %r1, [%rd1], %r2;",
+    "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%f1,%f2,%f3,%f4}, {%r1,%r2,%r3,%r4}, {%r5,%r6}, {%f5,%f6,%f7,%f8};",
+    "cvt.rn.satfinite.e4m3x2.f32 %r1, %f1, %f2;", "cvt.rn.f16x2.f32 %r1, %f1, %f2;", "cvt.sat.u8.s32 %r1, %r2;",
+    "cvt.f64.f32 %fd1, %f1;", "cvt.rn.f64.f32 %fd1, %f1;", "cvt.pred.u32 %p1, %r1;", "membar.gl;", "membar.sys;",
+    "ld.volatile.shared.v2.f32 {%f1,%f2}, [%rd1];", "st.release.sys.global.u32 [%rd1], %r1;", "st.mmio.relaxed.sys.u32 [%rd1], %r1;",
+    "lg2.f32.ftz.approx %f1, %f2;", "rsqrt.approx.ftz.f64 %fd1, %fd2;", "min.NaN.f32 %f1, %f2, %f3;",
+    "mad.hi.sat.s32 %r1, %r2, %r3, %r4;", "mad.lo.cc.u32 %r1, %r2, %r3, %r4;", "madc.hi.cc.u32 %r1, %r2, %r3, %r4;",
+    "prefetch.global.L2 [%rd1];", "ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%r1,%r2,%r3,%r4}, [%rd1];",
+    "griddepcontrol.wait;", "redux.sync.add.s32 %r1, %r2, -1;", "match.any.sync.b32 %r1, %r2, -1;", "trap;", "exit;",
+    "ret.uni;", "bra.uni L;", "nanosleep.u32 100;", "activemask.b32 %r1;", "bfind.shiftamt.u32 %r1, %r2;",
+    "dp2a.lo.u32.s32 %r1, %r2, %r3, %r4;", "set.lt.and.ftz.u32.f32 %r1, %f1, %f2, !%p1;", "setp.eq.and.b32 %p1|%p2, %r1, %r2, %p3;",
+    "mov.b32 %r1, %r2+4;", "mov.b32 %r1, [%r2];", "st.global.u32 [%rd1+-4], %r1;", "ld.param.u64 %rd1, [k_param_0];",
+    ".local .align 8 .b8 buf[16];", ".shared .v2 .f32 sm;", ".param .b32 pp;", ".global .u32 gg = 5;", ".reg .v4 .f32 %vec, %vec2;",
+]
+
+MODULES = [
+    ".version 6.5\n.target sm_90ab\n", ".version 6.5 .target sm_30, debug", HEADER + "#", HEADER + "/* never",
+    HEADER + "\"open", HEADER + ".visible .entry k() { # ret; }", "", "// only comment\n",
+    ".version 6.5\n.target sm_30\n.address_size 16\n.visible .entry k() { ret; }",
+    ".version 0d401F333333333333\n.target sm_30\n", ".version 6.5\n.target add\n", ".version 65\n.target sm_30\n",
+    HEADER + ".global .bad_type foo;\n.const .b32 bar;\n",
+    HEADER + ".broken_directive_fail; 34; {\n.visible .entry add(.param .u64 input)\n{\n ret;\n}\nsection foobar }",
+    HEADER + ".global .b32 global[4] = {  unknown (1),   2,   3,   4};\n.visible .entry func1()\n{\nst.u64 [out_addr], temp2;\nret;\n}\n"
+             ".visible .entry func1()\n{\nbroken_instruction;\nret;\n}",
+    HEADER + ".func (.reg .b32 r) f(.reg .b32 a, .reg .b32 b);\n.visible .entry k()\n{\n .reg .b32 %r<4>;\n call (%r1), f, (%r2, %r3);\n"
+             " call (%r1), f, (%r2);\n call g;\n call.uni k;\n ret;\n}\n",
+    HEADER + ".func (.reg .b32 r) f(.reg .b32 a, .reg .b32 b)\n{\n ret;\n}\n.func f(.reg .b32 a);\n.visible .entry k()\n{\n"
+             " .reg .b32 %r<4>;\n call (%r1), f, (%r2, %r3);\n call f, (%r2);\n ret;\n}\n",
+    HEADER + ".func f(.reg .b32 a)\n{\n call f, (a);\n ret;\n}\n.func f(.reg .b32 a)\n{\n call f, (a);\n ret;\n}\n",
+    HEADER + ".const .align 4 .b8 constData[8];\n.global .s32 x[4] = {1};\n.global .f32 y[2] = {0f3F800000};\n.global .b32 z<4>;\n"
+             ".extern .shared .b8 sh[];\n.global .texref tex;\n.global .v2 .f32 vv = 1.0;\n.global .b8 e[2] = {};\n.global .u32 a[2][2];",
+    HEADER + ".file 1 \"a.cu\"\n.file 2 \"b.cu\", 123, 456\n.section .debug_abbrev\n{\n.b8 1\n.b8 17, 2\n.b32 .debug_info\nlbl:\n.b64 foo\n}\n"
+             ".visible .entry k() { ret; }",
+    HEADER + ".visible .entry k(.param .u64 .ptr .global .align 8 p, .param .align 4 .b8 q[16])\n.maxntid 128, 1\n.minnctapersm 2\n{\n ret;\n}",
+    HEADER + ".visible .entry k() { ret; } garbage", HEADER + ".visible .entry k() { ret; } garbage more",
+    HEADER + ".visible .entry k() { ret;", HEADER + "}", HEADER + ".visible .entry k() { ret; } }",
+    HEADER + ".weak .func w() { ret; }\n.extern .func e();\n.visible .func (.param .align 16 .b8 r[32]) g(.param .b64 a) .noreturn;",
+    HEADER + ".visible .entry k()\n{\n .reg .b32 %r<4>;\n {\n  .reg .b32 %t;\n  {\n   add.s32 %t, %r1, %r2;\n  }\n }\n ret;\n}",
+    HEADER + ".visible .entry k() { ld.global.u32 %r1, [%rd1]; .global .u32 inner; bogus }\n.global .u32 after;",
+    HEADER + ".visible .entry " + "k" * 300 + "() { ret; }",
+    HEADER + "// c1\n/* c2 */ .visible /* mid */ .entry k() // tail\n{ ret; /* x */ }\n/**/",
+    HEADER + ".visible .entry k() { mov.u32 %r1, 0x" + "F" * 200 + "; ret; }",
+]
+
+
+def all_cases():
+    out = [body("mov.b64 %rd1, " + lit + ";") for lit in LITERALS]
+    out += [body(s) for s in STATEMENTS]
+    out += MODULES
+    return out

@@ -24,10 +24,10 @@ struct HostBackend {
     }
     void zero(void* p, size_t bytes) { memset(p, 0, bytes); }
     void download(void* host, const void* dev, size_t bytes) { memcpy(host, dev, bytes); }
-    template <class F> void pf(size_t n, F f) {
+    template <class F> void pf(const char*, size_t n, F f) {
         for (size_t i = 0; i < n; i++) f(i);
     }
-    template <class T, class Ld, class St, class Op> void scan(size_t n, Ld ld, St st, Op op, T identity) {
+    template <class T, class Ld, class St, class Op> void scan(const char*, size_t n, Ld ld, St st, Op op, T identity) {
         T acc = identity;
         for (size_t i = 0; i < n; i++) {
             acc = op(acc, ld(i));

@@ -1,0 +1,129 @@
+"""GPU parity: the CUDA path, called through the C ABI (include/ptxfe.h), against the CPU oracle on the same inputs.
+Bit-exact: the canonical dumps (tree + ordered error list) must be byte-equal."""
+import hashlib
+import json
+import os
+import random
+
+import pytest
+
+import cases
+import zluda_b200
+from zluda_b200 import corpus
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = zluda_b200.Context(0)
+    yield c
+    c.close()
+
+
+def first_difference(a, b):
+    al, bl = a.split("\n"), b.split("\n")
+    for i, (x, y) in enumerate(zip(al, bl)):
+        if x != y:
+            return "line %d\n oracle: %s\n gpu:    %s" % (i, x[:300], y[:300])
+    return "length %d vs %d" % (len(al), len(bl))
+
+
+def assert_parity(oracle, ctx, texts, modes=(0, 1, 2)):
+    for mode in modes:
+        b = ctx.parse_batch(texts, mode)
+        assert len(b) == len(texts)
+        for i, t in enumerate(texts):
+            st, o = oracle.parse(t, mode)
+            d = b.dump(i)
+            assert o == d, (mode, i, first_difference(o, d))
+            assert (b.status(i) == 0) == (st == 0)
+        b.free()
+    return ctx.stats()
+
+
+def test_edge_cases_and_golden_hashes(oracle, ctx):
+    texts = cases.all_cases()
+    stats = assert_parity(oracle, ctx, texts)
+    assert stats["n_kernel_launches"] > 20
+    golden = json.load(open(os.path.join(HERE, "golden", "cases.json")))
+    for mode in (0, 1, 2):
+        b = ctx.parse_batch(texts, mode)
+        for row in golden["cases"]:
+            assert hashlib.sha256(b.dump(row["index"]).encode()).hexdigest() == row["sha256"][mode], (row["index"], mode)
+        b.free()
+
+
+def test_lexer_tokens(oracle, ctx):
+    rng = random.Random(7)
+    pieces = ["add", ".f32", "%r1", ",", ";", " ", "\n", "// c\n", "/* x */", "/*", "*/", "\"s\"", "\"", "0f3F800000", "0x1F", "1.5e-3",
+              "1.5e", ".5", "12U", ".L2::cache_hint", ".shared::cta", ".shared::", "::", ":", "+", "-", "{", "}", "[", "]", "#", "$L_1",
+              "%", ".", ".1d", "WARP_SZ", "0d3FF0000000000000", "abc" * 60, "/", "*", "é", "a.b", "1e5", "0xU"]
+    for trial in range(60):
+        text = "".join(rng.choice(pieces) for _ in range(rng.randrange(1, 120)))
+        ot, oe = oracle.lex(text)
+        gt, ge = ctx.lex(text)
+        assert ot == gt, text
+        assert oe == ge, text
+    for pad in range(0, 140, 3):
+        text = " " * pad + "ld.global.L2::cache_hint.v4.f32 {%f1,%f2,%f3,%f4}, [%rd1+16]; /* c */ 0f3F800000 1.25e-3 // e\n\"str\""
+        assert oracle.lex(text) == ctx.lex(text), pad
+
+
+def test_corpora(oracle, ctx):
+    sets = {
+        "config0": corpus.config0(n_kernels=8, n_instr=2000),
+        "config1": corpus.config1(n_modules=256, total_bytes=16 << 20, pool_lines=40000),
+        "config2": corpus.config2(n_arrays=4, n_init=50000, n_consts=20000),
+        "config3": corpus.config3(total_bytes=4 << 20, n_funcs=16, n_labels=1000),
+    }
+    for name, mods in sets.items():
+        stats = assert_parity(oracle, ctx, mods, modes=(0,))
+        assert stats["n_sequential"] == 0, name
+
+
+def test_mutated_modules(oracle, ctx):
+    rng = random.Random(11)
+    base = corpus.config1(n_modules=4, total_bytes=24 << 10, pool_lines=2000) + corpus.config3(total_bytes=24 << 10, n_funcs=4, n_labels=20)
+    junk = [";", "{", "}", ":", ",", "(", ")", "foo", ".bar", "[", "]", "@", "\"", "/*", "#", ".global", ".entry", ".func", "<", "0x", "-", "ret", ""]
+    texts = []
+    for t in base:
+        s = t.decode()
+        for _ in range(12):
+            m = s
+            for _ in range(rng.randrange(1, 4)):
+                pos = rng.randrange(len(m))
+                m = m[:pos] + rng.choice(junk) + m[pos:] if rng.random() < 0.5 else m[:pos] + m[pos + rng.randrange(1, 12):]
+            texts.append(m)
+    assert_parity(oracle, ctx, texts)
+
+
+def test_full_size_properties(ctx):
+    """At benchmark scale the oracle is too slow to run on everything: check size-independent properties instead.
+    (1) parsing a batch twice gives identical records; (2) a module's result does not depend on its neighbours:
+    the dump hash of every module in a shuffled batch equals its hash in the original order; (3) clean input
+    produces no errors and never takes the recovery path."""
+    mods = corpus.config1(n_modules=512, total_bytes=128 << 20)
+    b = ctx.parse_batch(mods)
+    h1 = [b.dump_hash(i) for i in range(0, len(mods), 7)]
+    assert all(b.error_count(i) == 0 for i in range(len(mods)))
+    assert ctx.stats()["n_sequential"] == 0
+    b.free()
+    order = list(range(len(mods)))
+    random.Random(1).shuffle(order)
+    b = ctx.parse_batch([mods[i] for i in order])
+    pos = {m: k for k, m in enumerate(order)}
+    h2 = [b.dump_hash(pos[i]) for i in range(0, len(mods), 7)]
+    b.free()
+    assert h1 == h2
+
+
+def test_public_api(oracle):
+    text = cases.body("add.s32 %r1, %r2, %r3;")
+    r = zluda_b200.parse_module_checked(text)
+    assert r.ok and r.dump == oracle.parse(text, 0)[1]
+    bad = cases.body("bogus %r1;")
+    assert not zluda_b200.parse_module_checked(bad).ok
+    assert zluda_b200.parse_module_unchecked(bad).ok
+    assert zluda_b200.parse_for_errors(bad) == oracle.errors(bad, 2)

@@ -1,0 +1,186 @@
+"""The product's pipeline steps (lexer chunks, unit speculation, decoders, record format, dump) run on the host through
+the sequential test backend and compared with the oracle.  No GPU needed; the GPU runs of the same comparisons are in
+test_gpu_parity.py."""
+import glob
+import hashlib
+import json
+import os
+import random
+import struct
+
+import numpy as np
+import pytest
+
+import cases
+import emu_lib
+from zluda_b200 import corpus
+
+REFERENCE = os.environ.get("PTXFE_REFERENCE", "/root/reference")
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.fixture(scope="module")
+def emu():
+    return emu_lib.load()
+
+
+def first_difference(a, b):
+    al, bl = a.split("\n"), b.split("\n")
+    for i, (x, y) in enumerate(zip(al, bl)):
+        if x != y:
+            return "line %d\n oracle: %s\n ours:   %s" % (i, x[:300], y[:300])
+    return "length %d vs %d" % (len(al), len(bl))
+
+
+def assert_parity(oracle, emu, texts, modes=(0, 1, 2)):
+    for mode in modes:
+        dumps, stats = emu.parse(texts, mode)
+        for t, d in zip(texts, dumps):
+            o = oracle.parse(t, mode)[1]
+            assert o == d, (mode, t[-200:], first_difference(o, d))
+    return stats
+
+
+def test_golden_oracle_hashes(oracle):
+    golden = json.load(open(os.path.join(HERE, "golden", "cases.json")))
+    texts = cases.all_cases()
+    assert golden["n"] == len(texts)
+    for row, t in zip(golden["cases"], texts):
+        for mode in (0, 1, 2):
+            assert hashlib.sha256(oracle.parse(t, mode)[1].encode()).hexdigest() == row["sha256"][mode], (row["index"], mode)
+
+
+def test_edge_cases(oracle, emu):
+    stats = assert_parity(oracle, emu, cases.all_cases())
+    assert stats["sequential"] > 0      # the recovery path is exercised
+    assert stats["sequential"] < len(cases.all_cases()) // 2
+
+
+def test_lexer_tokens_match_oracle(oracle, emu):
+    rng = random.Random(7)
+    pieces = ["add", ".f32", "%r1", ",", ";", " ", "\n", "\t", "// c\n", "/* x */", "/*", "*/", "\"s\"", "\"", "0f3F800000", "0x1F",
+              "1.5e-3", "1.5e", ".5", "12U", ".L2::cache_hint", ".shared::cta", ".shared::", ".param::funcx", "::", ":", "+", "-", "{",
+              "}", "[", "]", "(", ")", "<", ">", "=", "@", "!", "|", "#", "~", "$L_1", "_a", "%", "$", ".", "..", ".1d", ".2dx", "WARP_SZ",
+              "0d3FF0000000000000", "0f123", "abc" * 60, "/", "*", "é", "\r\n", "a.b", "a:b", "1e5", "0X", "0xU", "09"]
+    for trial in range(300):
+        n = rng.randrange(1, 80)
+        text = "".join(rng.choice(pieces) for _ in range(n))
+        ot, oe = oracle.lex(text)
+        et, ee = emu.lex(text)
+        assert ot == et, (text, ot[:5], et[:5])
+        assert oe == ee, text
+    # tokens and comments that straddle chunk boundaries at every offset
+    for pad in range(0, 140):
+        text = " " * pad + "ld.global.L2::cache_hint.v4.f32 {%f1,%f2,%f3,%f4}, [%rd1+16]; /* c */ 0f3F800000 1.25e-3 // e\n\"str\""
+        assert oracle.lex(text) == emu.lex(text), pad
+    for size in (0, 1, 127, 128, 129, 255, 256, 257):
+        text = ("a" * size)
+        assert oracle.lex(text) == emu.lex(text)
+        text = "/*" + "x" * size + "*/b"
+        assert oracle.lex(text) == emu.lex(text)
+
+
+def test_corpora_small(oracle, emu):
+    sets = {
+        "config0": corpus.config0(n_kernels=3, n_instr=400),
+        "config1": corpus.config1(n_modules=24, total_bytes=1 << 20, pool_lines=8000),
+        "config2": corpus.config2(n_arrays=4, n_init=3000, n_consts=3000),
+        "config3": corpus.config3(total_bytes=400 << 10, n_funcs=8, n_labels=200),
+    }
+    for name, mods in sets.items():
+        for m in mods:
+            st, dump = oracle.parse(m)
+            assert st == 0, (name, dump[-400:])     # every generated statement is one the reference accepts
+        stats = assert_parity(oracle, emu, mods, modes=(0,))
+        assert stats["sequential"] == 0, name       # clean input never takes the recovery path
+
+
+def test_mutated_modules(oracle, emu):
+    """Random token-level damage: the data-parallel path or the sequential recovery must still agree with the oracle."""
+    rng = random.Random(11)
+    base = corpus.config1(n_modules=4, total_bytes=24 << 10, pool_lines=2000) + corpus.config3(total_bytes=24 << 10, n_funcs=4, n_labels=20)
+    junk = [";", "{", "}", ":", ",", "(", ")", "foo", ".bar", "[", "]", "@", "\"", "/*", "#", ".global", ".entry", ".func", "<", "0x", "-", "ret", ""]
+    texts = []
+    for t in base:
+        s = t.decode()
+        for _ in range(12):
+            k = rng.randrange(1, 4)
+            m = s
+            for _ in range(k):
+                pos = rng.randrange(len(m))
+                if rng.random() < 0.5:
+                    m = m[:pos] + rng.choice(junk) + m[pos:]
+                else:
+                    m = m[:pos] + m[pos + rng.randrange(1, 12):]
+            texts.append(m)
+    assert_parity(oracle, emu, texts)
+
+
+@pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="reference checkout not mounted")
+def test_reference_fixtures(oracle, emu):
+    texts = []
+    for f in sorted(glob.glob(os.path.join(REFERENCE, "**", "*.ptx"), recursive=True)):
+        t = open(f, "rb").read()
+        if "/pass/test/" in f:
+            t = t.split(b"// %%% output %%%")[0].strip()
+        texts.append(t)
+    assert len(texts) >= 240
+    assert_parity(oracle, emu, texts)
+
+
+def _f64_bits(s):
+    return struct.unpack("<Q", struct.pack("<d", float(s)))[0]
+
+
+def test_decimal_to_f64_bit_exact(emu):
+    rng = random.Random(3)
+    fixed = ["1.5", ".5", "0.1", "1.7976931348623157e308", "1.7976931348623159e308", "4.9e-324", "2.4703282292062327e-324",
+             "2.4703282292062328e-324", "1.0e400", "1.0e-400", "9007199254740993.0", "9007199254740992.9999999999999999999999",
+             "2.2250738585072011e-308", "2.2250738585072014e-308", "8.98846567431158e307", "0.0", "000.000e5",
+             "123456789012345678901234567890.5e-10"]
+    for s in fixed:
+        assert emu.parse_f64(s) == _f64_bits(s), s
+    for _ in range(20000):
+        k = rng.random()
+        if k < 0.3:
+            s = "%.8e" % abs(rng.gauss(0, 1))
+        elif k < 0.6:
+            s = "%.16e" % abs(rng.gauss(0, 1))
+        elif k < 0.8:
+            s = "%d.%de%d" % (rng.randrange(10 ** rng.randrange(1, 25)), rng.randrange(10 ** rng.randrange(1, 30)), rng.randrange(-340, 300))
+        else:
+            x = struct.unpack("<d", struct.pack("<Q", rng.getrandbits(63)))[0]
+            if x != x or x == float("inf"):
+                continue
+            s = "%.17e" % x
+        assert emu.parse_f64(s) == _f64_bits(s), s
+    # exact halfway points between adjacent doubles and their neighbours (many more than 19 digits)
+    from decimal import Decimal, getcontext
+    getcontext().prec = 1200
+    for _ in range(300):
+        bits = rng.getrandbits(62) | (rng.randrange(1, 2046) << 52) if rng.random() < 0.8 else rng.getrandbits(52)
+        bits &= (1 << 63) - 1
+        if (bits >> 52) == 2047:
+            continue
+        x = struct.unpack("<d", struct.pack("<Q", bits))[0]
+        y = struct.unpack("<d", struct.pack("<Q", bits + 1))[0]
+        if y == float("inf"):
+            continue
+        mid = (Decimal(x) + Decimal(y)) / 2
+        for delta in (Decimal(0), Decimal(1), Decimal(-1)):
+            d = mid + delta * Decimal(10) ** (mid.adjusted() - 60)
+            s = format(d, "e")
+            if "." not in s:
+                s = s.replace("e", ".0e")
+            s = s.replace("e+", "e")
+            assert emu.parse_f64(s) == _f64_bits(s), s
+
+
+def test_greedy_partition_is_balanced():
+    rng = np.random.default_rng(5)
+    sizes = np.clip(rng.lognormal(np.log(128 * 1024), 1.0, 4096), 4096, 8 << 20).astype(np.int64)
+    for n in (1, 2, 4, 8):
+        parts = corpus.greedy_partition(sizes, n)
+        assert sorted(i for p in parts for i in p) == list(range(len(sizes)))
+        loads = [int(sizes[p].sum()) for p in parts]
+        assert max(loads) - min(loads) <= sizes.max()

@@ -14,16 +14,6 @@
 
 #include "ptxfe_pipeline.h"
 
-struct PtxBatchView {
-    uint32_t n_modules = 0, mode = 0;
-    const PtxModuleLayout* layout = nullptr;
-    const PtxModuleResult* results = nullptr;
-    const uint32_t* words = nullptr;
-    const PtxErrRec* errs = nullptr;
-    const uint32_t* lexerrs = nullptr;
-    const char* const* texts = nullptr;
-};
-
 namespace ptxdump {
 
 struct Out {

@@ -12,6 +12,14 @@
 #include "gen/ptx_tables.h"
 #include "gen/ptx_pow5.h"
 
+#ifndef PTX_NOINLINE
+#ifdef __CUDACC__
+#define PTX_NOINLINE __noinline__
+#else
+#define PTX_NOINLINE __attribute__((noinline))
+#endif
+#endif
+
 struct PtxAdjMant {
     uint64_t mantissa;
     int32_t power2;   // biased exponent; 0x7FF = infinity
@@ -36,7 +44,7 @@ PTX_HD inline int ptx_clz64(uint64_t x) {
 }
 
 // value = w * 10^q, w != 0
-PTX_HD inline PtxAdjMant ptx_eisel_lemire(int64_t q, uint64_t w) {
+PTX_HD PTX_NOINLINE inline PtxAdjMant ptx_eisel_lemire(int64_t q, uint64_t w) {
     PtxAdjMant ans;
     ans.mantissa = 0;
     ans.power2 = 0;
@@ -134,7 +142,7 @@ PTX_HD inline int big_cmp(const PtxBig& a, const PtxBig& b) {
 
 // digits: the token text; [d0, d1) covers the significand characters (digits and one '.'), leading zeros allowed.
 // Returns sign of (decimal value - M * 2^P).  exp10 is the exponent applied after the last significand digit.
-PTX_HD inline int ptx_cmp_decimal_to_binary(const uint8_t* s, uint32_t d0, uint32_t d1, int64_t exp10, uint64_t M, int32_t P) {
+PTX_HD PTX_NOINLINE inline int ptx_cmp_decimal_to_binary(const uint8_t* s, uint32_t d0, uint32_t d1, int64_t exp10, uint64_t M, int32_t P) {
     PtxBig a, b;
     a.n = 0;
     const int max_digits = 800;   // more digits cannot change the comparison except through "sticky"
@@ -166,7 +174,7 @@ PTX_HD inline int ptx_cmp_decimal_to_binary(const uint8_t* s, uint32_t d0, uint3
 }
 
 // Convert a token matching [0-9]*\.[0-9]+([eE][-+]?[0-9]+)? to the bits of the nearest binary64.
-PTX_HD inline uint64_t ptx_parse_f64(const uint8_t* s, uint32_t len) {
+PTX_HD PTX_NOINLINE inline uint64_t ptx_parse_f64(const uint8_t* s, uint32_t len) {
     uint64_t w = 0;
     int ndigits = 0;          // significant digits accumulated into w (max 19)
     int64_t exp10 = 0;

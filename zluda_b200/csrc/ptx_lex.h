@@ -14,6 +14,14 @@
 #pragma once
 #include "gen/ptx_tables.h"
 
+#ifndef PTX_NOINLINE
+#ifdef __CUDACC__
+#define PTX_NOINLINE __noinline__
+#else
+#define PTX_NOINLINE __attribute__((noinline))
+#endif
+#endif
+
 #define PTX_CHUNK 128u
 
 enum { CX_CODE = 0, CX_SLASH = 1, CX_LINE = 2, CX_BLOCK = 3, CX_STAR = 4, CX_STR = 5, CX_STATES = 6 };
@@ -85,7 +93,7 @@ PTX_HD inline bool lx_ws(unsigned c) { return c == ' ' || (c - 9u) < 5u; }
 PTX_HD inline bool lx_soft(unsigned c) { return lx_identc(c) || c == '%' || c == '.' || c == ':' || c == '+' || c == '-'; }
 
 // ------------------------------------------------------------------------------------------------ keyword lookup
-PTX_HD inline uint16_t lx_keyword(const uint8_t* s, uint32_t len) {
+PTX_HD PTX_NOINLINE inline uint16_t lx_keyword(const uint8_t* s, uint32_t len) {
     if (len > PTX_KW_MAXLEN) return T_ERROR;
     uint32_t h = 2166136261u;
     for (uint32_t i = 0; i < len; i++) h = (h ^ s[i]) * PTX_KW_MULT;
@@ -105,7 +113,7 @@ PTX_HD inline uint16_t lx_keyword(const uint8_t* s, uint32_t len) {
 
 // ".L1::" ".L2::" ".param::" ".shared::" literals: `p` is at the '.', `q` at the first ':' ; returns the literal's
 // length and kind when the text continues with one of the known suffixes (longest match beats the DotIdent prefix)
-PTX_HD inline uint32_t lx_colon_literal(const uint8_t* s, uint64_t p, uint64_t q, uint64_t n, uint16_t* kind) {
+PTX_HD PTX_NOINLINE inline uint32_t lx_colon_literal(const uint8_t* s, uint64_t p, uint64_t q, uint64_t n, uint16_t* kind) {
     uint64_t r = q + 2;
     if (r >= n) return 0;
     uint64_t e = r;
@@ -120,7 +128,7 @@ PTX_HD inline uint32_t lx_colon_literal(const uint8_t* s, uint64_t p, uint64_t q
 
 // Longest token at p (p < n; text[p] is not whitespace, '/', or '"').  Returns its kind; *len = its length.
 // T_ERROR: no rule matches here (*len = 1).
-PTX_HD inline uint16_t lx_one(const uint8_t* s, uint64_t p, uint64_t n, uint32_t* len) {
+PTX_HD PTX_NOINLINE inline uint16_t lx_one(const uint8_t* s, uint64_t p, uint64_t n, uint32_t* len) {
     unsigned c = s[p];
     switch (c) {
     case ',': *len = 1; return T_COMMA;

@@ -1,0 +1,601 @@
+// CUDA backend and C ABI of the PTX front end (include/ptxfe.h).  Built for sm_100a only.
+//
+// Every pipeline step of ptxfe_pipeline.h runs as a kernel on the context's stream: a grid-stride-free parallel-for
+// (one thread per chunk, token or unit) or a three-phase block scan (reduce tiles, scan tile totals, rescan tiles).
+// Device memory comes from a per-context arena of retained cudaMalloc blocks, so a steady stream of batches allocates
+// nothing.  There is no host parsing path: without a device every entry point returns PTXFE_ERR_CUDA.
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <string>
+#include <vector>
+
+#define PTX_HD __device__
+#define PTX_TABLE static __device__ const
+#include "../../include/ptxfe.h"
+#include "ptxfe_pipeline.h"
+
+// host side (ptxfe_dump.cpp)
+std::string ptxfe_dump_module_impl(const PtxBatchView& v, uint32_t m, int* status);
+
+#define CUDA_TRY(call)                                                                      \
+    do {                                                                                    \
+        cudaError_t e_ = (call);                                                            \
+        if (e_ != cudaSuccess) {                                                            \
+            snprintf(ctx->err, sizeof ctx->err, "%s: %s", #call, cudaGetErrorString(e_));   \
+            return PTXFE_ERR_CUDA;                                                          \
+        }                                                                                   \
+    } while (0)
+
+// ------------------------------------------------------------------------------------------------ kernels
+template <class F>
+__global__ void __launch_bounds__(256) pf_kernel(size_t n, F f) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) f(i);
+}
+
+constexpr int SCAN_THREADS = 256;
+constexpr int SCAN_ITEMS = 8;
+constexpr int SCAN_TILE = SCAN_THREADS * SCAN_ITEMS;
+
+// ordered block-wide inclusive scan of one value per thread (associative, not necessarily commutative)
+template <class T, class Op>
+__device__ inline T block_scan_inclusive(T v, Op op, T* smem) {
+    int t = threadIdx.x;
+    smem[t] = v;
+    __syncthreads();
+    for (int off = 1; off < SCAN_THREADS; off <<= 1) {
+        T x = smem[t];
+        if (t >= off) x = op(smem[t - off], x);
+        __syncthreads();
+        smem[t] = x;
+        __syncthreads();
+    }
+    return smem[t];
+}
+
+template <class T, class Op, class Ld>
+__global__ void __launch_bounds__(SCAN_THREADS) scan_reduce_kernel(size_t n, Ld ld, Op op, T identity, T* partial) {
+    __shared__ T smem[SCAN_THREADS];
+    size_t base = (size_t)blockIdx.x * SCAN_TILE + (size_t)threadIdx.x * SCAN_ITEMS;
+    T acc = identity;
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++)
+        if (base + k < n) acc = op(acc, ld(base + k));
+    T incl = block_scan_inclusive(acc, op, smem);
+    if (threadIdx.x == SCAN_THREADS - 1) partial[blockIdx.x] = incl;
+}
+
+template <class T, class Op, class Ld, class St>
+__global__ void __launch_bounds__(SCAN_THREADS) scan_apply_kernel(size_t n, Ld ld, St st, Op op, T identity, const T* partial_incl) {
+    __shared__ T smem[SCAN_THREADS];
+    size_t base = (size_t)blockIdx.x * SCAN_TILE + (size_t)threadIdx.x * SCAN_ITEMS;
+    T vals[SCAN_ITEMS];
+    T acc = identity;
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++) {
+        if (base + k < n) acc = op(acc, ld(base + k));
+        vals[k] = acc;
+    }
+    T incl = block_scan_inclusive(acc, op, smem);
+    __syncthreads();
+    // exclusive prefix of this thread = inclusive of the previous thread, after the tiles before this block
+    T prefix = blockIdx.x ? partial_incl[blockIdx.x - 1] : identity;
+    if (threadIdx.x) prefix = op(prefix, smem[threadIdx.x - 1]);
+    (void)incl;
+#pragma unroll
+    for (int k = 0; k < SCAN_ITEMS; k++)
+        if (base + k < n) st(base + k, op(prefix, vals[k]));
+}
+
+template <class T> struct ArrayLoad {
+    const T* p;
+    __device__ T operator()(size_t i) const { return p[i]; }
+};
+template <class T> struct ArrayStore {
+    T* p;
+    __device__ void operator()(size_t i, T v) const { p[i] = v; }
+};
+
+// ------------------------------------------------------------------------------------------------ context
+struct ArenaBlock {
+    char* base;
+    size_t size, used;
+};
+
+struct ptxfe_batch {
+    ptxfe_ctx* ctx;
+    uint32_t n, mode;
+    std::vector<const char*> texts;
+    std::vector<PtxModuleLayout> layout;
+    std::vector<PtxModuleResult> results;
+    std::vector<int> status;        // lazily filled by dump
+    const uint32_t* words;
+    const PtxErrRec* errs;
+    const uint32_t* lexerrs;
+};
+
+struct ptxfe_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev[8] = {nullptr};
+    std::vector<ArenaBlock> blocks;
+    char err[512] = {0};
+    bool failed = false;
+    uint64_t launches = 0;
+    // staged batch
+    std::vector<const char*> texts;
+    std::vector<PtxModuleLayout> layout;
+    std::vector<uint32_t> mcb;
+    uint64_t text_bytes = 0, padded_bytes = 0;
+    uint8_t* d_text = nullptr;
+    size_t d_text_cap = 0;
+    PtxWork work;
+    PtxCounters counters;
+    bool staged = false, ran = false;
+    uint32_t mode = 0;
+    // pinned result buffers
+    void* h_words = nullptr; size_t h_words_cap = 0;
+    void* h_errs = nullptr; size_t h_errs_cap = 0;
+    void* h_lexerrs = nullptr; size_t h_lexerrs_cap = 0;
+    void* h_results = nullptr; size_t h_results_cap = 0;
+    PtxCounters* h_counters = nullptr;
+    ptxfe_stats stats;
+    ptxfe_batch* live = nullptr;
+    // per-step profile
+    bool profile = false;
+    std::vector<cudaEvent_t> prof_events;
+    std::vector<const char*> prof_names;
+    size_t prof_used = 0;
+    std::string prof_text;
+};
+
+struct CudaBackend {
+    ptxfe_ctx* ctx;
+    void* alloc(size_t bytes) {
+        bytes = (bytes + 255) & ~(size_t)255;
+        for (ArenaBlock& b : ctx->blocks)
+            if (b.size - b.used >= bytes) {
+                void* p = b.base + b.used;
+                b.used += bytes;
+                return p;
+            }
+        size_t sz = bytes > ((size_t)256 << 20) ? bytes : ((size_t)256 << 20);
+        ArenaBlock nb;
+        nb.base = nullptr;
+        if (cudaMalloc((void**)&nb.base, sz) != cudaSuccess) {
+            if (!ctx->failed) snprintf(ctx->err, sizeof ctx->err, "cudaMalloc of %zu bytes failed", sz);
+            ctx->failed = true;
+            cudaGetLastError();
+            // keep going with a small dummy block is not possible: callers check ctx->failed before launching
+            return nullptr;
+        }
+        nb.size = sz;
+        nb.used = bytes;
+        ctx->blocks.push_back(nb);
+        return nb.base;
+    }
+    void reset() {
+        for (ArenaBlock& b : ctx->blocks) b.used = 0;
+    }
+    void zero(void* p, size_t bytes) {
+        if (ctx->failed || !p) return;
+        cudaMemsetAsync(p, 0, bytes, ctx->stream);
+    }
+    void download(void* host, const void* dev, size_t bytes) {
+        if (ctx->failed) { memset(host, 0, bytes); return; }
+        cudaMemcpyAsync(ctx->h_counters, dev, bytes, cudaMemcpyDeviceToHost, ctx->stream);
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) {
+            snprintf(ctx->err, sizeof ctx->err, "kernel or copy failed: %s", cudaGetErrorString(e));
+            ctx->failed = true;
+            memset(host, 0, bytes);
+            return;
+        }
+        memcpy(host, ctx->h_counters, bytes);
+    }
+    // optional per-step timing (PTXFE_PROFILE=1): one event pair per step, read back by ptxfe_profile
+    void prof_begin(const char* name) {
+        if (!ctx->profile) return;
+        if (ctx->prof_used + 2 > ctx->prof_events.size()) {
+            for (int i = 0; i < 2; i++) {
+                cudaEvent_t e;
+                cudaEventCreate(&e);
+                ctx->prof_events.push_back(e);
+            }
+        }
+        ctx->prof_names.push_back(name);
+        cudaEventRecord(ctx->prof_events[ctx->prof_used++], ctx->stream);
+    }
+    void prof_end() {
+        if (!ctx->profile) return;
+        cudaEventRecord(ctx->prof_events[ctx->prof_used++], ctx->stream);
+    }
+    template <class F> void pf(const char* name, size_t n, F f) {
+        if (ctx->failed || n == 0) return;
+        size_t blocks = (n + 255) / 256;
+        prof_begin(name);
+        pf_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(n, f);
+        prof_end();
+        ctx->launches++;
+    }
+    template <class T, class Ld, class St, class Op> void scan(const char* name, size_t n, Ld ld, St st, Op op, T identity) {
+        if (ctx->failed || n == 0) return;
+        prof_begin(name);
+        scan_impl<T>(n, ld, st, op, identity);
+        prof_end();
+    }
+    template <class T, class Ld, class St, class Op> void scan_impl(size_t n, Ld ld, St st, Op op, T identity) {
+        if (ctx->failed || n == 0) return;
+        size_t tiles = (n + SCAN_TILE - 1) / SCAN_TILE;
+        T* partial = (T*)alloc(sizeof(T) * (tiles + 1));
+        if (!partial) return;
+        scan_reduce_kernel<T><<<(unsigned)tiles, SCAN_THREADS, 0, ctx->stream>>>(n, ld, op, identity, partial);
+        ctx->launches++;
+        if (tiles > 1) {
+            // scan the tile totals in place (recursively)
+            scan_impl<T>(tiles, ArrayLoad<T>{partial}, ArrayStore<T>{partial}, op, identity);
+        }
+        scan_apply_kernel<T><<<(unsigned)tiles, SCAN_THREADS, 0, ctx->stream>>>(n, ld, st, op, identity, partial);
+        ctx->launches++;
+    }
+};
+
+static int ensure_pinned(ptxfe_ctx* ctx, void** p, size_t* cap, size_t need) {
+    if (need <= *cap) return PTXFE_OK;
+    if (*p) cudaFreeHost(*p);
+    *p = nullptr;
+    size_t sz = need + need / 4 + 4096;
+    CUDA_TRY(cudaMallocHost(p, sz));
+    *cap = sz;
+    return PTXFE_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ C ABI
+extern "C" {
+
+const char* ptxfe_status_str(int s) {
+    switch (s) {
+    case PTXFE_OK: return "ok";
+    case PTXFE_ERR_BAD_ARG: return "bad argument";
+    case PTXFE_ERR_CUDA: return "CUDA error";
+    case PTXFE_ERR_TOO_LARGE: return "batch too large";
+    case PTXFE_ERR_OOM: return "out of memory";
+    default: return "unknown status";
+    }
+}
+
+int ptxfe_create(int device, ptxfe_ctx** out) {
+    if (!out) return PTXFE_ERR_BAD_ARG;
+    *out = nullptr;
+    ptxfe_ctx* ctx = new ptxfe_ctx();
+    ctx->device = device;
+    memset(&ctx->stats, 0, sizeof ctx->stats);
+    ctx->profile = getenv("PTXFE_PROFILE") && atoi(getenv("PTXFE_PROFILE")) != 0;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) {
+        fprintf(stderr, "ptxfe: no usable CUDA device %d (this library has no CPU path)\n", device);
+        delete ctx;
+        return PTXFE_ERR_CUDA;
+    }
+    cudaError_t e = cudaSetDevice(device);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    for (int i = 0; i < 8 && e == cudaSuccess; i++) e = cudaEventCreate(&ctx->ev[i]);
+    if (e == cudaSuccess) e = cudaMallocHost((void**)&ctx->h_counters, sizeof(PtxCounters) * 4);
+    if (e != cudaSuccess) {
+        fprintf(stderr, "ptxfe: context set-up failed: %s\n", cudaGetErrorString(e));
+        delete ctx;
+        return PTXFE_ERR_CUDA;
+    }
+    *out = ctx;
+    return PTXFE_OK;
+}
+
+void ptxfe_destroy(ptxfe_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    if (ctx->stream) cudaStreamSynchronize(ctx->stream);
+    for (ArenaBlock& b : ctx->blocks) cudaFree(b.base);
+    if (ctx->d_text) cudaFree(ctx->d_text);
+    if (ctx->h_words) cudaFreeHost(ctx->h_words);
+    if (ctx->h_errs) cudaFreeHost(ctx->h_errs);
+    if (ctx->h_lexerrs) cudaFreeHost(ctx->h_lexerrs);
+    if (ctx->h_results) cudaFreeHost(ctx->h_results);
+    if (ctx->h_counters) cudaFreeHost(ctx->h_counters);
+    for (int i = 0; i < 8; i++)
+        if (ctx->ev[i]) cudaEventDestroy(ctx->ev[i]);
+    if (ctx->stream) cudaStreamDestroy(ctx->stream);
+    if (ctx->live) ctx->live->ctx = nullptr;
+    delete ctx;
+}
+
+const char* ptxfe_last_error(const ptxfe_ctx* ctx) { return ctx ? ctx->err : "no context"; }
+
+int ptxfe_stage(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, uint32_t n) {
+    if (!ctx || (n && (!texts || !lens))) return PTXFE_ERR_BAD_ARG;
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    ctx->failed = false;
+    ctx->staged = ctx->ran = false;
+    ctx->texts.assign(texts, texts + n);
+    ctx->layout.resize(n);
+    ctx->mcb.resize((size_t)n + 1);
+    uint64_t off = 0, chunks = 0, total = 0;
+    for (uint32_t m = 0; m < n; m++) {
+        PtxModuleLayout& l = ctx->layout[m];
+        l.text_off = off;
+        l.text_len = lens[m];
+        l.chunk_begin = (uint32_t)chunks;
+        l.pad = 0;
+        ctx->mcb[m] = (uint32_t)chunks;
+        uint64_t c = (lens[m] + PTX_CHUNK - 1) / PTX_CHUNK;
+        chunks += c;
+        off += c * PTX_CHUNK;
+        total += lens[m];
+        if (off >= 0xFFFFFF00ull) return PTXFE_ERR_TOO_LARGE;
+    }
+    ctx->mcb[n] = (uint32_t)chunks;
+    ctx->text_bytes = total;
+    ctx->padded_bytes = off;
+    if (off + 256 > ctx->d_text_cap) {
+        if (ctx->d_text) cudaFree(ctx->d_text);
+        ctx->d_text = nullptr;
+        ctx->d_text_cap = 0;
+        size_t cap = off + off / 8 + 4096;
+        CUDA_TRY(cudaMalloc((void**)&ctx->d_text, cap));
+        ctx->d_text_cap = cap;
+    }
+    CUDA_TRY(cudaEventRecord(ctx->ev[0], ctx->stream));
+    for (uint32_t m = 0; m < n; m++)
+        if (lens[m])
+            CUDA_TRY(cudaMemcpyAsync(ctx->d_text + ctx->layout[m].text_off, texts[m], lens[m], cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(cudaEventRecord(ctx->ev[1], ctx->stream));
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(cudaEventElapsedTime(&ctx->stats.h2d_ms, ctx->ev[0], ctx->ev[1]));
+    ctx->stats.h2d_bytes = total;
+    ctx->stats.text_bytes = total;
+    ctx->stats.n_modules = n;
+    ctx->staged = true;
+    return PTXFE_OK;
+}
+
+int ptxfe_run(ptxfe_ctx* ctx, uint32_t mode) {
+    if (!ctx || !ctx->staged || mode > 2) return PTXFE_ERR_BAD_ARG;
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    if (ctx->live) { ctx->live->ctx = nullptr; ctx->live = nullptr; }
+    CudaBackend bk{ctx};
+    bk.reset();
+    ctx->failed = false;
+    ctx->launches = 0;
+    ctx->prof_used = 0;
+    ctx->prof_names.clear();
+    ctx->mode = mode;
+    uint32_t n = (uint32_t)ctx->layout.size();
+    PtxWork& w = ctx->work;
+    w = PtxWork();
+    w.text = ctx->d_text;
+    w.n_modules = n;
+    w.n_chunks = ctx->mcb[n];
+    w.layout = (PtxModuleLayout*)bk.alloc(sizeof(PtxModuleLayout) * ((size_t)n + 1));
+    w.mod_chunk_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n + 2));
+    w.results = (PtxModuleResult*)bk.alloc(sizeof(PtxModuleResult) * ((size_t)n + 1));
+    w.counters = (PtxCounters*)bk.alloc(sizeof(PtxCounters));
+    if (ctx->failed) return PTXFE_ERR_OOM;
+    CUDA_TRY(cudaEventRecord(ctx->ev[2], ctx->stream));
+    if (n) {
+        CUDA_TRY(cudaMemcpyAsync(w.layout, ctx->layout.data(), sizeof(PtxModuleLayout) * n, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    CUDA_TRY(cudaMemcpyAsync(w.mod_chunk_begin, ctx->mcb.data(), sizeof(uint32_t) * ((size_t)n + 1), cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(cudaMemsetAsync(w.counters, 0, sizeof(PtxCounters), ctx->stream));
+    memset(&ctx->counters, 0, sizeof ctx->counters);
+    ptx_stage_lex(bk, w, ctx->counters);
+    CUDA_TRY(cudaEventRecord(ctx->ev[3], ctx->stream));
+    if (!ctx->failed) ptx_stage_structure(bk, w, ctx->counters, mode);
+    CUDA_TRY(cudaEventRecord(ctx->ev[4], ctx->stream));
+    if (!ctx->failed) ptx_stage_decode(bk, w, ctx->counters);
+    CUDA_TRY(cudaEventRecord(ctx->ev[5], ctx->stream));
+    cudaError_t e = cudaStreamSynchronize(ctx->stream);
+    if (e == cudaSuccess) e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        snprintf(ctx->err, sizeof ctx->err, "pipeline failed: %s", cudaGetErrorString(e));
+        return PTXFE_ERR_CUDA;
+    }
+    if (ctx->failed) return strstr(ctx->err, "cudaMalloc") ? PTXFE_ERR_OOM : PTXFE_ERR_CUDA;
+    ptxfe_stats& s = ctx->stats;
+    cudaEventElapsedTime(&s.kernel_ms, ctx->ev[2], ctx->ev[5]);
+    cudaEventElapsedTime(&s.lex_ms, ctx->ev[2], ctx->ev[3]);
+    cudaEventElapsedTime(&s.structure_ms, ctx->ev[3], ctx->ev[4]);
+    cudaEventElapsedTime(&s.decode_ms, ctx->ev[4], ctx->ev[5]);
+    s.n_tokens = ctx->counters.n_tokens;
+    s.n_units = ctx->counters.n_units;
+    s.n_result_words = ctx->counters.n_words;
+    s.n_errors = ctx->counters.n_errs;
+    s.n_lex_errors = ctx->counters.n_lexerrs;
+    s.n_kernel_launches = ctx->launches;
+    s.n_sequential = 0;
+    ctx->ran = true;
+    if (ctx->profile) {
+        ctx->prof_text.clear();
+        for (size_t i = 0; i < ctx->prof_names.size(); i++) {
+            float ms = 0;
+            cudaEventElapsedTime(&ms, ctx->prof_events[2 * i], ctx->prof_events[2 * i + 1]);
+            char line[160];
+            snprintf(line, sizeof line, "%s %.6f\n", ctx->prof_names[i], ms);
+            ctx->prof_text += line;
+        }
+    }
+    return PTXFE_OK;
+}
+
+const char* ptxfe_profile(const ptxfe_ctx* ctx) { return ctx ? ctx->prof_text.c_str() : ""; }
+
+int ptxfe_fetch(ptxfe_ctx* ctx, ptxfe_batch** out) {
+    if (!ctx || !out || !ctx->ran) return PTXFE_ERR_BAD_ARG;
+    *out = nullptr;
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    const PtxCounters& c = ctx->counters;
+    uint32_t n = (uint32_t)ctx->layout.size();
+    size_t wb = sizeof(uint32_t) * (size_t)c.n_words, eb = sizeof(PtxErrRec) * (size_t)c.n_errs;
+    size_t lb = sizeof(uint32_t) * 2 * (size_t)c.n_lexerrs, rb = sizeof(PtxModuleResult) * (size_t)n;
+    int st;
+    if ((st = ensure_pinned(ctx, &ctx->h_words, &ctx->h_words_cap, wb + 16)) != PTXFE_OK) return st;
+    if ((st = ensure_pinned(ctx, &ctx->h_errs, &ctx->h_errs_cap, eb + 16)) != PTXFE_OK) return st;
+    if ((st = ensure_pinned(ctx, &ctx->h_lexerrs, &ctx->h_lexerrs_cap, lb + 16)) != PTXFE_OK) return st;
+    if ((st = ensure_pinned(ctx, &ctx->h_results, &ctx->h_results_cap, rb + 16)) != PTXFE_OK) return st;
+    CUDA_TRY(cudaEventRecord(ctx->ev[6], ctx->stream));
+    if (wb) CUDA_TRY(cudaMemcpyAsync(ctx->h_words, ctx->work.words, wb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (eb) CUDA_TRY(cudaMemcpyAsync(ctx->h_errs, ctx->work.errs, eb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (lb) CUDA_TRY(cudaMemcpyAsync(ctx->h_lexerrs, ctx->work.lexerrs, lb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (rb) CUDA_TRY(cudaMemcpyAsync(ctx->h_results, ctx->work.results, rb, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(cudaEventRecord(ctx->ev[7], ctx->stream));
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(cudaEventElapsedTime(&ctx->stats.d2h_ms, ctx->ev[6], ctx->ev[7]));
+    ctx->stats.d2h_bytes = wb + eb + lb + rb;
+    ptxfe_batch* b = new ptxfe_batch();
+    b->ctx = ctx;
+    b->n = n;
+    b->mode = ctx->mode;
+    b->texts = ctx->texts;
+    b->layout = ctx->layout;
+    b->results.assign((PtxModuleResult*)ctx->h_results, (PtxModuleResult*)ctx->h_results + n);
+    b->status.assign(n, -1);
+    b->words = (const uint32_t*)ctx->h_words;
+    b->errs = (const PtxErrRec*)ctx->h_errs;
+    b->lexerrs = (const uint32_t*)ctx->h_lexerrs;
+    uint64_t seq = 0;
+    for (uint32_t m = 0; m < n; m++) seq += b->results[m].sequential;
+    ctx->stats.n_sequential = seq;
+    ctx->live = b;
+    *out = b;
+    return PTXFE_OK;
+}
+
+int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, uint32_t n, uint32_t mode, ptxfe_batch** out) {
+    if (!out) return PTXFE_ERR_BAD_ARG;
+    *out = nullptr;
+    int st = ptxfe_stage(ctx, texts, lens, n);
+    if (st == PTXFE_OK) st = ptxfe_run(ctx, mode);
+    if (st == PTXFE_OK) st = ptxfe_fetch(ctx, out);
+    return st;
+}
+
+void ptxfe_batch_free(ptxfe_batch* b) {
+    if (!b) return;
+    if (b->ctx && b->ctx->live == b) b->ctx->live = nullptr;
+    delete b;
+}
+uint32_t ptxfe_batch_size(const ptxfe_batch* b) { return b ? b->n : 0; }
+void ptxfe_get_stats(const ptxfe_ctx* ctx, ptxfe_stats* out) {
+    if (ctx && out) *out = ctx->stats;
+}
+
+static PtxBatchView view_of(const ptxfe_batch* b) {
+    PtxBatchView v;
+    v.n_modules = b->n;
+    v.mode = b->mode;
+    v.layout = b->layout.data();
+    v.results = b->results.data();
+    v.words = b->words;
+    v.errs = b->errs;
+    v.lexerrs = b->lexerrs;
+    v.texts = b->texts.data();
+    return v;
+}
+
+int ptxfe_module_dump(const ptxfe_batch* b, uint32_t i, char** out, uint64_t* out_len) {
+    if (!b || !b->ctx || i >= b->n || !out) return PTXFE_ERR_BAD_ARG;
+    int status = 0;
+    std::string s = ptxfe_dump_module_impl(view_of(b), i, &status);
+    char* r = (char*)malloc(s.size() + 1);
+    if (!r) return PTXFE_ERR_OOM;
+    memcpy(r, s.data(), s.size() + 1);
+    *out = r;
+    if (out_len) *out_len = s.size();
+    return PTXFE_OK;
+}
+
+int ptxfe_module_dump_hash(const ptxfe_batch* b, uint32_t i, uint64_t* out_hash) {
+    if (!b || !b->ctx || i >= b->n || !out_hash) return PTXFE_ERR_BAD_ARG;
+    int status = 0;
+    std::string s = ptxfe_dump_module_impl(view_of(b), i, &status);
+    uint64_t h = 1469598103934665603ull;
+    for (unsigned char c : s) h = (h ^ c) * 1099511628211ull;
+    *out_hash = h;
+    return PTXFE_OK;
+}
+
+int ptxfe_module_status(const ptxfe_batch* b, uint32_t i) {
+    if (!b || !b->ctx || i >= b->n) return PTXFE_MODULE_ERR;
+    int status = 0;
+    std::string s = ptxfe_dump_module_impl(view_of(b), i, &status);
+    if (b->results[i].sequential && b->results[i].status == US_PANIC) return PTXFE_MODULE_REF_PANICS;
+    return status ? PTXFE_MODULE_ERR : PTXFE_MODULE_OK;
+}
+
+uint32_t ptxfe_module_error_count(const ptxfe_batch* b, uint32_t i) {
+    if (!b || !b->ctx || i >= b->n) return 0;
+    const PtxModuleResult& r = b->results[i];
+    uint32_t n = r.lexerr_end - r.lexerr_begin;
+    if (n && b->mode != PTXFE_ERRORS_ONLY) return n;
+    for (uint32_t e = r.err_begin; e < r.err_end; e++)
+        if ((b->errs[e].w0 & 0xFFFF) != E_NONE) n++;
+    return n;
+}
+
+int ptxfe_module_records(const ptxfe_batch* b, uint32_t i, const uint32_t** words, uint64_t* n_words, uint64_t* text_base) {
+    if (!b || !b->ctx || i >= b->n) return PTXFE_ERR_BAD_ARG;
+    if (words) *words = b->words + b->results[i].word_begin;
+    if (n_words) *n_words = b->results[i].word_end - b->results[i].word_begin;
+    if (text_base) *text_base = b->layout[i].text_off;
+    return PTXFE_OK;
+}
+
+void ptxfe_free(void* p) { free(p); }
+
+int ptxfe_lex_module(ptxfe_ctx* ctx, const char* text, uint64_t len, uint32_t** out, uint64_t* n_tokens, uint64_t* n_errors) {
+    if (!ctx || !out || !n_tokens || !n_errors) return PTXFE_ERR_BAD_ARG;
+    const char* texts[1] = {text};
+    uint64_t lens[1] = {len};
+    int st = ptxfe_stage(ctx, texts, lens, 1);
+    if (st != PTXFE_OK) return st;
+    CudaBackend bk{ctx};
+    bk.reset();
+    ctx->failed = false;
+    PtxWork& w = ctx->work;
+    w = PtxWork();
+    w.text = ctx->d_text;
+    w.n_modules = 1;
+    w.n_chunks = ctx->mcb[1];
+    w.layout = (PtxModuleLayout*)bk.alloc(sizeof(PtxModuleLayout) * 2);
+    w.mod_chunk_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * 3);
+    w.results = (PtxModuleResult*)bk.alloc(sizeof(PtxModuleResult) * 2);
+    w.counters = (PtxCounters*)bk.alloc(sizeof(PtxCounters));
+    if (ctx->failed) return PTXFE_ERR_OOM;
+    CUDA_TRY(cudaMemcpyAsync(w.layout, ctx->layout.data(), sizeof(PtxModuleLayout), cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(cudaMemcpyAsync(w.mod_chunk_begin, ctx->mcb.data(), sizeof(uint32_t) * 2, cudaMemcpyHostToDevice, ctx->stream));
+    CUDA_TRY(cudaMemsetAsync(w.counters, 0, sizeof(PtxCounters), ctx->stream));
+    memset(&ctx->counters, 0, sizeof ctx->counters);
+    ptx_stage_lex(bk, w, ctx->counters);
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    if (ctx->failed) return PTXFE_ERR_CUDA;
+    uint32_t nt = ctx->counters.n_tokens, ne = ctx->counters.n_lexerrs;
+    std::vector<PtxToken> toks(nt);
+    std::vector<uint32_t> errs((size_t)ne * 2);
+    if (nt) CUDA_TRY(cudaMemcpy(toks.data(), w.tokens, sizeof(PtxToken) * nt, cudaMemcpyDeviceToHost));
+    if (ne) CUDA_TRY(cudaMemcpy(errs.data(), w.lexerrs, sizeof(uint32_t) * 2 * ne, cudaMemcpyDeviceToHost));
+    uint32_t* r = (uint32_t*)malloc(((size_t)nt * 3 + (size_t)ne * 2 + 1) * 4);
+    if (!r) return PTXFE_ERR_OOM;
+    size_t k = 0;
+    for (uint32_t i = 0; i < nt; i++) {
+        r[k++] = toks[i].kind;
+        r[k++] = toks[i].start;
+        r[k++] = toks[i].len;   // 0xFFFF means "65535 or longer"
+    }
+    for (uint32_t i = 0; i < ne; i++) { r[k++] = errs[2 * i]; r[k++] = errs[2 * i + 1]; }
+    *out = r;
+    *n_tokens = nt;
+    *n_errors = ne;
+    return PTXFE_OK;
+}
+}

@@ -27,6 +27,18 @@ struct PtxModuleResult {
     uint32_t status;       // PtxUnitStatus of the sequential path
 };
 
+// host view of one fetched batch (input of the dump)
+struct PtxErrRec;
+struct PtxBatchView {
+    uint32_t n_modules = 0, mode = 0;
+    const PtxModuleLayout* layout = nullptr;
+    const PtxModuleResult* results = nullptr;
+    const uint32_t* words = nullptr;
+    const PtxErrRec* errs = nullptr;
+    const uint32_t* lexerrs = nullptr;
+    const char* const* texts = nullptr;
+};
+
 struct PtxDepth {
     int32_t scope, paren;
 };
@@ -107,8 +119,8 @@ struct SegDepthOp {
 };
 
 // Backend concept:
-//   template <class F> void pf(size_t n, F f);                                  f(i) for i in [0, n)
-//   template <class T, class Op, class Ld, class St> void scan(size_t n, Ld ld, St st, Op op, T identity);
+//   template <class F> void pf(const char* name, size_t n, F f);                f(i) for i in [0, n)
+//   template <class T, class Op, class Ld, class St> void scan(const char* name, size_t n, Ld ld, St st, Op op, T identity);
 //        inclusive scan: st(i, op(ld(0), ..., ld(i)))
 //   void* alloc(size_t bytes); void zero(void* p, size_t bytes);
 //   void download(void* host, const void* dev, size_t bytes);   (synchronises the stream)
@@ -128,7 +140,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     PtxCounters* counters = w.counters;
 
     // A1: transition vector of every chunk
-    bk.pf(n_chunks, [=] PTX_HD(size_t c) {
+    bk.pf("lex_context_vectors", n_chunks, [=] PTX_HD(size_t c) {
         uint32_t m = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)c) - 1;
         uint64_t cs = layout[m].text_off + (uint64_t)(c - mcb[m]) * PTX_CHUNK;
         uint64_t me = layout[m].text_off + layout[m].text_len;
@@ -137,10 +149,10 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         vec[c] = (c == mcb[m]) ? cx_restart(v) : v;
     });
     // A2: inclusive scan with composition; chunk c starts in state (prefix[c-1])[CODE]
-    bk.template scan<uint32_t>(n_chunks, [=] PTX_HD(size_t i) { return vec[i]; }, [=] PTX_HD(size_t i, uint32_t v) { vec[i] = v; },
+    bk.template scan<uint32_t>("scan_context", n_chunks, [=] PTX_HD(size_t i) { return vec[i]; }, [=] PTX_HD(size_t i, uint32_t v) { vec[i] = v; },
                                ComposeOp(), CX_IDENTITY);
     // A3: count the tokens that start in every chunk
-    bk.pf(n_chunks, [=] PTX_HD(size_t c) {
+    bk.pf("lex_count_tokens", n_chunks, [=] PTX_HD(size_t c) {
         uint32_t m = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)c) - 1;
         uint64_t ms = layout[m].text_off, me = ms + layout[m].text_len;
         uint64_t cs = ms + (uint64_t)(c - mcb[m]) * PTX_CHUNK;
@@ -154,9 +166,9 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         if (c == 0) { PtxPair z; z.a = z.b = 0; cnt[0] = z; }
     });
     // A4: exclusive offsets (cnt[c] = tokens before chunk c; cnt[n_chunks] = total)
-    bk.template scan<PtxPair>(n_chunks + 1, [=] PTX_HD(size_t i) { return cnt[i]; }, [=] PTX_HD(size_t i, PtxPair v) { cnt[i] = v; },
+    bk.template scan<PtxPair>("scan_token_counts", n_chunks + 1, [=] PTX_HD(size_t i) { return cnt[i]; }, [=] PTX_HD(size_t i, PtxPair v) { cnt[i] = v; },
                               PairAddOp(), PtxPair{0, 0});
-    bk.pf(1, [=] PTX_HD(size_t) {
+    bk.pf("set_token_total", 1, [=] PTX_HD(size_t) {
         counters->n_tokens = n_chunks ? cnt[n_chunks].a : 0;
         counters->n_lexerrs = n_chunks ? cnt[n_chunks].b : 0;
     });
@@ -165,7 +177,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     PtxToken* tokens = w.tokens = (PtxToken*)bk.alloc(sizeof(PtxToken) * (size_t)(n_tokens + 1));
     uint32_t* lexerrs = w.lexerrs = (uint32_t*)bk.alloc(sizeof(uint32_t) * 2 * (size_t)(n_lexerrs + 1));
     // A5: emit
-    bk.pf(n_chunks, [=] PTX_HD(size_t c) {
+    bk.pf("lex_emit_tokens", n_chunks, [=] PTX_HD(size_t c) {
         uint32_t m = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)c) - 1;
         uint64_t ms = layout[m].text_off, me = ms + layout[m].text_len;
         uint64_t cs = ms + (uint64_t)(c - mcb[m]) * PTX_CHUNK;
@@ -176,13 +188,13 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         lx_chunk(text, ms, me, cs, cs + PTX_CHUNK, state, sink);
     });
     uint32_t* mtb = w.mod_tok_begin;
-    bk.pf(n_modules + 1, [=] PTX_HD(size_t m) {
+    bk.pf("module_token_ranges", n_modules + 1, [=] PTX_HD(size_t m) {
         uint32_t c = mcb[m];   // mod_chunk_begin[n_modules] = n_chunks
         mtb[m] = n_chunks ? cnt[c].a : 0;
         mod_lexerr_begin[m] = n_chunks ? cnt[c].b : 0;
     });
     PtxModuleResult* results = w.results;
-    bk.pf(n_modules, [=] PTX_HD(size_t m) {
+    bk.pf("module_results_init", n_modules, [=] PTX_HD(size_t m) {
         PtxModuleResult r;
         r.tok_begin = mtb[m];
         r.tok_end = mtb[m + 1];
@@ -219,13 +231,13 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
     bk.zero(tflags, (size_t)n_tokens + 16);
     // B0: mark the first token of every module.  A module with a lex error is not parsed unless only its errors
     // are wanted (lib.rs:392-411 vs 447-449, 487-489)
-    bk.pf(n_modules, [=] PTX_HD(size_t m) {
+    bk.pf("mark_module_first", n_modules, [=] PTX_HD(size_t m) {
         if (mtb[m] < mtb[m + 1]) tflags[mtb[m]] = TF_MODULE_FIRST;
         bool lexerr = results[m].lexerr_end > results[m].lexerr_begin;
         mod_skip[m] = (mtb[m] == mtb[m + 1] || (lexerr && mode != 2)) ? 1u : 0u;
     });
     // B1: classify braces from their left neighbours
-    bk.pf(n_tokens, [=] PTX_HD(size_t i) {
+    bk.pf("classify_braces", n_tokens, [=] PTX_HD(size_t i) {
         uint16_t k = tokens[i].kind;
         uint8_t f = tflags[i];
         bool first = (f & TF_MODULE_FIRST) != 0;
@@ -241,7 +253,7 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
     });
     // B2: scope and paren depth, restarting at every module (inclusive)
     bk.template scan<PtxSeg3>(
-        n_tokens,
+        "scan_depth", n_tokens,
         [=] PTX_HD(size_t i) {
             PtxSeg3 v;
             uint8_t f = tflags[i];
@@ -259,7 +271,7 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
         },
         SegDepthOp(), PtxSeg3{0, 0, 0});
     // B3: speculate unit starts
-    bk.pf(n_tokens, [=] PTX_HD(size_t i) {
+    bk.pf("speculate_unit_starts", n_tokens, [=] PTX_HD(size_t i) {
         uint8_t f = tflags[i];
         bool first = (f & TF_MODULE_FIRST) != 0;
         bool start = first;
@@ -283,15 +295,15 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
         uot[i + 1] = start ? 1u : 0u;
         if (i == 0) uot[0] = 0;
     });
-    bk.template scan<uint32_t>((size_t)n_tokens + 1, [=] PTX_HD(size_t i) { return uot[i]; },
+    bk.template scan<uint32_t>("scan_unit_index", (size_t)n_tokens + 1, [=] PTX_HD(size_t i) { return uot[i]; },
                                [=] PTX_HD(size_t i, uint32_t v) { uot[i] = v; }, AddOp(), 0u);
-    bk.pf(1, [=] PTX_HD(size_t) { counters->n_units = n_tokens ? uot[n_tokens] : 0; });
+    bk.pf("set_unit_total", 1, [=] PTX_HD(size_t) { counters->n_units = n_tokens ? uot[n_tokens] : 0; });
     bk.download(&host_counters, counters, sizeof(PtxCounters));
     const uint32_t n_units = host_counters.n_units;
     uint32_t* ustart = w.unit_start = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 2));
     uint32_t* udepth = w.unit_depth = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
     // B5: compact
-    bk.pf(n_tokens, [=] PTX_HD(size_t i) {
+    bk.pf("compact_unit_starts", n_tokens, [=] PTX_HD(size_t i) {
         uint8_t f = tflags[i];
         if (!(f & TF_UNIT_START)) return;
         uint32_t u = uot[i];
@@ -301,7 +313,7 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
         udepth[u] = (uint32_t)(sd < 0 ? 0 : sd) | (first ? 0x80000000u : 0u);
     });
     uint32_t* mub = w.mod_unit_begin;
-    bk.pf(n_modules + 1, [=] PTX_HD(size_t m) { mub[m] = n_tokens ? uot[mtb[m]] : 0; });
+    bk.pf("module_unit_ranges", n_modules + 1, [=] PTX_HD(size_t m) { mub[m] = n_tokens ? uot[mtb[m]] : 0; });
 }
 
 // ------------------------------------------------------------------------------------------------ stage C: decode
@@ -332,9 +344,9 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     bk.zero(mod_seq_status, sizeof(uint32_t) * (n_modules + 1));
 
     // C0: ordinal of the enclosing top-level unit
-    bk.template scan<uint32_t>(n_units, [=] PTX_HD(size_t u) { return (udepth[u] & 0x7FFFFFFFu) == 0 ? 1u : 0u; },
+    bk.template scan<uint32_t>("scan_toplevel_ordinal", n_units, [=] PTX_HD(size_t u) { return (udepth[u] & 0x7FFFFFFFu) == 0 ? 1u : 0u; },
                                [=] PTX_HD(size_t u, uint32_t v) { udir[u] = v; }, AddOp(), 0u);
-    bk.pf(1, [=] PTX_HD(size_t) {
+    bk.pf("reset_func_count", 1, [=] PTX_HD(size_t) {
         counters->n_funcs = 0;
         counters->any_sequential = 0;
         counters->pad = n_units ? udir[n_units - 1] : 0;   // number of top-level units: bound for the function table
@@ -344,7 +356,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     PtxFnEntry* fn_entries = w.fn_entries = (PtxFnEntry*)bk.alloc(sizeof(PtxFnEntry) * ((size_t)max_funcs + 1));
 
     // C1: decode every unit, counting only
-    bk.pf(n_units, [=] PTX_HD(size_t u) {
+    bk.pf("decode_count", n_units, [=] PTX_HD(size_t u) {
         uint32_t start = ustart[u];
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         // modules without units share their begin with the next one: take the last module that starts at or before u
@@ -357,10 +369,10 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
             ustatus[u] = US_OK;
             return;
         }
-        DecCountSink sink;
-        PtxHashResolver res;
-        res.entries = nullptr; res.slots = nullptr; res.mask = 0; res.unit_off = nullptr; res.module = m; res.my_dir_ord = 0;
-        PtxDecoder<DecCountSink, PtxHashResolver> d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
+        PtxSink sink;
+        PtxResolver res;
+        res.module = m;
+        PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
         uint32_t dp = udepth[u];
         PtxUnitResult r = ptx_decode_unit(d, start, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
         uend[u] = r.end;
@@ -388,7 +400,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         }
     });
     // C2: do consecutive units meet, and does every module return to depth 0?
-    bk.pf(n_units, [=] PTX_HD(size_t u) {
+    bk.pf("chain_check", n_units, [=] PTX_HD(size_t u) {
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         if (mod_skip[m]) return;
         uint32_t next = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
@@ -397,14 +409,12 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         if (!ok) mod_bad[m] = 1;
     });
     // C3: modules whose units do not meet are parsed sequentially by one thread each (count)
-    bk.pf(n_modules, [=] PTX_HD(size_t m) {
+    bk.pf("sequential_count", n_modules, [=] PTX_HD(size_t m) {
         if (!mod_bad[m]) return;
         counters->any_sequential = 1;
-        DecCountSink sink;
-        PtxChainResolver res;
-        res.words = nullptr;
-        res.last_func = PTX_ABSENT;
-        PtxDecoder<DecCountSink, PtxChainResolver> d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
+        PtxSink sink;
+        PtxResolver res;
+        PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
         int st = ptx_decode_module_sequential(d, mtb[m], 0);
         PtxPair sz;
         sz.a = sink.nw;
@@ -413,16 +423,16 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         mod_seq_status[m] = (uint32_t)st;
     });
     // C4: sizes of sequential modules replace those of their units
-    bk.pf(n_units, [=] PTX_HD(size_t u) {
+    bk.pf("merge_sequential_sizes", n_units, [=] PTX_HD(size_t u) {
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         if (!mod_bad[m]) return;
         PtxPair z;
         z.a = z.b = 0;
         usize[u + 1] = (u == mub[m]) ? mod_seq[m] : z;
     });
-    bk.template scan<PtxPair>((size_t)n_units + 1, [=] PTX_HD(size_t i) { return usize[i]; },
+    bk.template scan<PtxPair>("scan_unit_sizes", (size_t)n_units + 1, [=] PTX_HD(size_t i) { return usize[i]; },
                               [=] PTX_HD(size_t i, PtxPair v) { usize[i] = v; }, PairAddOp(), PtxPair{0, 0});
-    bk.pf(1, [=] PTX_HD(size_t) {
+    bk.pf("set_output_totals", 1, [=] PTX_HD(size_t) {
         counters->n_words = n_units ? usize[n_units].a : 0;
         counters->n_errs = n_units ? usize[n_units].b : 0;
     });
@@ -436,8 +446,8 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     mask -= 1;
     uint32_t* slots = w.fn_slots = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)mask + 1));
     w.fn_mask = mask;
-    bk.pf((size_t)mask + 1, [=] PTX_HD(size_t i) { slots[i] = PTX_ABSENT; });
-    bk.pf(n_funcs, [=] PTX_HD(size_t i) {
+    bk.pf("fn_table_clear", (size_t)mask + 1, [=] PTX_HD(size_t i) { slots[i] = PTX_ABSENT; });
+    bk.pf("fn_table_insert", n_funcs, [=] PTX_HD(size_t i) {
         const PtxFnEntry e = fn_entries[i];
         uint32_t h = ptx_name_hash(text, e.name_off, e.name_len, e.module) & mask;
         for (;;) {
@@ -452,34 +462,33 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         }
     });
     // C6: decode again, writing
-    bk.pf(n_units, [=] PTX_HD(size_t u) {
+    bk.pf("decode_emit", n_units, [=] PTX_HD(size_t u) {
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
-        DecWriteSink sink;
+        PtxSink sink;
         sink.words = words + usize[u].a;
         sink.errs = errs + usize[u].b;
         uint64_t text_end = layout[m].text_off + layout[m].text_len;
         if (mod_skip[m]) return;
         if (mod_bad[m]) {
             if (u != mub[m]) return;
-            PtxChainResolver res;
+            PtxResolver res;
             res.words = words;
-            res.last_func = PTX_ABSENT;
-            PtxDecoder<DecWriteSink, PtxChainResolver> d(text, tokens, mtb[m + 1], text_end, sink, res);
+            PtxDecoder d(text, tokens, mtb[m + 1], text_end, sink, res);
             ptx_decode_module_sequential(d, mtb[m], usize[u].a);
             return;
         }
-        PtxHashResolver res;
+        PtxResolver res;
         res.entries = fn_entries;
         res.slots = slots;
         res.mask = mask;
         res.unit_off = usize;
         res.module = m;
         res.my_dir_ord = udir[u];
-        PtxDecoder<DecWriteSink, PtxHashResolver> d(text, tokens, mtb[m + 1], text_end, sink, res);
+        PtxDecoder d(text, tokens, mtb[m + 1], text_end, sink, res);
         uint32_t dp = udepth[u];
         ptx_decode_unit(d, ustart[u], dp & 0x7FFFFFFFu, (dp >> 31) != 0);
     });
-    bk.pf(n_modules, [=] PTX_HD(size_t m) {
+    bk.pf("module_results_final", n_modules, [=] PTX_HD(size_t m) {
         PtxModuleResult r = results[m];
         r.unit_begin = mub[m];
         r.unit_end = mub[m + 1];

@@ -556,6 +556,13 @@ def emit(spec, out_dirs):
     w("#define PTX_TABLE static const")
     w("#endif")
     w("#endif")
+    w("#ifndef PTX_NOINLINE")
+    w("#ifdef __CUDACC__")
+    w("#define PTX_NOINLINE __noinline__")
+    w("#else")
+    w("#define PTX_NOINLINE __attribute__((noinline))")
+    w("#endif")
+    w("#endif")
     w("#ifndef PTX_HOST_TABLE")
     w("#define PTX_HOST_TABLE static const")
     w("#endif")
@@ -840,7 +847,7 @@ def emit(spec, out_dirs):
     w("")
     w("// One case per pattern: append the variant's data words (schema order), then its operands.")
     w("template <class B>")
-    w("PTX_HD inline void ptx_build(int pattern, B& b, const int* mv, const int* av, const int* aneg, const int* auni) {")
+    w("PTX_HD PTX_NOINLINE inline void ptx_build(int pattern, B& b, const int* mv, const int* av, const int* aneg, const int* auni) {")
     w("    switch (pattern) {")
     for bd in bodies:
         w(bd)
