@@ -24,8 +24,15 @@ struct HostBackend {
     }
     void zero(void* p, size_t bytes) { memset(p, 0, bytes); }
     void download(void* host, const void* dev, size_t bytes) { memcpy(host, dev, bytes); }
+    // PTXFE_EMU_ORDER=reverse runs every parallel-for backwards: a step whose result depends on the order in which its
+    // indices run (a data race on the GPU) then shows up as a parity failure on the host.
+    bool reverse = getenv("PTXFE_EMU_ORDER") && !strcmp(getenv("PTXFE_EMU_ORDER"), "reverse");
     template <class F> void pf(const char*, size_t n, F f) {
-        for (size_t i = 0; i < n; i++) f(i);
+        if (reverse) {
+            for (size_t i = n; i-- > 0;) f(i);
+        } else {
+            for (size_t i = 0; i < n; i++) f(i);
+        }
     }
     template <class T, class Ld, class St, class Op> void scan(const char*, size_t n, Ld ld, St st, Op op, T identity) {
         T acc = identity;
@@ -95,6 +102,7 @@ char* emu_parse(const char* const* texts, const uint64_t* lens, uint32_t n, uint
         stats[2] = hc.n_words;
         stats[3] = hc.n_errs;
         stats[4] = seq;
+        stats[5] = hc.pad;
     }
     char* r = (char*)malloc(all.size() + 1);
     memcpy(r, all.data(), all.size());

@@ -56,6 +56,15 @@ def test_edge_cases(oracle, emu):
     assert stats["sequential"] < len(cases.all_cases()) // 2
 
 
+def test_edge_cases_in_reverse_thread_order(oracle, emu, monkeypatch):
+    """Every parallel-for of the pipeline run backwards: no step may depend on the order of its threads."""
+    monkeypatch.setenv("PTXFE_EMU_ORDER", "reverse")
+    stats = assert_parity(oracle, emu, cases.all_cases())
+    assert stats["pass_mismatch"] == 0
+    mods = corpus.config3(total_bytes=200 << 10, n_funcs=8, n_labels=100) + corpus.config1(n_modules=8, total_bytes=256 << 10, pool_lines=4000)
+    assert_parity(oracle, emu, mods, modes=(0,))
+
+
 def test_lexer_tokens_match_oracle(oracle, emu):
     rng = random.Random(7)
     pieces = ["add", ".f32", "%r1", ",", ";", " ", "\n", "\t", "// c\n", "/* x */", "/*", "*/", "\"s\"", "\"", "0f3F800000", "0x1F",

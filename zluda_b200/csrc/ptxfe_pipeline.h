@@ -353,6 +353,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     });
     bk.download(&host_counters, counters, sizeof(PtxCounters));
     const uint32_t max_funcs = host_counters.pad;
+    bk.pf("reset_mismatch", 1, [=] PTX_HD(size_t) { counters->pad = 0; });
     PtxFnEntry* fn_entries = w.fn_entries = (PtxFnEntry*)bk.alloc(sizeof(PtxFnEntry) * ((size_t)max_funcs + 1));
 
     // C1: decode every unit, counting only
@@ -378,7 +379,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         uend[u] = r.end;
         ustatus[u] = (uint8_t)r.status;
         PtxPair sz;
-        sz.a = sink.nw;
+        sz.a = sink.peak;
         sz.b = sink.ne;
         usize[u + 1] = sz;
         if (r.status == US_OK && r.kind == U_FUNC) {
@@ -417,7 +418,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
         int st = ptx_decode_module_sequential(d, mtb[m], 0);
         PtxPair sz;
-        sz.a = sink.nw;
+        sz.a = sink.peak;
         sz.b = sink.ne;
         mod_seq[m] = sz;
         mod_seq_status[m] = (uint32_t)st;
@@ -475,6 +476,8 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
             res.words = words;
             PtxDecoder d(text, tokens, mtb[m + 1], text_end, sink, res);
             ptx_decode_module_sequential(d, mtb[m], usize[u].a);
+            if (sink.peak != usize[u + 1].a - usize[u].a || sink.ne != usize[u + 1].b - usize[u].b) counters->pad = (uint32_t)u + 1;
+            sink.pad_to(usize[u + 1].a - usize[u].a);
             return;
         }
         PtxResolver res;
@@ -487,6 +490,9 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         PtxDecoder d(text, tokens, mtb[m + 1], text_end, sink, res);
         uint32_t dp = udepth[u];
         ptx_decode_unit(d, ustart[u], dp & 0x7FFFFFFFu, (dp >> 31) != 0);
+        // both passes must agree on the size of every record (a mismatch would overwrite a neighbour's record)
+        if (sink.peak != usize[u + 1].a - usize[u].a || sink.ne != usize[u + 1].b - usize[u].b) counters->pad = (uint32_t)u + 1;
+        sink.pad_to(usize[u + 1].a - usize[u].a);
     });
     bk.pf("module_results_final", n_modules, [=] PTX_HD(size_t m) {
         PtxModuleResult r = results[m];
@@ -500,5 +506,6 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         r.status = mod_seq_status[m];
         results[m] = r;
     });
+    bk.download(&host_counters, counters, sizeof(PtxCounters));   // .pad != 0: unit (index + 1) whose two passes disagreed
     (void)n_tokens;
 }
