@@ -34,6 +34,12 @@ struct HostBackend {
             for (size_t i = 0; i < n; i++) f(i);
         }
     }
+    void sort_by_key(const char*, size_t n, const uint16_t* key, uint32_t* order) {
+        std::vector<uint32_t> cursor(PTX_SORT_BUCKETS + 1, 0);
+        for (size_t i = 0; i < n; i++) cursor[key[i] + 1]++;
+        for (size_t b = 0; b < PTX_SORT_BUCKETS; b++) cursor[b + 1] += cursor[b];
+        for (size_t i = 0; i < n; i++) order[cursor[key[i]]++] = (uint32_t)i;
+    }
     template <class T, class Ld, class St, class Op> void scan(const char*, size_t n, Ld ld, St st, Op op, T identity) {
         T acc = identity;
         for (size_t i = 0; i < n; i++) {

@@ -90,6 +90,56 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_apply_kernel(size_t n, Ld l
         if (base + k < n) st(base + k, op(prefix, vals[k]));
 }
 
+// ---- counting sort of unit indices by a 12-bit key: block-local histograms / ranks in shared memory, one global
+// atomic per (block, non-empty bucket)
+constexpr int SORT_THREADS = 512;
+constexpr int SORT_ITEMS = 8;
+constexpr int SORT_TILE = SORT_THREADS * SORT_ITEMS;
+
+__global__ void __launch_bounds__(SORT_THREADS) sort_hist_kernel(size_t n, const uint16_t* key, uint32_t* hist) {
+    __shared__ uint32_t sh[PTX_SORT_BUCKETS];
+    for (int i = threadIdx.x; i < (int)PTX_SORT_BUCKETS; i += SORT_THREADS) sh[i] = 0;
+    __syncthreads();
+    size_t base = (size_t)blockIdx.x * SORT_TILE;
+    for (int k = 0; k < SORT_ITEMS; k++) {
+        size_t i = base + (size_t)k * SORT_THREADS + threadIdx.x;
+        if (i < n) atomicAdd(&sh[key[i]], 1u);
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < (int)PTX_SORT_BUCKETS; i += SORT_THREADS)
+        if (sh[i]) atomicAdd(&hist[i], sh[i]);
+}
+
+__global__ void __launch_bounds__(SORT_THREADS) sort_scatter_kernel(size_t n, const uint16_t* key, const uint32_t* bucket_begin,
+                                                                    uint32_t* cursor, uint32_t* order) {
+    __shared__ uint32_t sh[PTX_SORT_BUCKETS];
+    for (int i = threadIdx.x; i < (int)PTX_SORT_BUCKETS; i += SORT_THREADS) sh[i] = 0;
+    __syncthreads();
+    size_t base = (size_t)blockIdx.x * SORT_TILE;
+    uint32_t rank[SORT_ITEMS];
+    uint16_t kk[SORT_ITEMS];
+    for (int k = 0; k < SORT_ITEMS; k++) {
+        size_t i = base + (size_t)k * SORT_THREADS + threadIdx.x;
+        kk[k] = 0;
+        rank[k] = 0;
+        if (i < n) {
+            kk[k] = key[i];
+            rank[k] = atomicAdd(&sh[kk[k]], 1u);
+        }
+    }
+    __syncthreads();
+    // reserve this block's range in every non-empty bucket; sh[b] becomes the block's base inside the bucket
+    for (int i = threadIdx.x; i < (int)PTX_SORT_BUCKETS; i += SORT_THREADS) {
+        uint32_t c = sh[i];
+        sh[i] = c ? bucket_begin[i] + atomicAdd(&cursor[i], c) : 0;
+    }
+    __syncthreads();
+    for (int k = 0; k < SORT_ITEMS; k++) {
+        size_t i = base + (size_t)k * SORT_THREADS + threadIdx.x;
+        if (i < n) order[sh[kk[k]] + rank[k]] = (uint32_t)i;
+    }
+}
+
 template <class T> struct ArrayLoad {
     const T* p;
     __device__ T operator()(size_t i) const { return p[i]; }
@@ -97,6 +147,12 @@ template <class T> struct ArrayLoad {
 template <class T> struct ArrayStore {
     T* p;
     __device__ void operator()(size_t i, T v) const { p[i] = v; }
+};
+
+struct SubtractOwn {   // inclusive -> exclusive prefix
+    uint32_t* incl;
+    const uint32_t* own;
+    __device__ void operator()(size_t i) const { incl[i] -= own[i]; }
 };
 
 // ------------------------------------------------------------------------------------------------ context
@@ -220,6 +276,25 @@ struct CudaBackend {
         pf_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(n, f);
         prof_end();
         ctx->launches++;
+    }
+    void sort_by_key(const char* name, size_t n, const uint16_t* key, uint32_t* order) {
+        if (ctx->failed || n == 0) return;
+        uint32_t* hist = (uint32_t*)alloc(sizeof(uint32_t) * PTX_SORT_BUCKETS * 3);
+        if (!hist) return;
+        uint32_t* begin = hist + PTX_SORT_BUCKETS;
+        uint32_t* cursor = begin + PTX_SORT_BUCKETS;
+        prof_begin(name);
+        cudaMemsetAsync(hist, 0, sizeof(uint32_t) * PTX_SORT_BUCKETS * 3, ctx->stream);
+        size_t blocks = (n + SORT_TILE - 1) / SORT_TILE;
+        sort_hist_kernel<<<(unsigned)blocks, SORT_THREADS, 0, ctx->stream>>>(n, key, hist);
+        // exclusive scan of the 4096 counts: begin[b] = sum of hist[0..b)
+        ArrayLoad<uint32_t> ld{hist};
+        ArrayStore<uint32_t> st{begin};
+        scan_impl<uint32_t>((size_t)PTX_SORT_BUCKETS, ld, st, AddOp(), 0u);   // inclusive into begin[]
+        pf_kernel<<<(PTX_SORT_BUCKETS + 255) / 256, 256, 0, ctx->stream>>>((size_t)PTX_SORT_BUCKETS, SubtractOwn{begin, hist});
+        sort_scatter_kernel<<<(unsigned)blocks, SORT_THREADS, 0, ctx->stream>>>(n, key, begin, cursor, order);
+        prof_end();
+        ctx->launches += 3;
     }
     template <class T, class Ld, class St, class Op> void scan(const char* name, size_t n, Ld ld, St st, Op op, T identity) {
         if (ctx->failed || n == 0) return;

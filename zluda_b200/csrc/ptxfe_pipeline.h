@@ -46,6 +46,8 @@ struct PtxSeg3 {
     int32_t scope, paren, flag;
 };
 
+#define PTX_SORT_BUCKETS 4096u
+
 // token classification bits
 enum { TF_MODULE_FIRST = 1, TF_SCOPE_OPEN = 2, TF_SCOPE_CLOSE = 4, TF_UNIT_START = 8 };
 
@@ -122,6 +124,8 @@ struct SegDepthOp {
 //   template <class F> void pf(const char* name, size_t n, F f);                f(i) for i in [0, n)
 //   template <class T, class Op, class Ld, class St> void scan(const char* name, size_t n, Ld ld, St st, Op op, T identity);
 //        inclusive scan: st(i, op(ld(0), ..., ld(i)))
+//   void sort_by_key(const char* name, size_t n, const uint16_t* key, uint32_t* order);
+//        order = the indices 0..n-1 grouped by key (keys < PTX_SORT_BUCKETS; order inside a group is free)
 //   void* alloc(size_t bytes); void zero(void* p, size_t bytes);
 //   void download(void* host, const void* dev, size_t bytes);   (synchronises the stream)
 // The pipeline allocates through the backend and never frees: the backend's arena is reset per batch.
@@ -356,8 +360,26 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     bk.pf("reset_mismatch", 1, [=] PTX_HD(size_t) { counters->pad = 0; });
     PtxFnEntry* fn_entries = w.fn_entries = (PtxFnEntry*)bk.alloc(sizeof(PtxFnEntry) * ((size_t)max_funcs + 1));
 
+    // Units are decoded in the order of a "shape key" (a hash of their token kinds): the decoder's control flow depends
+    // on token kinds only, so the threads of a warp then follow the same path.  Results are still written at
+    // offsets computed in unit order, so the order of processing does not show in the output.
+    uint16_t* ukey = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_units + 2));
+    uint32_t* order = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    bk.pf("unit_shape_key", n_units, [=] PTX_HD(size_t u) {
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        uint32_t start = ustart[u];
+        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        if (end > start + 20) end = start + 20;
+        uint32_t h = 2166136261u ^ (udepth[u] >> 31) ^ ((udepth[u] & 0x7FFFFFFFu) ? 2u : 0u);
+        for (uint32_t i = start; i < end; i++) h = (h ^ tokens[i].kind) * 16777619u;
+        h ^= h >> 15;
+        ukey[u] = (uint16_t)(h & (PTX_SORT_BUCKETS - 1));
+    });
+    bk.sort_by_key("sort_units_by_shape", n_units, ukey, order);
+
     // C1: decode every unit, counting only
-    bk.pf("decode_count", n_units, [=] PTX_HD(size_t u) {
+    bk.pf("decode_count", n_units, [=] PTX_HD(size_t idx) {
+        size_t u = order[idx];
         uint32_t start = ustart[u];
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         // modules without units share their begin with the next one: take the last module that starts at or before u
@@ -463,7 +485,8 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         }
     });
     // C6: decode again, writing
-    bk.pf("decode_emit", n_units, [=] PTX_HD(size_t u) {
+    bk.pf("decode_emit", n_units, [=] PTX_HD(size_t idx) {
+        size_t u = order[idx];
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         PtxSink sink;
         sink.words = words + usize[u].a;
