@@ -140,6 +140,23 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_scatter_kernel(size_t n, co
     }
 }
 
+// token sink of the allocation-free lexer: writes into a caller-provided table, dropping what does not fit
+struct LexCapSink {
+    PtxToken* tokens;
+    uint64_t next, capacity;
+    __device__ void token(uint64_t start, uint32_t len, uint16_t kind) {
+        if (next < capacity) {
+            PtxToken t;
+            t.start = (uint32_t)start;
+            t.len = len >= 0xFFFFu ? (uint16_t)0xFFFF : (uint16_t)len;
+            t.kind = kind;
+            tokens[next] = t;
+        }
+        next++;
+    }
+    __device__ void error(uint64_t, uint32_t) {}
+};
+
 template <class T> struct ArrayLoad {
     const T* p;
     __device__ T operator()(size_t i) const { return p[i]; }
@@ -673,4 +690,105 @@ int ptxfe_lex_module(ptxfe_ctx* ctx, const char* text, uint64_t len, uint32_t** 
     *n_errors = ne;
     return PTXFE_OK;
 }
+}   // extern "C"
+
+// ------------------------------------------------------------------------------------------------ allocation-free lexer
+// Working memory of ptxfe_lex_device_noalloc: it lives in the library image, one copy per GPU that loads the library,
+// for the life of the process.  Layout (bytes): [0, 512K+4) chunk transition vectors, then the per-chunk
+// token/error counts, then two levels of scan tile totals.
+#define PTXFE_NOALLOC_MAX_TEXT (16u << 20)
+#define PTXFE_NOALLOC_MAX_CHUNKS (PTXFE_NOALLOC_MAX_TEXT / PTX_CHUNK)
+#define PTXFE_NOALLOC_SCRATCH_BYTES (2u << 20)
+static __device__ __align__(256) unsigned char ptxfe_noalloc_scratch[PTXFE_NOALLOC_SCRATCH_BYTES];
+
+// inclusive scan of at most SCAN_TILE * SCAN_TILE elements with caller-provided room for the tile totals
+template <class T, class Ld, class St, class Op>
+static void scan_in_scratch(cudaStream_t stream, size_t n, Ld ld, St st, Op op, T identity, T* partial) {
+    if (n == 0) return;
+    size_t tiles = (n + SCAN_TILE - 1) / SCAN_TILE;
+    scan_reduce_kernel<T><<<(unsigned)tiles, SCAN_THREADS, 0, stream>>>(n, ld, op, identity, partial);
+    if (tiles > 1) {
+        T* partial2 = partial + tiles;   // one tile is enough for the second level
+        scan_reduce_kernel<T><<<1, SCAN_THREADS, 0, stream>>>(tiles, ArrayLoad<T>{partial}, op, identity, partial2);
+        scan_apply_kernel<T><<<1, SCAN_THREADS, 0, stream>>>(tiles, ArrayLoad<T>{partial}, ArrayStore<T>{partial}, op, identity, partial2);
+    }
+    scan_apply_kernel<T><<<(unsigned)tiles, SCAN_THREADS, 0, stream>>>(n, ld, st, op, identity, partial);
+}
+
+extern "C" int ptxfe_lex_device_noalloc(int device, const void* d_text_v, uint64_t len, void* d_tokens_v, uint64_t token_capacity,
+                             uint32_t* d_counts, void* stream_v) {
+    // Device addresses of the scratch array, looked up once per device.  The array's name is only a host-side handle:
+    // kernels must be given the address that cudaGetSymbolAddress returns while that device is current.
+    static unsigned char* scratch_addr[64] = {nullptr};
+    if (!d_text_v || !d_tokens_v || !d_counts || device < 0 || device >= 64) return PTXFE_ERR_BAD_ARG;
+    if (len > PTXFE_NOALLOC_MAX_TEXT) {
+        fprintf(stderr, "ptxfe_lex_device_noalloc: %llu bytes of text exceed the fixed working memory (limit %u bytes)\n",
+                (unsigned long long)len, PTXFE_NOALLOC_MAX_TEXT);
+        return PTXFE_ERR_TOO_LARGE;
+    }
+    if (cudaSetDevice(device) != cudaSuccess) return PTXFE_ERR_CUDA;
+    if (!scratch_addr[device]) {
+        void* p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, ptxfe_noalloc_scratch);
+        if (e != cudaSuccess || !p) {
+            fprintf(stderr, "ptxfe_lex_device_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
+            return PTXFE_ERR_CUDA;
+        }
+        scratch_addr[device] = (unsigned char*)p;
+    }
+    cudaStream_t stream = (cudaStream_t)stream_v;
+    const uint8_t* text = (const uint8_t*)d_text_v;
+    PtxToken* tokens = (PtxToken*)d_tokens_v;
+    const uint32_t n_chunks = (uint32_t)((len + PTX_CHUNK - 1) / PTX_CHUNK);
+    unsigned char* base = scratch_addr[device];
+    uint32_t* vec = (uint32_t*)base;                                                    // n_chunks + 1
+    PtxPair* cnt = (PtxPair*)(base + sizeof(uint32_t) * (PTXFE_NOALLOC_MAX_CHUNKS + 64));   // n_chunks + 2
+    unsigned char* tail = (unsigned char*)(cnt + PTXFE_NOALLOC_MAX_CHUNKS + 64);
+    uint32_t* partial_u32 = (uint32_t*)tail;                                            // <= 64 + 1 tile totals
+    PtxPair* partial_pair = (PtxPair*)(tail + 4096);
+    if (n_chunks == 0) {
+        if (cudaMemsetAsync(d_counts, 0, 2 * sizeof(uint32_t), stream) != cudaSuccess) return PTXFE_ERR_CUDA;
+        return PTXFE_OK;
+    }
+    const uint64_t me = len;
+    // every scratch word that is read below is written first by this call, so what an earlier call left behind
+    // does not matter
+    pf_kernel<<<(n_chunks + 255) / 256, 256, 0, stream>>>((size_t)n_chunks, [=] __device__(size_t c) {
+        uint64_t cs = (uint64_t)c * PTX_CHUNK;
+        uint64_t ce = cs + PTX_CHUNK < me ? cs + PTX_CHUNK : me;
+        uint32_t v = cx_chunk_vector(text, cs, ce);
+        vec[c] = c == 0 ? cx_restart(v) : v;
+    });
+    scan_in_scratch<uint32_t>(stream, n_chunks, ArrayLoad<uint32_t>{vec}, ArrayStore<uint32_t>{vec}, ComposeOp(), CX_IDENTITY, partial_u32);
+    pf_kernel<<<(n_chunks + 255) / 256, 256, 0, stream>>>((size_t)n_chunks, [=] __device__(size_t c) {
+        uint64_t cs = (uint64_t)c * PTX_CHUNK;
+        int state = c == 0 ? CX_CODE : (int)(vec[c - 1] & 7u);
+        LexCountSink sink;
+        lx_chunk(text, 0, me, cs, cs + PTX_CHUNK, state, sink);
+        PtxPair p;
+        p.a = sink.n_tokens;
+        p.b = sink.n_errors;
+        cnt[c + 1] = p;
+        if (c == 0) { PtxPair z; z.a = z.b = 0; cnt[0] = z; }
+    });
+    scan_in_scratch<PtxPair>(stream, (size_t)n_chunks + 1, ArrayLoad<PtxPair>{cnt}, ArrayStore<PtxPair>{cnt}, PairAddOp(), PtxPair{0, 0}, partial_pair);
+    pf_kernel<<<(n_chunks + 255) / 256, 256, 0, stream>>>((size_t)n_chunks, [=] __device__(size_t c) {
+        uint64_t cs = (uint64_t)c * PTX_CHUNK;
+        int state = c == 0 ? CX_CODE : (int)(vec[c - 1] & 7u);
+        LexCapSink sink;
+        sink.tokens = tokens;
+        sink.next = cnt[c].a;
+        sink.capacity = token_capacity;
+        lx_chunk(text, 0, me, cs, cs + PTX_CHUNK, state, sink);
+        if (c == 0) {
+            d_counts[0] = cnt[n_chunks].a;
+            d_counts[1] = cnt[n_chunks].b;
+        }
+    });
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        fprintf(stderr, "ptxfe_lex_device_noalloc: launch failed: %s\n", cudaGetErrorString(e));
+        return PTXFE_ERR_CUDA;
+    }
+    return PTXFE_OK;
 }
