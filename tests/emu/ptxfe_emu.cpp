@@ -34,6 +34,11 @@ struct HostBackend {
             for (size_t i = 0; i < n; i++) f(i);
         }
     }
+    // per-chunk lexer steps: the reader is plain memory (n chunks of text are readable)
+    template <class F> void pf_text(const char* name, size_t n, const uint8_t* text, F f) {
+        PtxGlobalReader rd{text, (uint32_t)(n * PTX_CHUNK)};
+        pf(name, n, [&](size_t c) { f(c, rd); });
+    }
     void sort_by_key(const char*, size_t n, const uint16_t* key, uint32_t* order) {
         std::vector<uint32_t> cursor(PTX_SORT_BUCKETS + 1, 0);
         for (size_t i = 0; i < n; i++) cursor[key[i] + 1]++;

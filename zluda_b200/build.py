@@ -36,6 +36,7 @@ def generate():
     g = os.path.join(PKG, "grammar")
     _run([sys.executable, os.path.join(g, "gen_tables.py"), "--out", os.path.join(CSRC, "gen"), "--out", os.path.join(ROOT, "oracle", "gen")])
     _run([sys.executable, os.path.join(g, "gen_pow5.py"), "--out", os.path.join(CSRC, "gen")])
+    _run([sys.executable, os.path.join(g, "gen_lex_tables.py"), "--out", os.path.join(CSRC, "gen")])
 
 
 def build_library(force=False):

@@ -13,6 +13,7 @@
 //      re-lexing that run; it then owns every token that starts inside its chunk (a token may run past the end).
 #pragma once
 #include "gen/ptx_tables.h"
+#include "gen/ptx_lex_tables.h"
 
 #ifndef PTX_NOINLINE
 #ifdef __CUDACC__
@@ -70,14 +71,19 @@ PTX_HD inline uint32_t cx_compose(uint32_t f, uint32_t g) {
 // a vector that ignores its input and always yields the state reached from CX_CODE (first chunk of a module)
 PTX_HD inline uint32_t cx_restart(uint32_t f) { return (f & 7u) * 0x111111u; }
 
-// transition vector of text[begin, end)
-PTX_HD inline uint32_t cx_chunk_vector(const uint8_t* text, uint64_t begin, uint64_t end) {
-    // only '/', '*', '"', newline and the byte after '/' or '*' can change the vector; track the six states directly
-    int s0 = 0, s1 = 1, s2 = 2, s3 = 3, s4 = 4, s5 = 5;
-    for (uint64_t p = begin; p < end; p++) {
-        unsigned c = text[p];
-        s0 = cx_step(s0, c); s1 = cx_step(s1, c); s2 = cx_step(s2, c);
-        s3 = cx_step(s3, c); s4 = cx_step(s4, c); s5 = cx_step(s5, c);
+// transition vector of text[begin, end); begin is a multiple of 4.  `rd` is a text reader (see PtxGlobalReader).
+template <class R>
+PTX_HD inline uint32_t cx_chunk_vector(const R& rd, uint32_t begin, uint32_t end) {
+    // track the six states directly; every thread runs the same instructions whatever the bytes are
+    uint32_t s0 = 0, s1 = 1, s2 = 2, s3 = 3, s4 = 4, s5 = 5;
+    for (uint32_t p = begin; p < end; p += 4) {
+        uint32_t wd = rd.word(p);
+        uint32_t nb = end - p < 4u ? end - p : 4u;
+        for (uint32_t k = 0; k < nb; k++) {
+            uint32_t v = cx_byte_vector((wd >> (8 * k)) & 0xFFu);
+            s0 = (v >> (4 * s0)) & 7u; s1 = (v >> (4 * s1)) & 7u; s2 = (v >> (4 * s2)) & 7u;
+            s3 = (v >> (4 * s3)) & 7u; s4 = (v >> (4 * s4)) & 7u; s5 = (v >> (4 * s5)) & 7u;
+        }
     }
     return s0 | (s1 << 4) | (s2 << 8) | (s3 << 12) | (s4 << 16) | (s5 << 20);
 }
@@ -260,74 +266,142 @@ struct LexWriteSink {
     }
 };
 
-// Lex the tokens that START in [cs, ce) of a module occupying [ms, me).  `state` is the context at cs.
-template <class Sink>
-PTX_HD inline void lx_chunk(const uint8_t* s, uint64_t ms, uint64_t me, uint64_t cs, uint64_t ce, int state, Sink& out) {
+// Text readers: the lockstep lexer gets bytes and table entries through one of these.  This one reads global memory;
+// the CUDA backend has another that serves a shared-memory tile of the text and a fused copy of the tables.
+struct PtxGlobalReader {
+    const uint8_t* s;
+    uint32_t n;      // readable bytes
+    PTX_HD unsigned operator[](uint32_t p) const { return s[p]; }
+    PTX_HD uint32_t word(uint32_t p) const {
+        if (p + 4 <= n) return (uint32_t)s[p] | ((uint32_t)s[p + 1] << 8) | ((uint32_t)s[p + 2] << 16) | ((uint32_t)s[p + 3] << 24);
+        uint32_t w = 0;
+        for (uint32_t k = 0; p + k < n; k++) w |= (uint32_t)s[p + k] << (8 * k);
+        return w;
+    }
+    // transition-table entry (next state | action << 8) and the kind of a single-character token
+    PTX_HD unsigned lookup(int st, unsigned c) const { return ptx_lex_trans[st * LX_STRIDE + ptx_lex_class[c]]; }
+    PTX_HD uint16_t single(unsigned c, unsigned) const { return ptx_lex_single[c]; }
+};
+
+PTX_HD inline bool lx_state_open(int st) {
+    // a token (or a '/' whose meaning depends on the next byte) is in progress
+    return st != LS_S0 && st != LS_LINE && st != LS_BLOCK && st != LS_STAR && st != LS_SLASH_IN;
+}
+
+// Lex the tokens that START in [cs, ce) of a module occupying [ms, me).  `cx` is the comment/string context at cs.
+// One byte per loop iteration, driven by ptx_lex_trans: all threads of a warp run the same loop body.
+// `g` is the text in global memory (used by the rare helpers), `tx` the reader for the byte loop.
+// Offsets are 32-bit: a batch holds less than 4 GiB of text.
+template <class TX, class Sink>
+PTX_HD inline void lx_chunk(const TX& tx, const uint8_t* g, uint32_t ms, uint32_t me, uint32_t cs, uint32_t ce, int cx, Sink& out) {
     if (ce > me) ce = me;
-    uint64_t p = cs;
-    if (state == CX_CODE && cs > ms && lx_soft(s[cs - 1]) && cs < me && lx_soft(s[cs])) {
-        // cs may be inside a token: re-lex the run of soft bytes that reaches into this chunk
-        uint64_t q = cs - 1;
-        while (q > ms && lx_soft(s[q - 1])) q--;
-        while (q < cs) {
-            uint32_t l;
-            lx_one(s, q, me, &l);
-            q += l;
+    if (cs >= me) return;
+    uint32_t p = cs, tstart = cs ? cs - 1 : 0, acc_pos = 0;
+    uint32_t acc_kind = T_ERROR, cnt = 0, need = 0;
+    int st;
+    switch (cx) {
+    case CX_SLASH: st = LS_SLASH_IN; break;
+    case CX_LINE: st = LS_LINE; break;
+    case CX_BLOCK: st = LS_BLOCK; break;
+    case CX_STAR: st = LS_STAR; break;
+    case CX_STR: st = LS_STR; break;
+    default:
+        st = LS_S0;
+        if (cs > ms && lx_soft(tx[cs - 1]) && lx_soft(tx[cs])) {
+            // cs may be inside a token: start at the beginning of the run of soft bytes that reaches into this chunk
+            uint32_t q = cs - 1;
+            while (q > ms && lx_soft(tx[q - 1])) q--;
+            p = q;
         }
-        p = q;
+        break;
     }
-    while (p < ce) {
-        unsigned c = s[p];
-        switch (state) {
-        case CX_CODE:
-            if (lx_ws(c)) { p++; break; }
-            if (c == '/') {
-                unsigned d = p + 1 < me ? s[p + 1] : 0;
-                if (d == '/') { state = CX_LINE; p += 2; }
-                else if (d == '*') { state = CX_BLOCK; p += 2; }
-                else { out.error(p, 1); p++; }
-                break;
-            }
-            if (c == '"') {
-                uint64_t q = p + 1;
-                while (q < me && s[q] != '"') q++;
-                if (q >= me) { out.error(p, (uint32_t)(me - p)); p = me; }
-                else { out.token(p, (uint32_t)(q + 1 - p), T_STRING); p = q + 1; }
-                break;
-            }
-            {
-                uint32_t l;
-                uint16_t k = lx_one(s, p, me, &l);
-                if (k == T_ERROR) out.error(p, l);
-                else out.token(p, l, k);
-                p += l;
-            }
+    while (p <= me && (p < ce || (lx_state_open(st) && tstart >= cs))) {
+        unsigned c = p < me ? tx[p] : ' ';
+        unsigned e = tx.lookup(st, c);
+        int prev = st;
+        st = (int)(e & 0xFF);
+        switch (e >> 8) {
+        case LA_NONE: p++; break;
+        case LA_BEGIN: tstart = p; p++; break;
+        case LA_SINGLE:
+            if (p >= cs) out.token(p, 1, tx.single(c, e));
+            st = LS_S0;
+            p++;
             break;
-        case CX_SLASH:   // the '/' is the last byte of the previous chunk; its owner already classified it
-            if (c == '/') { state = CX_LINE; p++; }
-            else if (c == '*') { state = CX_BLOCK; p++; }
-            else state = CX_CODE;
+        case LA_END:
+            if (tstart >= cs) out.token(tstart, (p - tstart), ptx_lex_end_kind[prev]);
             break;
-        case CX_LINE:
-            while (p < ce && s[p] != '\n' && s[p] != '\r') p++;
-            if (p < ce) state = CX_CODE;
+        case LA_END_INCL:
+            if (tstart >= cs) out.token(tstart, (p + 1 - tstart), ptx_lex_end_kind[prev]);
+            p++;
             break;
-        case CX_BLOCK:
-        case CX_STAR:
-            while (p < ce) {
-                unsigned b = s[p++];
-                if (state == CX_STAR && b == '/') { state = CX_CODE; break; }
-                state = b == '*' ? CX_STAR : CX_BLOCK;
+        case LA_ACCEPT: acc_pos = p; acc_kind = ptx_lex_end_kind[prev]; p++; break;
+        case LA_BACKUP:
+            if (prev != LS_SLASH_IN) {
+                if (tstart >= cs) out.token(tstart, (acc_pos - tstart), (uint16_t)acc_kind);
+                p = acc_pos;
             }
             break;
-        default:   // CX_STR: the string's owner emitted the token; skip to the closing quote
-            while (p < ce && s[p] != '"') p++;
-            if (p < ce) { p++; state = CX_CODE; }
+        case LA_ERR_HERE:
+            if (p >= cs) out.error(p, 1);
+            p++;
+            break;
+        case LA_ERR_TOKEN:
+        case LA_ERR_SLASH:
+            if (tstart >= cs) out.error(tstart, 1);
+            break;
+        case LA_COUNT:
+            if (++cnt == need) {
+                if (tstart >= cs) out.token(tstart, (p + 1 - tstart), need == 8 ? T_F32HEX : T_F64HEX);
+                st = LS_S0;
+            }
+            p++;
+            break;
+        case LA_BEGIN_HF32: acc_pos = p; acc_kind = T_DECIMAL; cnt = 0; need = 8; p++; break;
+        case LA_BEGIN_HF64: acc_pos = p; acc_kind = T_DECIMAL; cnt = 0; need = 16; p++; break;
+        case LA_COLON_CHECK: {
+            uint16_t k = T_DOTIDENT;
+            uint32_t l = 0;
+            if (p + 1 < me && tx[p + 1] == ':') l = lx_colon_literal(g, tstart, p, me, &k);
+            if (l) {
+                if (tstart >= cs) out.token(tstart, l, k);
+                p = tstart + l;
+            } else if (tstart >= cs) {
+                out.token(tstart, (p - tstart), T_DOTIDENT);
+            }
+            break;
+        }
+        case LA_REWIND_DOT:
+            if (tstart >= cs) out.token(tstart, 1, T_DOT);
+            p = tstart + 1;
+            break;
+        default:   // LA_DIM: ".1d" ".2d" ".3d" are literals; an upper-case D ends the F64 in front of it
+            if (c == 'd') {
+                unsigned digit = tx[tstart + 1];
+                if (tstart >= cs) out.token(tstart, 3, digit == '1' ? T_MOD_1d : digit == '2' ? T_MOD_2d : T_MOD_3d);
+                p++;
+            } else if (tstart >= cs) {
+                out.token(tstart, (p - tstart), T_F64);
+            }
             break;
         }
     }
-    // an unterminated block comment is reported at the end of the module by the owner of its last byte
-    if (ce == me && p >= me && cs < me && (state == CX_BLOCK || state == CX_STAR)) out.error(me, 0);
+    if (p > me || (p == me && ce == me)) {
+        // this thread saw the end of the module
+        if (st == LS_STR && tstart >= cs) out.error(tstart, (me - tstart));
+        if ((st == LS_BLOCK || st == LS_STAR) && ce == me) out.error(me, 0);
+    }
+}
+
+// identifiers and dot-identifiers that spell a keyword (opcode, modifier, directive word): one thread per token
+PTX_HD inline uint16_t lx_classify(const uint8_t* g, uint32_t start, uint32_t len, uint16_t kind) {
+    if (kind == T_IDENT) {
+        if (!lx_alpha(g[start])) return kind;
+    } else if (kind != T_DOTIDENT) {
+        return kind;
+    }
+    uint16_t k = lx_keyword(g + start, len);
+    return k == T_ERROR ? kind : k;
 }
 
 PTX_HD inline uint32_t ptx_token_len(const uint8_t* s, const PtxToken& t, uint64_t me) {

@@ -10,6 +10,7 @@
 #include <string.h>
 
 #include <string>
+#include <type_traits>
 #include <vector>
 
 #define PTX_HD __device__
@@ -34,6 +35,59 @@ template <class F>
 __global__ void __launch_bounds__(256) pf_kernel(size_t n, F f) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) f(i);
+}
+
+// ---- per-chunk lexer steps over a shared-memory tile of the text
+// One block = 256 chunks = 32 KiB of text, staged with coalesced 16-byte loads.  Thread t then walks chunk t byte by
+// byte; rows are padded to 33 words so that 32 threads reading the same column of 32 rows hit 32 different banks.
+// The token automaton's two tables (byte class, transition) are fused into one [state][byte] table in shared memory,
+// with the token kind of single-character tokens stored in the entry's state byte.
+#define LEX_TILE_CHUNKS 256u
+#define LEX_ROW_WORDS 33u
+struct PtxTileReader {
+    const uint32_t* tile;      // [LEX_TILE_CHUNKS][LEX_ROW_WORDS]
+    const uint16_t* fused;     // [LS_COUNT][256]
+    const uint8_t* g;          // the whole text, for bytes outside the tile
+    uint32_t base;             // text offset of the tile
+    __device__ unsigned operator[](uint32_t p) const {
+        uint32_t o = p - base;
+        if (o < LEX_TILE_CHUNKS * PTX_CHUNK) return ((const uint8_t*)tile)[(o >> 7) * (LEX_ROW_WORDS * 4) + (o & 127u)];
+        return g[p];
+    }
+    __device__ uint32_t word(uint32_t p) const {   // p is a multiple of 4 inside the tile
+        uint32_t o = p - base;
+        return tile[(o >> 7) * LEX_ROW_WORDS + ((o & 127u) >> 2)];
+    }
+    __device__ unsigned lookup(int st, unsigned c) const { return fused[st * 256 + c]; }
+    __device__ uint16_t single(unsigned, unsigned e) const { return (uint16_t)(e & 0xFFu); }
+};
+
+template <bool TABLES, class F>
+__global__ void __launch_bounds__(256) lex_tile_kernel(uint32_t n_chunks, const uint8_t* text, F f) {
+    __shared__ uint32_t tile[LEX_TILE_CHUNKS * LEX_ROW_WORDS];
+    __shared__ uint16_t fused[TABLES ? LS_COUNT * 256 : 1];
+    const uint32_t c0 = blockIdx.x * LEX_TILE_CHUNKS;
+    const uint4* src = (const uint4*)text + (size_t)c0 * (PTX_CHUNK / 16);
+#pragma unroll
+    for (uint32_t k = 0; k < 8; k++) {
+        uint32_t idx = threadIdx.x + k * 256;      // 16-byte piece of the tile
+        uint32_t row = idx >> 3;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (c0 + row < n_chunks) v = src[idx];
+        uint32_t* d = tile + row * LEX_ROW_WORDS + (idx & 7u) * 4;
+        d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
+    }
+    if (TABLES) {
+        for (uint32_t i = threadIdx.x; i < LS_COUNT * 256; i += 256) {
+            uint32_t st = i >> 8, c = i & 255u;
+            unsigned e = ptx_lex_trans[st * LX_STRIDE + ptx_lex_class[c]];
+            if ((e >> 8) == LA_SINGLE) e = (LA_SINGLE << 8) | ptx_lex_single[c];
+            fused[i] = (uint16_t)e;
+        }
+    }
+    __syncthreads();
+    uint32_t c = c0 + threadIdx.x;
+    if (c < n_chunks) f((size_t)c, PtxTileReader{tile, fused, text, c0 * PTX_CHUNK});
 }
 
 constexpr int SCAN_THREADS = 256;
@@ -143,13 +197,14 @@ __global__ void __launch_bounds__(SORT_THREADS) sort_scatter_kernel(size_t n, co
 // token sink of the allocation-free lexer: writes into a caller-provided table, dropping what does not fit
 struct LexCapSink {
     PtxToken* tokens;
+    const uint8_t* text;
     uint64_t next, capacity;
     __device__ void token(uint64_t start, uint32_t len, uint16_t kind) {
         if (next < capacity) {
             PtxToken t;
             t.start = (uint32_t)start;
             t.len = len >= 0xFFFFu ? (uint16_t)0xFFFF : (uint16_t)len;
-            t.kind = kind;
+            t.kind = lx_classify(text, t.start, len, kind);
             tokens[next] = t;
         }
         next++;
@@ -291,6 +346,18 @@ struct CudaBackend {
         size_t blocks = (n + 255) / 256;
         prof_begin(name);
         pf_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(n, f);
+        prof_end();
+        ctx->launches++;
+    }
+    // per-chunk lexer steps; text holds n whole chunks and is 16-byte aligned (it is an arena block)
+    template <class F> void pf_text(const char* name, size_t n, const uint8_t* text, F f) {
+        if (ctx->failed || n == 0) return;
+        unsigned blocks = (unsigned)((n + LEX_TILE_CHUNKS - 1) / LEX_TILE_CHUNKS);
+        prof_begin(name);
+        if constexpr (std::is_same<F, PtxLexVectorsStep>::value)
+            lex_tile_kernel<false><<<blocks, 256, 0, ctx->stream>>>((uint32_t)n, text, f);
+        else
+            lex_tile_kernel<true><<<blocks, 256, 0, ctx->stream>>>((uint32_t)n, text, f);
         prof_end();
         ctx->launches++;
     }
@@ -756,7 +823,7 @@ extern "C" int ptxfe_lex_device_noalloc(int device, const void* d_text_v, uint64
     pf_kernel<<<(n_chunks + 255) / 256, 256, 0, stream>>>((size_t)n_chunks, [=] __device__(size_t c) {
         uint64_t cs = (uint64_t)c * PTX_CHUNK;
         uint64_t ce = cs + PTX_CHUNK < me ? cs + PTX_CHUNK : me;
-        uint32_t v = cx_chunk_vector(text, cs, ce);
+        uint32_t v = cx_chunk_vector(PtxGlobalReader{text, (uint32_t)me}, (uint32_t)cs, (uint32_t)ce);
         vec[c] = c == 0 ? cx_restart(v) : v;
     });
     scan_in_scratch<uint32_t>(stream, n_chunks, ArrayLoad<uint32_t>{vec}, ArrayStore<uint32_t>{vec}, ComposeOp(), CX_IDENTITY, partial_u32);
@@ -764,7 +831,7 @@ extern "C" int ptxfe_lex_device_noalloc(int device, const void* d_text_v, uint64
         uint64_t cs = (uint64_t)c * PTX_CHUNK;
         int state = c == 0 ? CX_CODE : (int)(vec[c - 1] & 7u);
         LexCountSink sink;
-        lx_chunk(text, 0, me, cs, cs + PTX_CHUNK, state, sink);
+        lx_chunk(PtxGlobalReader{text, (uint32_t)me}, text, 0u, (uint32_t)me, (uint32_t)cs, (uint32_t)cs + PTX_CHUNK, state, sink);
         PtxPair p;
         p.a = sink.n_tokens;
         p.b = sink.n_errors;
@@ -777,9 +844,10 @@ extern "C" int ptxfe_lex_device_noalloc(int device, const void* d_text_v, uint64
         int state = c == 0 ? CX_CODE : (int)(vec[c - 1] & 7u);
         LexCapSink sink;
         sink.tokens = tokens;
+        sink.text = text;
         sink.next = cnt[c].a;
         sink.capacity = token_capacity;
-        lx_chunk(text, 0, me, cs, cs + PTX_CHUNK, state, sink);
+        lx_chunk(PtxGlobalReader{text, (uint32_t)me}, text, 0u, (uint32_t)me, (uint32_t)cs, (uint32_t)cs + PTX_CHUNK, state, sink);
         if (c == 0) {
             d_counts[0] = cnt[n_chunks].a;
             d_counts[1] = cnt[n_chunks].b;

@@ -131,6 +131,69 @@ struct SegDepthOp {
 // The pipeline allocates through the backend and never frees: the backend's arena is reset per batch.
 
 // ------------------------------------------------------------------------------------------------ stage A: lexer
+// The three per-chunk steps are functors (not lambdas) because the backend hands them a text reader of its own type:
+// plain global memory on the host, a shared-memory tile on the GPU.  Chunk c covers text[c * PTX_CHUNK, ...).
+struct PtxLexChunkInfo {
+    const PtxModuleLayout* layout;
+    const uint32_t* mcb;
+    uint32_t n_modules;
+    PTX_HD void locate(size_t c, uint32_t& ms, uint32_t& me, bool& first) const {
+        uint32_t m = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)c) - 1;
+        ms = (uint32_t)layout[m].text_off;
+        me = ms + (uint32_t)layout[m].text_len;
+        first = c == mcb[m];
+    }
+};
+struct PtxLexVectorsStep {
+    PtxLexChunkInfo info;
+    uint32_t* vec;
+    template <class R> PTX_HD void operator()(size_t c, const R& rd) const {
+        uint32_t ms, me, cs = (uint32_t)c * PTX_CHUNK;
+        bool first;
+        info.locate(c, ms, me, first);
+        uint32_t ce = cs + PTX_CHUNK < me ? cs + PTX_CHUNK : me;
+        uint32_t v = cx_chunk_vector(rd, cs, ce);
+        vec[c] = first ? cx_restart(v) : v;
+    }
+};
+struct PtxLexCountStep {
+    PtxLexChunkInfo info;
+    const uint8_t* text;
+    const uint32_t* vec;
+    PtxPair* cnt;
+    template <class R> PTX_HD void operator()(size_t c, const R& rd) const {
+        uint32_t ms, me, cs = (uint32_t)c * PTX_CHUNK;
+        bool first;
+        info.locate(c, ms, me, first);
+        int state = first ? CX_CODE : (int)(vec[c - 1] & 7u);
+        LexCountSink sink;
+        lx_chunk(rd, text, ms, me, cs, cs + PTX_CHUNK, state, sink);
+        PtxPair p;
+        p.a = sink.n_tokens;
+        p.b = sink.n_errors;
+        cnt[c + 1] = p;
+        if (c == 0) { PtxPair z; z.a = z.b = 0; cnt[0] = z; }
+    }
+};
+struct PtxLexEmitStep {
+    PtxLexChunkInfo info;
+    const uint8_t* text;
+    const uint32_t* vec;
+    const PtxPair* cnt;
+    PtxToken* tokens;
+    uint32_t* lexerrs;
+    template <class R> PTX_HD void operator()(size_t c, const R& rd) const {
+        uint32_t ms, me, cs = (uint32_t)c * PTX_CHUNK;
+        bool first;
+        info.locate(c, ms, me, first);
+        int state = first ? CX_CODE : (int)(vec[c - 1] & 7u);
+        LexWriteSink sink;
+        sink.tokens = tokens + cnt[c].a;
+        sink.errors = lexerrs + 2 * (size_t)cnt[c].b;
+        lx_chunk(rd, text, ms, me, cs, cs + PTX_CHUNK, state, sink);
+    }
+};
+
 template <class BK>
 inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     const uint8_t* text = w.text;
@@ -142,33 +205,15 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     w.mod_tok_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 2));
     uint32_t* mod_lexerr_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 2));
     PtxCounters* counters = w.counters;
+    const PtxLexChunkInfo info{layout, mcb, n_modules};
 
     // A1: transition vector of every chunk
-    bk.pf("lex_context_vectors", n_chunks, [=] PTX_HD(size_t c) {
-        uint32_t m = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)c) - 1;
-        uint64_t cs = layout[m].text_off + (uint64_t)(c - mcb[m]) * PTX_CHUNK;
-        uint64_t me = layout[m].text_off + layout[m].text_len;
-        uint64_t ce = cs + PTX_CHUNK < me ? cs + PTX_CHUNK : me;
-        uint32_t v = cx_chunk_vector(text, cs, ce);
-        vec[c] = (c == mcb[m]) ? cx_restart(v) : v;
-    });
+    bk.pf_text("lex_context_vectors", n_chunks, text, PtxLexVectorsStep{info, vec});
     // A2: inclusive scan with composition; chunk c starts in state (prefix[c-1])[CODE]
     bk.template scan<uint32_t>("scan_context", n_chunks, [=] PTX_HD(size_t i) { return vec[i]; }, [=] PTX_HD(size_t i, uint32_t v) { vec[i] = v; },
                                ComposeOp(), CX_IDENTITY);
     // A3: count the tokens that start in every chunk
-    bk.pf("lex_count_tokens", n_chunks, [=] PTX_HD(size_t c) {
-        uint32_t m = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)c) - 1;
-        uint64_t ms = layout[m].text_off, me = ms + layout[m].text_len;
-        uint64_t cs = ms + (uint64_t)(c - mcb[m]) * PTX_CHUNK;
-        int state = (c == mcb[m]) ? CX_CODE : (int)(vec[c - 1] & 7u);
-        LexCountSink sink;
-        lx_chunk(text, ms, me, cs, cs + PTX_CHUNK, state, sink);
-        PtxPair p;
-        p.a = sink.n_tokens;
-        p.b = sink.n_errors;
-        cnt[c + 1] = p;
-        if (c == 0) { PtxPair z; z.a = z.b = 0; cnt[0] = z; }
-    });
+    bk.pf_text("lex_count_tokens", n_chunks, text, PtxLexCountStep{info, text, vec, cnt});
     // A4: exclusive offsets (cnt[c] = tokens before chunk c; cnt[n_chunks] = total)
     bk.template scan<PtxPair>("scan_token_counts", n_chunks + 1, [=] PTX_HD(size_t i) { return cnt[i]; }, [=] PTX_HD(size_t i, PtxPair v) { cnt[i] = v; },
                               PairAddOp(), PtxPair{0, 0});
@@ -181,15 +226,12 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     PtxToken* tokens = w.tokens = (PtxToken*)bk.alloc(sizeof(PtxToken) * (size_t)(n_tokens + 1));
     uint32_t* lexerrs = w.lexerrs = (uint32_t*)bk.alloc(sizeof(uint32_t) * 2 * (size_t)(n_lexerrs + 1));
     // A5: emit
-    bk.pf("lex_emit_tokens", n_chunks, [=] PTX_HD(size_t c) {
-        uint32_t m = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)c) - 1;
-        uint64_t ms = layout[m].text_off, me = ms + layout[m].text_len;
-        uint64_t cs = ms + (uint64_t)(c - mcb[m]) * PTX_CHUNK;
-        int state = (c == mcb[m]) ? CX_CODE : (int)(vec[c - 1] & 7u);
-        LexWriteSink sink;
-        sink.tokens = tokens + cnt[c].a;
-        sink.errors = lexerrs + 2 * (size_t)cnt[c].b;
-        lx_chunk(text, ms, me, cs, cs + PTX_CHUNK, state, sink);
+    bk.pf_text("lex_emit_tokens", n_chunks, text, PtxLexEmitStep{info, text, vec, cnt, tokens, lexerrs});
+    // A6: identifiers that spell an opcode, modifier or directive word get that token kind
+    bk.pf("lex_classify_keywords", n_tokens, [=] PTX_HD(size_t i) {
+        PtxToken t = tokens[i];
+        uint16_t k = lx_classify(text, t.start, t.len, t.kind);
+        if (k != t.kind) tokens[i].kind = k;
     });
     uint32_t* mtb = w.mod_tok_begin;
     bk.pf("module_token_ranges", n_modules + 1, [=] PTX_HD(size_t m) {
