@@ -133,6 +133,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--modules", type=int, default=4096)
     ap.add_argument("--bytes", type=int, default=1 << 30)
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="small profiling runs: skip the end-to-end and CPU legs and print only the per-step kernel times")
     a = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -204,6 +206,13 @@ def main():
     barrier()
     wall_ms = (time.perf_counter() - t_wall) * 1e3
     stats = ctx.stats()
+    if a.kernels_only:
+        sampler.stop_flag = True
+        sampler.join()
+        print(json.dumps({"kernels_only": True, "text_bytes": nbytes, "steps": a.steps, "ms_per_step": kernel_ms / a.steps,
+                          "kernels_ms": {k: v / a.steps for k, v in sorted(prof.items(), key=lambda kv: -kv[1])},
+                          "gpu_launches": int(stats["n_kernel_launches"]) * a.steps}))
+        return
     # ---- end to end through the public call: pinned host text in, records out
     for _ in range(min(2, a.warmup)):
         ctx.parse_batch(spans).free()
