@@ -39,6 +39,21 @@ struct HostBackend {
         PtxGlobalReader rd{text, (uint32_t)(n * PTX_CHUNK)};
         pf(name, n, [&](size_t c) { f(c, rd); });
     }
+    template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f) {
+        const uint32_t cap = 47;
+        std::vector<uint32_t> stage(cap);
+        pf(name, n, [&](size_t i) {
+            PtxStaged r = f(i, stage.data(), 1u, cap);
+            for (uint32_t k = 0; k < r.n; k++) table[(size_t)r.unit * row_words + k] = stage[k];
+        });
+    }
+    void gather_records(const char* name, size_t n_units, const uint32_t* table, uint32_t row_words, const PtxPair* off, const uint8_t* flag,
+                        uint32_t* words) {
+        pf(name, n_units, [&](size_t u) {
+            if (flag[u]) return;
+            for (uint32_t k = 0, n = off[u + 1].a - off[u].a; k < n; k++) words[off[u].a + k] = table[u * row_words + k];
+        });
+    }
     void sort_by_key(const char*, size_t n, const uint16_t* key, uint32_t* order) {
         std::vector<uint32_t> cursor(PTX_SORT_BUCKETS + 1, 0);
         for (size_t i = 0; i < n; i++) cursor[key[i] + 1]++;

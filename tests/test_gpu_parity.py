@@ -83,6 +83,38 @@ def test_corpora(oracle, ctx):
         assert stats["n_sequential"] == 0, name
 
 
+def test_sliced_batches(oracle, ctx, monkeypatch):
+    """The one-call entry point cuts a batch into slices and overlaps their copies with the kernels: with slices of a
+    few KB every edge case, error list and lexer error lands in a different slice and both working arenas are reused
+    many times.  The unsliced stage / run / fetch path must give the same dumps."""
+    texts = cases.all_cases() + corpus.config1(n_modules=16, total_bytes=1 << 20, pool_lines=5000)
+    for slice_bytes in ("1", "3000", "70000"):
+        monkeypatch.setenv("PTXFE_SLICE_BYTES", slice_bytes)
+        assert_parity(oracle, ctx, texts, modes=(0, 2))
+    monkeypatch.delenv("PTXFE_SLICE_BYTES")
+    b = ctx.parse_batch(texts, 0)
+    sliced = [b.dump_hash(i) for i in range(len(texts))]
+    b.free()
+    ctx.stage(texts)
+    ctx.run(0)
+    b = ctx.fetch()
+    assert sliced == [b.dump_hash(i) for i in range(len(texts))]
+    b.free()
+    # modules that lie back to back in host memory travel as one copy and are re-aligned on the device
+    import numpy as np
+    raw = [t.encode() if isinstance(t, str) else bytes(t) for t in texts]
+    blob = np.frombuffer(b"".join(raw), dtype=np.uint8).copy()
+    spans, off = [], 0
+    for t in raw:
+        spans.append((blob.ctypes.data + off, len(t)))
+        off += len(t)
+    for slice_bytes in ("5000", "1000000000"):
+        monkeypatch.setenv("PTXFE_SLICE_BYTES", slice_bytes)
+        b = ctx.parse_batch(spans, 0)
+        assert sliced == [b.dump_hash(i) for i in range(len(texts))], slice_bytes
+        b.free()
+
+
 def test_mutated_modules(oracle, ctx):
     rng = random.Random(11)
     base = corpus.config1(n_modules=4, total_bytes=24 << 10, pool_lines=2000) + corpus.config3(total_bytes=24 << 10, n_funcs=4, n_labels=20)

@@ -53,6 +53,16 @@ struct Reader {
     Reader(const PtxBatchView& view, uint32_t mod) : v(view), m(mod), text(view.texts[mod]), text_off(view.layout[mod].text_off) {}
     const char* at(uint32_t off) const { return text + ((uint64_t)off - text_off); }
     void span(Out& o, uint32_t off, uint32_t len) const { o.str(at(off), len); }
+    // a name written by PtxDecoder::w_name: head word (length in bits 8..31) and text offset
+    void name(Out& o, uint32_t head, uint32_t off) const {
+        uint32_t len = head >> 8;
+        if (len == 0xFFFFFFu) {
+            const char* s = at(off);
+            len = 1;
+            while (s[len] == '_' || s[len] == '$' || (s[len] >= '0' && s[len] <= '9') || ((s[len] | 32) >= 'a' && (s[len] | 32) <= 'z')) len++;
+        }
+        o.str(at(off), len);
+    }
 };
 
 inline void imm(Out& o, uint32_t kind, uint32_t lo, uint32_t hi) {
@@ -65,17 +75,17 @@ inline void imm(Out& o, uint32_t kind, uint32_t lo, uint32_t hi) {
     }
 }
 inline const uint32_t* reg_or_imm(const Reader& r, Out& o, const uint32_t* w) {
-    if (w[0] == 0) { o.put("Reg("); r.span(o, w[1], w[2]); o.put(")"); }
-    else { o.put("Imm("); imm(o, w[0] - 1, w[1], w[2]); o.put(")"); }
+    if ((w[0] & 0xFF) == 0) { o.put("Reg("); r.name(o, w[0], w[1]); o.put(")"); return w + 2; }
+    o.put("Imm("); imm(o, w[0] - 1, w[1], w[2]); o.put(")");
     return w + 3;
 }
 inline const uint32_t* operand(const Reader& r, Out& o, const uint32_t* w) {
-    uint32_t kind = w[0] & 0xFF, aux = w[0] >> 8;
+    uint32_t kind = w[0] & 0xF, aux = (w[0] >> 4) & 0xF;
     switch (kind) {
-    case OPK_REG: o.put("Reg("); r.span(o, w[1], w[2]); o.put(")"); return w + 3;
-    case OPK_REG_OFFSET: o.put("RegOffset("); r.span(o, w[1], w[2]); o.putf(", %d)", (int32_t)w[3]); return w + 4;
+    case OPK_REG: o.put("Reg("); r.name(o, w[0], w[1]); o.put(")"); return w + 2;
+    case OPK_REG_OFFSET: o.put("RegOffset("); r.name(o, w[0], w[1]); o.putf(", %d)", (int32_t)w[2]); return w + 3;
     case OPK_IMM: o.put("Imm("); imm(o, aux, w[1], w[2]); o.put(")"); return w + 3;
-    case OPK_VEC_MEMBER: o.put("VecMember("); r.span(o, w[1], w[2]); o.putf(", %u)", aux); return w + 3;
+    case OPK_VEC_MEMBER: o.put("VecMember("); r.name(o, w[0], w[1]); o.putf(", %u)", aux); return w + 2;
     default:
         o.put("VecPack([");
         w++;
@@ -104,6 +114,10 @@ inline void zero_of(Out& o, uint32_t scalar) {
     int k = scalar_kind((int)scalar);
     o.put(k == KIND_SIGNED ? "Imm(S64(0))" : k == KIND_FLOAT ? "Imm(F64(bits=0x0000000000000000))" : "Imm(U64(0))");
 }
+inline const uint32_t* skip_inits(const uint32_t* p, uint32_t n) {
+    for (uint32_t i = 0; i < n; i++) p += (p[0] & 0xFF) == 0 ? 2 : 3;   // name: 2 words, immediate: 3
+    return p;
+}
 // INFO record: [w0, align, ndims, dims..., n_init, RegOrImm...]
 inline const uint32_t* info(const Reader& r, Out& o, const uint32_t* w, bool type_space_only = false) {
     uint32_t w0 = w[0], align = w[1], ndims = w[2];
@@ -115,7 +129,7 @@ inline const uint32_t* info(const Reader& r, Out& o, const uint32_t* w, bool typ
         o.put("(");
         type_of(o, w0, dims, ndims);
         o.putf(", %s)", StateSpace_names[space]);
-        return p + 3 * n_init;
+        return skip_inits(p, n_init);
     }
     if (w0 & 1) o.putf("VariableInfo { align: Some(%u), v_type: ", align);
     else o.put("VariableInfo { align: None, v_type: ");
@@ -151,7 +165,7 @@ inline const uint32_t* skip_variable(const uint32_t* w) {
     uint32_t ndims = w[2];
     const uint32_t* p = w + 3 + ndims;
     uint32_t n_init = *p++;
-    return p + 3 * n_init + 2;
+    return skip_inits(p, n_init) + 2;
 }
 
 inline void schema(Out& o, int type, const uint32_t*& w) {

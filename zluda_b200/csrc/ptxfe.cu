@@ -90,6 +90,84 @@ __global__ void __launch_bounds__(256) lex_tile_kernel(uint32_t n_chunks, const 
     if (c < n_chunks) f((size_t)c, PtxTileReader{tile, fused, text, c0 * PTX_CHUNK});
 }
 
+// ---- first decode pass: every thread builds its record in shared memory, then each warp copies its 32 records to
+// their rows of the staging table with coalesced stores.  Word k of thread t lives at stage[k * STAGE_STRIDE + t]:
+// threads of a warp decode units of the same shape in lockstep, so they write the same k at the same time (32
+// consecutive banks), and the copy loop reads one thread's words with a stride that is odd (no bank conflicts).
+#define STAGE_CAP 47u
+#define STAGE_STRIDE 257u
+template <class F>
+__global__ void __launch_bounds__(256) staged_kernel(size_t n, uint32_t* table, uint32_t row_words, F f) {
+    __shared__ uint32_t stage[STAGE_CAP * STAGE_STRIDE];
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    PtxStaged r;
+    r.unit = 0;
+    r.n = 0;
+    if (i < n) r = f(i, stage + threadIdx.x, STAGE_STRIDE, STAGE_CAP);
+    __syncwarp();
+    const uint32_t lane = threadIdx.x & 31u, warp_base = threadIdx.x & ~31u;
+    for (uint32_t l = 0; l < 32; l++) {
+        uint32_t cnt = __shfl_sync(0xFFFFFFFFu, r.n, l);
+        uint32_t unit = __shfl_sync(0xFFFFFFFFu, r.unit, l);
+        uint32_t* row = table + (size_t)unit * row_words;
+        for (uint32_t k = lane; k < cnt; k += 32) row[k] = stage[k * STAGE_STRIDE + warp_base + l];
+    }
+}
+
+// ---- records from the staging table to their final places: one block per 256 consecutive units, whose records are
+// contiguous in the output; every thread copies output words, finding the unit of each by binary search
+__global__ void __launch_bounds__(256) gather_records_kernel(uint32_t n_units, const uint32_t* table, uint32_t row_words, const PtxPair* off,
+                                                             const uint8_t* flag, uint32_t* words) {
+    __shared__ uint32_t so[257];
+    __shared__ uint8_t sf[256];
+    const uint32_t u0 = blockIdx.x * 256;
+    const uint32_t nu = n_units - u0 < 256u ? n_units - u0 : 256u;
+    for (uint32_t k = threadIdx.x; k <= nu; k += 256) so[k] = off[u0 + k].a;
+    if (threadIdx.x < nu) sf[threadIdx.x] = flag[u0 + threadIdx.x];
+    __syncthreads();
+    const uint32_t first = so[0], total = so[nu] - so[0];
+    for (uint32_t j = threadIdx.x; j < total; j += 256) {
+        uint32_t o = first + j;
+        uint32_t lo = 0, hi = nu;          // last k with so[k] <= o
+        while (hi - lo > 1) {
+            uint32_t mid = (lo + hi) >> 1;
+            if (so[mid] <= o) lo = mid; else hi = mid;
+        }
+        if (!sf[lo]) words[o] = table[(size_t)(u0 + lo) * row_words + (o - so[lo])];
+    }
+}
+
+__global__ void copy_words_kernel(uint32_t* dst, const uint32_t* src, uint32_t n) {
+    for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) dst[i] = src[i];
+    __threadfence_system();
+}
+
+// ---- text that arrived as one host-contiguous run: move every module to its chunk-aligned slot
+// One thread per 16 bytes of destination.  `raw_off` of a module is where its first byte lies in `raw`.
+struct RepackModule {
+    uint32_t chunk_begin, raw_off, len;
+};
+__global__ void __launch_bounds__(256) repack_text_kernel(uint32_t n_pieces, uint32_t n_modules, const RepackModule* mods, const uint32_t* mcb,
+                                                          const uint8_t* raw, uint8_t* text) {
+    uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_pieces) return;
+    uint32_t chunk = i >> 3;
+    uint32_t m = ptx_upper_bound_u32(mcb, n_modules, chunk) - 1;
+    uint32_t o = (chunk - mods[m].chunk_begin) * PTX_CHUNK + (i & 7u) * 16;   // offset inside the module
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (o < mods[m].len) {
+        size_t a = (size_t)mods[m].raw_off + o;
+        const uint32_t* w = (const uint32_t*)(raw + (a & ~(size_t)3));       // the raw buffer has 32 spare bytes at its end
+        uint32_t sh = (uint32_t)(a & 3) * 8;
+        uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3], w4 = w[4];
+        v.x = __funnelshift_r(w0, w1, sh);
+        v.y = __funnelshift_r(w1, w2, sh);
+        v.z = __funnelshift_r(w2, w3, sh);
+        v.w = __funnelshift_r(w3, w4, sh);
+    }
+    ((uint4*)text)[i] = v;
+}
+
 constexpr int SCAN_THREADS = 256;
 constexpr int SCAN_ITEMS = 8;
 constexpr int SCAN_TILE = SCAN_THREADS * SCAN_ITEMS;
@@ -247,9 +325,13 @@ struct ptxfe_batch {
 
 struct ptxfe_ctx {
     int device = 0;
-    cudaStream_t stream = nullptr;
+    cudaStream_t stream = nullptr;        // kernels (and everything of the stage / run / fetch calls)
+    cudaStream_t s_in = nullptr;          // host -> device copies of the pipelined parse
+    cudaStream_t s_out = nullptr;         // device -> host copies of the pipelined parse
     cudaEvent_t ev[8] = {nullptr};
-    std::vector<ArenaBlock> blocks;
+    std::vector<cudaEvent_t> slice_ev;    // 5 per slice: text arrived, kernels begin / end, results begin / end
+    std::vector<ArenaBlock> arenas[2];    // device working memory; the pipelined parse alternates between the two
+    int cur = 0;
     char err[512] = {0};
     bool failed = false;
     uint64_t launches = 0;
@@ -260,6 +342,8 @@ struct ptxfe_ctx {
     uint64_t text_bytes = 0, padded_bytes = 0;
     uint8_t* d_text = nullptr;
     size_t d_text_cap = 0;
+    uint8_t* d_raw = nullptr;             // host-contiguous runs land here before they are repacked into d_text
+    size_t d_raw_cap = 0;
     PtxWork work;
     PtxCounters counters;
     bool staged = false, ran = false;
@@ -269,7 +353,8 @@ struct ptxfe_ctx {
     void* h_errs = nullptr; size_t h_errs_cap = 0;
     void* h_lexerrs = nullptr; size_t h_lexerrs_cap = 0;
     void* h_results = nullptr; size_t h_results_cap = 0;
-    PtxCounters* h_counters = nullptr;
+    PtxCounters* h_counters = nullptr;    // mapped pinned memory, written by the device
+    void* d_counters_mapped = nullptr;    // its device address
     ptxfe_stats stats;
     ptxfe_batch* live = nullptr;
     // per-step profile
@@ -284,7 +369,7 @@ struct CudaBackend {
     ptxfe_ctx* ctx;
     void* alloc(size_t bytes) {
         bytes = (bytes + 255) & ~(size_t)255;
-        for (ArenaBlock& b : ctx->blocks)
+        for (ArenaBlock& b : ctx->arenas[ctx->cur])
             if (b.size - b.used >= bytes) {
                 void* p = b.base + b.used;
                 b.used += bytes;
@@ -302,11 +387,11 @@ struct CudaBackend {
         }
         nb.size = sz;
         nb.used = bytes;
-        ctx->blocks.push_back(nb);
+        ctx->arenas[ctx->cur].push_back(nb);
         return nb.base;
     }
     void reset() {
-        for (ArenaBlock& b : ctx->blocks) b.used = 0;
+        for (ArenaBlock& b : ctx->arenas[ctx->cur]) b.used = 0;
     }
     void zero(void* p, size_t bytes) {
         if (ctx->failed || !p) return;
@@ -314,7 +399,9 @@ struct CudaBackend {
     }
     void download(void* host, const void* dev, size_t bytes) {
         if (ctx->failed) { memset(host, 0, bytes); return; }
-        cudaMemcpyAsync(ctx->h_counters, dev, bytes, cudaMemcpyDeviceToHost, ctx->stream);
+        // a kernel writes the few words into mapped host memory: a copy-engine transfer would queue behind the
+        // result copies of the previous slice, which run on another stream at the same time
+        copy_words_kernel<<<1, 32, 0, ctx->stream>>>((uint32_t*)ctx->d_counters_mapped, (const uint32_t*)dev, (uint32_t)(bytes / 4));
         cudaError_t e = cudaStreamSynchronize(ctx->stream);
         if (e != cudaSuccess) {
             snprintf(ctx->err, sizeof ctx->err, "kernel or copy failed: %s", cudaGetErrorString(e));
@@ -346,6 +433,21 @@ struct CudaBackend {
         size_t blocks = (n + 255) / 256;
         prof_begin(name);
         pf_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(n, f);
+        prof_end();
+        ctx->launches++;
+    }
+    template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f) {
+        if (ctx->failed || n == 0) return;
+        prof_begin(name);
+        staged_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(n, table, row_words, f);
+        prof_end();
+        ctx->launches++;
+    }
+    void gather_records(const char* name, size_t n_units, const uint32_t* table, uint32_t row_words, const PtxPair* off, const uint8_t* flag,
+                        uint32_t* words) {
+        if (ctx->failed || n_units == 0) return;
+        prof_begin(name);
+        gather_records_kernel<<<(unsigned)((n_units + 255) / 256), 256, 0, ctx->stream>>>((uint32_t)n_units, table, row_words, off, flag, words);
         prof_end();
         ctx->launches++;
     }
@@ -402,16 +504,6 @@ struct CudaBackend {
     }
 };
 
-static int ensure_pinned(ptxfe_ctx* ctx, void** p, size_t* cap, size_t need) {
-    if (need <= *cap) return PTXFE_OK;
-    if (*p) cudaFreeHost(*p);
-    *p = nullptr;
-    size_t sz = need + need / 4 + 4096;
-    CUDA_TRY(cudaMallocHost(p, sz));
-    *cap = sz;
-    return PTXFE_OK;
-}
-
 // ------------------------------------------------------------------------------------------------ C ABI
 extern "C" {
 
@@ -441,8 +533,11 @@ int ptxfe_create(int device, ptxfe_ctx** out) {
     }
     cudaError_t e = cudaSetDevice(device);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->s_in, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->s_out, cudaStreamNonBlocking);
     for (int i = 0; i < 8 && e == cudaSuccess; i++) e = cudaEventCreate(&ctx->ev[i]);
-    if (e == cudaSuccess) e = cudaMallocHost((void**)&ctx->h_counters, sizeof(PtxCounters) * 4);
+    if (e == cudaSuccess) e = cudaHostAlloc((void**)&ctx->h_counters, sizeof(PtxCounters) * 4, cudaHostAllocMapped);
+    if (e == cudaSuccess) e = cudaHostGetDevicePointer(&ctx->d_counters_mapped, ctx->h_counters, 0);
     if (e != cudaSuccess) {
         fprintf(stderr, "ptxfe: context set-up failed: %s\n", cudaGetErrorString(e));
         delete ctx;
@@ -456,8 +551,14 @@ void ptxfe_destroy(ptxfe_ctx* ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     if (ctx->stream) cudaStreamSynchronize(ctx->stream);
-    for (ArenaBlock& b : ctx->blocks) cudaFree(b.base);
+    for (int a = 0; a < 2; a++)
+        for (ArenaBlock& b : ctx->arenas[a]) cudaFree(b.base);
+    for (cudaEvent_t e : ctx->slice_ev) cudaEventDestroy(e);
+    for (cudaEvent_t e : ctx->prof_events) cudaEventDestroy(e);
+    if (ctx->s_in) cudaStreamDestroy(ctx->s_in);
+    if (ctx->s_out) cudaStreamDestroy(ctx->s_out);
     if (ctx->d_text) cudaFree(ctx->d_text);
+    if (ctx->d_raw) cudaFree(ctx->d_raw);
     if (ctx->h_words) cudaFreeHost(ctx->h_words);
     if (ctx->h_errs) cudaFreeHost(ctx->h_errs);
     if (ctx->h_lexerrs) cudaFreeHost(ctx->h_lexerrs);
@@ -472,6 +573,35 @@ void ptxfe_destroy(ptxfe_ctx* ctx) {
 
 const char* ptxfe_last_error(const ptxfe_ctx* ctx) { return ctx ? ctx->err : "no context"; }
 
+// Lay the modules [m0, m1) out as one slice: module i starts at a multiple of PTX_CHUNK inside the slice.
+// Returns the padded size of the slice.
+static uint64_t layout_slice(ptxfe_ctx* ctx, const uint64_t* lens, uint32_t m0, uint32_t m1) {
+    uint64_t off = 0, chunks = 0;
+    for (uint32_t m = m0; m < m1; m++) {
+        PtxModuleLayout& l = ctx->layout[m];
+        l.text_off = off;
+        l.text_len = lens[m];
+        l.chunk_begin = (uint32_t)chunks;
+        l.pad = 0;
+        uint64_t c = (lens[m] + PTX_CHUNK - 1) / PTX_CHUNK;
+        chunks += c;
+        off += c * PTX_CHUNK;
+    }
+    return off;
+}
+
+static int ensure_text(ptxfe_ctx* ctx, uint64_t bytes) {
+    if (bytes + 256 > ctx->d_text_cap) {
+        if (ctx->d_text) cudaFree(ctx->d_text);
+        ctx->d_text = nullptr;
+        ctx->d_text_cap = 0;
+        size_t cap = bytes + bytes / 8 + 4096;
+        CUDA_TRY(cudaMalloc((void**)&ctx->d_text, cap));
+        ctx->d_text_cap = cap;
+    }
+    return PTXFE_OK;
+}
+
 int ptxfe_stage(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, uint32_t n) {
     if (!ctx || (n && (!texts || !lens))) return PTXFE_ERR_BAD_ARG;
     CUDA_TRY(cudaSetDevice(ctx->device));
@@ -479,32 +609,14 @@ int ptxfe_stage(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, 
     ctx->staged = ctx->ran = false;
     ctx->texts.assign(texts, texts + n);
     ctx->layout.resize(n);
-    ctx->mcb.resize((size_t)n + 1);
-    uint64_t off = 0, chunks = 0, total = 0;
-    for (uint32_t m = 0; m < n; m++) {
-        PtxModuleLayout& l = ctx->layout[m];
-        l.text_off = off;
-        l.text_len = lens[m];
-        l.chunk_begin = (uint32_t)chunks;
-        l.pad = 0;
-        ctx->mcb[m] = (uint32_t)chunks;
-        uint64_t c = (lens[m] + PTX_CHUNK - 1) / PTX_CHUNK;
-        chunks += c;
-        off += c * PTX_CHUNK;
-        total += lens[m];
-        if (off >= 0xFFFFFF00ull) return PTXFE_ERR_TOO_LARGE;
-    }
-    ctx->mcb[n] = (uint32_t)chunks;
+    uint64_t total = 0;
+    for (uint32_t m = 0; m < n; m++) total += lens[m];
+    uint64_t off = layout_slice(ctx, lens, 0, n);
+    if (off >= 0xFFFFFF00ull) return PTXFE_ERR_TOO_LARGE;
     ctx->text_bytes = total;
     ctx->padded_bytes = off;
-    if (off + 256 > ctx->d_text_cap) {
-        if (ctx->d_text) cudaFree(ctx->d_text);
-        ctx->d_text = nullptr;
-        ctx->d_text_cap = 0;
-        size_t cap = off + off / 8 + 4096;
-        CUDA_TRY(cudaMalloc((void**)&ctx->d_text, cap));
-        ctx->d_text_cap = cap;
-    }
+    int st = ensure_text(ctx, off);
+    if (st != PTXFE_OK) return st;
     CUDA_TRY(cudaEventRecord(ctx->ev[0], ctx->stream));
     for (uint32_t m = 0; m < n; m++)
         if (lens[m])
@@ -519,41 +631,51 @@ int ptxfe_stage(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, 
     return PTXFE_OK;
 }
 
-int ptxfe_run(ptxfe_ctx* ctx, uint32_t mode) {
-    if (!ctx || !ctx->staged || mode > 2) return PTXFE_ERR_BAD_ARG;
-    CUDA_TRY(cudaSetDevice(ctx->device));
-    if (ctx->live) { ctx->live->ctx = nullptr; ctx->live = nullptr; }
+// The three stages over one slice: `text` is the slice's text on the device, `layout` its n module layouts (host).
+// Uses the current arena; leaves the device results in ctx->work and the totals in ctx->counters.  Returns after
+// the kernels have finished.
+static int run_pipeline(ptxfe_ctx* ctx, uint8_t* text, const PtxModuleLayout* layout, uint32_t n, uint32_t mode,
+                        cudaEvent_t ev_begin, cudaEvent_t ev_lex, cudaEvent_t ev_structure, cudaEvent_t ev_end,
+                        const RepackModule* repack = nullptr, const uint8_t* raw = nullptr) {
     CudaBackend bk{ctx};
     bk.reset();
-    ctx->failed = false;
-    ctx->launches = 0;
-    ctx->prof_used = 0;
-    ctx->prof_names.clear();
-    ctx->mode = mode;
-    uint32_t n = (uint32_t)ctx->layout.size();
+    ctx->mcb.resize((size_t)n + 1);
+    uint32_t chunks = 0;
+    for (uint32_t m = 0; m < n; m++) {
+        ctx->mcb[m] = layout[m].chunk_begin;
+        chunks = layout[m].chunk_begin + (uint32_t)((layout[m].text_len + PTX_CHUNK - 1) / PTX_CHUNK);
+    }
+    ctx->mcb[n] = chunks;
     PtxWork& w = ctx->work;
     w = PtxWork();
-    w.text = ctx->d_text;
+    w.text = text;
     w.n_modules = n;
-    w.n_chunks = ctx->mcb[n];
+    w.n_chunks = chunks;
     w.layout = (PtxModuleLayout*)bk.alloc(sizeof(PtxModuleLayout) * ((size_t)n + 1));
     w.mod_chunk_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n + 2));
     w.results = (PtxModuleResult*)bk.alloc(sizeof(PtxModuleResult) * ((size_t)n + 1));
     w.counters = (PtxCounters*)bk.alloc(sizeof(PtxCounters));
     if (ctx->failed) return PTXFE_ERR_OOM;
-    CUDA_TRY(cudaEventRecord(ctx->ev[2], ctx->stream));
-    if (n) {
-        CUDA_TRY(cudaMemcpyAsync(w.layout, ctx->layout.data(), sizeof(PtxModuleLayout) * n, cudaMemcpyHostToDevice, ctx->stream));
-    }
+    CUDA_TRY(cudaEventRecord(ev_begin, ctx->stream));
+    if (n) CUDA_TRY(cudaMemcpyAsync(w.layout, layout, sizeof(PtxModuleLayout) * n, cudaMemcpyHostToDevice, ctx->stream));
     CUDA_TRY(cudaMemcpyAsync(w.mod_chunk_begin, ctx->mcb.data(), sizeof(uint32_t) * ((size_t)n + 1), cudaMemcpyHostToDevice, ctx->stream));
     CUDA_TRY(cudaMemsetAsync(w.counters, 0, sizeof(PtxCounters), ctx->stream));
+    // layout and mcb are pageable host memory: the copies above have consumed them when the calls return
+    if (repack && chunks) {
+        RepackModule* d_mods = (RepackModule*)bk.alloc(sizeof(RepackModule) * (size_t)n);
+        if (ctx->failed) return PTXFE_ERR_OOM;
+        CUDA_TRY(cudaMemcpyAsync(d_mods, repack, sizeof(RepackModule) * (size_t)n, cudaMemcpyHostToDevice, ctx->stream));
+        uint32_t pieces = chunks * (PTX_CHUNK / 16);
+        repack_text_kernel<<<(pieces + 255) / 256, 256, 0, ctx->stream>>>(pieces, n, d_mods, w.mod_chunk_begin, raw, text);
+        ctx->launches++;
+    }
     memset(&ctx->counters, 0, sizeof ctx->counters);
     ptx_stage_lex(bk, w, ctx->counters);
-    CUDA_TRY(cudaEventRecord(ctx->ev[3], ctx->stream));
+    if (ev_lex) CUDA_TRY(cudaEventRecord(ev_lex, ctx->stream));
     if (!ctx->failed) ptx_stage_structure(bk, w, ctx->counters, mode);
-    CUDA_TRY(cudaEventRecord(ctx->ev[4], ctx->stream));
+    if (ev_structure) CUDA_TRY(cudaEventRecord(ev_structure, ctx->stream));
     if (!ctx->failed) ptx_stage_decode(bk, w, ctx->counters);
-    CUDA_TRY(cudaEventRecord(ctx->ev[5], ctx->stream));
+    CUDA_TRY(cudaEventRecord(ev_end, ctx->stream));
     cudaError_t e = cudaStreamSynchronize(ctx->stream);
     if (e == cudaSuccess) e = cudaGetLastError();
     if (e != cudaSuccess) {
@@ -561,6 +683,34 @@ int ptxfe_run(ptxfe_ctx* ctx, uint32_t mode) {
         return PTXFE_ERR_CUDA;
     }
     if (ctx->failed) return strstr(ctx->err, "cudaMalloc") ? PTXFE_ERR_OOM : PTXFE_ERR_CUDA;
+    return PTXFE_OK;
+}
+
+static void collect_profile(ptxfe_ctx* ctx) {
+    if (!ctx->profile) return;
+    ctx->prof_text.clear();
+    for (size_t i = 0; i < ctx->prof_names.size(); i++) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, ctx->prof_events[2 * i], ctx->prof_events[2 * i + 1]);
+        char line[160];
+        snprintf(line, sizeof line, "%s %.6f\n", ctx->prof_names[i], ms);
+        ctx->prof_text += line;
+    }
+}
+
+int ptxfe_run(ptxfe_ctx* ctx, uint32_t mode) {
+    if (!ctx || !ctx->staged || mode > 2) return PTXFE_ERR_BAD_ARG;
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    if (ctx->live) { ctx->live->ctx = nullptr; ctx->live = nullptr; }
+    ctx->failed = false;
+    ctx->launches = 0;
+    ctx->prof_used = 0;
+    ctx->prof_names.clear();
+    ctx->mode = mode;
+    ctx->cur = 0;
+    uint32_t n = (uint32_t)ctx->layout.size();
+    int st = run_pipeline(ctx, ctx->d_text, ctx->layout.data(), n, mode, ctx->ev[2], ctx->ev[3], ctx->ev[4], ctx->ev[5]);
+    if (st != PTXFE_OK) return st;
     ptxfe_stats& s = ctx->stats;
     cudaEventElapsedTime(&s.kernel_ms, ctx->ev[2], ctx->ev[5]);
     cudaEventElapsedTime(&s.lex_ms, ctx->ev[2], ctx->ev[3]);
@@ -574,43 +724,26 @@ int ptxfe_run(ptxfe_ctx* ctx, uint32_t mode) {
     s.n_kernel_launches = ctx->launches;
     s.n_sequential = 0;
     ctx->ran = true;
-    if (ctx->profile) {
-        ctx->prof_text.clear();
-        for (size_t i = 0; i < ctx->prof_names.size(); i++) {
-            float ms = 0;
-            cudaEventElapsedTime(&ms, ctx->prof_events[2 * i], ctx->prof_events[2 * i + 1]);
-            char line[160];
-            snprintf(line, sizeof line, "%s %.6f\n", ctx->prof_names[i], ms);
-            ctx->prof_text += line;
-        }
-    }
+    collect_profile(ctx);
     return PTXFE_OK;
 }
 
 const char* ptxfe_profile(const ptxfe_ctx* ctx) { return ctx ? ctx->prof_text.c_str() : ""; }
 
-int ptxfe_fetch(ptxfe_ctx* ctx, ptxfe_batch** out) {
-    if (!ctx || !out || !ctx->ran) return PTXFE_ERR_BAD_ARG;
-    *out = nullptr;
-    CUDA_TRY(cudaSetDevice(ctx->device));
-    const PtxCounters& c = ctx->counters;
-    uint32_t n = (uint32_t)ctx->layout.size();
-    size_t wb = sizeof(uint32_t) * (size_t)c.n_words, eb = sizeof(PtxErrRec) * (size_t)c.n_errs;
-    size_t lb = sizeof(uint32_t) * 2 * (size_t)c.n_lexerrs, rb = sizeof(PtxModuleResult) * (size_t)n;
-    int st;
-    if ((st = ensure_pinned(ctx, &ctx->h_words, &ctx->h_words_cap, wb + 16)) != PTXFE_OK) return st;
-    if ((st = ensure_pinned(ctx, &ctx->h_errs, &ctx->h_errs_cap, eb + 16)) != PTXFE_OK) return st;
-    if ((st = ensure_pinned(ctx, &ctx->h_lexerrs, &ctx->h_lexerrs_cap, lb + 16)) != PTXFE_OK) return st;
-    if ((st = ensure_pinned(ctx, &ctx->h_results, &ctx->h_results_cap, rb + 16)) != PTXFE_OK) return st;
-    CUDA_TRY(cudaEventRecord(ctx->ev[6], ctx->stream));
-    if (wb) CUDA_TRY(cudaMemcpyAsync(ctx->h_words, ctx->work.words, wb, cudaMemcpyDeviceToHost, ctx->stream));
-    if (eb) CUDA_TRY(cudaMemcpyAsync(ctx->h_errs, ctx->work.errs, eb, cudaMemcpyDeviceToHost, ctx->stream));
-    if (lb) CUDA_TRY(cudaMemcpyAsync(ctx->h_lexerrs, ctx->work.lexerrs, lb, cudaMemcpyDeviceToHost, ctx->stream));
-    if (rb) CUDA_TRY(cudaMemcpyAsync(ctx->h_results, ctx->work.results, rb, cudaMemcpyDeviceToHost, ctx->stream));
-    CUDA_TRY(cudaEventRecord(ctx->ev[7], ctx->stream));
-    CUDA_TRY(cudaStreamSynchronize(ctx->stream));
-    CUDA_TRY(cudaEventElapsedTime(&ctx->stats.d2h_ms, ctx->ev[6], ctx->ev[7]));
-    ctx->stats.d2h_bytes = wb + eb + lb + rb;
+// Grow a pinned host buffer, keeping its first `keep` bytes.  Copies that target the old buffer must have finished.
+static int grow_pinned(ptxfe_ctx* ctx, void** p, size_t* cap, size_t need, size_t keep) {
+    if (need <= *cap) return PTXFE_OK;
+    void* np = nullptr;
+    size_t sz = need + need / 4 + 4096;
+    CUDA_TRY(cudaMallocHost(&np, sz));
+    if (*p && keep) memcpy(np, *p, keep);
+    if (*p) cudaFreeHost(*p);
+    *p = np;
+    *cap = sz;
+    return PTXFE_OK;
+}
+
+static ptxfe_batch* make_batch(ptxfe_ctx* ctx, uint32_t n) {
     ptxfe_batch* b = new ptxfe_batch();
     b->ctx = ctx;
     b->n = n;
@@ -622,6 +755,32 @@ int ptxfe_fetch(ptxfe_ctx* ctx, ptxfe_batch** out) {
     b->words = (const uint32_t*)ctx->h_words;
     b->errs = (const PtxErrRec*)ctx->h_errs;
     b->lexerrs = (const uint32_t*)ctx->h_lexerrs;
+    return b;
+}
+
+int ptxfe_fetch(ptxfe_ctx* ctx, ptxfe_batch** out) {
+    if (!ctx || !out || !ctx->ran) return PTXFE_ERR_BAD_ARG;
+    *out = nullptr;
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    const PtxCounters& c = ctx->counters;
+    uint32_t n = (uint32_t)ctx->layout.size();
+    size_t wb = sizeof(uint32_t) * (size_t)c.n_words, eb = sizeof(PtxErrRec) * (size_t)c.n_errs;
+    size_t lb = sizeof(uint32_t) * 2 * (size_t)c.n_lexerrs, rb = sizeof(PtxModuleResult) * (size_t)n;
+    int st;
+    if ((st = grow_pinned(ctx, &ctx->h_words, &ctx->h_words_cap, wb + 16, 0)) != PTXFE_OK) return st;
+    if ((st = grow_pinned(ctx, &ctx->h_errs, &ctx->h_errs_cap, eb + 16, 0)) != PTXFE_OK) return st;
+    if ((st = grow_pinned(ctx, &ctx->h_lexerrs, &ctx->h_lexerrs_cap, lb + 16, 0)) != PTXFE_OK) return st;
+    if ((st = grow_pinned(ctx, &ctx->h_results, &ctx->h_results_cap, rb + 16, 0)) != PTXFE_OK) return st;
+    CUDA_TRY(cudaEventRecord(ctx->ev[6], ctx->stream));
+    if (wb) CUDA_TRY(cudaMemcpyAsync(ctx->h_words, ctx->work.words, wb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (eb) CUDA_TRY(cudaMemcpyAsync(ctx->h_errs, ctx->work.errs, eb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (lb) CUDA_TRY(cudaMemcpyAsync(ctx->h_lexerrs, ctx->work.lexerrs, lb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (rb) CUDA_TRY(cudaMemcpyAsync(ctx->h_results, ctx->work.results, rb, cudaMemcpyDeviceToHost, ctx->stream));
+    CUDA_TRY(cudaEventRecord(ctx->ev[7], ctx->stream));
+    CUDA_TRY(cudaStreamSynchronize(ctx->stream));
+    CUDA_TRY(cudaEventElapsedTime(&ctx->stats.d2h_ms, ctx->ev[6], ctx->ev[7]));
+    ctx->stats.d2h_bytes = wb + eb + lb + rb;
+    ptxfe_batch* b = make_batch(ctx, n);
     uint64_t seq = 0;
     for (uint32_t m = 0; m < n; m++) seq += b->results[m].sequential;
     ctx->stats.n_sequential = seq;
@@ -630,13 +789,210 @@ int ptxfe_fetch(ptxfe_ctx* ctx, ptxfe_batch** out) {
     return PTXFE_OK;
 }
 
+// One call, host text in, host records out.  The batch is cut into slices of whole modules; the text of slice k+1
+// travels to the device and the records of slice k-1 travel back while the kernels of slice k run (three streams,
+// two working arenas).  Text offsets inside the records are relative to the slice, as ptxfe_module_records reports.
 int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, uint32_t n, uint32_t mode, ptxfe_batch** out) {
     if (!out) return PTXFE_ERR_BAD_ARG;
     *out = nullptr;
-    int st = ptxfe_stage(ctx, texts, lens, n);
-    if (st == PTXFE_OK) st = ptxfe_run(ctx, mode);
-    if (st == PTXFE_OK) st = ptxfe_fetch(ctx, out);
-    return st;
+    if (!ctx || (n && (!texts || !lens)) || mode > 2) return PTXFE_ERR_BAD_ARG;
+    CUDA_TRY(cudaSetDevice(ctx->device));
+    if (ctx->live) { ctx->live->ctx = nullptr; ctx->live = nullptr; }
+    ctx->failed = false;
+    ctx->staged = ctx->ran = false;
+    ctx->launches = 0;
+    ctx->prof_used = 0;
+    ctx->prof_names.clear();
+    ctx->mode = mode;
+    ctx->texts.assign(texts, texts + n);
+    ctx->layout.resize(n);
+    // ---- slices
+    // Small slices at both ends (the first text copy and the last result copy overlap with nothing), large ones in
+    // between (every slice costs a few host synchronisations and ~70 launches).  PTXFE_SLICE_BYTES forces one size.
+    uint64_t grand_total = 0;
+    for (uint32_t m = 0; m < n; m++) grand_total += lens[m];
+    uint64_t edge = (uint64_t)32 << 20, middle = grand_total / 6;
+    if (middle < ((uint64_t)64 << 20)) middle = (uint64_t)64 << 20;
+    if (middle > ((uint64_t)256 << 20)) middle = (uint64_t)256 << 20;
+    if (const char* e = getenv("PTXFE_SLICE_BYTES")) {
+        uint64_t v = strtoull(e, nullptr, 10);
+        if (v) edge = middle = v;
+    }
+    struct Slice { uint32_t m0, m1; uint64_t text_off, padded, bytes; };
+    std::vector<Slice> slices;
+    uint64_t total = 0, text_off = 0;
+    for (uint32_t m = 0; m < n;) {
+        uint64_t left = grand_total - total;
+        uint64_t target = slices.empty() ? edge : middle;
+        if (!slices.empty() && left > edge && left <= middle + edge) target = left - edge;   // leave a small last slice
+        uint32_t m1 = m;
+        uint64_t bytes = 0;
+        while (m1 < n && (m1 == m || bytes + lens[m1] <= target)) bytes += lens[m1++];
+        uint64_t padded = layout_slice(ctx, lens, m, m1);
+        if (padded >= 0xFFFFFF00ull) return PTXFE_ERR_TOO_LARGE;
+        slices.push_back(Slice{m, m1, text_off, padded, bytes});
+        text_off += padded;
+        total += bytes;
+        m = m1;
+    }
+    if (slices.empty()) slices.push_back(Slice{0, 0, 0, 0, 0});
+    const size_t ns = slices.size();
+    int st = ensure_text(ctx, text_off);
+    if (st != PTXFE_OK) return st;
+    while (ctx->slice_ev.size() < ns * 5) {
+        cudaEvent_t e;
+        CUDA_TRY(cudaEventCreate(&e));
+        ctx->slice_ev.push_back(e);
+    }
+    // ---- text copies, in slice order, on their own stream; submitted two slices ahead of the kernels.
+    // Modules that follow one another in host memory travel as one copy into a raw buffer and are moved to their
+    // chunk-aligned slots by a kernel; modules scattered over the host are copied straight into their slots.
+    std::vector<RepackModule> repack(n);
+    std::vector<uint64_t> raw_base(ns, 0);
+    std::vector<char> use_raw(ns, 0);
+    uint64_t raw_total = 0;
+    for (size_t k = 0; k < ns; k++) {
+        const Slice& sl = slices[k];
+        uint32_t runs = 0;
+        for (uint32_t m = sl.m0; m < sl.m1; m++)
+            if (m == sl.m0 || texts[m] != texts[m - 1] + lens[m - 1]) runs++;
+        if (runs * 2 <= sl.m1 - sl.m0) {
+            use_raw[k] = 1;
+            raw_base[k] = raw_total;
+            raw_total += ((sl.bytes + 15) & ~(uint64_t)15) + 16 * (uint64_t)runs;
+        }
+    }
+    if (raw_total + 64 > ctx->d_raw_cap) {
+        if (ctx->d_raw) cudaFree(ctx->d_raw);
+        ctx->d_raw = nullptr;
+        ctx->d_raw_cap = 0;
+        size_t cap = raw_total + raw_total / 8 + 4096;
+        CUDA_TRY(cudaMalloc((void**)&ctx->d_raw, cap));
+        ctx->d_raw_cap = cap;
+    }
+    auto submit_text = [&](size_t k) -> int {
+        const Slice& sl = slices[k];
+        if (k == 0) CUDA_TRY(cudaEventRecord(ctx->ev[0], ctx->s_in));
+        if (use_raw[k]) {
+            uint64_t at = 0;     // offset of the current run inside the slice's raw region (multiple of 16)
+            for (uint32_t m = sl.m0; m < sl.m1;) {
+                uint32_t e = m + 1;
+                uint64_t bytes = lens[m];
+                while (e < sl.m1 && texts[e] == texts[e - 1] + lens[e - 1]) bytes += lens[e++];
+                if (bytes) CUDA_TRY(cudaMemcpyAsync(ctx->d_raw + raw_base[k] + at, texts[m], bytes, cudaMemcpyHostToDevice, ctx->s_in));
+                for (uint32_t j = m; j < e; j++) {
+                    repack[j].chunk_begin = ctx->layout[j].chunk_begin;
+                    repack[j].raw_off = (uint32_t)(at + (uint64_t)(texts[j] - texts[m]));
+                    repack[j].len = (uint32_t)lens[j];
+                }
+                at += (bytes + 15) & ~(uint64_t)15;
+                m = e;
+            }
+        } else {
+            for (uint32_t m = sl.m0; m < sl.m1; m++)
+                if (lens[m])
+                    CUDA_TRY(cudaMemcpyAsync(ctx->d_text + sl.text_off + ctx->layout[m].text_off, texts[m], lens[m], cudaMemcpyHostToDevice, ctx->s_in));
+        }
+        CUDA_TRY(cudaEventRecord(ctx->slice_ev[5 * k], ctx->s_in));
+        if (k + 1 == ns) CUDA_TRY(cudaEventRecord(ctx->ev[1], ctx->s_in));
+        return PTXFE_OK;
+    };
+    for (size_t k = 0; k < ns && k < 2; k++)
+        if ((st = submit_text(k)) != PTXFE_OK) return st;
+    // ---- host result buffers: sized from the text; grown (after the copies in flight have landed) if a slice needs more
+    int rc;
+    if ((rc = grow_pinned(ctx, &ctx->h_results, &ctx->h_results_cap, sizeof(PtxModuleResult) * (size_t)n + 16, 0)) != PTXFE_OK) return rc;
+    if ((rc = grow_pinned(ctx, &ctx->h_words, &ctx->h_words_cap, (size_t)(total * 2) + 4096, 0)) != PTXFE_OK) return rc;
+    size_t words_done = 0, errs_done = 0, lexerrs_done = 0;
+    std::vector<size_t> base_w(ns), base_e(ns), base_l(ns);
+    ptxfe_stats& s = ctx->stats;
+    s.n_tokens = s.n_units = s.n_result_words = s.n_errors = s.n_lex_errors = 0;
+    for (size_t k = 0; k < ns; k++) {
+        const Slice& sl = slices[k];
+        ctx->cur = (int)(k & 1);
+        // this arena held the results of slice k-2: wait until they have left the device
+        if (k >= 2) CUDA_TRY(cudaEventSynchronize(ctx->slice_ev[5 * (k - 2) + 4]));
+        CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ctx->slice_ev[5 * k], 0));
+        if (k + 2 < ns && (rc = submit_text(k + 2)) != PTXFE_OK) return rc;
+        rc = run_pipeline(ctx, ctx->d_text + sl.text_off, ctx->layout.data() + sl.m0, sl.m1 - sl.m0, mode,
+                          ctx->slice_ev[5 * k + 1], nullptr, nullptr, ctx->slice_ev[5 * k + 2],
+                          use_raw[k] ? repack.data() + sl.m0 : nullptr, ctx->d_raw + raw_base[k]);
+        if (rc != PTXFE_OK) {
+            cudaStreamSynchronize(ctx->s_in);
+            cudaStreamSynchronize(ctx->s_out);
+            return rc;
+        }
+        const PtxCounters& c = ctx->counters;
+        size_t nw = c.n_words, ne = c.n_errs, nl = c.n_lexerrs, nm = sl.m1 - sl.m0;
+        if ((words_done + nw) * sizeof(uint32_t) + 16 > ctx->h_words_cap || (errs_done + ne) * sizeof(PtxErrRec) + 16 > ctx->h_errs_cap ||
+            (lexerrs_done + nl) * 8 + 16 > ctx->h_lexerrs_cap) {
+            CUDA_TRY(cudaStreamSynchronize(ctx->s_out));
+            // extrapolate from what the slices so far produced
+            double done_bytes = 0;
+            for (size_t j = 0; j <= k; j++) done_bytes += (double)slices[j].bytes;
+            double scale = done_bytes > 0 ? (double)total / done_bytes * 1.1 : 1.0;
+            if ((rc = grow_pinned(ctx, &ctx->h_words, &ctx->h_words_cap, (size_t)((words_done + nw) * scale) * 4 + 4096, words_done * 4)) != PTXFE_OK) return rc;
+            if ((rc = grow_pinned(ctx, &ctx->h_errs, &ctx->h_errs_cap, (size_t)((errs_done + ne) * scale) * sizeof(PtxErrRec) + 4096, errs_done * sizeof(PtxErrRec))) != PTXFE_OK) return rc;
+            if ((rc = grow_pinned(ctx, &ctx->h_lexerrs, &ctx->h_lexerrs_cap, (size_t)((lexerrs_done + nl) * scale) * 8 + 4096, lexerrs_done * 8)) != PTXFE_OK) return rc;
+        }
+        // the kernels of this slice have finished (run_pipeline waits for them)
+        CUDA_TRY(cudaEventRecord(ctx->slice_ev[5 * k + 3], ctx->s_out));
+        if (nw) CUDA_TRY(cudaMemcpyAsync((uint32_t*)ctx->h_words + words_done, ctx->work.words, nw * 4, cudaMemcpyDeviceToHost, ctx->s_out));
+        if (ne) CUDA_TRY(cudaMemcpyAsync((PtxErrRec*)ctx->h_errs + errs_done, ctx->work.errs, ne * sizeof(PtxErrRec), cudaMemcpyDeviceToHost, ctx->s_out));
+        if (nl) CUDA_TRY(cudaMemcpyAsync((uint32_t*)ctx->h_lexerrs + 2 * lexerrs_done, ctx->work.lexerrs, nl * 8, cudaMemcpyDeviceToHost, ctx->s_out));
+        if (nm) CUDA_TRY(cudaMemcpyAsync((PtxModuleResult*)ctx->h_results + sl.m0, ctx->work.results, nm * sizeof(PtxModuleResult), cudaMemcpyDeviceToHost, ctx->s_out));
+        CUDA_TRY(cudaEventRecord(ctx->slice_ev[5 * k + 4], ctx->s_out));
+        if (words_done + nw > 0xFFFFFFFFull) return PTXFE_ERR_TOO_LARGE;   // module results index words with 32 bits
+        base_w[k] = words_done; base_e[k] = errs_done; base_l[k] = lexerrs_done;
+        words_done += nw; errs_done += ne; lexerrs_done += nl;
+        s.n_tokens += c.n_tokens;
+        s.n_units += c.n_units;
+        s.n_result_words += nw;
+        s.n_errors += ne;
+        s.n_lex_errors += nl;
+    }
+    CUDA_TRY(cudaStreamSynchronize(ctx->s_out));
+    CUDA_TRY(cudaStreamSynchronize(ctx->s_in));
+    // ---- module results index the batch-wide host arrays
+    PtxModuleResult* res = (PtxModuleResult*)ctx->h_results;
+    uint64_t seq = 0;
+    for (size_t k = 0; k < ns; k++)
+        for (uint32_t m = slices[k].m0; m < slices[k].m1; m++) {
+            res[m].word_begin += (uint32_t)base_w[k]; res[m].word_end += (uint32_t)base_w[k];
+            res[m].err_begin += (uint32_t)base_e[k]; res[m].err_end += (uint32_t)base_e[k];
+            res[m].lexerr_begin += (uint32_t)base_l[k]; res[m].lexerr_end += (uint32_t)base_l[k];
+            seq += res[m].sequential;
+        }
+    // ---- statistics: busy time of each of the three streams
+    cudaEventElapsedTime(&s.h2d_ms, ctx->ev[0], ctx->ev[1]);
+    s.kernel_ms = s.d2h_ms = 0;
+    s.lex_ms = s.structure_ms = s.decode_ms = 0;
+    for (size_t k = 0; k < ns; k++) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, ctx->slice_ev[5 * k + 1], ctx->slice_ev[5 * k + 2]);
+        s.kernel_ms += ms;
+        cudaEventElapsedTime(&ms, ctx->slice_ev[5 * k + 3], ctx->slice_ev[5 * k + 4]);
+        s.d2h_ms += ms;
+    }
+    if (getenv("PTXFE_TRACE")) {
+        // device-side timeline of the three streams, milliseconds since the first text copy was submitted
+        for (size_t k = 0; k < ns; k++) {
+            float t[5];
+            for (int j = 0; j < 5; j++) cudaEventElapsedTime(&t[j], ctx->ev[0], ctx->slice_ev[5 * k + j]);
+            fprintf(stderr, "ptxfe slice %zu: text arrived %.2f, kernels %.2f - %.2f, results %.2f - %.2f\n", k, t[0], t[1], t[2], t[3], t[4]);
+        }
+    }
+    s.h2d_bytes = total;
+    s.text_bytes = total;
+    s.n_modules = n;
+    s.d2h_bytes = words_done * 4 + errs_done * sizeof(PtxErrRec) + lexerrs_done * 8 + sizeof(PtxModuleResult) * (size_t)n;
+    s.n_kernel_launches = ctx->launches;
+    s.n_sequential = seq;
+    collect_profile(ctx);
+    ptxfe_batch* b = make_batch(ctx, n);
+    ctx->live = b;
+    *out = b;
+    return PTXFE_OK;
 }
 
 void ptxfe_batch_free(ptxfe_batch* b) {
@@ -725,6 +1081,7 @@ int ptxfe_lex_module(ptxfe_ctx* ctx, const char* text, uint64_t len, uint32_t** 
     w = PtxWork();
     w.text = ctx->d_text;
     w.n_modules = 1;
+    ctx->mcb.assign({0u, (uint32_t)((len + PTX_CHUNK - 1) / PTX_CHUNK)});
     w.n_chunks = ctx->mcb[1];
     w.layout = (PtxModuleLayout*)bk.alloc(sizeof(PtxModuleLayout) * 2);
     w.mod_chunk_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * 3);

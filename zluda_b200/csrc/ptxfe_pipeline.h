@@ -47,12 +47,19 @@ struct PtxSeg3 {
 };
 
 #define PTX_SORT_BUCKETS 4096u
+#define PTX_TMP_STRIDE 48u     // words per unit in the staging table of the first decode pass (192 bytes: sector aligned)
+
+// what a staged decoder hands back to the backend: copy n words of this thread's staging buffer to row `unit`
+struct PtxStaged {
+    uint32_t unit, n;
+};
 
 // token classification bits
 enum { TF_MODULE_FIRST = 1, TF_SCOPE_OPEN = 2, TF_SCOPE_CLOSE = 4, TF_UNIT_START = 8 };
 
 struct PtxCounters {
     uint32_t n_tokens, n_lexerrs, n_units, n_words, n_errs, n_funcs, any_sequential, pad;
+    uint32_t n_flagged, pad2;   // units whose records are written by the second decode pass
 };
 
 PTX_HD inline uint32_t ptx_upper_bound_u32(const uint32_t* a, uint32_t n, uint32_t x) {
@@ -125,7 +132,14 @@ struct SegDepthOp {
 //   template <class T, class Op, class Ld, class St> void scan(const char* name, size_t n, Ld ld, St st, Op op, T identity);
 //        inclusive scan: st(i, op(ld(0), ..., ld(i)))
 //   void sort_by_key(const char* name, size_t n, const uint16_t* key, uint32_t* order);
-//        order = the indices 0..n-1 grouped by key (keys < PTX_SORT_BUCKETS; order inside a group is free)
+//        order = a permutation of 0..n-1 that puts equal keys next to each other, either over the whole range or
+//        inside consecutive segments of the backend's choice (keys < PTX_SORT_BUCKETS; order inside a group is free)
+//   template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f);
+//        PtxStaged r = f(i, stage, stride, cap) for i in [0, n): f may keep up to `cap` words in stage[k * stride];
+//        afterwards the backend copies the first r.n of them to table[r.unit * row_words ...]
+//   void gather_records(const char* name, size_t n_units, const uint32_t* table, uint32_t row_words, const PtxPair* off,
+//                       const uint8_t* flag, uint32_t* words);
+//        for every unit u with flag[u] == 0: copy off[u + 1].a - off[u].a words from table row u to words[off[u].a ...]
 //   void* alloc(size_t bytes); void zero(void* p, size_t bytes);
 //   void download(void* host, const void* dev, size_t bytes);   (synchronises the stream)
 // The pipeline allocates through the backend and never frees: the backend's arena is reset per batch.
@@ -419,9 +433,18 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     });
     bk.sort_by_key("sort_units_by_shape", n_units, ukey, order);
 
-    // C1: decode every unit, counting only
-    bk.pf("decode_count", n_units, [=] PTX_HD(size_t idx) {
+    // C1: decode every unit once.  The record is built in a small per-thread staging buffer (failed alternatives are
+    // rolled back there) and lands in row u of a table; its final place is known only after the sizes are scanned.
+    // Units that report errors (every `call` reserves one), or whose record outgrows the buffer, are only measured
+    // here and written by the second pass (C6), which also has the function table.
+    uint8_t* uflag = (uint8_t*)bk.alloc((size_t)n_units + 16);
+    uint32_t* table = (uint32_t*)bk.alloc(sizeof(uint32_t) * PTX_TMP_STRIDE * ((size_t)n_units + 1));
+    bk.pf("reset_flagged", 1, [=] PTX_HD(size_t) { counters->n_flagged = 0; });
+    bk.pf_staged("decode_units", n_units, table, PTX_TMP_STRIDE, [=] PTX_HD(size_t idx, uint32_t* stage, uint32_t stride, uint32_t cap) -> PtxStaged {
+        PtxStaged ret;
         size_t u = order[idx];
+        ret.unit = (uint32_t)u;
+        ret.n = 0;
         uint32_t start = ustart[u];
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         // modules without units share their begin with the next one: take the last module that starts at or before u
@@ -432,9 +455,13 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
             usize[u + 1] = z;
             uend[u] = 0;
             ustatus[u] = US_OK;
-            return;
+            uflag[u] = 0;
+            return ret;
         }
         PtxSink sink;
+        sink.stage = stage;
+        sink.stage_stride = stride;
+        sink.stage_cap = cap < PTX_TMP_STRIDE ? cap : PTX_TMP_STRIDE;
         PtxResolver res;
         res.module = m;
         PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
@@ -442,10 +469,21 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         PtxUnitResult r = ptx_decode_unit(d, start, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
         uend[u] = r.end;
         ustatus[u] = (uint8_t)r.status;
+        bool flagged = sink.peak > sink.stage_cap || sink.ne > 0;
         PtxPair sz;
-        sz.a = sink.peak;
+        sz.a = flagged ? sink.peak : sink.nw;
         sz.b = sink.ne;
         usize[u + 1] = sz;
+        uflag[u] = flagged ? 1 : 0;
+        if (flagged) {
+#ifdef __CUDA_ARCH__
+            atomicAdd(&counters->n_flagged, 1u);
+#else
+            counters->n_flagged++;
+#endif
+        } else {
+            ret.n = sink.nw;
+        }
         if (r.status == US_OK && r.kind == U_FUNC) {
 #ifdef __CUDA_ARCH__
             uint32_t slot = atomicAdd(&counters->n_funcs, 1u);
@@ -463,6 +501,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
             e.pad = 0;
             fn_entries[slot] = e;
         }
+        return ret;
     });
     // C2: do consecutive units meet, and does every module return to depth 0?
     bk.pf("chain_check", n_units, [=] PTX_HD(size_t u) {
@@ -494,41 +533,47 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         PtxPair z;
         z.a = z.b = 0;
         usize[u + 1] = (u == mub[m]) ? mod_seq[m] : z;
+        uflag[u] = (u == mub[m]) ? 1 : 2;    // the module's first unit stands for the whole module in C6; the others write nothing
     });
     bk.template scan<PtxPair>("scan_unit_sizes", (size_t)n_units + 1, [=] PTX_HD(size_t i) { return usize[i]; },
                               [=] PTX_HD(size_t i, PtxPair v) { usize[i] = v; }, PairAddOp(), PtxPair{0, 0});
     bk.pf("set_output_totals", 1, [=] PTX_HD(size_t) {
         counters->n_words = n_units ? usize[n_units].a : 0;
         counters->n_errs = n_units ? usize[n_units].b : 0;
+        if (counters->any_sequential) counters->n_flagged += 1;
     });
     bk.download(&host_counters, counters, sizeof(PtxCounters));
     const uint32_t n_words = host_counters.n_words, n_errs = host_counters.n_errs, n_funcs = host_counters.n_funcs;
     uint32_t* words = w.words = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_words + 4));
     PtxErrRec* errs = w.errs = (PtxErrRec*)bk.alloc(sizeof(PtxErrRec) * ((size_t)n_errs + 1));
-    // C5: function table for `call`
-    uint32_t mask = 1;
-    while (mask < 2 * n_funcs + 2) mask <<= 1;
-    mask -= 1;
-    uint32_t* slots = w.fn_slots = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)mask + 1));
-    w.fn_mask = mask;
-    bk.pf("fn_table_clear", (size_t)mask + 1, [=] PTX_HD(size_t i) { slots[i] = PTX_ABSENT; });
-    bk.pf("fn_table_insert", n_funcs, [=] PTX_HD(size_t i) {
-        const PtxFnEntry e = fn_entries[i];
-        uint32_t h = ptx_name_hash(text, e.name_off, e.name_len, e.module) & mask;
-        for (;;) {
+    // C5: records of the units that were staged go to their final place
+    bk.gather_records("gather_records", n_units, table, PTX_TMP_STRIDE, usize, uflag, words);
+    if (host_counters.n_flagged) {
+        // function table for `call`
+        uint32_t mask = 1;
+        while (mask < 2 * n_funcs + 2) mask <<= 1;
+        mask -= 1;
+        uint32_t* slots = w.fn_slots = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)mask + 1));
+        w.fn_mask = mask;
+        bk.pf("fn_table_clear", (size_t)mask + 1, [=] PTX_HD(size_t i) { slots[i] = PTX_ABSENT; });
+        bk.pf("fn_table_insert", n_funcs, [=] PTX_HD(size_t i) {
+            const PtxFnEntry e = fn_entries[i];
+            uint32_t h = ptx_name_hash(text, e.name_off, e.name_len, e.module) & mask;
+            for (;;) {
 #ifdef __CUDA_ARCH__
-            uint32_t old = atomicCAS(&slots[h], PTX_ABSENT, (uint32_t)i);
+                uint32_t old = atomicCAS(&slots[h], PTX_ABSENT, (uint32_t)i);
 #else
-            uint32_t old = slots[h];
-            if (old == PTX_ABSENT) slots[h] = (uint32_t)i;
+                uint32_t old = slots[h];
+                if (old == PTX_ABSENT) slots[h] = (uint32_t)i;
 #endif
-            if (old == PTX_ABSENT) break;
-            h = (h + 1) & mask;
-        }
-    });
-    // C6: decode again, writing
-    bk.pf("decode_emit", n_units, [=] PTX_HD(size_t idx) {
+                if (old == PTX_ABSENT) break;
+                h = (h + 1) & mask;
+            }
+        });
+        // C6: decode the flagged units again, writing in place
+    bk.pf("decode_emit_flagged", n_units, [=] PTX_HD(size_t idx) {
         size_t u = order[idx];
+        if (uflag[u] != 1) return;
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         PtxSink sink;
         sink.words = words + usize[u].a;
@@ -559,6 +604,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         if (sink.peak != usize[u + 1].a - usize[u].a || sink.ne != usize[u + 1].b - usize[u].b) counters->pad = (uint32_t)u + 1;
         sink.pad_to(usize[u + 1].a - usize[u].a);
     });
+    }
     bk.pf("module_results_final", n_modules, [=] PTX_HD(size_t m) {
         PtxModuleResult r = results[m];
         r.unit_begin = mub[m];
