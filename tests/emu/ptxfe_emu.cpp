@@ -40,10 +40,12 @@ struct HostBackend {
         pf(name, n, [&](size_t c) { f(c, rd); });
     }
     template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f) {
-        const uint32_t cap = 47;
+        const uint32_t cap = 40, win_cap = 5;   // a small window, so that decoders cross its end
         std::vector<uint32_t> stage(cap);
+        std::vector<PtxTokenWord> win(win_cap);
+        PtxScratch sc{stage.data(), 1u, cap, win.data(), 1u, win_cap};
         pf(name, n, [&](size_t i) {
-            PtxStaged r = f(i, stage.data(), 1u, cap);
+            PtxStaged r = f(i, sc);
             for (uint32_t k = 0; k < r.n; k++) table[(size_t)r.unit * row_words + k] = stage[k];
         });
     }

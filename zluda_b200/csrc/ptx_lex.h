@@ -35,6 +35,11 @@ struct PtxToken {
     uint16_t kind;
 };
 
+// a token as two words (start, len | kind << 16): the form kept in the decoders' token window
+struct alignas(8) PtxTokenWord {
+    uint32_t x, y;
+};
+
 PTX_HD inline int cx_step(int s, unsigned c) {
     switch (s) {
     case CX_CODE: return c == '/' ? CX_SLASH : c == '"' ? CX_STR : CX_CODE;

@@ -20,7 +20,7 @@ PTX_HD PTX_NOINLINE inline PtxUnitResult ptx_decode_unit(PtxDecoder& d, uint32_t
     r.kind = 0;
     r.name_tok = r.n_rets = r.n_inputs = 0;
     d.pos = start;
-    d.unit_off = start < d.te ? d.tok[start].start : 0;
+    d.unit_off = start < d.te ? d.tk(start).start : 0;
     if (module_first) {
         if (d.header()) r.kind = U_HEADER;
         else r.status = US_FAIL;
@@ -64,7 +64,7 @@ PTX_HD PTX_NOINLINE inline PtxUnitResult ptx_decode_unit(PtxDecoder& d, uint32_t
 // Returns US_OK, or US_PANIC where the reference would panic.
 PTX_HD PTX_NOINLINE inline int ptx_decode_module_sequential(PtxDecoder& d, uint32_t tb, uint32_t base) {
     d.pos = tb;
-    d.unit_off = tb < d.te ? d.tok[tb].start : 0;
+    d.unit_off = tb < d.te ? d.tk(tb).start : 0;
     uint32_t m;
     if (!d.header()) {
         d.push(E_PARSER, 0, 0, 0);
@@ -75,7 +75,7 @@ PTX_HD PTX_NOINLINE inline int ptx_decode_module_sequential(PtxDecoder& d, uint3
     for (;;) {
         uint32_t save = d.pos;
         uint32_t m0 = d.out.mark();
-        if (d.pos < d.te) d.unit_off = d.tok[d.pos].start;
+        if (d.pos < d.te) d.unit_off = d.tk(d.pos).start;
         bool has_body = false;
         uint32_t name_tok, n_rets, n_inputs;
         int k = d.directive(d.resolver.last_func, &has_body, &name_tok, &n_rets, &n_inputs);

@@ -94,16 +94,20 @@ __global__ void __launch_bounds__(256) lex_tile_kernel(uint32_t n_chunks, const 
 // their rows of the staging table with coalesced stores.  Word k of thread t lives at stage[k * STAGE_STRIDE + t]:
 // threads of a warp decode units of the same shape in lockstep, so they write the same k at the same time (32
 // consecutive banks), and the copy loop reads one thread's words with a stride that is odd (no bank conflicts).
-#define STAGE_CAP 47u
 #define STAGE_STRIDE 257u
+#define STAGE_CAP 40u
+#define WIN_CAP 12u
+#define STAGED_SMEM_BYTES (STAGE_CAP * STAGE_STRIDE * 4u + WIN_CAP * STAGE_STRIDE * 8u)
 template <class F>
 __global__ void __launch_bounds__(256) staged_kernel(size_t n, uint32_t* table, uint32_t row_words, F f) {
-    __shared__ uint32_t stage[STAGE_CAP * STAGE_STRIDE];
+    extern __shared__ __align__(16) unsigned char staged_smem[];
+    PtxTokenWord* win = (PtxTokenWord*)staged_smem;                                    // [WIN_CAP][STAGE_STRIDE]
+    uint32_t* stage = (uint32_t*)(staged_smem + WIN_CAP * STAGE_STRIDE * 8u);          // [STAGE_CAP][STAGE_STRIDE]
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     PtxStaged r;
     r.unit = 0;
     r.n = 0;
-    if (i < n) r = f(i, stage + threadIdx.x, STAGE_STRIDE, STAGE_CAP);
+    if (i < n) r = f(i, PtxScratch{stage + threadIdx.x, STAGE_STRIDE, STAGE_CAP, win + threadIdx.x, STAGE_STRIDE, WIN_CAP});
     __syncwarp();
     const uint32_t lane = threadIdx.x & 31u, warp_base = threadIdx.x & ~31u;
     for (uint32_t l = 0; l < 32; l++) {
@@ -439,7 +443,9 @@ struct CudaBackend {
     template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f) {
         if (ctx->failed || n == 0) return;
         prof_begin(name);
-        staged_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>(n, table, row_words, f);
+        // more shared memory than a kernel gets by default: opt in (cheap, so done at every launch)
+        cudaFuncSetAttribute(staged_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)STAGED_SMEM_BYTES);
+        staged_kernel<<<(unsigned)((n + 255) / 256), 256, STAGED_SMEM_BYTES, ctx->stream>>>(n, table, row_words, f);
         prof_end();
         ctx->launches++;
     }

@@ -49,6 +49,15 @@ struct PtxSeg3 {
 #define PTX_SORT_BUCKETS 4096u
 #define PTX_TMP_STRIDE 48u     // words per unit in the staging table of the first decode pass (192 bytes: sector aligned)
 
+// fast per-thread memory the backend lends to a staged decoder: room for `stage_cap` record words (word k at
+// stage[k * stage_stride]) and for `win_cap` tokens (token k at win[k * win_stride])
+struct PtxScratch {
+    uint32_t* stage;
+    uint32_t stage_stride, stage_cap;
+    PtxTokenWord* win;
+    uint32_t win_stride, win_cap;
+};
+
 // what a staged decoder hands back to the backend: copy n words of this thread's staging buffer to row `unit`
 struct PtxStaged {
     uint32_t unit, n;
@@ -135,8 +144,8 @@ struct SegDepthOp {
 //        order = a permutation of 0..n-1 that puts equal keys next to each other, either over the whole range or
 //        inside consecutive segments of the backend's choice (keys < PTX_SORT_BUCKETS; order inside a group is free)
 //   template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f);
-//        PtxStaged r = f(i, stage, stride, cap) for i in [0, n): f may keep up to `cap` words in stage[k * stride];
-//        afterwards the backend copies the first r.n of them to table[r.unit * row_words ...]
+//        PtxStaged r = f(i, scratch) for i in [0, n), scratch a PtxScratch of the backend's;
+//        afterwards the backend copies the first r.n staged words to table[r.unit * row_words ...]
 //   void gather_records(const char* name, size_t n_units, const uint32_t* table, uint32_t row_words, const PtxPair* off,
 //                       const uint8_t* flag, uint32_t* words);
 //        for every unit u with flag[u] == 0: copy off[u + 1].a - off[u].a words from table row u to words[off[u].a ...]
@@ -440,7 +449,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     uint8_t* uflag = (uint8_t*)bk.alloc((size_t)n_units + 16);
     uint32_t* table = (uint32_t*)bk.alloc(sizeof(uint32_t) * PTX_TMP_STRIDE * ((size_t)n_units + 1));
     bk.pf("reset_flagged", 1, [=] PTX_HD(size_t) { counters->n_flagged = 0; });
-    bk.pf_staged("decode_units", n_units, table, PTX_TMP_STRIDE, [=] PTX_HD(size_t idx, uint32_t* stage, uint32_t stride, uint32_t cap) -> PtxStaged {
+    bk.pf_staged("decode_units", n_units, table, PTX_TMP_STRIDE, [=] PTX_HD(size_t idx, const PtxScratch& sc) -> PtxStaged {
         PtxStaged ret;
         size_t u = order[idx];
         ret.unit = (uint32_t)u;
@@ -459,12 +468,24 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
             return ret;
         }
         PtxSink sink;
-        sink.stage = stage;
-        sink.stage_stride = stride;
-        sink.stage_cap = cap < PTX_TMP_STRIDE ? cap : PTX_TMP_STRIDE;
+        sink.stage = sc.stage;
+        sink.stage_stride = sc.stage_stride;
+        sink.stage_cap = sc.stage_cap < PTX_TMP_STRIDE ? sc.stage_cap : PTX_TMP_STRIDE;
         PtxResolver res;
         res.module = m;
         PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
+        // the unit's first tokens go to the fast window: the decoder looks at every token many times
+        {
+            uint32_t avail = mtb[m + 1] - start;
+            uint32_t nwin = avail < sc.win_cap ? avail : sc.win_cap;
+            const PtxTokenWord* src = (const PtxTokenWord*)(tokens + start);
+            for (uint32_t k = 0; k < sc.win_cap; k++)
+                if (k < nwin) sc.win[k * sc.win_stride] = src[k];
+            d.win = sc.win;
+            d.win_base = start;
+            d.win_n = nwin;
+            d.win_stride = sc.win_stride;
+        }
         uint32_t dp = udepth[u];
         PtxUnitResult r = ptx_decode_unit(d, start, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
         uend[u] = r.end;
