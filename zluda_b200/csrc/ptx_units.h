@@ -20,6 +20,9 @@ PTX_HD PTX_NOINLINE inline PtxUnitResult ptx_decode_unit(PtxDecoder& d, uint32_t
     r.kind = 0;
     r.name_tok = r.n_rets = r.n_inputs = 0;
     d.pos = start;
+    d.unit_tok0 = start;
+    d.max_seen = start;
+    d.pos_is_unit_mode = true;
     d.unit_off = start < d.te ? d.tk(start).start : 0;
     if (module_first) {
         if (d.header()) r.kind = U_HEADER;

@@ -58,6 +58,66 @@ struct PtxScratch {
     uint32_t win_stride, win_cap;
 };
 
+// ---- unit classes and record templates
+// Two units are in the same class when they have the same token kinds, the same text in every token whose text the
+// decoder reads (numbers, dot-identifiers, strings, `%envreg` names) and the same depth class.  The decoder then takes
+// the same path for both, and their records differ only in words copied from tokens (offsets, lengths).  One
+// representative per class is decoded with tagged output (PtxSink::tags); every other unit is compared with its
+// representative token by token and its record is instantiated from the template.
+#define PTX_TMPL_WORDS 40u            // longest record that gets a template
+#define PTX_MAX_CLASSES (1u << 18)    // templates per batch slice; later classes are decoded the ordinary way
+#define PTX_MAX_CLASS_TOKENS 250u
+enum { PTX_UNIT_STAGED = 0, PTX_UNIT_FLAGGED = 1, PTX_UNIT_NOTHING = 2, PTX_UNIT_TEMPLATED = 3, PTX_UNIT_UNDECIDED = 0xFF };
+struct PtxTemplateInfo {
+    uint32_t n_words, n_tokens, ok, depth1;
+};
+PTX_HD inline bool ptx_text_matters(uint16_t k) {
+    return k == T_DECIMAL || k == T_HEX || k == T_F32HEX || k == T_F64HEX || k == T_F64 || k == T_DOTIDENT || k == T_STRING;
+}
+// 64-bit class key of the tokens [start, end); 0 = this unit gets no template
+PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens, uint32_t start, uint32_t end, uint32_t depth, bool module_first) {
+    if (depth == 0 || module_first || end - start > PTX_MAX_CLASS_TOKENS || end <= start) return 0;
+    uint32_t h1 = 2166136261u ^ (depth == 1 ? 1u : 0u), h2 = 0x811C9DC5u + (end - start);
+    for (uint32_t i = start; i < end; i++) {
+        const PtxToken t = tokens[i];
+        h1 = (h1 ^ t.kind) * 16777619u;
+        h2 = (h2 + t.kind) * 0x9E3779B1u;
+        h2 ^= h2 >> 15;
+        if (ptx_text_matters(t.kind)) {
+            if (t.len == 0xFFFF) return 0;
+            h2 = (h2 ^ t.len) * 0x85EBCA6Bu;
+            for (uint32_t j = 0; j < t.len; j++) {
+                uint32_t c = text[t.start + j];
+                h1 = (h1 ^ c) * 16777619u;
+                h2 = (h2 + c) * 0x9E3779B1u;
+            }
+        } else if (t.kind == T_IDENT) {
+            if (t.len == 0xFFFF) return 0;
+            if ((t.len == 8 || t.len == 9) && ptx_envreg_number(text + t.start, t.len)) h1 = (h1 ^ 0x1234u) * 16777619u;
+        }
+    }
+    uint64_t k = ((uint64_t)h1 << 32) | h2;
+    return k ? k : 1;
+}
+// exact check that unit A (tokens [a, a + n)) is in the class of unit B (tokens [b, b + n))
+PTX_HD inline bool ptx_same_class(const uint8_t* text, const PtxToken* tokens, uint32_t a, uint32_t b, uint32_t n) {
+    for (uint32_t i = 0; i < n; i++) {
+        const PtxToken x = tokens[a + i], y = tokens[b + i];
+        if (x.kind != y.kind) return false;
+        if (ptx_text_matters(x.kind)) {
+            if (x.len != y.len || x.len == 0xFFFF) return false;
+            for (uint32_t j = 0; j < x.len; j++)
+                if (text[x.start + j] != text[y.start + j]) return false;
+        } else if (x.kind == T_IDENT) {
+            if (x.len == 0xFFFF || y.len == 0xFFFF) return false;
+            bool ex = (x.len == 8 || x.len == 9) && ptx_envreg_number(text + x.start, x.len);
+            bool ey = (y.len == 8 || y.len == 9) && ptx_envreg_number(text + y.start, y.len);
+            if (ex != ey) return false;
+        }
+    }
+    return true;
+}
+
 // what a staged decoder hands back to the backend: copy n words of this thread's staging buffer to row `unit`
 struct PtxStaged {
     uint32_t unit, n;
@@ -68,7 +128,8 @@ enum { TF_MODULE_FIRST = 1, TF_SCOPE_OPEN = 2, TF_SCOPE_CLOSE = 4, TF_UNIT_START
 
 struct PtxCounters {
     uint32_t n_tokens, n_lexerrs, n_units, n_words, n_errs, n_funcs, any_sequential, pad;
-    uint32_t n_flagged, pad2;   // units whose records are written by the second decode pass
+    uint32_t n_flagged;         // units whose records are written by the second decode pass
+    uint32_t n_classes;         // distinct unit classes (see the template steps of the decode stage)
 };
 
 PTX_HD inline uint32_t ptx_upper_bound_u32(const uint32_t* a, uint32_t n, uint32_t x) {
@@ -430,10 +491,13 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     // offsets computed in unit order, so the order of processing does not show in the output.
     uint16_t* ukey = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_units + 2));
     uint32_t* order = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    uint64_t* ckey_of = (uint64_t*)bk.alloc(sizeof(uint64_t) * ((size_t)n_units + 1));
     bk.pf("unit_shape_key", n_units, [=] PTX_HD(size_t u) {
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         uint32_t start = ustart[u];
         uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        uint32_t dp = udepth[u];
+        ckey_of[u] = mod_skip[m] ? 0 : ptx_class_key(text, tokens, start, end, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
         if (end > start + 20) end = start + 20;
         uint32_t h = 2166136261u ^ (udepth[u] >> 31) ^ ((udepth[u] & 0x7FFFFFFFu) ? 2u : 0u);
         for (uint32_t i = start; i < end; i++) h = (h ^ tokens[i].kind) * 16777619u;
@@ -442,18 +506,116 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     });
     bk.sort_by_key("sort_units_by_shape", n_units, ukey, order);
 
+    // T1: class table (open addressing on the 64-bit key); the thread that inserts a key makes its unit the
+    // representative of the class
+    uint32_t cmask = 1024;
+    while (cmask < n_units / 2) cmask <<= 1;
+    cmask -= 1;
+    unsigned long long* ckeys = (unsigned long long*)bk.alloc(sizeof(unsigned long long) * ((size_t)cmask + 1));
+    uint32_t* slot_tmpl = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)cmask + 1));
+    uint32_t* uclass = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    uint32_t* utmpl = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    uint32_t* rep_unit = (uint32_t*)bk.alloc(sizeof(uint32_t) * PTX_MAX_CLASSES);
+    uint32_t* tmpl_words = (uint32_t*)bk.alloc(sizeof(uint32_t) * PTX_TMPL_WORDS * PTX_MAX_CLASSES);
+    uint16_t* tmpl_tags = (uint16_t*)bk.alloc(sizeof(uint16_t) * PTX_TMPL_WORDS * PTX_MAX_CLASSES);
+    PtxTemplateInfo* tmpl_info = (PtxTemplateInfo*)bk.alloc(sizeof(PtxTemplateInfo) * PTX_MAX_CLASSES);
+    uint8_t* uflag = (uint8_t*)bk.alloc((size_t)n_units + 16);
+    bk.zero(ckeys, sizeof(unsigned long long) * ((size_t)cmask + 1));
+    bk.pf("reset_flagged", 1, [=] PTX_HD(size_t) { counters->n_flagged = 0; counters->n_classes = 0; });
+    bk.pf("class_insert", n_units, [=] PTX_HD(size_t u) {
+        uclass[u] = PTX_ABSENT;
+        unsigned long long key = ckey_of[u];
+        if (!key) return;
+        uint32_t h = (uint32_t)(key ^ (key >> 29)) & cmask;
+        for (int probe = 0; probe < 64; probe++) {
+#ifdef __CUDA_ARCH__
+            unsigned long long old = atomicCAS(&ckeys[h], 0ull, key);
+#else
+            unsigned long long old = ckeys[h];
+            if (old == 0) ckeys[h] = key;
+#endif
+            if (old == 0) {
+#ifdef __CUDA_ARCH__
+                uint32_t id = atomicAdd(&counters->n_classes, 1u);
+#else
+                uint32_t id = counters->n_classes++;
+#endif
+                if (id < PTX_MAX_CLASSES) {
+                    rep_unit[id] = (uint32_t)u;
+                    slot_tmpl[h] = id;
+                } else {
+                    slot_tmpl[h] = PTX_ABSENT;
+                }
+                uclass[u] = h;
+                return;
+            }
+            if (old == key) { uclass[u] = h; return; }
+            h = (h + 1) & cmask;
+        }
+    });
+    // T2: decode the representatives with tagged output
+    bk.pf("decode_representatives", PTX_MAX_CLASSES, [=] PTX_HD(size_t id) {
+        if (id >= counters->n_classes) return;
+        uint32_t u = rep_unit[id];
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, u) - 1;
+        uint32_t start = ustart[u];
+        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        PtxSink sink;
+        sink.words = tmpl_words + (size_t)id * PTX_TMPL_WORDS;
+        sink.tags = tmpl_tags + (size_t)id * PTX_TMPL_WORDS;
+        sink.words_cap = PTX_TMPL_WORDS;
+        PtxResolver res;
+        res.module = m;
+        PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
+        uint32_t dp = udepth[u];
+        PtxUnitResult r = ptx_decode_unit(d, start, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
+        PtxTemplateInfo ti;
+        ti.n_words = sink.nw;
+        ti.n_tokens = end - start;
+        ti.depth1 = (dp & 0x7FFFFFFFu) == 1 ? 1u : 0u;
+        ti.ok = (r.status == US_OK && sink.ne == 0 && sink.peak <= PTX_TMPL_WORDS && !sink.poison && r.kind != U_FUNC && r.end == end &&
+                 d.max_seen < end) ? 1u : 0u;
+        tmpl_info[id] = ti;
+    });
+    // T3: every unit of a class with a usable template is checked against the representative and takes its size
+    bk.pf("apply_templates", n_units, [=] PTX_HD(size_t u) {
+        uflag[u] = PTX_UNIT_UNDECIDED;
+        utmpl[u] = PTX_ABSENT;
+        uint32_t slot = uclass[u];
+        if (slot == PTX_ABSENT) return;
+        uint32_t id = slot_tmpl[slot];
+        if (id == PTX_ABSENT) return;
+        const PtxTemplateInfo ti = tmpl_info[id];
+        if (!ti.ok) return;
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        uint32_t start = ustart[u];
+        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        uint32_t dp = udepth[u];
+        if (end - start != ti.n_tokens || ((dp & 0x7FFFFFFFu) == 1 ? 1u : 0u) != ti.depth1) return;
+        uint32_t r = rep_unit[id];
+        if (r != u && !ptx_same_class(text, tokens, start, ustart[r], ti.n_tokens)) return;
+        PtxPair sz;
+        sz.a = ti.n_words;
+        sz.b = 0;
+        usize[u + 1] = sz;
+        if (u == 0) { PtxPair z; z.a = z.b = 0; usize[0] = z; }
+        uend[u] = end;
+        ustatus[u] = US_OK;
+        uflag[u] = PTX_UNIT_TEMPLATED;
+        utmpl[u] = id;
+    });
+
     // C1: decode every unit once.  The record is built in a small per-thread staging buffer (failed alternatives are
     // rolled back there) and lands in row u of a table; its final place is known only after the sizes are scanned.
     // Units that report errors (every `call` reserves one), or whose record outgrows the buffer, are only measured
     // here and written by the second pass (C6), which also has the function table.
-    uint8_t* uflag = (uint8_t*)bk.alloc((size_t)n_units + 16);
     uint32_t* table = (uint32_t*)bk.alloc(sizeof(uint32_t) * PTX_TMP_STRIDE * ((size_t)n_units + 1));
-    bk.pf("reset_flagged", 1, [=] PTX_HD(size_t) { counters->n_flagged = 0; });
     bk.pf_staged("decode_units", n_units, table, PTX_TMP_STRIDE, [=] PTX_HD(size_t idx, const PtxScratch& sc) -> PtxStaged {
         PtxStaged ret;
         size_t u = order[idx];
         ret.unit = (uint32_t)u;
         ret.n = 0;
+        if (uflag[u] == PTX_UNIT_TEMPLATED) return ret;
         uint32_t start = ustart[u];
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         // modules without units share their begin with the next one: take the last module that starts at or before u
@@ -569,6 +731,24 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     PtxErrRec* errs = w.errs = (PtxErrRec*)bk.alloc(sizeof(PtxErrRec) * ((size_t)n_errs + 1));
     // C5: records of the units that were staged go to their final place
     bk.gather_records("gather_records", n_units, table, PTX_TMP_STRIDE, usize, uflag, words);
+    bk.pf("instantiate_templates", n_units, [=] PTX_HD(size_t u) {
+        if (uflag[u] != PTX_UNIT_TEMPLATED) return;
+        uint32_t id = utmpl[u];
+        const uint32_t n = tmpl_info[id].n_words;
+        const uint32_t* tw = tmpl_words + (size_t)id * PTX_TMPL_WORDS;
+        const uint16_t* tg = tmpl_tags + (size_t)id * PTX_TMPL_WORDS;
+        const PtxToken* ut = tokens + ustart[u];
+        uint32_t* out = words + usize[u].a;
+        for (uint32_t i = 0; i < n; i++) {
+            uint32_t x = tw[i], g = tg[i];
+            if (g) {
+                const PtxToken t = ut[g & 0xFFu];
+                uint32_t type = g >> 8;
+                x = type == PTX_TAG_START ? t.start : type == PTX_TAG_LEN ? (uint32_t)t.len : ((x & 0xFFu) | ((uint32_t)t.len << 8));
+            }
+            out[i] = x;
+        }
+    });
     if (host_counters.n_flagged) {
         // function table for `call`
         uint32_t mask = 1;
