@@ -49,11 +49,9 @@ struct HostBackend {
             for (uint32_t k = 0; k < r.n; k++) table[(size_t)r.unit * row_words + k] = stage[k];
         });
     }
-    void gather_records(const char* name, size_t n_units, const uint32_t* table, uint32_t row_words, const PtxPair* off, const uint8_t* flag,
-                        uint32_t* words) {
-        pf(name, n_units, [&](size_t u) {
-            if (flag[u]) return;
-            for (uint32_t k = 0, n = off[u + 1].a - off[u].a; k < n; k++) words[off[u].a + k] = table[u * row_words + k];
+    template <class F> void pf_segments(const char* name, size_t n, const PtxPair* off, F f) {
+        pf(name, n, [&](size_t s) {
+            for (uint32_t i = 0, cnt = off[s + 1].a - off[s].a; i < cnt; i++) f(s, i, off[s].a + i);
         });
     }
     void sort_by_key(const char*, size_t n, const uint16_t* key, uint32_t* order) {

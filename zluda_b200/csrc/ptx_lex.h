@@ -250,29 +250,41 @@ PTX_HD PTX_NOINLINE inline uint16_t lx_one(const uint8_t* s, uint64_t p, uint64_
 // Sink concept: void token(uint64_t start, uint32_t len, uint16_t kind); void error(uint64_t start, uint32_t len);
 struct LexCountSink {
     uint32_t n_tokens = 0, n_errors = 0;
-    PTX_HD void token(uint64_t, uint32_t, uint16_t) { n_tokens++; }
-    PTX_HD void error(uint64_t, uint32_t) { n_errors++; }
+    PTX_HD void token(uint32_t, uint32_t, uint16_t, uint32_t) { n_tokens++; }
+    PTX_HD void error(uint32_t, uint32_t) { n_errors++; }
 };
-struct LexWriteSink {
-    PtxToken* tokens;      // already offset to this chunk's first slot
-    uint32_t* errors;      // pairs (start, len), already offset
-    uint32_t n_tokens = 0, n_errors = 0;
-    PTX_HD void token(uint64_t start, uint32_t len, uint16_t kind) {
-        PtxToken t;
-        t.start = (uint32_t)start;
-        t.len = len >= 0xFFFFu ? (uint16_t)0xFFFF : (uint16_t)len;
-        t.kind = kind;
-        tokens[n_tokens++] = t;
-    }
-    PTX_HD void error(uint64_t start, uint32_t len) {
-        errors[2 * n_errors] = (uint32_t)start;
+// writes lexer errors only (second pass, run only when the first found some)
+struct LexErrorSink {
+    uint32_t* errors;      // pairs (start, len), already offset to this chunk's first error
+    uint32_t n_errors = 0;
+    PTX_HD void token(uint32_t, uint32_t, uint16_t, uint32_t) {}
+    PTX_HD void error(uint32_t start, uint32_t len) {
+        errors[2 * n_errors] = start;
         errors[2 * n_errors + 1] = len;
         n_errors++;
     }
 };
+// Token slots: every chunk owns PTX_CHUNK slots (a token is at least one byte long), so one pass can write the
+// tokens before their final positions are known.  Keyword candidates also leave their spelling's hash.
+struct LexSlotSink {
+    PtxToken* slots;       // this chunk's row
+    uint32_t* hashes;      // this chunk's row
+    const uint8_t* text;
+    uint32_t n_tokens = 0, n_errors = 0;
+    PTX_HD void token(uint32_t start, uint32_t len, uint16_t kind, uint32_t h) {
+        PtxToken t;
+        t.start = start;
+        t.len = len >= 0xFFFFu ? (uint16_t)0xFFFF : (uint16_t)len;
+        t.kind = kind;
+        slots[n_tokens] = t;
+        if (kind == T_IDENT || kind == T_DOTIDENT) hashes[n_tokens] = h;
+        n_tokens++;
+    }
+    PTX_HD void error(uint32_t, uint32_t) { n_errors++; }
+};
 
 // Text readers: the lockstep lexer gets bytes and table entries through one of these.  This one reads global memory;
-// the CUDA backend has another that serves a shared-memory tile of the text and a fused copy of the tables.
+// the CUDA backend has another that serves a shared-memory tile of the text and a shared-memory copy of the table.
 struct PtxGlobalReader {
     const uint8_t* s;
     uint32_t n;      // readable bytes
@@ -283,9 +295,8 @@ struct PtxGlobalReader {
         for (uint32_t k = 0; p + k < n; k++) w |= (uint32_t)s[p + k] << (8 * k);
         return w;
     }
-    // transition-table entry (next state | action << 8) and the kind of a single-character token
-    PTX_HD unsigned lookup(int st, unsigned c) const { return ptx_lex_trans[st * LX_STRIDE + ptx_lex_class[c]]; }
-    PTX_HD uint16_t single(unsigned c, unsigned) const { return ptx_lex_single[c]; }
+    // table entry of (state, byte): see ptx_lex_fused in gen/ptx_lex_tables.h
+    PTX_HD uint32_t lookup(int st, unsigned c) const { return ptx_lex_fused[st * 256 + c]; }
 };
 
 PTX_HD inline bool lx_state_open(int st) {
@@ -293,8 +304,12 @@ PTX_HD inline bool lx_state_open(int st) {
     return st != LS_S0 && st != LS_LINE && st != LS_BLOCK && st != LS_STAR && st != LS_SLASH_IN;
 }
 
+#define LX_HASH_INIT 2166136261u
+
 // Lex the tokens that START in [cs, ce) of a module occupying [ms, me).  `cx` is the comment/string context at cs.
-// One byte per loop iteration, driven by ptx_lex_trans: all threads of a warp run the same loop body.
+// One byte per loop iteration, driven by ptx_lex_fused; the common cases (advance, begin a token, emit a token) are
+// flag bits handled without branching on an action code, so the threads of a warp stay together.  The running
+// FNV-1a hash of the current token is handed to the sink with every token (the keyword step probes with it).
 // `g` is the text in global memory (used by the rare helpers), `tx` the reader for the byte loop.
 // Offsets are 32-bit: a batch holds less than 4 GiB of text.
 template <class TX, class Sink>
@@ -302,7 +317,7 @@ PTX_HD inline void lx_chunk(const TX& tx, const uint8_t* g, uint32_t ms, uint32_
     if (ce > me) ce = me;
     if (cs >= me) return;
     uint32_t p = cs, tstart = cs ? cs - 1 : 0, acc_pos = 0;
-    uint32_t acc_kind = T_ERROR, cnt = 0, need = 0;
+    uint32_t acc_kind = T_ERROR, cnt = 0, need = 0, h = LX_HASH_INIT;
     int st;
     switch (cx) {
     case CX_SLASH: st = LS_SLASH_IN; break;
@@ -321,80 +336,97 @@ PTX_HD inline void lx_chunk(const TX& tx, const uint8_t* g, uint32_t ms, uint32_
         break;
     }
     while (p <= me && (p < ce || (lx_state_open(st) && tstart >= cs))) {
-        unsigned c = p < me ? tx[p] : ' ';
-        unsigned e = tx.lookup(st, c);
-        int prev = st;
-        st = (int)(e & 0xFF);
-        switch (e >> 8) {
-        case LA_NONE: p++; break;
-        case LA_BEGIN: tstart = p; p++; break;
-        case LA_SINGLE:
-            if (p >= cs) out.token(p, 1, tx.single(c, e));
-            st = LS_S0;
-            p++;
-            break;
-        case LA_END:
-            if (tstart >= cs) out.token(tstart, (p - tstart), ptx_lex_end_kind[prev]);
-            break;
-        case LA_END_INCL:
-            if (tstart >= cs) out.token(tstart, (p + 1 - tstart), ptx_lex_end_kind[prev]);
-            p++;
-            break;
-        case LA_ACCEPT: acc_pos = p; acc_kind = ptx_lex_end_kind[prev]; p++; break;
-        case LA_BACKUP:
-            if (prev != LS_SLASH_IN) {
-                if (tstart >= cs) out.token(tstart, (acc_pos - tstart), (uint16_t)acc_kind);
-                p = acc_pos;
-            }
-            break;
-        case LA_ERR_HERE:
-            if (p >= cs) out.error(p, 1);
-            p++;
-            break;
-        case LA_ERR_TOKEN:
-        case LA_ERR_SLASH:
-            if (tstart >= cs) out.error(tstart, 1);
-            break;
-        case LA_COUNT:
-            if (++cnt == need) {
-                if (tstart >= cs) out.token(tstart, (p + 1 - tstart), need == 8 ? T_F32HEX : T_F64HEX);
-                st = LS_S0;
-            }
-            p++;
-            break;
-        case LA_BEGIN_HF32: acc_pos = p; acc_kind = T_DECIMAL; cnt = 0; need = 8; p++; break;
-        case LA_BEGIN_HF64: acc_pos = p; acc_kind = T_DECIMAL; cnt = 0; need = 16; p++; break;
-        case LA_COLON_CHECK: {
-            uint16_t k = T_DOTIDENT;
-            uint32_t l = 0;
-            if (p + 1 < me && tx[p + 1] == ':') l = lx_colon_literal(g, tstart, p, me, &k);
-            if (l) {
-                if (tstart >= cs) out.token(tstart, l, k);
-                p = tstart + l;
-            } else if (tstart >= cs) {
-                out.token(tstart, (p - tstart), T_DOTIDENT);
-            }
-            break;
+        const unsigned c = p < me ? tx[p] : ' ';
+        const uint32_t e = tx.lookup(st, c);
+        const int prev = st;
+        st = (int)(e & 0xFFu);
+        if (e & (LF_BEGIN << 8)) { tstart = p; h = LX_HASH_INIT; }
+        if (e & (LF_EMIT << 8)) {
+            const uint32_t aux = e >> 12;
+            const uint32_t s0 = (aux & LF_SELF) ? p : tstart;
+            if (s0 >= cs) out.token(s0, p + (aux & LF_INCL) - s0, (uint16_t)(e >> 16), h);
         }
-        case LA_REWIND_DOT:
-            if (tstart >= cs) out.token(tstart, 1, T_DOT);
-            p = tstart + 1;
-            break;
-        default:   // LA_DIM: ".1d" ".2d" ".3d" are literals; an upper-case D ends the F64 in front of it
-            if (c == 'd') {
-                unsigned digit = tx[tstart + 1];
-                if (tstart >= cs) out.token(tstart, 3, digit == '1' ? T_MOD_1d : digit == '2' ? T_MOD_2d : T_MOD_3d);
+        if (e & (LF_RARE << 8)) {
+            switch ((e >> 12) & 0xFu) {
+            case LA_ACCEPT: acc_pos = p; acc_kind = ptx_lex_end_kind[prev]; p++; break;
+            case LA_BACKUP:
+                if (prev != LS_SLASH_IN) {
+                    if (tstart >= cs) out.token(tstart, acc_pos - tstart, (uint16_t)acc_kind, 0);
+                    p = acc_pos;
+                }
+                break;
+            case LA_ERR_HERE:
+                if (p >= cs) out.error(p, 1);
                 p++;
-            } else if (tstart >= cs) {
-                out.token(tstart, (p - tstart), T_F64);
+                break;
+            case LA_ERR_TOKEN:
+            case LA_ERR_SLASH:
+                if (tstart >= cs) out.error(tstart, 1);
+                break;
+            case LA_COUNT:
+                if (++cnt == need) {
+                    if (tstart >= cs) out.token(tstart, p + 1 - tstart, need == 8 ? T_F32HEX : T_F64HEX, 0);
+                    st = LS_S0;
+                }
+                p++;
+                break;
+            case LA_BEGIN_HF32: acc_pos = p; acc_kind = T_DECIMAL; cnt = 0; need = 8; p++; break;
+            case LA_BEGIN_HF64: acc_pos = p; acc_kind = T_DECIMAL; cnt = 0; need = 16; p++; break;
+            case LA_COLON_CHECK: {
+                uint16_t k = T_DOTIDENT;
+                uint32_t l = 0;
+                if (p + 1 < me && tx[p + 1] == ':') l = lx_colon_literal(g, tstart, p, me, &k);
+                if (l) {
+                    // a literal with "::" inside: its kind is final (hash 0 = nothing to look up)
+                    if (tstart >= cs) out.token(tstart, l, k, 0);
+                    p = tstart + l;
+                } else if (tstart >= cs) {
+                    out.token(tstart, p - tstart, T_DOTIDENT, h);
+                }
+                break;
             }
-            break;
+            case LA_REWIND_DOT:
+                if (tstart >= cs) out.token(tstart, 1, T_DOT, 0);
+                p = tstart + 1;
+                break;
+            default:   // LA_DIM: ".1d" ".2d" ".3d" are literals; an upper-case D ends the F64 in front of it
+                if (c == 'd') {
+                    unsigned digit = tx[tstart + 1];
+                    if (tstart >= cs) out.token(tstart, 3, digit == '1' ? T_MOD_1d : digit == '2' ? T_MOD_2d : T_MOD_3d, 0);
+                    p++;
+                } else if (tstart >= cs) {
+                    out.token(tstart, p - tstart, T_F64, 0);
+                }
+                break;
+            }
         }
+        h = (h ^ c) * PTX_KW_MULT;
+        p += (e >> 8) & LF_ADV;
     }
     if (p > me || (p == me && ce == me)) {
         // this thread saw the end of the module
-        if (st == LS_STR && tstart >= cs) out.error(tstart, (me - tstart));
+        if (st == LS_STR && tstart >= cs) out.error(tstart, me - tstart);
         if ((st == LS_BLOCK || st == LS_STAR) && ce == me) out.error(me, 0);
+    }
+}
+
+// A token's kind once its spelling is known.  `h` is the FNV-1a hash of its bytes as lx_chunk computes it.
+PTX_HD inline bool lx_keyword_candidate(const uint8_t* g, uint32_t start, uint16_t kind) {
+    return kind == T_DOTIDENT || (kind == T_IDENT && lx_alpha(g[start]));
+}
+PTX_HD inline uint16_t lx_keyword_hashed(const uint8_t* s, uint32_t len, uint32_t h) {
+    if (len > PTX_KW_MAXLEN) return T_ERROR;
+    h = (h ^ (h >> 15)) & (PTX_KW_SIZE - 1);
+    for (;;) {
+        PtxKwEntry e = ptx_kw_table[h];
+        if (e.kind == 0xFFFF) return T_ERROR;
+        if (e.len == len) {
+            bool same = true;
+            for (uint32_t i = 0; i < len; i++)
+                if ((uint8_t)ptx_kw_pool[e.off + i] != s[i]) { same = false; break; }
+            if (same) return e.kind;
+        }
+        h = (h + 1) & (PTX_KW_SIZE - 1);
     }
 }
 

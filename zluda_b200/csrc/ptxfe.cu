@@ -40,13 +40,12 @@ __global__ void __launch_bounds__(256) pf_kernel(size_t n, F f) {
 // ---- per-chunk lexer steps over a shared-memory tile of the text
 // One block = 256 chunks = 32 KiB of text, staged with coalesced 16-byte loads.  Thread t then walks chunk t byte by
 // byte; rows are padded to 33 words so that 32 threads reading the same column of 32 rows hit 32 different banks.
-// The token automaton's two tables (byte class, transition) are fused into one [state][byte] table in shared memory,
-// with the token kind of single-character tokens stored in the entry's state byte.
+// The token automaton's [state][byte] table (ptx_lex_fused) is copied to shared memory as well.
 #define LEX_TILE_CHUNKS 256u
 #define LEX_ROW_WORDS 33u
 struct PtxTileReader {
     const uint32_t* tile;      // [LEX_TILE_CHUNKS][LEX_ROW_WORDS]
-    const uint16_t* fused;     // [LS_COUNT][256]
+    const uint32_t* fused;     // [LS_COUNT][256], copy of ptx_lex_fused
     const uint8_t* g;          // the whole text, for bytes outside the tile
     uint32_t base;             // text offset of the tile
     __device__ unsigned operator[](uint32_t p) const {
@@ -58,14 +57,16 @@ struct PtxTileReader {
         uint32_t o = p - base;
         return tile[(o >> 7) * LEX_ROW_WORDS + ((o & 127u) >> 2)];
     }
-    __device__ unsigned lookup(int st, unsigned c) const { return fused[st * 256 + c]; }
-    __device__ uint16_t single(unsigned, unsigned e) const { return (uint16_t)(e & 0xFFu); }
+    __device__ uint32_t lookup(int st, unsigned c) const { return fused[st * 256 + c]; }
 };
 
+#define LEX_TILE_BYTES (LEX_TILE_CHUNKS * LEX_ROW_WORDS * 4u)
+#define LEX_TABLE_BYTES (LS_COUNT * 256u * 4u)
 template <bool TABLES, class F>
 __global__ void __launch_bounds__(256) lex_tile_kernel(uint32_t n_chunks, const uint8_t* text, F f) {
-    __shared__ uint32_t tile[LEX_TILE_CHUNKS * LEX_ROW_WORDS];
-    __shared__ uint16_t fused[TABLES ? LS_COUNT * 256 : 1];
+    extern __shared__ __align__(16) uint32_t lex_smem[];
+    uint32_t* tile = lex_smem;                                       // [LEX_TILE_CHUNKS][LEX_ROW_WORDS]
+    uint32_t* fused = lex_smem + LEX_TILE_CHUNKS * LEX_ROW_WORDS;    // [LS_COUNT][256] when TABLES
     const uint32_t c0 = blockIdx.x * LEX_TILE_CHUNKS;
     const uint4* src = (const uint4*)text + (size_t)c0 * (PTX_CHUNK / 16);
 #pragma unroll
@@ -78,12 +79,7 @@ __global__ void __launch_bounds__(256) lex_tile_kernel(uint32_t n_chunks, const 
         d[0] = v.x; d[1] = v.y; d[2] = v.z; d[3] = v.w;
     }
     if (TABLES) {
-        for (uint32_t i = threadIdx.x; i < LS_COUNT * 256; i += 256) {
-            uint32_t st = i >> 8, c = i & 255u;
-            unsigned e = ptx_lex_trans[st * LX_STRIDE + ptx_lex_class[c]];
-            if ((e >> 8) == LA_SINGLE) e = (LA_SINGLE << 8) | ptx_lex_single[c];
-            fused[i] = (uint16_t)e;
-        }
+        for (uint32_t i = threadIdx.x; i < LS_COUNT * 256; i += 256) fused[i] = ptx_lex_fused[i];
     }
     __syncthreads();
     uint32_t c = c0 + threadIdx.x;
@@ -118,16 +114,14 @@ __global__ void __launch_bounds__(256) staged_kernel(size_t n, uint32_t* table, 
     }
 }
 
-// ---- records from the staging table to their final places: one block per 256 consecutive units, whose records are
-// contiguous in the output; every thread copies output words, finding the unit of each by binary search
-__global__ void __launch_bounds__(256) gather_records_kernel(uint32_t n_units, const uint32_t* table, uint32_t row_words, const PtxPair* off,
-                                                             const uint8_t* flag, uint32_t* words) {
+// ---- one thread per item of a segmented range: a block takes 256 consecutive segments, whose items are contiguous,
+// and every thread finds the segment of its item by binary search over the block's offsets in shared memory
+template <class F>
+__global__ void __launch_bounds__(256) segments_kernel(uint32_t n_units, const PtxPair* off, F f) {
     __shared__ uint32_t so[257];
-    __shared__ uint8_t sf[256];
     const uint32_t u0 = blockIdx.x * 256;
     const uint32_t nu = n_units - u0 < 256u ? n_units - u0 : 256u;
     for (uint32_t k = threadIdx.x; k <= nu; k += 256) so[k] = off[u0 + k].a;
-    if (threadIdx.x < nu) sf[threadIdx.x] = flag[u0 + threadIdx.x];
     __syncthreads();
     const uint32_t first = so[0], total = so[nu] - so[0];
     for (uint32_t j = threadIdx.x; j < total; j += 256) {
@@ -137,7 +131,7 @@ __global__ void __launch_bounds__(256) gather_records_kernel(uint32_t n_units, c
             uint32_t mid = (lo + hi) >> 1;
             if (so[mid] <= o) lo = mid; else hi = mid;
         }
-        if (!sf[lo]) words[o] = table[(size_t)(u0 + lo) * row_words + (o - so[lo])];
+        f((size_t)(u0 + lo), o - so[lo], o);
     }
 }
 
@@ -281,7 +275,7 @@ struct LexCapSink {
     PtxToken* tokens;
     const uint8_t* text;
     uint64_t next, capacity;
-    __device__ void token(uint64_t start, uint32_t len, uint16_t kind) {
+    __device__ void token(uint32_t start, uint32_t len, uint16_t kind, uint32_t) {
         if (next < capacity) {
             PtxToken t;
             t.start = (uint32_t)start;
@@ -291,7 +285,7 @@ struct LexCapSink {
         }
         next++;
     }
-    __device__ void error(uint64_t, uint32_t) {}
+    __device__ void error(uint32_t, uint32_t) {}
 };
 
 template <class T> struct ArrayLoad {
@@ -449,11 +443,10 @@ struct CudaBackend {
         prof_end();
         ctx->launches++;
     }
-    void gather_records(const char* name, size_t n_units, const uint32_t* table, uint32_t row_words, const PtxPair* off, const uint8_t* flag,
-                        uint32_t* words) {
-        if (ctx->failed || n_units == 0) return;
+    template <class F> void pf_segments(const char* name, size_t n, const PtxPair* off, F f) {
+        if (ctx->failed || n == 0) return;
         prof_begin(name);
-        gather_records_kernel<<<(unsigned)((n_units + 255) / 256), 256, 0, ctx->stream>>>((uint32_t)n_units, table, row_words, off, flag, words);
+        segments_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>((uint32_t)n, off, f);
         prof_end();
         ctx->launches++;
     }
@@ -462,10 +455,13 @@ struct CudaBackend {
         if (ctx->failed || n == 0) return;
         unsigned blocks = (unsigned)((n + LEX_TILE_CHUNKS - 1) / LEX_TILE_CHUNKS);
         prof_begin(name);
-        if constexpr (std::is_same<F, PtxLexVectorsStep>::value)
-            lex_tile_kernel<false><<<blocks, 256, 0, ctx->stream>>>((uint32_t)n, text, f);
-        else
-            lex_tile_kernel<true><<<blocks, 256, 0, ctx->stream>>>((uint32_t)n, text, f);
+        if constexpr (std::is_same<F, PtxLexVectorsStep>::value) {
+            lex_tile_kernel<false><<<blocks, 256, LEX_TILE_BYTES, ctx->stream>>>((uint32_t)n, text, f);
+        } else {
+            // tile + table need more shared memory than a kernel gets by default
+            cudaFuncSetAttribute(lex_tile_kernel<true, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(LEX_TILE_BYTES + LEX_TABLE_BYTES));
+            lex_tile_kernel<true><<<blocks, 256, LEX_TILE_BYTES + LEX_TABLE_BYTES, ctx->stream>>>((uint32_t)n, text, f);
+        }
         prof_end();
         ctx->launches++;
     }

@@ -207,9 +207,8 @@ struct SegDepthOp {
 //   template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f);
 //        PtxStaged r = f(i, scratch) for i in [0, n), scratch a PtxScratch of the backend's;
 //        afterwards the backend copies the first r.n staged words to table[r.unit * row_words ...]
-//   void gather_records(const char* name, size_t n_units, const uint32_t* table, uint32_t row_words, const PtxPair* off,
-//                       const uint8_t* flag, uint32_t* words);
-//        for every unit u with flag[u] == 0: copy off[u + 1].a - off[u].a words from table row u to words[off[u].a ...]
+//   template <class F> void pf_segments(const char* name, size_t n, const PtxPair* off, F f);
+//        segment s owns the items [off[s].a, off[s + 1].a): f(s, i, off[s].a + i) for every s < n and every item i of s
 //   void* alloc(size_t bytes); void zero(void* p, size_t bytes);
 //   void download(void* host, const void* dev, size_t bytes);   (synchronises the stream)
 // The pipeline allocates through the backend and never frees: the backend's arena is reset per batch.
@@ -240,17 +239,22 @@ struct PtxLexVectorsStep {
         vec[c] = first ? cx_restart(v) : v;
     }
 };
-struct PtxLexCountStep {
+struct PtxLexTokensStep {
     PtxLexChunkInfo info;
     const uint8_t* text;
     const uint32_t* vec;
     PtxPair* cnt;
+    PtxToken* slots;
+    uint32_t* hashes;
     template <class R> PTX_HD void operator()(size_t c, const R& rd) const {
         uint32_t ms, me, cs = (uint32_t)c * PTX_CHUNK;
         bool first;
         info.locate(c, ms, me, first);
         int state = first ? CX_CODE : (int)(vec[c - 1] & 7u);
-        LexCountSink sink;
+        LexSlotSink sink;
+        sink.slots = slots + c * PTX_CHUNK;
+        sink.hashes = hashes + c * PTX_CHUNK;
+        sink.text = text;
         lx_chunk(rd, text, ms, me, cs, cs + PTX_CHUNK, state, sink);
         PtxPair p;
         p.a = sink.n_tokens;
@@ -259,20 +263,19 @@ struct PtxLexCountStep {
         if (c == 0) { PtxPair z; z.a = z.b = 0; cnt[0] = z; }
     }
 };
-struct PtxLexEmitStep {
+struct PtxLexErrorsStep {
     PtxLexChunkInfo info;
     const uint8_t* text;
     const uint32_t* vec;
     const PtxPair* cnt;
-    PtxToken* tokens;
     uint32_t* lexerrs;
     template <class R> PTX_HD void operator()(size_t c, const R& rd) const {
+        if (cnt[c + 1].b == cnt[c].b) return;     // no error starts in this chunk
         uint32_t ms, me, cs = (uint32_t)c * PTX_CHUNK;
         bool first;
         info.locate(c, ms, me, first);
         int state = first ? CX_CODE : (int)(vec[c - 1] & 7u);
-        LexWriteSink sink;
-        sink.tokens = tokens + cnt[c].a;
+        LexErrorSink sink;
         sink.errors = lexerrs + 2 * (size_t)cnt[c].b;
         lx_chunk(rd, text, ms, me, cs, cs + PTX_CHUNK, state, sink);
     }
@@ -296,8 +299,10 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     // A2: inclusive scan with composition; chunk c starts in state (prefix[c-1])[CODE]
     bk.template scan<uint32_t>("scan_context", n_chunks, [=] PTX_HD(size_t i) { return vec[i]; }, [=] PTX_HD(size_t i, uint32_t v) { vec[i] = v; },
                                ComposeOp(), CX_IDENTITY);
-    // A3: count the tokens that start in every chunk
-    bk.pf_text("lex_count_tokens", n_chunks, text, PtxLexCountStep{info, text, vec, cnt});
+    // A3: the token pass.  Every chunk writes its tokens into its own row of PTX_CHUNK slots
+    PtxToken* slots = (PtxToken*)bk.alloc(sizeof(PtxToken) * PTX_CHUNK * ((size_t)n_chunks + 1));
+    uint32_t* hashes = (uint32_t*)bk.alloc(sizeof(uint32_t) * PTX_CHUNK * ((size_t)n_chunks + 1));
+    bk.pf_text("lex_tokens", n_chunks, text, PtxLexTokensStep{info, text, vec, cnt, slots, hashes});
     // A4: exclusive offsets (cnt[c] = tokens before chunk c; cnt[n_chunks] = total)
     bk.template scan<PtxPair>("scan_token_counts", n_chunks + 1, [=] PTX_HD(size_t i) { return cnt[i]; }, [=] PTX_HD(size_t i, PtxPair v) { cnt[i] = v; },
                               PairAddOp(), PtxPair{0, 0});
@@ -309,14 +314,18 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     const uint32_t n_tokens = host_counters.n_tokens, n_lexerrs = host_counters.n_lexerrs;
     PtxToken* tokens = w.tokens = (PtxToken*)bk.alloc(sizeof(PtxToken) * (size_t)(n_tokens + 1));
     uint32_t* lexerrs = w.lexerrs = (uint32_t*)bk.alloc(sizeof(uint32_t) * 2 * (size_t)(n_lexerrs + 1));
-    // A5: emit
-    bk.pf_text("lex_emit_tokens", n_chunks, text, PtxLexEmitStep{info, text, vec, cnt, tokens, lexerrs});
-    // A6: identifiers that spell an opcode, modifier or directive word get that token kind
-    bk.pf("lex_classify_keywords", n_tokens, [=] PTX_HD(size_t i) {
-        PtxToken t = tokens[i];
-        uint16_t k = lx_classify(text, t.start, t.len, t.kind);
-        if (k != t.kind) tokens[i].kind = k;
+    // A5: tokens to their final places, one thread per token; identifiers that spell an opcode, modifier or directive
+    // word get that kind on the way (table probe with the hash from the token pass, then a string compare)
+    bk.pf_segments("lex_compact_classify", n_chunks, cnt, [=] PTX_HD(size_t c, uint32_t i, uint32_t j) {
+        PtxToken t = slots[c * PTX_CHUNK + i];
+        if (lx_keyword_candidate(text, t.start, t.kind)) {
+            uint16_t k = lx_keyword_hashed(text + t.start, t.len, hashes[c * PTX_CHUNK + i]);
+            if (k != T_ERROR) t.kind = k;
+        }
+        tokens[j] = t;
     });
+    // A6: lexer errors are rare: a second walk, only when there are any, and only over the chunks that have one
+    if (n_lexerrs) bk.pf_text("lex_emit_errors", n_chunks, text, PtxLexErrorsStep{info, text, vec, cnt, lexerrs});
     uint32_t* mtb = w.mod_tok_begin;
     bk.pf("module_token_ranges", n_modules + 1, [=] PTX_HD(size_t m) {
         uint32_t c = mcb[m];   // mod_chunk_begin[n_modules] = n_chunks
@@ -529,7 +538,9 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         uint32_t h = (uint32_t)(key ^ (key >> 29)) & cmask;
         for (int probe = 0; probe < 64; probe++) {
 #ifdef __CUDA_ARCH__
-            unsigned long long old = atomicCAS(&ckeys[h], 0ull, key);
+            // most units find their class already there: look before competing for the slot
+            unsigned long long old = *(volatile unsigned long long*)&ckeys[h];
+            if (old == 0) old = atomicCAS(&ckeys[h], 0ull, key);
 #else
             unsigned long long old = ckeys[h];
             if (old == 0) ckeys[h] = key;
@@ -730,24 +741,23 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     uint32_t* words = w.words = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_words + 4));
     PtxErrRec* errs = w.errs = (PtxErrRec*)bk.alloc(sizeof(PtxErrRec) * ((size_t)n_errs + 1));
     // C5: records of the units that were staged go to their final place
-    bk.gather_records("gather_records", n_units, table, PTX_TMP_STRIDE, usize, uflag, words);
-    bk.pf("instantiate_templates", n_units, [=] PTX_HD(size_t u) {
-        if (uflag[u] != PTX_UNIT_TEMPLATED) return;
-        uint32_t id = utmpl[u];
-        const uint32_t n = tmpl_info[id].n_words;
-        const uint32_t* tw = tmpl_words + (size_t)id * PTX_TMPL_WORDS;
-        const uint16_t* tg = tmpl_tags + (size_t)id * PTX_TMPL_WORDS;
-        const PtxToken* ut = tokens + ustart[u];
-        uint32_t* out = words + usize[u].a;
-        for (uint32_t i = 0; i < n; i++) {
-            uint32_t x = tw[i], g = tg[i];
-            if (g) {
-                const PtxToken t = ut[g & 0xFFu];
-                uint32_t type = g >> 8;
-                x = type == PTX_TAG_START ? t.start : type == PTX_TAG_LEN ? (uint32_t)t.len : ((x & 0xFFu) | ((uint32_t)t.len << 8));
-            }
-            out[i] = x;
+    // one thread per output word (the backend maps words to units): staged records come from their table row,
+    // templated ones are instantiated from the class template and the unit's own tokens
+    bk.pf_segments("emit_records", n_units, usize, [=] PTX_HD(size_t u, uint32_t i, uint32_t j) {
+        uint8_t fl = uflag[u];
+        if (fl == PTX_UNIT_STAGED) {
+            words[j] = table[u * PTX_TMP_STRIDE + i];
+            return;
         }
+        if (fl != PTX_UNIT_TEMPLATED) return;
+        size_t at = (size_t)utmpl[u] * PTX_TMPL_WORDS + i;
+        uint32_t x = tmpl_words[at], g = tmpl_tags[at];
+        if (g) {
+            const PtxToken t = tokens[ustart[u] + (g & 0xFFu)];
+            uint32_t type = g >> 8;
+            x = type == PTX_TAG_START ? t.start : type == PTX_TAG_LEN ? (uint32_t)t.len : ((x & 0xFFu) | ((uint32_t)t.len << 8));
+        }
+        words[j] = x;
     });
     if (host_counters.n_flagged) {
         // function table for `call`
