@@ -124,7 +124,6 @@ struct PtxStaged {
 };
 
 // token classification bits
-enum { TF_MODULE_FIRST = 1, TF_SCOPE_OPEN = 2, TF_SCOPE_CLOSE = 4, TF_UNIT_START = 8 };
 
 struct PtxCounters {
     uint32_t n_tokens, n_lexerrs, n_units, n_words, n_errs, n_funcs, any_sequential, pad;
@@ -154,8 +153,8 @@ struct PtxWork {
     PtxToken* tokens = nullptr;            // [n_tokens]
     uint32_t* lexerrs = nullptr;           // [2 * n_lexerrs]
     uint32_t* mod_tok_begin = nullptr;     // [n_modules + 1]
-    uint8_t* tflags = nullptr;             // [n_tokens]
-    PtxDepth* depth = nullptr;             // [n_tokens] inclusive segmented scan of scope/paren deltas
+    uint8_t* tfirst = nullptr;             // [n_tokens] 1 = first token of a module
+    int32_t* mod_final_scope = nullptr;    // [n_modules] scope depth behind the module's last token
     uint32_t* unit_of_tok = nullptr;       // [n_tokens + 1] exclusive scan of unit-start flags
     uint32_t* unit_start = nullptr;        // [n_units + 1]
     uint32_t* unit_depth = nullptr;        // [n_units]  scope depth in front of the unit | module-first << 31
@@ -355,101 +354,95 @@ PTX_HD inline bool ptx_is_directive_start(uint16_t k) {
            k == T_MOD_global || k == T_MOD_const || k == T_MOD_shared || k == T_DOT_FILE || k == T_DOT_SECTION;
 }
 
+// scope delta of token i: +1 for a '{' that opens a scope, -1 for a '}' that closes one, 0 otherwise (also for the
+// braces of vector operands, initialisers and .section bodies, told apart by two tokens of left context)
+PTX_HD inline int ptx_brace_class(const PtxToken* tokens, const uint8_t* tfirst, size_t i) {
+    uint16_t k = tokens[i].kind;
+    if (k != T_LBRACE && k != T_RBRACE) return 0;
+    bool first = tfirst[i] != 0;
+    uint16_t prev = first ? (uint16_t)0xFFFE : tokens[i - 1].kind;
+    if (k == T_LBRACE) {
+        bool section = false;
+        if (!first && i >= 2 && !tfirst[i - 1]) section = tokens[i - 2].kind == T_DOT_SECTION;
+        return (!ptx_opens_operand(prev) && !section) ? 1 : 0;
+    }
+    return (prev == T_SEMI || prev == T_COLON || prev == T_LBRACE || prev == T_RBRACE) ? -1 : 0;
+}
+
 template <class BK>
 inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, uint32_t mode) {
     const uint32_t n_tokens = host_counters.n_tokens, n_modules = w.n_modules;
     const PtxToken* tokens = w.tokens;
     const uint32_t* mtb = w.mod_tok_begin;
     const PtxModuleResult* results = w.results;
-    uint8_t* tflags = w.tflags = (uint8_t*)bk.alloc((size_t)n_tokens + 16);
-    PtxDepth* depth = w.depth = (PtxDepth*)bk.alloc(sizeof(PtxDepth) * ((size_t)n_tokens + 1));
+    uint8_t* tfirst = w.tfirst = (uint8_t*)bk.alloc((size_t)n_tokens + 16);
+    // per token: 0 = no unit starts here; else 1 + scope depth in front of it (clamped), bit 15 = first token of a module
+    uint16_t* sd16 = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_tokens + 2));
     uint32_t* uot = w.unit_of_tok = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_tokens + 2));
+    int32_t* mod_final_scope = w.mod_final_scope = (int32_t*)bk.alloc(sizeof(int32_t) * (n_modules + 1));
     w.mod_unit_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 2));
     PtxCounters* counters = w.counters;
     uint32_t* mod_skip = w.mod_skip = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 1));
-    bk.zero(tflags, (size_t)n_tokens + 16);
+    bk.zero(tfirst, (size_t)n_tokens + 16);
+    bk.zero(mod_final_scope, sizeof(int32_t) * (n_modules + 1));
     // B0: mark the first token of every module.  A module with a lex error is not parsed unless only its errors
     // are wanted (lib.rs:392-411 vs 447-449, 487-489)
     bk.pf("mark_module_first", n_modules, [=] PTX_HD(size_t m) {
-        if (mtb[m] < mtb[m + 1]) tflags[mtb[m]] = TF_MODULE_FIRST;
+        if (mtb[m] < mtb[m + 1]) tfirst[mtb[m]] = 1;
         bool lexerr = results[m].lexerr_end > results[m].lexerr_begin;
         mod_skip[m] = (mtb[m] == mtb[m + 1] || (lexerr && mode != 2)) ? 1u : 0u;
     });
-    // B1: classify braces from their left neighbours
-    bk.pf("classify_braces", n_tokens, [=] PTX_HD(size_t i) {
-        uint16_t k = tokens[i].kind;
-        uint8_t f = tflags[i];
-        bool first = (f & TF_MODULE_FIRST) != 0;
-        uint16_t prev = first ? (uint16_t)0xFFFE : tokens[i - 1].kind;
-        if (k == T_LBRACE) {
-            bool section = false;
-            if (!first && i >= 2 && !(tflags[i - 1] & TF_MODULE_FIRST)) section = tokens[i - 2].kind == T_DOT_SECTION;
-            if (!ptx_opens_operand(prev) && !section) f |= TF_SCOPE_OPEN;
-        } else if (k == T_RBRACE) {
-            if (prev == T_SEMI || prev == T_COLON || prev == T_LBRACE || prev == T_RBRACE) f |= TF_SCOPE_CLOSE;
-        }
-        tflags[i] = f;
-    });
-    // B2: scope and paren depth, restarting at every module (inclusive)
+    // B1: one segmented scan of (scope, paren) depth, restarting at every module.  Nothing per token is kept of it:
+    // as soon as the depth behind token i is known, the scan decides whether a unit starts at token i + 1 and
+    // leaves two bytes for it; the depth behind a module's last token goes to mod_final_scope.
     bk.template scan<PtxSeg3>(
         "scan_depth", n_tokens,
         [=] PTX_HD(size_t i) {
             PtxSeg3 v;
-            uint8_t f = tflags[i];
             uint16_t k = tokens[i].kind;
-            v.scope = (f & TF_SCOPE_OPEN) ? 1 : (f & TF_SCOPE_CLOSE) ? -1 : 0;
+            v.scope = ptx_brace_class(tokens, tfirst, i);
             v.paren = k == T_LPAREN ? 1 : k == T_RPAREN ? -1 : 0;
-            v.flag = (f & TF_MODULE_FIRST) ? 1 : 0;
+            v.flag = tfirst[i] ? 1 : 0;
             return v;
         },
         [=] PTX_HD(size_t i, PtxSeg3 v) {
-            PtxDepth d;
-            d.scope = v.scope;
-            d.paren = v.paren;
-            depth[i] = d;
-        },
-        SegDepthOp(), PtxSeg3{0, 0, 0});
-    // B3: speculate unit starts
-    bk.pf("speculate_unit_starts", n_tokens, [=] PTX_HD(size_t i) {
-        uint8_t f = tflags[i];
-        bool first = (f & TF_MODULE_FIRST) != 0;
-        bool start = first;
-        if (!first) {
-            int32_t sd = depth[i - 1].scope, pd = depth[i - 1].paren;
-            uint16_t k = tokens[i].kind;
-            uint8_t pf_ = tflags[i - 1];
-            uint16_t prev = tokens[i - 1].kind;
+            if (i == 0) sd16[0] = (uint16_t)(1u | 0x8000u);     // token 0 is the first token of a module
+            size_t j = i + 1;
+            bool last_of_module = j == n_tokens || tfirst[j] != 0;
+            if (last_of_module) mod_final_scope[ptx_upper_bound_u32(mtb, n_modules, (uint32_t)i) - 1] = v.scope;
+            if (j == n_tokens) return;
+            if (tfirst[j]) { sd16[j] = (uint16_t)(1u | 0x8000u); return; }
+            int32_t sd = v.scope, pd = v.paren;
+            uint16_t k = tokens[j].kind, prev = tokens[i].kind;
+            bool start;
             if (sd <= 0) {
                 // top level: a directive keyword outside parentheses that does not continue a run of linking keywords
+                // (the token after a function's closing brace or after a directive's terminator is not a start by
+                // itself: a well-formed module continues with a directive keyword there)
                 start = sd == 0 && pd == 0 && ptx_is_directive_start(k) &&
                         !(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak);
-                // the token after a function's closing brace or after a directive's terminator is not a start by
-                // itself: a well-formed module continues with a directive keyword there
             } else {
-                start = (f & (TF_SCOPE_OPEN | TF_SCOPE_CLOSE)) != 0 || (pf_ & (TF_SCOPE_OPEN | TF_SCOPE_CLOSE)) != 0 ||
-                        prev == T_SEMI || prev == T_COLON;
+                start = prev == T_SEMI || prev == T_COLON || ptx_brace_class(tokens, tfirst, j) != 0 || ptx_brace_class(tokens, tfirst, i) != 0;
             }
-        }
-        if (start) tflags[i] = f | TF_UNIT_START;
-        uot[i + 1] = start ? 1u : 0u;
-        if (i == 0) uot[0] = 0;
-    });
-    bk.template scan<uint32_t>("scan_unit_index", (size_t)n_tokens + 1, [=] PTX_HD(size_t i) { return uot[i]; },
+            uint32_t clamped = sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
+            sd16[j] = start ? (uint16_t)(1u + clamped) : (uint16_t)0;
+        },
+        SegDepthOp(), PtxSeg3{0, 0, 0});
+    // B2: unit index of every token (exclusive count of unit starts)
+    bk.template scan<uint32_t>("scan_unit_index", (size_t)n_tokens + 1, [=] PTX_HD(size_t i) { return (i && sd16[i - 1]) ? 1u : 0u; },
                                [=] PTX_HD(size_t i, uint32_t v) { uot[i] = v; }, AddOp(), 0u);
     bk.pf("set_unit_total", 1, [=] PTX_HD(size_t) { counters->n_units = n_tokens ? uot[n_tokens] : 0; });
     bk.download(&host_counters, counters, sizeof(PtxCounters));
     const uint32_t n_units = host_counters.n_units;
     uint32_t* ustart = w.unit_start = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 2));
     uint32_t* udepth = w.unit_depth = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
-    // B5: compact
+    // B3: compact
     bk.pf("compact_unit_starts", n_tokens, [=] PTX_HD(size_t i) {
-        uint8_t f = tflags[i];
-        if (!(f & TF_UNIT_START)) return;
+        uint32_t code = sd16[i];
+        if (!code) return;
         uint32_t u = uot[i];
         ustart[u] = (uint32_t)i;
-        bool first = (f & TF_MODULE_FIRST) != 0;
-        int32_t sd = first ? 0 : depth[i - 1].scope;
-        udepth[u] = (uint32_t)(sd < 0 ? 0 : sd) | (first ? 0x80000000u : 0u);
+        udepth[u] = ((code & 0x7FFFu) - 1u) | ((code & 0x8000u) ? 0x80000000u : 0u);
     });
     uint32_t* mub = w.mod_unit_begin;
     bk.pf("module_unit_ranges", n_modules + 1, [=] PTX_HD(size_t m) { mub[m] = n_tokens ? uot[mtb[m]] : 0; });
@@ -466,7 +459,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     const uint32_t* mub = w.mod_unit_begin;
     const uint32_t* ustart = w.unit_start;
     const uint32_t* udepth = w.unit_depth;
-    const PtxDepth* depth = w.depth;
+    const int32_t* mod_final_scope = w.mod_final_scope;
     const uint32_t* mod_skip = w.mod_skip;
     PtxModuleResult* results = w.results;
     PtxCounters* counters = w.counters;
@@ -703,7 +696,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         if (mod_skip[m]) return;
         uint32_t next = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
         bool ok = ustatus[u] == US_OK && uend[u] == next;
-        if (u + 1 == mub[m + 1]) ok = ok && depth[mtb[m + 1] - 1].scope == 0;
+        if (u + 1 == mub[m + 1]) ok = ok && mod_final_scope[m] == 0;
         if (!ok) mod_bad[m] = 1;
     });
     // C3: modules whose units do not meet are parsed sequentially by one thread each (count)
