@@ -50,28 +50,45 @@ def measured_hbm_peak():
     return 6650.0, "fallback"
 
 
-class ClockSampler(threading.Thread):
-    def __init__(self, index):
-        super().__init__(daemon=True)
-        self.index, self.samples, self.reasons, self.stop_flag, self.max_mhz = index, [], set(), False, None
+class ClockSampler:
+    """SM clock and throttle reasons during the timed region: ONE nvidia-smi process in loop mode (a new process per
+    sample would re-initialise NVML every time and disturb the host thread that drives the GPU)."""
 
-    def run(self):
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+
+    def __init__(self, index):
+        self.index, self.samples, self.reasons, self.max_mhz, self.proc, self.stop_flag = index, [], set(), None, None, False
+
+    def start(self):
         q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        while not self.stop_flag:
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def join(self):
+        if not self.proc:
+            return
+        self.proc.terminate()        # the exact process started above
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        for line in out.strip().split("\n"):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q, "--format=csv,noheader,nounits"],
-                                     stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True, timeout=5).stdout.strip()
-                f = [x.strip() for x in out.split(",")]
                 self.samples.append(float(f[0]))
                 self.max_mhz = float(f[1])
-                for n, v in zip(names, f[2:]):
-                    if v.lower().startswith("active"):
-                        self.reasons.add(n)
-            except Exception:
-                pass
-            time.sleep(0.2)
+            except ValueError:
+                continue
+            for n, v in zip(self.NAMES, f[2:]):
+                if v.lower().startswith("active"):
+                    self.reasons.add(n)
 
     def summary(self):
         return {"sm_mhz": float(np.median(self.samples)) if self.samples else None, "sm_max_mhz": self.max_mhz,
@@ -189,6 +206,7 @@ def main():
         spans.append((blob.data_ptr() + off, len(m)))
         off += len(m)
     ctx = zluda_b200.Context(local_rank)
+    spans = zluda_b200.Texts(spans)      # the (char**, uint64*) arrays of the C call, built once
 
     def barrier():
         torch.cuda.synchronize()

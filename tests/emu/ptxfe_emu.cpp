@@ -39,6 +39,17 @@ struct HostBackend {
         PtxGlobalReader rd{text, (uint32_t)(n * PTX_CHUNK)};
         pf(name, n, [&](size_t c) { f(c, rd); });
     }
+    std::vector<char> store_mem;
+    PtxClassStore class_store(bool reset) {
+        PtxClassStore cs;
+        if (store_mem.empty()) { store_mem.assign(PtxClassStore::bytes(), 0); reset = false; }
+        cs.carve(store_mem.data());
+        if (reset) {
+            memset(cs.keys, 0, sizeof(unsigned long long) * PTX_CLASS_SLOTS);
+            memset(cs.state, 0, 16);
+        }
+        return cs;
+    }
     template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f) {
         const uint32_t cap = 40, win_cap = 5;   // a small window, so that decoders cross its end
         std::vector<uint32_t> stage(cap);

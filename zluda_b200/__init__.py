@@ -76,8 +76,20 @@ def lib():
     return _lib
 
 
+class Texts:
+    """Module texts already converted to the C ABI's (char**, uint64*) form: build once, parse many times."""
+
+    def __init__(self, texts):
+        self.buffers = _as_buffers(texts)
+
+    def __len__(self):
+        return len(self.buffers[1])
+
+
 def _as_buffers(texts):
     """-> (keepalive list, char* array, length array).  Accepts bytes, str, or (address, length) pairs."""
+    if isinstance(texts, Texts):
+        return texts.buffers
     keep, ptrs, lens = [], [], []
     for t in texts:
         if isinstance(t, tuple):

@@ -272,11 +272,10 @@ struct LexSlotSink {
     const uint8_t* text;
     uint32_t n_tokens = 0, n_errors = 0;
     PTX_HD void token(uint32_t start, uint32_t len, uint16_t kind, uint32_t h) {
-        PtxToken t;
-        t.start = start;
-        t.len = len >= 0xFFFFu ? (uint16_t)0xFFFF : (uint16_t)len;
-        t.kind = kind;
-        slots[n_tokens] = t;
+        PtxTokenWord t;       // one 8-byte store
+        t.x = start;
+        t.y = (len >= 0xFFFFu ? 0xFFFFu : len) | ((uint32_t)kind << 16);
+        ((PtxTokenWord*)slots)[n_tokens] = t;
         if (kind == T_IDENT || kind == T_DOTIDENT) hashes[n_tokens] = h;
         n_tokens++;
     }
@@ -301,7 +300,8 @@ struct PtxGlobalReader {
 
 PTX_HD inline bool lx_state_open(int st) {
     // a token (or a '/' whose meaning depends on the next byte) is in progress
-    return st != LS_S0 && st != LS_LINE && st != LS_BLOCK && st != LS_STAR && st != LS_SLASH_IN;
+    const uint32_t closed = (1u << LS_S0) | (1u << LS_LINE) | (1u << LS_BLOCK) | (1u << LS_STAR) | (1u << LS_SLASH_IN);
+    return ((closed >> st) & 1u) == 0;
 }
 
 #define LX_HASH_INIT 2166136261u

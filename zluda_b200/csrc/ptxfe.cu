@@ -170,37 +170,52 @@ constexpr int SCAN_THREADS = 256;
 constexpr int SCAN_ITEMS = 8;
 constexpr int SCAN_TILE = SCAN_THREADS * SCAN_ITEMS;
 
-// ordered block-wide inclusive scan of one value per thread (associative, not necessarily commutative)
+// Ordered block-wide scan of one value per thread (associative, not necessarily commutative): warp shuffles, then
+// the eight warp totals through shared memory.  incl = everything up to and including this thread, excl = before it.
+template <class T>
+__device__ inline T shfl_up_words(T v, int d) {
+    static_assert(sizeof(T) % 4 == 0, "scan element must be made of 32-bit words");
+    union { T t; uint32_t w[sizeof(T) / 4]; } a, b;
+    a.t = v;
+#pragma unroll
+    for (size_t i = 0; i < sizeof(T) / 4; i++) b.w[i] = __shfl_up_sync(0xFFFFFFFFu, a.w[i], d);
+    return b.t;
+}
 template <class T, class Op>
-__device__ inline T block_scan_inclusive(T v, Op op, T* smem) {
-    int t = threadIdx.x;
-    smem[t] = v;
-    __syncthreads();
-    for (int off = 1; off < SCAN_THREADS; off <<= 1) {
-        T x = smem[t];
-        if (t >= off) x = op(smem[t - off], x);
-        __syncthreads();
-        smem[t] = x;
-        __syncthreads();
+__device__ inline void block_scan(T v, Op op, T identity, T* warp_tot, T& incl, T& excl) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    T x = v;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        T y = shfl_up_words(x, d);
+        if (lane >= d) x = op(y, x);
     }
-    return smem[t];
+    T prev = shfl_up_words(x, 1);
+    if (lane == 0) prev = identity;
+    if (lane == 31) warp_tot[warp] = x;
+    __syncthreads();
+    T wp = identity;
+    for (int w = 0; w < warp; w++) wp = op(wp, warp_tot[w]);
+    incl = op(wp, x);
+    excl = op(wp, prev);
 }
 
 template <class T, class Op, class Ld>
 __global__ void __launch_bounds__(SCAN_THREADS) scan_reduce_kernel(size_t n, Ld ld, Op op, T identity, T* partial) {
-    __shared__ T smem[SCAN_THREADS];
+    __shared__ T warp_tot[SCAN_THREADS / 32];
     size_t base = (size_t)blockIdx.x * SCAN_TILE + (size_t)threadIdx.x * SCAN_ITEMS;
     T acc = identity;
 #pragma unroll
     for (int k = 0; k < SCAN_ITEMS; k++)
         if (base + k < n) acc = op(acc, ld(base + k));
-    T incl = block_scan_inclusive(acc, op, smem);
+    T incl, excl;
+    block_scan(acc, op, identity, warp_tot, incl, excl);
     if (threadIdx.x == SCAN_THREADS - 1) partial[blockIdx.x] = incl;
 }
 
 template <class T, class Op, class Ld, class St>
 __global__ void __launch_bounds__(SCAN_THREADS) scan_apply_kernel(size_t n, Ld ld, St st, Op op, T identity, const T* partial_incl) {
-    __shared__ T smem[SCAN_THREADS];
+    __shared__ T warp_tot[SCAN_THREADS / 32];
     size_t base = (size_t)blockIdx.x * SCAN_TILE + (size_t)threadIdx.x * SCAN_ITEMS;
     T vals[SCAN_ITEMS];
     T acc = identity;
@@ -209,12 +224,10 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_apply_kernel(size_t n, Ld l
         if (base + k < n) acc = op(acc, ld(base + k));
         vals[k] = acc;
     }
-    T incl = block_scan_inclusive(acc, op, smem);
-    __syncthreads();
-    // exclusive prefix of this thread = inclusive of the previous thread, after the tiles before this block
-    T prefix = blockIdx.x ? partial_incl[blockIdx.x - 1] : identity;
-    if (threadIdx.x) prefix = op(prefix, smem[threadIdx.x - 1]);
-    (void)incl;
+    T incl, excl;
+    block_scan(acc, op, identity, warp_tot, incl, excl);
+    // everything before this thread: the tiles before this block, then the threads before it in the block
+    T prefix = blockIdx.x ? op(partial_incl[blockIdx.x - 1], excl) : excl;
 #pragma unroll
     for (int k = 0; k < SCAN_ITEMS; k++)
         if (base + k < n) st(base + k, op(prefix, vals[k]));
@@ -340,6 +353,7 @@ struct ptxfe_ctx {
     uint64_t text_bytes = 0, padded_bytes = 0;
     uint8_t* d_text = nullptr;
     size_t d_text_cap = 0;
+    void* d_class_store = nullptr;        // PtxClassStore arrays (one allocation, made at the first parse)
     uint8_t* d_raw = nullptr;             // host-contiguous runs land here before they are repacked into d_text
     size_t d_raw_cap = 0;
     PtxWork work;
@@ -433,6 +447,24 @@ struct CudaBackend {
         pf_kernel<<<(unsigned)blocks, 256, 0, ctx->stream>>>(n, f);
         prof_end();
         ctx->launches++;
+    }
+    PtxClassStore class_store(bool reset) {
+        PtxClassStore cs;
+        if (!ctx->d_class_store) {
+            if (cudaMalloc(&ctx->d_class_store, PtxClassStore::bytes()) != cudaSuccess) {
+                if (!ctx->failed) snprintf(ctx->err, sizeof ctx->err, "cudaMalloc of the class store (%zu bytes) failed", PtxClassStore::bytes());
+                ctx->failed = true;
+                cudaGetLastError();
+                ctx->d_class_store = nullptr;
+            }
+            reset = true;
+        }
+        cs.carve(ctx->d_class_store);
+        if (reset && ctx->d_class_store) {
+            cudaMemsetAsync(cs.keys, 0, sizeof(unsigned long long) * PTX_CLASS_SLOTS, ctx->stream);
+            cudaMemsetAsync(cs.state, 0, 16, ctx->stream);
+        }
+        return cs;
     }
     template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f) {
         if (ctx->failed || n == 0) return;
@@ -561,6 +593,7 @@ void ptxfe_destroy(ptxfe_ctx* ctx) {
     if (ctx->s_out) cudaStreamDestroy(ctx->s_out);
     if (ctx->d_text) cudaFree(ctx->d_text);
     if (ctx->d_raw) cudaFree(ctx->d_raw);
+    if (ctx->d_class_store) cudaFree(ctx->d_class_store);
     if (ctx->h_words) cudaFreeHost(ctx->h_words);
     if (ctx->h_errs) cudaFreeHost(ctx->h_errs);
     if (ctx->h_lexerrs) cudaFreeHost(ctx->h_lexerrs);
@@ -638,7 +671,7 @@ int ptxfe_stage(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, 
 // the kernels have finished.
 static int run_pipeline(ptxfe_ctx* ctx, uint8_t* text, const PtxModuleLayout* layout, uint32_t n, uint32_t mode,
                         cudaEvent_t ev_begin, cudaEvent_t ev_lex, cudaEvent_t ev_structure, cudaEvent_t ev_end,
-                        const RepackModule* repack = nullptr, const uint8_t* raw = nullptr) {
+                        const RepackModule* repack = nullptr, const uint8_t* raw = nullptr, bool first_slice = true) {
     CudaBackend bk{ctx};
     bk.reset();
     ctx->mcb.resize((size_t)n + 1);
@@ -650,6 +683,7 @@ static int run_pipeline(ptxfe_ctx* ctx, uint8_t* text, const PtxModuleLayout* la
     ctx->mcb[n] = chunks;
     PtxWork& w = ctx->work;
     w = PtxWork();
+    w.first_slice = first_slice;
     w.text = text;
     w.n_modules = n;
     w.n_chunks = chunks;
@@ -918,7 +952,7 @@ int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* 
         if (k + 2 < ns && (rc = submit_text(k + 2)) != PTXFE_OK) return rc;
         rc = run_pipeline(ctx, ctx->d_text + sl.text_off, ctx->layout.data() + sl.m0, sl.m1 - sl.m0, mode,
                           ctx->slice_ev[5 * k + 1], nullptr, nullptr, ctx->slice_ev[5 * k + 2],
-                          use_raw[k] ? repack.data() + sl.m0 : nullptr, ctx->d_raw + raw_base[k]);
+                          use_raw[k] ? repack.data() + sl.m0 : nullptr, ctx->d_raw + raw_base[k], k == 0);
         if (rc != PTXFE_OK) {
             cudaStreamSynchronize(ctx->s_in);
             cudaStreamSynchronize(ctx->s_out);

@@ -99,20 +99,87 @@ PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens
     uint64_t k = ((uint64_t)h1 << 32) | h2;
     return k ? k : 1;
 }
-// exact check that unit A (tokens [a, a + n)) is in the class of unit B (tokens [b, b + n))
-PTX_HD inline bool ptx_same_class(const uint8_t* text, const PtxToken* tokens, uint32_t a, uint32_t b, uint32_t n) {
+// The class store lives as long as a batch: the slices of one ptxfe_parse_batch call share it, so a class met in
+// slice 3 is not decoded again in slice 4.  A class keeps a SIGNATURE (what ptx_class_key hashed, spelled out), so that
+// membership can be checked exactly without the representative's tokens, which are gone when its slice is.
+//   signature = [n_tokens | depth1 << 31, then per token: kind | len << 16, and for tokens whose text matters
+//                ceil(len / 4) words of text; for identifiers: kind | envreg << 16]
+#define PTX_CLASS_SLOTS (1u << 20)          // hash slots (power of two)
+#define PTX_SIG_POOL_WORDS (16u << 20)      // 64 MiB of signatures
+struct PtxClassStore {
+    unsigned long long* keys;   // [PTX_CLASS_SLOTS] 0 = empty
+    uint32_t* slot_tmpl;        // [PTX_CLASS_SLOTS] template id of the slot's class, PTX_ABSENT = none
+    uint32_t* tmpl_words;       // [PTX_MAX_CLASSES][PTX_TMPL_WORDS]
+    uint16_t* tmpl_tags;        // [PTX_MAX_CLASSES][PTX_TMPL_WORDS]
+    PtxTemplateInfo* info;      // [PTX_MAX_CLASSES]
+    uint32_t* sig_off;          // [PTX_MAX_CLASSES] word offset of the signature in sig_pool
+    uint32_t* sig_pool;         // [PTX_SIG_POOL_WORDS]
+    uint32_t* rep_unit;         // [PTX_MAX_CLASSES] representative unit (valid for the classes added by the current slice)
+    uint32_t* state;            // [0] classes so far, [1] signature words used, [2] classes before the current slice
+    static size_t bytes() {
+        return sizeof(unsigned long long) * PTX_CLASS_SLOTS + 4ull * PTX_CLASS_SLOTS + 4ull * PTX_TMPL_WORDS * PTX_MAX_CLASSES +
+               2ull * PTX_TMPL_WORDS * PTX_MAX_CLASSES + sizeof(PtxTemplateInfo) * PTX_MAX_CLASSES + 4ull * PTX_MAX_CLASSES +
+               4ull * PTX_SIG_POOL_WORDS + 4ull * PTX_MAX_CLASSES + 256;
+    }
+    // carve the arrays out of one allocation of bytes() bytes (256-byte aligned)
+    void carve(void* base) {
+        char* p = (char*)base;
+        keys = (unsigned long long*)p; p += sizeof(unsigned long long) * PTX_CLASS_SLOTS;
+        slot_tmpl = (uint32_t*)p; p += 4ull * PTX_CLASS_SLOTS;
+        tmpl_words = (uint32_t*)p; p += 4ull * PTX_TMPL_WORDS * PTX_MAX_CLASSES;
+        tmpl_tags = (uint16_t*)p; p += 2ull * PTX_TMPL_WORDS * PTX_MAX_CLASSES;
+        info = (PtxTemplateInfo*)p; p += sizeof(PtxTemplateInfo) * PTX_MAX_CLASSES;
+        sig_off = (uint32_t*)p; p += 4ull * PTX_MAX_CLASSES;
+        sig_pool = (uint32_t*)p; p += 4ull * PTX_SIG_POOL_WORDS;
+        rep_unit = (uint32_t*)p; p += 4ull * PTX_MAX_CLASSES;
+        state = (uint32_t*)p;
+    }
+};
+PTX_HD inline uint32_t ptx_signature_words(const PtxToken* tokens, uint32_t start, uint32_t n) {
+    uint32_t w = 1 + n;
     for (uint32_t i = 0; i < n; i++) {
-        const PtxToken x = tokens[a + i], y = tokens[b + i];
-        if (x.kind != y.kind) return false;
-        if (ptx_text_matters(x.kind)) {
-            if (x.len != y.len || x.len == 0xFFFF) return false;
-            for (uint32_t j = 0; j < x.len; j++)
-                if (text[x.start + j] != text[y.start + j]) return false;
-        } else if (x.kind == T_IDENT) {
-            if (x.len == 0xFFFF || y.len == 0xFFFF) return false;
-            bool ex = (x.len == 8 || x.len == 9) && ptx_envreg_number(text + x.start, x.len);
-            bool ey = (y.len == 8 || y.len == 9) && ptx_envreg_number(text + y.start, y.len);
-            if (ex != ey) return false;
+        const PtxToken t = tokens[start + i];
+        if (ptx_text_matters(t.kind)) w += (t.len + 3u) / 4u;
+    }
+    return w;
+}
+PTX_HD inline void ptx_signature_write(uint32_t* sig, const uint8_t* text, const PtxToken* tokens, uint32_t start, uint32_t n, uint32_t depth1) {
+    *sig++ = n | (depth1 << 31);
+    for (uint32_t i = 0; i < n; i++) {
+        const PtxToken t = tokens[start + i];
+        if (ptx_text_matters(t.kind)) {
+            *sig++ = t.kind | ((uint32_t)t.len << 16);
+            for (uint32_t j = 0; j < t.len; j += 4) {
+                uint32_t v = 0;
+                for (uint32_t k = 0; k < 4 && j + k < t.len; k++) v |= (uint32_t)text[t.start + j + k] << (8 * k);
+                *sig++ = v;
+            }
+        } else if (t.kind == T_IDENT) {
+            bool e = (t.len == 8 || t.len == 9) && ptx_envreg_number(text + t.start, t.len);
+            *sig++ = t.kind | (e ? 1u << 16 : 0u);
+        } else {
+            *sig++ = t.kind;
+        }
+    }
+}
+// exact check that the unit with tokens [start, start + n) at depth class depth1 has this signature
+PTX_HD inline bool ptx_signature_matches(const uint32_t* sig, const uint8_t* text, const PtxToken* tokens, uint32_t start, uint32_t n, uint32_t depth1) {
+    if (*sig++ != (n | (depth1 << 31))) return false;
+    for (uint32_t i = 0; i < n; i++) {
+        const PtxToken t = tokens[start + i];
+        uint32_t head = *sig++;
+        if ((head & 0xFFFFu) != t.kind) return false;
+        if (ptx_text_matters(t.kind)) {
+            if ((head >> 16) != t.len || t.len == 0xFFFF) return false;
+            for (uint32_t j = 0; j < t.len; j += 4) {
+                uint32_t v = 0;
+                for (uint32_t k = 0; k < 4 && j + k < t.len; k++) v |= (uint32_t)text[t.start + j + k] << (8 * k);
+                if (*sig++ != v) return false;
+            }
+        } else if (t.kind == T_IDENT) {
+            if (t.len == 0xFFFF) return false;
+            bool e = (t.len == 8 || t.len == 9) && ptx_envreg_number(text + t.start, t.len);
+            if ((head >> 16) != (e ? 1u : 0u)) return false;
         }
     }
     return true;
@@ -128,7 +195,7 @@ struct PtxStaged {
 struct PtxCounters {
     uint32_t n_tokens, n_lexerrs, n_units, n_words, n_errs, n_funcs, any_sequential, pad;
     uint32_t n_flagged;         // units whose records are written by the second decode pass
-    uint32_t n_classes;         // distinct unit classes (see the template steps of the decode stage)
+    uint32_t pad2;
 };
 
 PTX_HD inline uint32_t ptx_upper_bound_u32(const uint32_t* a, uint32_t n, uint32_t x) {
@@ -153,6 +220,7 @@ struct PtxWork {
     PtxToken* tokens = nullptr;            // [n_tokens]
     uint32_t* lexerrs = nullptr;           // [2 * n_lexerrs]
     uint32_t* mod_tok_begin = nullptr;     // [n_modules + 1]
+    bool first_slice = true;               // the class store is emptied before the first slice of a batch
     uint8_t* tfirst = nullptr;             // [n_tokens] 1 = first token of a module
     int32_t* mod_final_scope = nullptr;    // [n_modules] scope depth behind the module's last token
     uint32_t* unit_of_tok = nullptr;       // [n_tokens + 1] exclusive scan of unit-start flags
@@ -208,6 +276,7 @@ struct SegDepthOp {
 //        afterwards the backend copies the first r.n staged words to table[r.unit * row_words ...]
 //   template <class F> void pf_segments(const char* name, size_t n, const PtxPair* off, F f);
 //        segment s owns the items [off[s].a, off[s + 1].a): f(s, i, off[s].a + i) for every s < n and every item i of s
+//   PtxClassStore class_store(bool reset);   the batch's class store (device memory that outlives the arena), emptied if asked
 //   void* alloc(size_t bytes); void zero(void* p, size_t bytes);
 //   void download(void* host, const void* dev, size_t bytes);   (synchronises the stream)
 // The pipeline allocates through the backend and never frees: the backend's arena is reset per batch.
@@ -508,65 +577,60 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     });
     bk.sort_by_key("sort_units_by_shape", n_units, ukey, order);
 
-    // T1: class table (open addressing on the 64-bit key); the thread that inserts a key makes its unit the
-    // representative of the class
-    uint32_t cmask = 1024;
-    while (cmask < n_units / 2) cmask <<= 1;
-    cmask -= 1;
-    unsigned long long* ckeys = (unsigned long long*)bk.alloc(sizeof(unsigned long long) * ((size_t)cmask + 1));
-    uint32_t* slot_tmpl = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)cmask + 1));
+    // T1: class table (open addressing on the 64-bit key), shared by the slices of a batch; the thread that inserts
+    // a key makes its unit the representative of the class
+    const PtxClassStore cs = bk.class_store(w.first_slice);
     uint32_t* uclass = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
     uint32_t* utmpl = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
-    uint32_t* rep_unit = (uint32_t*)bk.alloc(sizeof(uint32_t) * PTX_MAX_CLASSES);
-    uint32_t* tmpl_words = (uint32_t*)bk.alloc(sizeof(uint32_t) * PTX_TMPL_WORDS * PTX_MAX_CLASSES);
-    uint16_t* tmpl_tags = (uint16_t*)bk.alloc(sizeof(uint16_t) * PTX_TMPL_WORDS * PTX_MAX_CLASSES);
-    PtxTemplateInfo* tmpl_info = (PtxTemplateInfo*)bk.alloc(sizeof(PtxTemplateInfo) * PTX_MAX_CLASSES);
     uint8_t* uflag = (uint8_t*)bk.alloc((size_t)n_units + 16);
-    bk.zero(ckeys, sizeof(unsigned long long) * ((size_t)cmask + 1));
-    bk.pf("reset_flagged", 1, [=] PTX_HD(size_t) { counters->n_flagged = 0; counters->n_classes = 0; });
+    bk.pf("reset_flagged", 1, [=] PTX_HD(size_t) {
+        counters->n_flagged = 0;
+        cs.state[2] = cs.state[0] < PTX_MAX_CLASSES ? cs.state[0] : PTX_MAX_CLASSES;
+    });
     bk.pf("class_insert", n_units, [=] PTX_HD(size_t u) {
         uclass[u] = PTX_ABSENT;
         unsigned long long key = ckey_of[u];
         if (!key) return;
-        uint32_t h = (uint32_t)(key ^ (key >> 29)) & cmask;
+        uint32_t h = (uint32_t)(key ^ (key >> 29)) & (PTX_CLASS_SLOTS - 1);
         for (int probe = 0; probe < 64; probe++) {
 #ifdef __CUDA_ARCH__
             // most units find their class already there: look before competing for the slot
-            unsigned long long old = *(volatile unsigned long long*)&ckeys[h];
-            if (old == 0) old = atomicCAS(&ckeys[h], 0ull, key);
+            unsigned long long old = *(volatile unsigned long long*)&cs.keys[h];
+            if (old == 0) old = atomicCAS(&cs.keys[h], 0ull, key);
 #else
-            unsigned long long old = ckeys[h];
-            if (old == 0) ckeys[h] = key;
+            unsigned long long old = cs.keys[h];
+            if (old == 0) cs.keys[h] = key;
 #endif
             if (old == 0) {
 #ifdef __CUDA_ARCH__
-                uint32_t id = atomicAdd(&counters->n_classes, 1u);
+                uint32_t id = atomicAdd(&cs.state[0], 1u);
 #else
-                uint32_t id = counters->n_classes++;
+                uint32_t id = cs.state[0]++;
 #endif
                 if (id < PTX_MAX_CLASSES) {
-                    rep_unit[id] = (uint32_t)u;
-                    slot_tmpl[h] = id;
+                    cs.rep_unit[id] = (uint32_t)u;
+                    cs.slot_tmpl[h] = id;
                 } else {
-                    slot_tmpl[h] = PTX_ABSENT;
+                    cs.slot_tmpl[h] = PTX_ABSENT;
                 }
                 uclass[u] = h;
                 return;
             }
             if (old == key) { uclass[u] = h; return; }
-            h = (h + 1) & cmask;
+            h = (h + 1) & (PTX_CLASS_SLOTS - 1);
         }
     });
-    // T2: decode the representatives with tagged output
-    bk.pf("decode_representatives", PTX_MAX_CLASSES, [=] PTX_HD(size_t id) {
-        if (id >= counters->n_classes) return;
-        uint32_t u = rep_unit[id];
+    // T2: decode the representatives of the classes this slice added, with tagged output, and spell out their signature
+    bk.pf("decode_representatives", PTX_MAX_CLASSES, [=] PTX_HD(size_t k) {
+        size_t id = (size_t)cs.state[2] + k;
+        if (id >= cs.state[0] || id >= PTX_MAX_CLASSES) return;
+        uint32_t u = cs.rep_unit[id];
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, u) - 1;
         uint32_t start = ustart[u];
         uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
         PtxSink sink;
-        sink.words = tmpl_words + (size_t)id * PTX_TMPL_WORDS;
-        sink.tags = tmpl_tags + (size_t)id * PTX_TMPL_WORDS;
+        sink.words = cs.tmpl_words + id * PTX_TMPL_WORDS;
+        sink.tags = cs.tmpl_tags + id * PTX_TMPL_WORDS;
         sink.words_cap = PTX_TMPL_WORDS;
         PtxResolver res;
         res.module = m;
@@ -579,25 +643,39 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         ti.depth1 = (dp & 0x7FFFFFFFu) == 1 ? 1u : 0u;
         ti.ok = (r.status == US_OK && sink.ne == 0 && sink.peak <= PTX_TMPL_WORDS && !sink.poison && r.kind != U_FUNC && r.end == end &&
                  d.max_seen < end) ? 1u : 0u;
-        tmpl_info[id] = ti;
+        if (ti.ok) {
+            uint32_t need = ptx_signature_words(tokens, start, ti.n_tokens);
+#ifdef __CUDA_ARCH__
+            uint32_t at = atomicAdd(&cs.state[1], need);
+#else
+            uint32_t at = cs.state[1];
+            cs.state[1] += need;
+#endif
+            if (at + need <= PTX_SIG_POOL_WORDS) {
+                cs.sig_off[id] = at;
+                ptx_signature_write(cs.sig_pool + at, text, tokens, start, ti.n_tokens, ti.depth1);
+            } else {
+                ti.ok = 0;
+            }
+        }
+        cs.info[id] = ti;
     });
-    // T3: every unit of a class with a usable template is checked against the representative and takes its size
+    // T3: every unit of a class with a usable template is checked against the class signature and takes its size
     bk.pf("apply_templates", n_units, [=] PTX_HD(size_t u) {
         uflag[u] = PTX_UNIT_UNDECIDED;
         utmpl[u] = PTX_ABSENT;
         uint32_t slot = uclass[u];
         if (slot == PTX_ABSENT) return;
-        uint32_t id = slot_tmpl[slot];
+        uint32_t id = cs.slot_tmpl[slot];
         if (id == PTX_ABSENT) return;
-        const PtxTemplateInfo ti = tmpl_info[id];
+        const PtxTemplateInfo ti = cs.info[id];
         if (!ti.ok) return;
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         uint32_t start = ustart[u];
         uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
         uint32_t dp = udepth[u];
-        if (end - start != ti.n_tokens || ((dp & 0x7FFFFFFFu) == 1 ? 1u : 0u) != ti.depth1) return;
-        uint32_t r = rep_unit[id];
-        if (r != u && !ptx_same_class(text, tokens, start, ustart[r], ti.n_tokens)) return;
+        uint32_t depth1 = (dp & 0x7FFFFFFFu) == 1 ? 1u : 0u;
+        if (end - start != ti.n_tokens || !ptx_signature_matches(cs.sig_pool + cs.sig_off[id], text, tokens, start, ti.n_tokens, depth1)) return;
         PtxPair sz;
         sz.a = ti.n_words;
         sz.b = 0;
@@ -744,7 +822,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         }
         if (fl != PTX_UNIT_TEMPLATED) return;
         size_t at = (size_t)utmpl[u] * PTX_TMPL_WORDS + i;
-        uint32_t x = tmpl_words[at], g = tmpl_tags[at];
+        uint32_t x = cs.tmpl_words[at], g = cs.tmpl_tags[at];
         if (g) {
             const PtxToken t = tokens[ustart[u] + (g & 0xFFu)];
             uint32_t type = g >> 8;
