@@ -75,15 +75,17 @@ PTX_HD inline bool ptx_text_matters(uint16_t k) {
     return k == T_DECIMAL || k == T_HEX || k == T_F32HEX || k == T_F64HEX || k == T_F64 || k == T_DOTIDENT || k == T_STRING;
 }
 // 64-bit class key of the tokens [start, end); 0 = this unit gets no template
-PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens, uint32_t start, uint32_t end, uint32_t depth, bool module_first) {
+PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens, const uint16_t* kinds, uint32_t start, uint32_t end, uint32_t depth,
+                                     bool module_first) {
     if (depth == 0 || module_first || end - start > PTX_MAX_CLASS_TOKENS || end <= start) return 0;
     uint32_t h1 = 2166136261u ^ (depth == 1 ? 1u : 0u), h2 = 0x811C9DC5u + (end - start);
     for (uint32_t i = start; i < end; i++) {
-        const PtxToken t = tokens[i];
-        h1 = (h1 ^ t.kind) * 16777619u;
-        h2 = (h2 + t.kind) * 0x9E3779B1u;
+        const uint16_t kind = kinds[i];
+        h1 = (h1 ^ kind) * 16777619u;
+        h2 = (h2 + kind) * 0x9E3779B1u;
         h2 ^= h2 >> 15;
-        if (ptx_text_matters(t.kind)) {
+        if (ptx_text_matters(kind)) {
+            const PtxToken t = tokens[i];
             if (t.len == 0xFFFF) return 0;
             h2 = (h2 ^ t.len) * 0x85EBCA6Bu;
             for (uint32_t j = 0; j < t.len; j++) {
@@ -91,7 +93,8 @@ PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens
                 h1 = (h1 ^ c) * 16777619u;
                 h2 = (h2 + c) * 0x9E3779B1u;
             }
-        } else if (t.kind == T_IDENT) {
+        } else if (kind == T_IDENT) {
+            const PtxToken t = tokens[i];
             if (t.len == 0xFFFF) return 0;
             if ((t.len == 8 || t.len == 9) && ptx_envreg_number(text + t.start, t.len)) h1 = (h1 ^ 0x1234u) * 16777619u;
         }
@@ -221,6 +224,7 @@ struct PtxWork {
     uint32_t* lexerrs = nullptr;           // [2 * n_lexerrs]
     uint32_t* mod_tok_begin = nullptr;     // [n_modules + 1]
     bool first_slice = true;               // the class store is emptied before the first slice of a batch
+    uint16_t* kinds = nullptr;             // [n_tokens] tokens[i].kind
     uint8_t* tfirst = nullptr;             // [n_tokens] 1 = first token of a module
     int32_t* mod_final_scope = nullptr;    // [n_modules] scope depth behind the module's last token
     uint32_t* unit_of_tok = nullptr;       // [n_tokens + 1] exclusive scan of unit-start flags
@@ -381,6 +385,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     bk.download(&host_counters, counters, sizeof(PtxCounters));
     const uint32_t n_tokens = host_counters.n_tokens, n_lexerrs = host_counters.n_lexerrs;
     PtxToken* tokens = w.tokens = (PtxToken*)bk.alloc(sizeof(PtxToken) * (size_t)(n_tokens + 1));
+    uint16_t* kinds = w.kinds = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_tokens + 8));   // the kinds alone, for the passes that read nothing else
     uint32_t* lexerrs = w.lexerrs = (uint32_t*)bk.alloc(sizeof(uint32_t) * 2 * (size_t)(n_lexerrs + 1));
     // A5: tokens to their final places, one thread per token; identifiers that spell an opcode, modifier or directive
     // word get that kind on the way (table probe with the hash from the token pass, then a string compare)
@@ -391,6 +396,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
             if (k != T_ERROR) t.kind = k;
         }
         tokens[j] = t;
+        kinds[j] = t.kind;
     });
     // A6: lexer errors are rare: a second walk, only when there are any, and only over the chunks that have one
     if (n_lexerrs) bk.pf_text("lex_emit_errors", n_chunks, text, PtxLexErrorsStep{info, text, vec, cnt, lexerrs});
@@ -425,14 +431,14 @@ PTX_HD inline bool ptx_is_directive_start(uint16_t k) {
 
 // scope delta of token i: +1 for a '{' that opens a scope, -1 for a '}' that closes one, 0 otherwise (also for the
 // braces of vector operands, initialisers and .section bodies, told apart by two tokens of left context)
-PTX_HD inline int ptx_brace_class(const PtxToken* tokens, const uint8_t* tfirst, size_t i) {
-    uint16_t k = tokens[i].kind;
+PTX_HD inline int ptx_brace_class(const uint16_t* kinds, const uint8_t* tfirst, size_t i) {
+    uint16_t k = kinds[i];
     if (k != T_LBRACE && k != T_RBRACE) return 0;
     bool first = tfirst[i] != 0;
-    uint16_t prev = first ? (uint16_t)0xFFFE : tokens[i - 1].kind;
+    uint16_t prev = first ? (uint16_t)0xFFFE : kinds[i - 1];
     if (k == T_LBRACE) {
         bool section = false;
-        if (!first && i >= 2 && !tfirst[i - 1]) section = tokens[i - 2].kind == T_DOT_SECTION;
+        if (!first && i >= 2 && !tfirst[i - 1]) section = kinds[i - 2] == T_DOT_SECTION;
         return (!ptx_opens_operand(prev) && !section) ? 1 : 0;
     }
     return (prev == T_SEMI || prev == T_COLON || prev == T_LBRACE || prev == T_RBRACE) ? -1 : 0;
@@ -441,7 +447,7 @@ PTX_HD inline int ptx_brace_class(const PtxToken* tokens, const uint8_t* tfirst,
 template <class BK>
 inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, uint32_t mode) {
     const uint32_t n_tokens = host_counters.n_tokens, n_modules = w.n_modules;
-    const PtxToken* tokens = w.tokens;
+    const uint16_t* kinds = w.kinds;
     const uint32_t* mtb = w.mod_tok_begin;
     const PtxModuleResult* results = w.results;
     uint8_t* tfirst = w.tfirst = (uint8_t*)bk.alloc((size_t)n_tokens + 16);
@@ -468,8 +474,8 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
         "scan_depth", n_tokens,
         [=] PTX_HD(size_t i) {
             PtxSeg3 v;
-            uint16_t k = tokens[i].kind;
-            v.scope = ptx_brace_class(tokens, tfirst, i);
+            uint16_t k = kinds[i];
+            v.scope = ptx_brace_class(kinds, tfirst, i);
             v.paren = k == T_LPAREN ? 1 : k == T_RPAREN ? -1 : 0;
             v.flag = tfirst[i] ? 1 : 0;
             return v;
@@ -482,7 +488,7 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
             if (j == n_tokens) return;
             if (tfirst[j]) { sd16[j] = (uint16_t)(1u | 0x8000u); return; }
             int32_t sd = v.scope, pd = v.paren;
-            uint16_t k = tokens[j].kind, prev = tokens[i].kind;
+            uint16_t k = kinds[j], prev = kinds[i];
             bool start;
             if (sd <= 0) {
                 // top level: a directive keyword outside parentheses that does not continue a run of linking keywords
@@ -491,7 +497,7 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
                 start = sd == 0 && pd == 0 && ptx_is_directive_start(k) &&
                         !(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak);
             } else {
-                start = prev == T_SEMI || prev == T_COLON || ptx_brace_class(tokens, tfirst, j) != 0 || ptx_brace_class(tokens, tfirst, i) != 0;
+                start = prev == T_SEMI || prev == T_COLON || ptx_brace_class(kinds, tfirst, j) != 0 || ptx_brace_class(kinds, tfirst, i) != 0;
             }
             uint32_t clamped = sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
             sd16[j] = start ? (uint16_t)(1u + clamped) : (uint16_t)0;
@@ -523,6 +529,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     const uint32_t n_tokens = host_counters.n_tokens, n_units = host_counters.n_units, n_modules = w.n_modules;
     const uint8_t* text = w.text;
     const PtxToken* tokens = w.tokens;
+    const uint16_t* kinds = w.kinds;
     const PtxModuleLayout* layout = w.layout;
     const uint32_t* mtb = w.mod_tok_begin;
     const uint32_t* mub = w.mod_unit_begin;
@@ -568,10 +575,10 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         uint32_t start = ustart[u];
         uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
         uint32_t dp = udepth[u];
-        ckey_of[u] = mod_skip[m] ? 0 : ptx_class_key(text, tokens, start, end, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
+        ckey_of[u] = mod_skip[m] ? 0 : ptx_class_key(text, tokens, kinds, start, end, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
         if (end > start + 20) end = start + 20;
         uint32_t h = 2166136261u ^ (udepth[u] >> 31) ^ ((udepth[u] & 0x7FFFFFFFu) ? 2u : 0u);
-        for (uint32_t i = start; i < end; i++) h = (h ^ tokens[i].kind) * 16777619u;
+        for (uint32_t i = start; i < end; i++) h = (h ^ kinds[i]) * 16777619u;
         h ^= h >> 15;
         ukey[u] = (uint16_t)(h & (PTX_SORT_BUCKETS - 1));
     });
