@@ -250,14 +250,14 @@ PTX_HD PTX_NOINLINE inline uint16_t lx_one(const uint8_t* s, uint64_t p, uint64_
 // Sink concept: void token(uint64_t start, uint32_t len, uint16_t kind); void error(uint64_t start, uint32_t len);
 struct LexCountSink {
     uint32_t n_tokens = 0, n_errors = 0;
-    PTX_HD void token(uint32_t, uint32_t, uint16_t, uint32_t) { n_tokens++; }
+    PTX_HD void token(uint32_t, uint32_t, uint16_t) { n_tokens++; }
     PTX_HD void error(uint32_t, uint32_t) { n_errors++; }
 };
 // writes lexer errors only (second pass, run only when the first found some)
 struct LexErrorSink {
     uint32_t* errors;      // pairs (start, len), already offset to this chunk's first error
     uint32_t n_errors = 0;
-    PTX_HD void token(uint32_t, uint32_t, uint16_t, uint32_t) {}
+    PTX_HD void token(uint32_t, uint32_t, uint16_t) {}
     PTX_HD void error(uint32_t start, uint32_t len) {
         errors[2 * n_errors] = start;
         errors[2 * n_errors + 1] = len;
@@ -265,18 +265,15 @@ struct LexErrorSink {
     }
 };
 // Token slots: every chunk owns PTX_CHUNK slots (a token is at least one byte long), so one pass can write the
-// tokens before their final positions are known.  Keyword candidates also leave their spelling's hash.
+// tokens before their final positions are known.
 struct LexSlotSink {
     PtxToken* slots;       // this chunk's row
-    uint32_t* hashes;      // this chunk's row
-    const uint8_t* text;
     uint32_t n_tokens = 0, n_errors = 0;
-    PTX_HD void token(uint32_t start, uint32_t len, uint16_t kind, uint32_t h) {
+    PTX_HD void token(uint32_t start, uint32_t len, uint16_t kind) {
         PtxTokenWord t;       // one 8-byte store
         t.x = start;
         t.y = (len >= 0xFFFFu ? 0xFFFFu : len) | ((uint32_t)kind << 16);
         ((PtxTokenWord*)slots)[n_tokens] = t;
-        if (kind == T_IDENT || kind == T_DOTIDENT) hashes[n_tokens] = h;
         n_tokens++;
     }
     PTX_HD void error(uint32_t, uint32_t) { n_errors++; }
@@ -304,12 +301,9 @@ PTX_HD inline bool lx_state_open(int st) {
     return ((closed >> st) & 1u) == 0;
 }
 
-#define LX_HASH_INIT 2166136261u
-
 // Lex the tokens that START in [cs, ce) of a module occupying [ms, me).  `cx` is the comment/string context at cs.
 // One byte per loop iteration, driven by ptx_lex_fused; the common cases (advance, begin a token, emit a token) are
-// flag bits handled without branching on an action code, so the threads of a warp stay together.  The running
-// FNV-1a hash of the current token is handed to the sink with every token (the keyword step probes with it).
+// flag bits handled without branching on an action code, so the threads of a warp stay together.
 // `g` is the text in global memory (used by the rare helpers), `tx` the reader for the byte loop.
 // Offsets are 32-bit: a batch holds less than 4 GiB of text.
 template <class TX, class Sink>
@@ -317,7 +311,7 @@ PTX_HD inline void lx_chunk(const TX& tx, const uint8_t* g, uint32_t ms, uint32_
     if (ce > me) ce = me;
     if (cs >= me) return;
     uint32_t p = cs, tstart = cs ? cs - 1 : 0, acc_pos = 0;
-    uint32_t acc_kind = T_ERROR, cnt = 0, need = 0, h = LX_HASH_INIT;
+    uint32_t acc_kind = T_ERROR, cnt = 0, need = 0;
     int st;
     switch (cx) {
     case CX_SLASH: st = LS_SLASH_IN; break;
@@ -339,19 +333,19 @@ PTX_HD inline void lx_chunk(const TX& tx, const uint8_t* g, uint32_t ms, uint32_
         const unsigned c = p < me ? tx[p] : ' ';
         const uint32_t e = tx.lookup(st, c);
         const int prev = st;
-        st = (int)(e & 0xFFu);
-        if (e & (LF_BEGIN << 8)) { tstart = p; h = LX_HASH_INIT; }
-        if (e & (LF_EMIT << 8)) {
-            const uint32_t aux = e >> 12;
+        const uint32_t flags = e >> LF_FLAG_SHIFT, aux = e >> LF_AUX_SHIFT;
+        st = (int)(e & LF_STATE_MASK);
+        if (flags & LF_BEGIN) tstart = p;
+        if (flags & LF_EMIT) {
             const uint32_t s0 = (aux & LF_SELF) ? p : tstart;
-            if (s0 >= cs) out.token(s0, p + (aux & LF_INCL) - s0, (uint16_t)(e >> 16), h);
+            if (s0 >= cs) out.token(s0, p + (aux & LF_INCL) - s0, (aux & LF_SELF) ? ptx_lex_single[c] : ptx_lex_end_kind[prev]);
         }
-        if (e & (LF_RARE << 8)) {
-            switch ((e >> 12) & 0xFu) {
+        if (flags & LF_RARE) {
+            switch (aux & 0xFu) {
             case LA_ACCEPT: acc_pos = p; acc_kind = ptx_lex_end_kind[prev]; p++; break;
             case LA_BACKUP:
                 if (prev != LS_SLASH_IN) {
-                    if (tstart >= cs) out.token(tstart, acc_pos - tstart, (uint16_t)acc_kind, 0);
+                    if (tstart >= cs) out.token(tstart, acc_pos - tstart, (uint16_t)acc_kind);
                     p = acc_pos;
                 }
                 break;
@@ -365,7 +359,7 @@ PTX_HD inline void lx_chunk(const TX& tx, const uint8_t* g, uint32_t ms, uint32_
                 break;
             case LA_COUNT:
                 if (++cnt == need) {
-                    if (tstart >= cs) out.token(tstart, p + 1 - tstart, need == 8 ? T_F32HEX : T_F64HEX, 0);
+                    if (tstart >= cs) out.token(tstart, p + 1 - tstart, need == 8 ? T_F32HEX : T_F64HEX);
                     st = LS_S0;
                 }
                 p++;
@@ -377,56 +371,35 @@ PTX_HD inline void lx_chunk(const TX& tx, const uint8_t* g, uint32_t ms, uint32_
                 uint32_t l = 0;
                 if (p + 1 < me && tx[p + 1] == ':') l = lx_colon_literal(g, tstart, p, me, &k);
                 if (l) {
-                    // a literal with "::" inside: its kind is final (hash 0 = nothing to look up)
-                    if (tstart >= cs) out.token(tstart, l, k, 0);
+                    // a literal with "::" inside: its kind is final
+                    if (tstart >= cs) out.token(tstart, l, k);
                     p = tstart + l;
                 } else if (tstart >= cs) {
-                    out.token(tstart, p - tstart, T_DOTIDENT, h);
+                    out.token(tstart, p - tstart, T_DOTIDENT);
                 }
                 break;
             }
             case LA_REWIND_DOT:
-                if (tstart >= cs) out.token(tstart, 1, T_DOT, 0);
+                if (tstart >= cs) out.token(tstart, 1, T_DOT);
                 p = tstart + 1;
                 break;
             default:   // LA_DIM: ".1d" ".2d" ".3d" are literals; an upper-case D ends the F64 in front of it
                 if (c == 'd') {
                     unsigned digit = tx[tstart + 1];
-                    if (tstart >= cs) out.token(tstart, 3, digit == '1' ? T_MOD_1d : digit == '2' ? T_MOD_2d : T_MOD_3d, 0);
+                    if (tstart >= cs) out.token(tstart, 3, digit == '1' ? T_MOD_1d : digit == '2' ? T_MOD_2d : T_MOD_3d);
                     p++;
                 } else if (tstart >= cs) {
-                    out.token(tstart, p - tstart, T_F64, 0);
+                    out.token(tstart, p - tstart, T_F64);
                 }
                 break;
             }
         }
-        h = (h ^ c) * PTX_KW_MULT;
-        p += (e >> 8) & LF_ADV;
+        p += flags & LF_ADV;
     }
     if (p > me || (p == me && ce == me)) {
         // this thread saw the end of the module
         if (st == LS_STR && tstart >= cs) out.error(tstart, me - tstart);
         if ((st == LS_BLOCK || st == LS_STAR) && ce == me) out.error(me, 0);
-    }
-}
-
-// A token's kind once its spelling is known.  `h` is the FNV-1a hash of its bytes as lx_chunk computes it.
-PTX_HD inline bool lx_keyword_candidate(const uint8_t* g, uint32_t start, uint16_t kind) {
-    return kind == T_DOTIDENT || (kind == T_IDENT && lx_alpha(g[start]));
-}
-PTX_HD inline uint16_t lx_keyword_hashed(const uint8_t* s, uint32_t len, uint32_t h) {
-    if (len > PTX_KW_MAXLEN) return T_ERROR;
-    h = (h ^ (h >> 15)) & (PTX_KW_SIZE - 1);
-    for (;;) {
-        PtxKwEntry e = ptx_kw_table[h];
-        if (e.kind == 0xFFFF) return T_ERROR;
-        if (e.len == len) {
-            bool same = true;
-            for (uint32_t i = 0; i < len; i++)
-                if ((uint8_t)ptx_kw_pool[e.off + i] != s[i]) { same = false; break; }
-            if (same) return e.kind;
-        }
-        h = (h + 1) & (PTX_KW_SIZE - 1);
     }
 }
 

@@ -45,7 +45,7 @@ __global__ void __launch_bounds__(256) pf_kernel(size_t n, F f) {
 #define LEX_ROW_WORDS 33u
 struct PtxTileReader {
     const uint32_t* tile;      // [LEX_TILE_CHUNKS][LEX_ROW_WORDS]
-    const uint32_t* fused;     // [LS_COUNT][256], copy of ptx_lex_fused
+    const uint16_t* fused;     // [LS_COUNT][256], copy of ptx_lex_fused
     const uint8_t* g;          // the whole text, for bytes outside the tile
     uint32_t base;             // text offset of the tile
     __device__ unsigned operator[](uint32_t p) const {
@@ -61,12 +61,12 @@ struct PtxTileReader {
 };
 
 #define LEX_TILE_BYTES (LEX_TILE_CHUNKS * LEX_ROW_WORDS * 4u)
-#define LEX_TABLE_BYTES (LS_COUNT * 256u * 4u)
+#define LEX_TABLE_BYTES (LS_COUNT * 256u * 2u)
 template <bool TABLES, class F>
 __global__ void __launch_bounds__(256) lex_tile_kernel(uint32_t n_chunks, const uint8_t* text, F f) {
     extern __shared__ __align__(16) uint32_t lex_smem[];
     uint32_t* tile = lex_smem;                                       // [LEX_TILE_CHUNKS][LEX_ROW_WORDS]
-    uint32_t* fused = lex_smem + LEX_TILE_CHUNKS * LEX_ROW_WORDS;    // [LS_COUNT][256] when TABLES
+    uint16_t* fused = (uint16_t*)(lex_smem + LEX_TILE_CHUNKS * LEX_ROW_WORDS);    // [LS_COUNT][256] when TABLES
     const uint32_t c0 = blockIdx.x * LEX_TILE_CHUNKS;
     const uint4* src = (const uint4*)text + (size_t)c0 * (PTX_CHUNK / 16);
 #pragma unroll
@@ -288,7 +288,7 @@ struct LexCapSink {
     PtxToken* tokens;
     const uint8_t* text;
     uint64_t next, capacity;
-    __device__ void token(uint32_t start, uint32_t len, uint16_t kind, uint32_t) {
+    __device__ void token(uint32_t start, uint32_t len, uint16_t kind) {
         if (next < capacity) {
             PtxToken t;
             t.start = (uint32_t)start;

@@ -317,7 +317,6 @@ struct PtxLexTokensStep {
     const uint32_t* vec;
     PtxPair* cnt;
     PtxToken* slots;
-    uint32_t* hashes;
     template <class R> PTX_HD void operator()(size_t c, const R& rd) const {
         uint32_t ms, me, cs = (uint32_t)c * PTX_CHUNK;
         bool first;
@@ -325,8 +324,6 @@ struct PtxLexTokensStep {
         int state = first ? CX_CODE : (int)(vec[c - 1] & 7u);
         LexSlotSink sink;
         sink.slots = slots + c * PTX_CHUNK;
-        sink.hashes = hashes + c * PTX_CHUNK;
-        sink.text = text;
         lx_chunk(rd, text, ms, me, cs, cs + PTX_CHUNK, state, sink);
         PtxPair p;
         p.a = sink.n_tokens;
@@ -373,8 +370,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
                                ComposeOp(), CX_IDENTITY);
     // A3: the token pass.  Every chunk writes its tokens into its own row of PTX_CHUNK slots
     PtxToken* slots = (PtxToken*)bk.alloc(sizeof(PtxToken) * PTX_CHUNK * ((size_t)n_chunks + 1));
-    uint32_t* hashes = (uint32_t*)bk.alloc(sizeof(uint32_t) * PTX_CHUNK * ((size_t)n_chunks + 1));
-    bk.pf_text("lex_tokens", n_chunks, text, PtxLexTokensStep{info, text, vec, cnt, slots, hashes});
+    bk.pf_text("lex_tokens", n_chunks, text, PtxLexTokensStep{info, text, vec, cnt, slots});
     // A4: exclusive offsets (cnt[c] = tokens before chunk c; cnt[n_chunks] = total)
     bk.template scan<PtxPair>("scan_token_counts", n_chunks + 1, [=] PTX_HD(size_t i) { return cnt[i]; }, [=] PTX_HD(size_t i, PtxPair v) { cnt[i] = v; },
                               PairAddOp(), PtxPair{0, 0});
@@ -388,13 +384,10 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     uint16_t* kinds = w.kinds = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_tokens + 8));   // the kinds alone, for the passes that read nothing else
     uint32_t* lexerrs = w.lexerrs = (uint32_t*)bk.alloc(sizeof(uint32_t) * 2 * (size_t)(n_lexerrs + 1));
     // A5: tokens to their final places, one thread per token; identifiers that spell an opcode, modifier or directive
-    // word get that kind on the way (table probe with the hash from the token pass, then a string compare)
+    // word get that kind on the way
     bk.pf_segments("lex_compact_classify", n_chunks, cnt, [=] PTX_HD(size_t c, uint32_t i, uint32_t j) {
         PtxToken t = slots[c * PTX_CHUNK + i];
-        if (lx_keyword_candidate(text, t.start, t.kind)) {
-            uint16_t k = lx_keyword_hashed(text + t.start, t.len, hashes[c * PTX_CHUNK + i]);
-            if (k != T_ERROR) t.kind = k;
-        }
+        t.kind = lx_classify(text, t.start, t.len, t.kind);
         tokens[j] = t;
         kinds[j] = t.kind;
     });

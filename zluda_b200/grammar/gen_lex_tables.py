@@ -214,37 +214,37 @@ def main():
     L.append("};")
     L.append("// token kind that END / END_INCL / BACKUP-from produce in each state")
     L.append("PTX_TABLE uint16_t ptx_lex_end_kind[LS_COUNT] = {" + ", ".join(END_KIND.get(s, "T_ERROR") for s in STATES) + "};")
-    # ---- the table the byte loop reads: one 32-bit entry per (state, byte)
-    #   bits 0..7   next state
-    #   bits 8..11  flags: 1 advance, 2 a token begins here, 4 emit a token, 8 rare action
-    #   bits 12..15 with "emit": 1 = the token includes this byte, 2 = the token IS this byte; with "rare": the action
-    #   bits 16..31 kind of the emitted token
-    L.append("enum { LF_ADV = 1, LF_BEGIN = 2, LF_EMIT = 4, LF_RARE = 8, LF_INCL = 1, LF_SELF = 2 };")
-    L.append("#define LXK(name) ((uint32_t)(name) << 16)")
-    L.append("PTX_TABLE uint32_t ptx_lex_fused[LS_COUNT * 256] = {")
-    hard = dict(HARD_KIND)
+    # ---- the table the byte loop reads: one 16-bit entry per (state, byte)
+    #   bits 0..4   next state
+    #   bits 5..8   flags: 1 advance, 2 a token begins here, 4 emit a token, 8 rare action
+    #   bits 9..12  with "emit": 1 = the token includes this byte, 2 = the token IS this byte; with "rare": the action
+    # The kind of an emitted token is ptx_lex_single[byte] when the token is the byte itself, else
+    # ptx_lex_end_kind[state before the byte].
+    assert len(STATES) <= 32
+    L.append("enum { LF_ADV = 1, LF_BEGIN = 2, LF_EMIT = 4, LF_RARE = 8, LF_INCL = 1, LF_SELF = 2, LF_FLAG_SHIFT = 5, LF_AUX_SHIFT = 9, LF_STATE_MASK = 31 };")
+    L.append("PTX_TABLE uint16_t ptx_lex_fused[LS_COUNT * 256] = {")
     for s_i, sname in enumerate(STATES):
         row = []
         for b in range(256):
             nxt, act = T[s_i][byte_class(b)]
             an = ACTIONS[act]
             if an == "NONE":
-                e = "%d" % (nxt | (1 << 8))
+                e = nxt | (1 << 5)
             elif an == "BEGIN":
-                e = "%d" % (nxt | (3 << 8))
+                e = nxt | (3 << 5)
             elif an == "END":
-                e = "%d|LXK(%s)" % (nxt | (4 << 8), END_KIND.get(sname, "T_ERROR"))
+                e = nxt | (4 << 5)
             elif an == "END_INCL":
-                e = "%d|LXK(%s)" % (nxt | (5 << 8) | (1 << 12), END_KIND.get(sname, "T_ERROR"))
+                e = nxt | (5 << 5) | (1 << 9)
             elif an == "SINGLE":
-                e = "%d|LXK(%s)" % (0 | (5 << 8) | (3 << 12), hard.get(chr(b), "T_ERROR"))
+                e = 0 | (5 << 5) | (3 << 9)
             else:
-                e = "%d" % (nxt | (8 << 8) | (act << 12))
                 assert act < 16
-            row.append(e)
+                e = nxt | (8 << 5) | (act << 9)
+            row.append(str(e))
         L.append("    // " + sname)
-        for r in range(0, 256, 16):
-            L.append("    " + ",".join(row[r:r + 16]) + ",")
+        for r in range(0, 256, 32):
+            L.append("    " + ",".join(row[r:r + 32]) + ",")
     L.append("};")
     L.append("// kind of the single-character tokens")
     kinds = ["T_ERROR"] * 256
