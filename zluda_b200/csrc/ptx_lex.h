@@ -76,16 +76,29 @@ PTX_HD inline uint32_t cx_compose(uint32_t f, uint32_t g) {
 // a vector that ignores its input and always yields the state reached from CX_CODE (first chunk of a module)
 PTX_HD inline uint32_t cx_restart(uint32_t f) { return (f & 7u) * 0x111111u; }
 
+PTX_HD inline bool cx_word_has(uint32_t w, uint32_t byte) {
+    uint32_t x = w ^ (0x01010101u * byte);
+    return ((x - 0x01010101u) & ~x & 0x80808080u) != 0;
+}
 // transition vector of text[begin, end); begin is a multiple of 4.  `rd` is a text reader (see PtxGlobalReader).
+// Four bytes at a time: a word without '/', '*' and '"' acts as one map (the newline map if it holds a newline, else
+// the map of an ordinary byte: both are idempotent and the newline map absorbs the other), so only words inside or
+// next to comments and strings are walked byte by byte.
 template <class R>
 PTX_HD inline uint32_t cx_chunk_vector(const R& rd, uint32_t begin, uint32_t end) {
-    // track the six states directly; every thread runs the same instructions whatever the bytes are
     uint32_t s0 = 0, s1 = 1, s2 = 2, s3 = 3, s4 = 4, s5 = 5;
     for (uint32_t p = begin; p < end; p += 4) {
         uint32_t wd = rd.word(p);
         uint32_t nb = end - p < 4u ? end - p : 4u;
-        for (uint32_t k = 0; k < nb; k++) {
-            uint32_t v = cx_byte_vector((wd >> (8 * k)) & 0xFFu);
+        if (nb < 4) wd &= (1u << (8 * nb)) - 1u;          // bytes past the end read as NUL: ordinary bytes
+        if (cx_word_has(wd, '/') || cx_word_has(wd, '*') || cx_word_has(wd, '"')) {
+            for (uint32_t k = 0; k < nb; k++) {
+                uint32_t v = cx_byte_vector((wd >> (8 * k)) & 0xFFu);
+                s0 = (v >> (4 * s0)) & 7u; s1 = (v >> (4 * s1)) & 7u; s2 = (v >> (4 * s2)) & 7u;
+                s3 = (v >> (4 * s3)) & 7u; s4 = (v >> (4 * s4)) & 7u; s5 = (v >> (4 * s5)) & 7u;
+            }
+        } else {
+            uint32_t v = (cx_word_has(wd, '\n') || cx_word_has(wd, '\r')) ? cx_byte_vector('\n') : cx_byte_vector('a');
             s0 = (v >> (4 * s0)) & 7u; s1 = (v >> (4 * s1)) & 7u; s2 = (v >> (4 * s2)) & 7u;
             s3 = (v >> (4 * s3)) & 7u; s4 = (v >> (4 * s4)) & 7u; s5 = (v >> (4 * s5)) & 7u;
         }
@@ -403,6 +416,45 @@ PTX_HD inline void lx_chunk(const TX& tx, const uint8_t* g, uint32_t ms, uint32_
     }
 }
 
+// The same lookup through the table keyed by a word's first eight bytes.  Reads up to 11 bytes past `start`: the text
+// buffer must have that much slack (the pipeline's buffers do; a caller's buffer may not: use lx_keyword there).
+PTX_HD inline uint16_t lx_keyword8(const uint8_t* g, uint32_t start, uint32_t len) {
+    if (len > PTX_KW_MAXLEN) return T_ERROR;
+    const uint8_t* a = g + start;
+    const uint32_t sh = (uint32_t)((uintptr_t)a & 3u) * 8u;
+    const uint32_t* w = (const uint32_t*)(a - ((uintptr_t)a & 3u));
+    uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+    uint32_t lo = sh ? (w0 >> sh) | (w1 << (32u - sh)) : w0;
+    uint32_t hi = sh ? (w1 >> sh) | (w2 << (32u - sh)) : w1;
+    if (len < 4) { lo &= (1u << (8u * len)) - 1u; hi = 0; }
+    else if (len < 8) hi &= (1u << (8u * (len - 4u))) - 1u;
+    uint32_t h = (lo ^ hi) * 0x9E3779B1u;
+    h ^= len * 0x85EBCA6Bu;
+    h ^= h >> 15;
+    h *= 0x2C1B3C6Du;
+    h ^= h >> 12;
+    h &= PTX_KW8_SIZE - 1;
+    for (;;) {
+        const PtxKw8Entry e = ptx_kw8_table[h];
+        if (e.kind == 0xFFFF) return T_ERROR;
+        if (e.lo == lo && e.hi == hi && e.len == len) {
+            bool same = true;
+            for (uint32_t i = 8; i < len; i++)
+                if ((uint8_t)ptx_kw_pool[e.off + i] != a[i]) { same = false; break; }
+            if (same) return e.kind;
+        }
+        h = (h + 1) & (PTX_KW8_SIZE - 1);
+    }
+}
+PTX_HD inline uint16_t lx_classify8(const uint8_t* g, uint32_t start, uint32_t len, uint16_t kind) {
+    if (kind == T_IDENT) {
+        if (!lx_alpha(g[start])) return kind;
+    } else if (kind != T_DOTIDENT) {
+        return kind;
+    }
+    uint16_t k = lx_keyword8(g, start, len);
+    return k == T_ERROR ? kind : k;
+}
 // identifiers and dot-identifiers that spell a keyword (opcode, modifier, directive word): one thread per token
 PTX_HD inline uint16_t lx_classify(const uint8_t* g, uint32_t start, uint32_t len, uint16_t kind) {
     if (kind == T_IDENT) {

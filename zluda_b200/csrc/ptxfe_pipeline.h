@@ -387,7 +387,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     // word get that kind on the way
     bk.pf_segments("lex_compact_classify", n_chunks, cnt, [=] PTX_HD(size_t c, uint32_t i, uint32_t j) {
         PtxToken t = slots[c * PTX_CHUNK + i];
-        t.kind = lx_classify(text, t.start, t.len, t.kind);
+        t.kind = lx_classify8(text, t.start, t.len, t.kind);
         tokens[j] = t;
         kinds[j] = t.kind;
     });

@@ -624,6 +624,41 @@ def emit(spec, out_dirs):
             row = []
     w("};")
     w('PTX_TABLE char ptx_kw_pool[] = "%s";' % pool)
+    # ---- the same keywords keyed by their first eight bytes (little-endian, zero padded) and length: a lookup is one
+    # probe and two word compares for keywords of up to eight bytes
+    M32 = 0xFFFFFFFF
+
+    def hash8(lo, hi, ln):
+        h = ((lo ^ hi) * 0x9E3779B1) & M32
+        h ^= (ln * 0x85EBCA6B) & M32
+        h ^= h >> 15
+        h = (h * 0x2C1B3C6D) & M32
+        h ^= h >> 12
+        return h
+
+    size8 = 1024
+    table8 = {}
+    for t in words:
+        b8 = t.encode()[:8].ljust(8, b"\0")
+        lo, hi = int.from_bytes(b8[:4], "little"), int.from_bytes(b8[4:], "little")
+        h = hash8(lo, hi, len(t)) & (size8 - 1)
+        while h in table8:
+            h = (h + 1) & (size8 - 1)
+        table8[h] = (lo, hi, t)
+    w("#define PTX_KW8_SIZE %d" % size8)
+    w("struct PtxKw8Entry { uint32_t lo, hi; uint16_t kind; uint8_t len; uint8_t pad; uint16_t off; uint16_t pad2; };")
+    w("PTX_TABLE PtxKw8Entry ptx_kw8_table[PTX_KW8_SIZE] = {")
+    row = []
+    for h in range(size8):
+        if h in table8:
+            lo, hi, t = table8[h]
+            row.append("{%du,%du,%d,%d,0,%d,0}" % (lo, hi, kind_of[t], len(t), offs[t]))
+        else:
+            row.append("{0,0,0xFFFF,0,0,0,0}")
+        if len(row) == 4:
+            w("    " + ",".join(row) + ",")
+            row = []
+    w("};")
     w("// token text for every literal token kind (host side: dump, oracle lexer)")
     w("PTX_HOST_TABLE char* const ptx_tok_text[T_COUNT] = {")
     texts = [t if t is not None else "" for _, t in BASE_TOKENS] + [t for _, t in WORD_TOKENS] + opcodes + modifiers
