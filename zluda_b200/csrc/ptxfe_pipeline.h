@@ -227,7 +227,6 @@ struct PtxWork {
     uint16_t* kinds = nullptr;             // [n_tokens] tokens[i].kind
     uint8_t* tfirst = nullptr;             // [n_tokens] 1 = first token of a module
     int32_t* mod_final_scope = nullptr;    // [n_modules] scope depth behind the module's last token
-    uint32_t* unit_of_tok = nullptr;       // [n_tokens + 1] exclusive scan of unit-start flags
     uint32_t* unit_start = nullptr;        // [n_units + 1]
     uint32_t* unit_depth = nullptr;        // [n_units]  scope depth in front of the unit | module-first << 31
     uint32_t* unit_end = nullptr;          // [n_units]
@@ -446,7 +445,6 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
     uint8_t* tfirst = w.tfirst = (uint8_t*)bk.alloc((size_t)n_tokens + 16);
     // per token: 0 = no unit starts here; else 1 + scope depth in front of it (clamped), bit 15 = first token of a module
     uint16_t* sd16 = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_tokens + 2));
-    uint32_t* uot = w.unit_of_tok = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_tokens + 2));
     int32_t* mod_final_scope = w.mod_final_scope = (int32_t*)bk.alloc(sizeof(int32_t) * (n_modules + 1));
     w.mod_unit_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 2));
     PtxCounters* counters = w.counters;
@@ -496,24 +494,37 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
             sd16[j] = start ? (uint16_t)(1u + clamped) : (uint16_t)0;
         },
         SegDepthOp(), PtxSeg3{0, 0, 0});
-    // B2: unit index of every token (exclusive count of unit starts)
-    bk.template scan<uint32_t>("scan_unit_index", (size_t)n_tokens + 1, [=] PTX_HD(size_t i) { return (i && sd16[i - 1]) ? 1u : 0u; },
-                               [=] PTX_HD(size_t i, uint32_t v) { uot[i] = v; }, AddOp(), 0u);
-    bk.pf("set_unit_total", 1, [=] PTX_HD(size_t) { counters->n_units = n_tokens ? uot[n_tokens] : 0; });
+    // B2: number the unit starts; the scan itself writes each unit's start token and depth (no per-token index is
+    // kept), the first unit of every module, and the total
+    uint32_t* ustart = w.unit_start = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_tokens + 2));   // at most one unit per token
+    uint32_t* udepth = w.unit_depth = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_tokens + 2));
+    uint32_t* mub = w.mod_unit_begin;
+    bk.pf("reset_unit_total", 1, [=] PTX_HD(size_t) { counters->n_units = 0; });
+    bk.template scan<uint32_t>("scan_unit_index", n_tokens, [=] PTX_HD(size_t i) { return sd16[i] ? 1u : 0u; },
+                               [=] PTX_HD(size_t i, uint32_t v) {
+                                   uint32_t code = sd16[i];
+                                   if (code) {
+                                       uint32_t u = v - 1;
+                                       ustart[u] = (uint32_t)i;
+                                       udepth[u] = ((code & 0x7FFFu) - 1u) | ((code & 0x8000u) ? 0x80000000u : 0u);
+                                       if (code & 0x8000u) mub[ptx_upper_bound_u32(mtb, n_modules, (uint32_t)i) - 1] = u;
+                                   }
+                                   if (i + 1 == n_tokens) counters->n_units = v;
+                               },
+                               AddOp(), 0u);
     bk.download(&host_counters, counters, sizeof(PtxCounters));
     const uint32_t n_units = host_counters.n_units;
-    uint32_t* ustart = w.unit_start = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 2));
-    uint32_t* udepth = w.unit_depth = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
-    // B3: compact
-    bk.pf("compact_unit_starts", n_tokens, [=] PTX_HD(size_t i) {
-        uint32_t code = sd16[i];
-        if (!code) return;
-        uint32_t u = uot[i];
-        ustart[u] = (uint32_t)i;
-        udepth[u] = ((code & 0x7FFFu) - 1u) | ((code & 0x8000u) ? 0x80000000u : 0u);
+    // modules without tokens begin where the next module with tokens begins; mub[n_modules] = n_units
+    bk.pf("module_unit_ranges", n_modules + 1, [=] PTX_HD(size_t m) {
+        if (m < n_modules && mtb[m] < mtb[m + 1]) return;      // written by the scan
+        size_t k = m;
+        while (k < n_modules && mtb[k] == mtb[k + 1]) k++;
+        mub[m] = k < n_modules ? (0x80000000u | (uint32_t)k) : n_units;   // a reference to module k is resolved below
     });
-    uint32_t* mub = w.mod_unit_begin;
-    bk.pf("module_unit_ranges", n_modules + 1, [=] PTX_HD(size_t m) { mub[m] = n_tokens ? uot[mtb[m]] : 0; });
+    bk.pf("module_unit_ranges_fill", n_modules + 1, [=] PTX_HD(size_t m) {
+        uint32_t v = mub[m];
+        if (v & 0x80000000u) mub[m] = mub[v & 0x7FFFFFFFu];
+    });
 }
 
 // ------------------------------------------------------------------------------------------------ stage C: decode
