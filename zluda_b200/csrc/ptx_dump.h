@@ -168,18 +168,39 @@ inline const uint32_t* skip_variable(const uint32_t* w) {
     return skip_inits(p, n_init) + 2;
 }
 
-inline void schema(Out& o, int type, const uint32_t*& w) {
+// cursor over the byte-packed data fields of an instruction record (PtxDecoder::put_packed)
+struct PackedCursor {
+    const uint32_t* w;
+    uint32_t acc = 0, left = 0;
+    uint32_t byte() {
+        if (!left) { acc = *w++; left = 4; }
+        uint32_t b = acc & 0xFFu;
+        acc >>= 8;
+        left--;
+        return b;
+    }
+    uint32_t next() {
+        uint32_t b = byte();
+        if (b != 0xFFu) return b;
+        uint32_t x = byte();
+        x |= byte() << 8;
+        x |= byte() << 16;
+        x |= byte() << 24;
+        return x;
+    }
+};
+inline void schema(Out& o, int type, PackedCursor& w) {
     const PtxType& ty = ptx_types[type];
     switch (ty.kind) {
     case 0:
         switch (ty.a) {
-        case 0: o.put(*w++ ? "true" : "false"); break;
-        case 3: { uint64_t x = w[0] | ((uint64_t)w[1] << 32); w += 2; o.putf("%llu", (unsigned long long)x); break; }
-        case 4: o.putf("bits=0x%08X", *w++); break;
-        default: o.putf("%u", *w++); break;
+        case 0: o.put(w.next() ? "true" : "false"); break;
+        case 3: { uint64_t x = w.next(); x |= (uint64_t)w.next() << 32; o.putf("%llu", (unsigned long long)x); break; }
+        case 4: o.putf("bits=0x%08X", w.next()); break;
+        default: o.putf("%u", w.next()); break;
         }
         break;
-    case 1: o.put(ptx_enum_names[type][*w++]); break;
+    case 1: o.put(ptx_enum_names[type][w.next()]); break;
     case 2:
         o.put(ty.name);
         if (ty.b) {
@@ -194,7 +215,7 @@ inline void schema(Out& o, int type, const uint32_t*& w) {
         }
         break;
     case 3: {
-        const PtxVariant& vr = ptx_variants[ty.a + *w++];
+        const PtxVariant& vr = ptx_variants[ty.a + w.next()];
         o.put(vr.name);
         if (vr.n_fields) {
             o.put(vr.named ? " { " : "(");
@@ -208,15 +229,20 @@ inline void schema(Out& o, int type, const uint32_t*& w) {
         break;
     }
     default:
-        if (*w++) { o.put("Some("); schema(o, ty.a, w); o.put(")"); }
+        if (w.next()) { o.put("Some("); schema(o, ty.a, w); o.put(")"); }
         else o.put("None");
         break;
     }
 }
 
-// U_INSTR payload (after the record header)
-inline void instruction(const Reader& r, Out& o, const uint32_t* w) {
-    uint32_t w1 = *w++;
+// payload words of a record, given its header word
+inline uint32_t rec_len(uint32_t w0) { return (w0 & 0xFF) == U_INSTR ? (w0 >> 8) & 0x3FFFu : w0 >> 8; }
+// U_INSTR / U_INSTR_LONG: `w` = the record (header word first)
+inline void instruction(const Reader& r, Out& o, const uint32_t* rec) {
+    uint32_t w0 = rec[0];
+    const uint32_t* w = rec + 1;
+    // head = has_pred | pred_not << 1 | variant << 16
+    uint32_t w1 = (w0 & 0xFF) == U_INSTR ? (((w0 >> 29) & 3u) | (((w0 >> 22) & 0x7Fu) << 16)) : rec[rec_len(w0)];
     int variant = (int)(w1 >> 16);
     o.put("Instruction(");
     if (w1 & 1) {
@@ -290,8 +316,14 @@ inline void instruction(const Reader& r, Out& o, const uint32_t* w) {
     o.put(" { ");
     if (in.data_type >= 0) {
         o.put("data: ");
-        if (ptx_types[in.data_type].kind == 2 && ptx_types[in.data_type].b == 0) o.put("()");
-        else schema(o, in.data_type, w);
+        if (ptx_types[in.data_type].kind == 2 && ptx_types[in.data_type].b == 0) {
+            o.put("()");
+        } else {
+            PackedCursor cur;
+            cur.w = w;
+            schema(o, in.data_type, cur);
+            w = cur.w;      // the operand records start at the next word
+        }
         if (in.n_args) o.put(", ");
     }
     if (in.n_args) {
@@ -392,7 +424,7 @@ inline std::string dump_module(const PtxBatchView& v, uint32_t m, int* status_ou
         parsed_ok = true;
         if (w == wend) parsed_ok = false;   // no tokens at all: the header does not parse
         while (w < wend) {
-            uint32_t kind = w[0] & 0xFF, len = w[0] >> 8;
+            uint32_t kind = w[0] & 0xFF, len = rec_len(w[0]);
             const uint32_t* next = w + 1 + len;
             switch (kind) {
             case U_HEADER: header = w; break;
@@ -406,8 +438,8 @@ inline std::string dump_module(const PtxBatchView& v, uint32_t m, int* status_ou
                 if (has_body) {
                     // the body runs to the matching U_FUNC_END
                     const uint32_t* q = next;
-                    while (q < wend && (q[0] & 0xFF) != U_FUNC_END) q += 1 + (q[0] >> 8);
-                    if (q < wend) q += 1 + (q[0] >> 8);
+                    while (q < wend && (q[0] & 0xFF) != U_FUNC_END) q += 1 + rec_len(q[0]);
+                    if (q < wend) q += 1 + rec_len(q[0]);
                     next = q;
                 }
                 d.end = next;
@@ -505,14 +537,15 @@ inline std::string dump_module(const PtxBatchView& v, uint32_t m, int* status_ou
             if (!(flags & FUNC_HAS_BODY)) { o.put("], body: None })\n"); continue; }
             o.put("], body: Some([\n");
             int depth = 1;
-            const uint32_t* q = p + 1 + (p[0] >> 8);
+            const uint32_t* q = p + 1 + rec_len(p[0]);
             while (q < d.end) {
-                uint32_t kind = q[0] & 0xFF, len = q[0] >> 8;
+                uint32_t kind = q[0] & 0xFF, len = rec_len(q[0]);
                 const uint32_t* payload = q + 1;
                 switch (kind) {
                 case U_LABEL: o.indent(depth); o.put("Label("); r.span(o, payload[0], payload[1]); o.put(")\n"); break;
                 case U_VAR: o.indent(depth); multi_variable_stmt(r, o, payload); break;
-                case U_INSTR: o.indent(depth); instruction(r, o, payload); break;
+                case U_INSTR:
+                case U_INSTR_LONG: o.indent(depth); instruction(r, o, q); break;
                 case U_BLOCK_OPEN: o.indent(depth); o.put("Block([\n"); depth++; break;
                 case U_BLOCK_CLOSE: depth--; o.indent(depth); o.put("])\n"); break;
                 default: break;
