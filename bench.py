@@ -36,11 +36,7 @@ UNIT = "GB/s"
 
 
 # (dram__bytes_read.sum + dram__bytes_write.sum) / text bytes, from the ncu captures summarised under profiles/
-NCU_DRAM_BYTES_PER_TEXT_BYTE = {
-    "decode_units": 25.30,          # profiles/decode_units_staged_kernel_config1_64MiB.md
-    "lex_context_vectors": 1.01, "lex_count_tokens": 1.05, "lex_emit_tokens": 4.84,   # profiles/lex_tile_kernels_config1_64MiB.md
-    "gather_records": 4.85,         # profiles/gather_records_config1_64MiB.md
-}
+NCU_DRAM_BYTES_PER_TEXT_BYTE = {}
 
 
 def measured_hbm_peak():
@@ -278,10 +274,10 @@ def main():
     T, W, N = stats["n_tokens"], stats["n_result_words"], nbytes
     U = stats["n_units"]
     algo = {   # algorithmic bytes per launch: text read once, tokens / records read or written once
-        "lex_context_vectors": N, "lex_count_tokens": N, "lex_emit_tokens": N + 8 * T, "lex_classify_keywords": 8 * T + N,
-        "classify_braces": 8 * T + T, "speculate_unit_starts": 8 * T + 8 * T + T, "scan_depth": 9 * T + 8 * T,
-        "unit_shape_key": 8 * T + 6 * U,
-        "decode_units": N + 8 * T + 4 * W, "gather_records": 8 * W + 9 * U, "decode_emit_flagged": 5 * U,
+        "lex_context_vectors": N, "lex_tokens": N + 8 * T, "lex_compact_classify": 18 * T + N,
+        "scan_depth": 8 * T, "scan_unit_index": 4 * T + 8 * U,
+        "unit_shape_key": 2 * T + 10 * U, "apply_templates": 2 * T + 16 * U, "class_insert": 12 * U,
+        "emit_records": 4 * W + 9 * U, "decode_units": N + 8 * T + 4 * W, "decode_emit_flagged": 5 * U,
     }
     top = max(prof, key=prof.get) if prof else None
     roof = None
@@ -295,9 +291,8 @@ def main():
         roof = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                 "frac": ach / peak if ach else None, "traffic": tpb * N if tpb else None, "ms_per_launch": ms, "algorithmic_bytes": ab,
                 "lexer_segmenter": None}
-        lex_ms = sum(prof.get(k, 0.0) for k in ("lex_context_vectors", "scan_context", "lex_count_tokens", "scan_token_counts",
-                                                  "lex_emit_tokens", "lex_classify_keywords", "classify_braces", "scan_depth", "speculate_unit_starts",
-                                                  "scan_unit_index", "compact_unit_starts")) / a.steps
+        lex_ms = sum(prof.get(k, 0.0) for k in ("lex_context_vectors", "scan_context", "lex_tokens", "scan_token_counts",
+                                                  "lex_compact_classify", "scan_depth", "scan_unit_index")) / a.steps
         if lex_ms > 0:
             a_lex = N + 8 * T
             roof["lexer_segmenter"] = {"ms": lex_ms, "algorithmic_bytes": a_lex, "achieved": a_lex / (lex_ms / 1e3) / 1e9,
