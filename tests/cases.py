@@ -79,3 +79,45 @@ def all_cases():
     out += [body(s) for s in STATEMENTS]
     out += MODULES
     return out
+
+
+def class_cases():
+    """Statements of one shape that must NOT share a record: the decoder's result depends on a token's text (numbers,
+    dot-identifiers, %envreg names) or on its surroundings, and statements of one shape that must (only names differ).
+    Every module repeats each statement, so that all but the first meet an existing class."""
+    groups = [
+        # same kinds, different identifier spellings and lengths: one class, records differ in offsets and lengths only
+        ["add.s32 %r1, %r2, %r3;", "add.s32 %rd10, %a, %bb;", "add.s32 %r1,%r2,%r3;", "add.s32   %x ,\n %yy , %zzz ;"],
+        # the spelling of a number is part of the class
+        ["mov.u32 %r1, 1;", "mov.u32 %r1, 2;", "mov.u32 %r1, 0x2;", "mov.u32 %r1, 02;", "mov.u32 %r1, 2U;", "mov.u32 %r1, 99999999999;"],
+        ["mov.f32 %f1, 0f3F800000;", "mov.f32 %f1, 0f40000000;", "mov.f64 %fd1, 1.5;", "mov.f64 %fd1, 1.5e3;", "mov.f64 %fd1, 0d3FF0000000000000;"],
+        ["ld.global.u32 %r1, [%rd1+4];", "ld.global.u32 %r1, [%rd1+8];", "ld.global.u32 %r1, [%rd1+-4];", "ld.global.u32 %r1, [%rd1];"],
+        # vector members and unknown dot words
+        ["mov.u32 %r1, %tid.x;", "mov.u32 %r1, %tid.y;", "mov.u32 %r1, %tid.z;", "mov.u32 %r1, %tid.w;", "mov.u32 %r1, %tid.q;"],
+        # %envreg names raise an error, other names of the same length do not
+        ["mov.b32 %r1, %envreg3;", "mov.b32 %r1, %envrex3;", "mov.b32 %r1, %envreg12;", "mov.b32 %r1, %envreg33;", "mov.b32 %r1, %envreg0;"],
+        # predicates, labels, branches, blocks
+        ["@%p1 bra L1;", "@!%p1 bra L1;", "@%p22 bra LONGER_LABEL;", "L1:", "LONGER_LABEL:", "bra.uni L1;", "{", "}", "ret;"],
+        # variables
+        [".reg .b32 %r<10>;", ".reg .b32 %r<11>;", ".reg .b32 %q<10>;", ".reg .pred %p;", ".reg .f32 %a, %b;", ".local .align 8 .b8 buf[16];",
+         ".local .align 8 .b8 buf[32];", ".shared .u32 s = 1;"],
+        # .loc lines ride with the next statement; the extended forms read identifier spellings
+        [".loc 1 2 3", ".loc 1 2 4", ".loc 1 2 3, function_name foo, inlined_at 1 2 3", ".loc 1 2 3, function_nam foo, inlined_at 1 2 3"],
+        # calls reserve an error slot and need the function table: never templated
+        ["call foo, (%r1);", "call (%r1), foo, (%r2);", "call bar;"],
+        # vectors, strings, pragmas
+        ["ld.global.v4.u32 {%r1,%r2,%r3,%r4}, [%rd1];", "ld.global.v4.u32 {%r1, %r2, %r3, _}, [%rd1];", "ld.global.v2.u32 {%r1,%r2}, [%rd1];",
+         ".pragma \"nounroll\";", ".pragma \"unroll 4\";"],
+        # errors inside one statement of a shape that is fine elsewhere
+        ["add.s32 %r1, %r2;", "add.s32 %r1, %r2, %r3, %r4;", "add.s33 %r1, %r2, %r3;", "add.s32 %r1, %r2, %r3"],
+    ]
+    out = []
+    for g in groups:
+        stmts = []
+        for rep in range(3):
+            stmts += g
+        out.append(body("\n".join(stmts)))
+    # everything together, twice, in two functions: classes are shared across functions and modules
+    allstmts = "\n".join(st for g in groups[:7] for st in g)
+    out.append(body(allstmts + "\n" + allstmts))
+    return out

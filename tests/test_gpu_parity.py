@@ -55,6 +55,14 @@ def test_edge_cases_and_golden_hashes(oracle, ctx):
         b.free()
 
 
+def test_statement_classes(oracle, ctx):
+    """Record templates: statements of one shape share the grammar work; what must stay different does.  Parsed twice
+    in one batch and as several batches through one context (the class store is emptied per batch)."""
+    texts = cases.class_cases()
+    assert_parity(oracle, ctx, texts)
+    assert_parity(oracle, ctx, texts + texts[::-1], modes=(0,))
+
+
 def test_lexer_tokens(oracle, ctx):
     rng = random.Random(7)
     pieces = ["add", ".f32", "%r1", ",", ";", " ", "\n", "// c\n", "/* x */", "/*", "*/", "\"s\"", "\"", "0f3F800000", "0x1F", "1.5e-3",

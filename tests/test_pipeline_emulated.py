@@ -56,6 +56,11 @@ def test_edge_cases(oracle, emu):
     assert stats["sequential"] < len(cases.all_cases()) // 2
 
 
+def test_statement_classes(oracle, emu):
+    """Record templates: statements of one shape share the grammar work; what must stay different does."""
+    assert_parity(oracle, emu, cases.class_cases())
+
+
 def test_edge_cases_in_reverse_thread_order(oracle, emu, monkeypatch):
     """Every parallel-for of the pipeline run backwards: no step may depend on the order of its threads."""
     monkeypatch.setenv("PTXFE_EMU_ORDER", "reverse")
