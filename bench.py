@@ -234,7 +234,8 @@ def main():
         sampler.join()
         print(json.dumps({"kernels_only": True, "text_bytes": nbytes, "steps": a.steps, "ms_per_step": kernel_ms / a.steps,
                           "kernels_ms": {k: v / a.steps for k, v in sorted(prof.items(), key=lambda kv: -kv[1])},
-                          "gpu_launches": int(stats["n_kernel_launches"]) * a.steps}))
+                          "gpu_launches": int(stats["n_kernel_launches"]) * a.steps,
+                          "step_order": [n for n, _ in ctx.profile_steps()]}))
         return
     # ---- end to end through the public call: pinned host text in, records out
     for _ in range(min(2, a.warmup)):

@@ -219,6 +219,15 @@ class Context:
                 out[name] = out.get(name, 0.0) + float(ms)
         return out
 
+    def profile_steps(self):
+        """[(step name, milliseconds)] of the last run in launch order (needs PTXFE_PROFILE=1 at creation)."""
+        out = []
+        for line in lib().ptxfe_profile(self._h).decode().split("\n"):
+            if line:
+                name, ms = line.split()
+                out.append((name, float(ms)))
+        return out
+
     def lex(self, text):
         """Lexer only: ([(kind, start, length)], [(start, length) of lex errors])."""
         if isinstance(text, str):

@@ -71,6 +71,12 @@ enum { PTX_UNIT_STAGED = 0, PTX_UNIT_FLAGGED = 1, PTX_UNIT_NOTHING = 2, PTX_UNIT
 struct PtxTemplateInfo {
     uint32_t n_words, n_tokens, ok, depth1;
 };
+// The per-token side array `kinds` holds kind | min(length, 127) << 9: most passes want the kind alone, and the class
+// passes can tell from the length whether they have to look at the token itself.
+#define PTX_KL_KIND(x) ((uint16_t)((x) & 0x1FFu))
+#define PTX_KL_LEN(x) ((uint32_t)(x) >> 9)
+#define PTX_KL_LONG 127u
+static_assert(T_COUNT <= 512, "token kinds must fit 9 bits of the kinds array");
 PTX_HD inline bool ptx_text_matters(uint16_t k) {
     return k == T_DECIMAL || k == T_HEX || k == T_F32HEX || k == T_F64HEX || k == T_F64 || k == T_DOTIDENT || k == T_STRING;
 }
@@ -80,7 +86,8 @@ PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens
     if (depth == 0 || module_first || end - start > PTX_MAX_CLASS_TOKENS || end <= start) return 0;
     uint32_t h1 = 2166136261u ^ (depth == 1 ? 1u : 0u), h2 = 0x811C9DC5u + (end - start);
     for (uint32_t i = start; i < end; i++) {
-        const uint16_t kind = kinds[i];
+        const uint32_t kl = kinds[i];
+        const uint16_t kind = PTX_KL_KIND(kl);
         h1 = (h1 ^ kind) * 16777619u;
         h2 = (h2 + kind) * 0x9E3779B1u;
         h2 ^= h2 >> 15;
@@ -94,9 +101,12 @@ PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens
                 h2 = (h2 + c) * 0x9E3779B1u;
             }
         } else if (kind == T_IDENT) {
-            const PtxToken t = tokens[i];
-            if (t.len == 0xFFFF) return 0;
-            if ((t.len == 8 || t.len == 9) && ptx_envreg_number(text + t.start, t.len)) h1 = (h1 ^ 0x1234u) * 16777619u;
+            const uint32_t l = PTX_KL_LEN(kl);
+            if (l == PTX_KL_LONG) {
+                if (tokens[i].len == 0xFFFF) return 0;
+            } else if (l == 8 || l == 9) {
+                if (ptx_envreg_number(text + tokens[i].start, l)) h1 = (h1 ^ 0x1234u) * 16777619u;
+            }
         }
     }
     uint64_t k = ((uint64_t)h1 << 32) | h2;
@@ -166,22 +176,30 @@ PTX_HD inline void ptx_signature_write(uint32_t* sig, const uint8_t* text, const
     }
 }
 // exact check that the unit with tokens [start, start + n) at depth class depth1 has this signature
-PTX_HD inline bool ptx_signature_matches(const uint32_t* sig, const uint8_t* text, const PtxToken* tokens, uint32_t start, uint32_t n, uint32_t depth1) {
+PTX_HD inline bool ptx_signature_matches(const uint32_t* sig, const uint8_t* text, const PtxToken* tokens, const uint16_t* kinds, uint32_t start,
+                                         uint32_t n, uint32_t depth1) {
     if (*sig++ != (n | (depth1 << 31))) return false;
     for (uint32_t i = 0; i < n; i++) {
-        const PtxToken t = tokens[start + i];
+        const uint32_t kl = kinds[start + i];
+        const uint16_t kind = PTX_KL_KIND(kl);
         uint32_t head = *sig++;
-        if ((head & 0xFFFFu) != t.kind) return false;
-        if (ptx_text_matters(t.kind)) {
+        if ((head & 0xFFFFu) != kind) return false;
+        if (ptx_text_matters(kind)) {
+            const PtxToken t = tokens[start + i];
             if ((head >> 16) != t.len || t.len == 0xFFFF) return false;
             for (uint32_t j = 0; j < t.len; j += 4) {
                 uint32_t v = 0;
                 for (uint32_t k = 0; k < 4 && j + k < t.len; k++) v |= (uint32_t)text[t.start + j + k] << (8 * k);
                 if (*sig++ != v) return false;
             }
-        } else if (t.kind == T_IDENT) {
-            if (t.len == 0xFFFF) return false;
-            bool e = (t.len == 8 || t.len == 9) && ptx_envreg_number(text + t.start, t.len);
+        } else if (kind == T_IDENT) {
+            const uint32_t l = PTX_KL_LEN(kl);
+            bool e = false;
+            if (l == PTX_KL_LONG) {
+                if (tokens[start + i].len == 0xFFFF) return false;
+            } else if (l == 8 || l == 9) {
+                e = ptx_envreg_number(text + tokens[start + i].start, l) != 0;
+            }
             if ((head >> 16) != (e ? 1u : 0u)) return false;
         }
     }
@@ -224,7 +242,7 @@ struct PtxWork {
     uint32_t* lexerrs = nullptr;           // [2 * n_lexerrs]
     uint32_t* mod_tok_begin = nullptr;     // [n_modules + 1]
     bool first_slice = true;               // the class store is emptied before the first slice of a batch
-    uint16_t* kinds = nullptr;             // [n_tokens] tokens[i].kind
+    uint16_t* kinds = nullptr;             // [n_tokens] tokens[i].kind | min(tokens[i].len, 127) << 9
     uint8_t* tfirst = nullptr;             // [n_tokens] 1 = first token of a module
     int32_t* mod_final_scope = nullptr;    // [n_modules] scope depth behind the module's last token
     uint32_t* unit_start = nullptr;        // [n_units + 1]
@@ -388,7 +406,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         PtxToken t = slots[c * PTX_CHUNK + i];
         t.kind = lx_classify8(text, t.start, t.len, t.kind);
         tokens[j] = t;
-        kinds[j] = t.kind;
+        kinds[j] = (uint16_t)(t.kind | ((t.len < PTX_KL_LONG ? t.len : PTX_KL_LONG) << 9));
     });
     // A6: lexer errors are rare: a second walk, only when there are any, and only over the chunks that have one
     if (n_lexerrs) bk.pf_text("lex_emit_errors", n_chunks, text, PtxLexErrorsStep{info, text, vec, cnt, lexerrs});
@@ -424,13 +442,13 @@ PTX_HD inline bool ptx_is_directive_start(uint16_t k) {
 // scope delta of token i: +1 for a '{' that opens a scope, -1 for a '}' that closes one, 0 otherwise (also for the
 // braces of vector operands, initialisers and .section bodies, told apart by two tokens of left context)
 PTX_HD inline int ptx_brace_class(const uint16_t* kinds, const uint8_t* tfirst, size_t i) {
-    uint16_t k = kinds[i];
+    uint16_t k = PTX_KL_KIND(kinds[i]);
     if (k != T_LBRACE && k != T_RBRACE) return 0;
     bool first = tfirst[i] != 0;
-    uint16_t prev = first ? (uint16_t)0xFFFE : kinds[i - 1];
+    uint16_t prev = first ? (uint16_t)0xFFFE : PTX_KL_KIND(kinds[i - 1]);
     if (k == T_LBRACE) {
         bool section = false;
-        if (!first && i >= 2 && !tfirst[i - 1]) section = kinds[i - 2] == T_DOT_SECTION;
+        if (!first && i >= 2 && !tfirst[i - 1]) section = PTX_KL_KIND(kinds[i - 2]) == T_DOT_SECTION;
         return (!ptx_opens_operand(prev) && !section) ? 1 : 0;
     }
     return (prev == T_SEMI || prev == T_COLON || prev == T_LBRACE || prev == T_RBRACE) ? -1 : 0;
@@ -465,7 +483,7 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
         "scan_depth", n_tokens,
         [=] PTX_HD(size_t i) {
             PtxSeg3 v;
-            uint16_t k = kinds[i];
+            uint16_t k = PTX_KL_KIND(kinds[i]);
             v.scope = ptx_brace_class(kinds, tfirst, i);
             v.paren = k == T_LPAREN ? 1 : k == T_RPAREN ? -1 : 0;
             v.flag = tfirst[i] ? 1 : 0;
@@ -479,7 +497,7 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
             if (j == n_tokens) return;
             if (tfirst[j]) { sd16[j] = (uint16_t)(1u | 0x8000u); return; }
             int32_t sd = v.scope, pd = v.paren;
-            uint16_t k = kinds[j], prev = kinds[i];
+            uint16_t k = PTX_KL_KIND(kinds[j]), prev = PTX_KL_KIND(kinds[i]);
             bool start;
             if (sd <= 0) {
                 // top level: a directive keyword outside parentheses that does not continue a run of linking keywords
@@ -568,25 +586,17 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     bk.pf("reset_mismatch", 1, [=] PTX_HD(size_t) { counters->pad = 0; });
     PtxFnEntry* fn_entries = w.fn_entries = (PtxFnEntry*)bk.alloc(sizeof(PtxFnEntry) * ((size_t)max_funcs + 1));
 
-    // Units are decoded in the order of a "shape key" (a hash of their token kinds): the decoder's control flow depends
-    // on token kinds only, so the threads of a warp then follow the same path.  Results are still written at
-    // offsets computed in unit order, so the order of processing does not show in the output.
+    // T0: class key of every unit (see "unit classes and record templates" above)
     uint16_t* ukey = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_units + 2));
     uint32_t* order = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
     uint64_t* ckey_of = (uint64_t*)bk.alloc(sizeof(uint64_t) * ((size_t)n_units + 1));
-    bk.pf("unit_shape_key", n_units, [=] PTX_HD(size_t u) {
+    bk.pf("unit_class_key", n_units, [=] PTX_HD(size_t u) {
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         uint32_t start = ustart[u];
         uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
         uint32_t dp = udepth[u];
         ckey_of[u] = mod_skip[m] ? 0 : ptx_class_key(text, tokens, kinds, start, end, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
-        if (end > start + 20) end = start + 20;
-        uint32_t h = 2166136261u ^ (udepth[u] >> 31) ^ ((udepth[u] & 0x7FFFFFFFu) ? 2u : 0u);
-        for (uint32_t i = start; i < end; i++) h = (h ^ kinds[i]) * 16777619u;
-        h ^= h >> 15;
-        ukey[u] = (uint16_t)(h & (PTX_SORT_BUCKETS - 1));
     });
-    bk.sort_by_key("sort_units_by_shape", n_units, ukey, order);
 
     // T1: class table (open addressing on the 64-bit key), shared by the slices of a batch; the thread that inserts
     // a key makes its unit the representative of the class
@@ -686,7 +696,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
         uint32_t dp = udepth[u];
         uint32_t depth1 = (dp & 0x7FFFFFFFu) == 1 ? 1u : 0u;
-        if (end - start != ti.n_tokens || !ptx_signature_matches(cs.sig_pool + cs.sig_off[id], text, tokens, start, ti.n_tokens, depth1)) return;
+        if (end - start != ti.n_tokens || !ptx_signature_matches(cs.sig_pool + cs.sig_off[id], text, tokens, kinds, start, ti.n_tokens, depth1)) return;
         PtxPair sz;
         sz.a = ti.n_words;
         sz.b = 0;
@@ -697,6 +707,22 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         uflag[u] = PTX_UNIT_TEMPLATED;
         utmpl[u] = id;
     });
+
+    // The units without a template are decoded in the order of a "shape key" (a hash of their token kinds): the
+    // decoder's control flow depends on token kinds only, so the threads of a warp then follow the same path.  Results
+    // are still written at offsets computed in unit order, so the order of processing does not show in the output.
+    bk.pf("unit_shape_key", n_units, [=] PTX_HD(size_t u) {
+        if (uflag[u] == PTX_UNIT_TEMPLATED) { ukey[u] = (uint16_t)(PTX_SORT_BUCKETS - 1); return; }
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        uint32_t start = ustart[u];
+        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        if (end > start + 20) end = start + 20;
+        uint32_t h = 2166136261u ^ (udepth[u] >> 31) ^ ((udepth[u] & 0x7FFFFFFFu) ? 2u : 0u);
+        for (uint32_t i = start; i < end; i++) h = (h ^ PTX_KL_KIND(kinds[i])) * 16777619u;
+        h ^= h >> 15;
+        ukey[u] = (uint16_t)(h & (PTX_SORT_BUCKETS - 1));
+    });
+    bk.sort_by_key("sort_units_by_shape", n_units, ukey, order);
 
     // C1: decode every unit once.  The record is built in a small per-thread staging buffer (failed alternatives are
     // rolled back there) and lands in row u of a table; its final place is known only after the sizes are scanned.
