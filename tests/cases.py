@@ -121,3 +121,43 @@ def class_cases():
     allstmts = "\n".join(st for g in groups[:7] for st in g)
     out.append(body(allstmts + "\n" + allstmts))
     return out
+
+
+def bulk_cases(n=9000):
+    """Arrays whose initialiser is long enough for the bulk path (one thread per element), regular and not."""
+    import random
+    rng = random.Random(5)
+
+    def elems(k):
+        out = []
+        for _ in range(k):
+            r = rng.random()
+            out.append(str(rng.randrange(1 << 31)) if r < 0.5 else hex(rng.randrange(1 << 32)) if r < 0.8 else "-%d" % rng.randrange(1000))
+        return out
+
+    def mod(decl, items, tail="};"):
+        return HEADER + decl + " = {" + ", ".join(items) + tail + "\n.visible .entry k()\n{\nret;\n}\n"
+
+    e = elems(n)
+    f = ["%d.5" % i for i in range(n)]
+    names = ["sym%d" % (i % 7) for i in range(n)]
+    out = [
+        mod(".global .align 4 .s64 a[%d]" % n, e),                               # regular
+        mod(".global .align 4 .s64 a[%d]" % (n + 100), e),                       # fewer elements than the dimension
+        mod(".global .align 4 .s64 a[%d]" % (n - 1), e),                         # one element too many
+        mod(".const .align 8 .f64 c[%d]" % n, f),                                # floats
+        mod(".global .align 8 .u64 p[%d]" % n, names),                           # names
+        mod(".global .align 4 .s64 a[%d]" % n, e[:-1] + ["99999999999999999999999"]),   # an element that overflows
+        mod(".global .align 4 .s64 a[%d]" % n, e, tail=",};"),                   # trailing comma
+        mod(".global .align 4 .s64 a[%d]" % n, e[:50] + ["{1}"] + e[51:]),       # a brace inside
+        mod(".global .align 4 .s64 a[%d]" % n, e[:50] + [""] + e[51:]),          # an empty element
+        mod(".global .align 4 .s64 a[%d]" % n, e, tail="}"),                     # no semicolon
+        mod(".global .align 4 .s64 a[%d]" % n, e[:70] + ["1 2"] + e[71:]),       # two numbers without a comma
+        mod(".global .align 4 .s64 a[]" , e),                                    # unsized array
+        mod(".global .align 4 .v2 .s64 a[%d]" % n, e),                           # vector type: no initialiser list allowed
+        mod(".extern .global .align 4 .s64 a[%d]" % n, e),
+    ]
+    # two long arrays and ordinary code in one module
+    out.append(HEADER + ".global .align 4 .s64 a[%d] = {%s};\n.global .align 4 .u32 b[%d] = {%s};\n" % (n, ", ".join(e), n, ", ".join(e[::-1]))
+               + ".visible .entry k()\n{\n" + DECLS + "\nadd.s32 %r1, %r2, %r3;\nret;\n}\n")
+    return out

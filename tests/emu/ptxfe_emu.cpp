@@ -140,6 +140,7 @@ char* emu_parse(const char* const* texts, const uint64_t* lens, uint32_t n, uint
         stats[3] = hc.n_errs;
         stats[4] = seq;
         stats[5] = hc.pad;
+        stats[6] = hc.n_bulk;
     }
     char* r = (char*)malloc(all.size() + 1);
     memcpy(r, all.data(), all.size());

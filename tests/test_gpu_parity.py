@@ -63,6 +63,11 @@ def test_statement_classes(oracle, ctx):
     assert_parity(oracle, ctx, texts + texts[::-1], modes=(0,))
 
 
+def test_bulk_initialisers(oracle, ctx):
+    """Initialiser lists long enough for the element-parallel path, regular and irregular."""
+    assert_parity(oracle, ctx, cases.bulk_cases(), modes=(0, 2))
+
+
 def test_lexer_tokens(oracle, ctx):
     rng = random.Random(7)
     pieces = ["add", ".f32", "%r1", ",", ";", " ", "\n", "// c\n", "/* x */", "/*", "*/", "\"s\"", "\"", "0f3F800000", "0x1F", "1.5e-3",

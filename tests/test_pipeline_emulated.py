@@ -61,6 +61,13 @@ def test_statement_classes(oracle, emu):
     assert_parity(oracle, emu, cases.class_cases())
 
 
+def test_bulk_initialisers(oracle, emu):
+    """Initialiser lists long enough for the element-parallel path, regular and irregular."""
+    texts = cases.bulk_cases()
+    stats = assert_parity(oracle, emu, texts, modes=(0, 2))
+    assert stats["bulk"] >= len(texts)      # every module has at least one statement that long
+
+
 def test_edge_cases_in_reverse_thread_order(oracle, emu, monkeypatch):
     """Every parallel-for of the pipeline run backwards: no step may depend on the order of its threads."""
     monkeypatch.setenv("PTXFE_EMU_ORDER", "reverse")

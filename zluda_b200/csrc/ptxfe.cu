@@ -570,7 +570,7 @@ int ptxfe_create(int device, ptxfe_ctx** out) {
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->s_in, cudaStreamNonBlocking);
     if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->s_out, cudaStreamNonBlocking);
     for (int i = 0; i < 8 && e == cudaSuccess; i++) e = cudaEventCreate(&ctx->ev[i]);
-    if (e == cudaSuccess) e = cudaHostAlloc((void**)&ctx->h_counters, sizeof(PtxCounters) * 4, cudaHostAllocMapped);
+    if (e == cudaSuccess) e = cudaHostAlloc((void**)&ctx->h_counters, 4096, cudaHostAllocMapped);   // counters and other small read-backs
     if (e == cudaSuccess) e = cudaHostGetDevicePointer(&ctx->d_counters_mapped, ctx->h_counters, 0);
     if (e != cudaSuccess) {
         fprintf(stderr, "ptxfe: context set-up failed: %s\n", cudaGetErrorString(e));

@@ -47,6 +47,8 @@ struct PtxSeg3 {
 };
 
 #define PTX_SORT_BUCKETS 4096u
+#define PTX_BULK_MIN_TOKENS 8192u   // statements at least this long get the bulk initialiser path
+#define PTX_MAX_BULK 32u            // per batch slice; further ones are decoded by one thread each
 #define PTX_TMP_STRIDE 48u     // words per unit in the staging table of the first decode pass (192 bytes: sector aligned)
 
 // fast per-thread memory the backend lends to a staged decoder: room for `stage_cap` record words (word k at
@@ -216,7 +218,7 @@ struct PtxStaged {
 struct PtxCounters {
     uint32_t n_tokens, n_lexerrs, n_units, n_words, n_errs, n_funcs, any_sequential, pad;
     uint32_t n_flagged;         // units whose records are written by the second decode pass
-    uint32_t pad2;
+    uint32_t n_bulk;            // statements long enough for the bulk initialiser path
 };
 
 PTX_HD inline uint32_t ptx_upper_bound_u32(const uint32_t* a, uint32_t n, uint32_t x) {
@@ -576,6 +578,33 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     // C0: ordinal of the enclosing top-level unit
     bk.template scan<uint32_t>("scan_toplevel_ordinal", n_units, [=] PTX_HD(size_t u) { return (udepth[u] & 0x7FFFFFFFu) == 0 ? 1u : 0u; },
                                [=] PTX_HD(size_t u, uint32_t v) { udir[u] = v; }, AddOp(), 0u);
+    // Very long top-level statements (arrays with huge initialisers) are listed for the bulk path
+    PtxBulkInfo* bulk_info = (PtxBulkInfo*)bk.alloc(sizeof(PtxBulkInfo) * PTX_MAX_BULK);
+    bk.pf("reset_bulk", 1, [=] PTX_HD(size_t) { counters->n_bulk = 0; });
+    bk.pf("find_bulk_units", n_units, [=] PTX_HD(size_t u) {
+        uint32_t dp = udepth[u];
+        if (dp != 0) return;       // top level, not the module header
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        if (mod_skip[m]) return;
+        uint32_t start = ustart[u];
+        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        if (end - start < PTX_BULK_MIN_TOKENS) return;
+#ifdef __CUDA_ARCH__
+        uint32_t slot = atomicAdd(&counters->n_bulk, 1u);
+#else
+        uint32_t slot = counters->n_bulk++;
+#endif
+        if (slot >= PTX_MAX_BULK) return;
+        PtxBulkInfo bi;
+        bi.first_tok = start;      // for now: the statement's token range
+        bi.close_tok = end;
+        bi.n_elems = bi.n_words = 0;
+        bi.bad = 1;
+        bi.unit = (uint32_t)u;
+        bi.elems = nullptr;
+        bi.dst = nullptr;
+        bulk_info[slot] = bi;
+    });
     bk.pf("reset_func_count", 1, [=] PTX_HD(size_t) {
         counters->n_funcs = 0;
         counters->any_sequential = 0;
@@ -584,6 +613,98 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     bk.download(&host_counters, counters, sizeof(PtxCounters));
     const uint32_t max_funcs = host_counters.pad;
     bk.pf("reset_mismatch", 1, [=] PTX_HD(size_t) { counters->pad = 0; });
+    // Bulk path: the elements of each listed statement's initialiser are decoded one thread per element into a dense
+    // run; the statement's own decoder later takes the run in one step (PtxDecoder::multi_variable).  A list that is
+    // not plainly "element, element, ... }" followed by ';' stays marked bad and is decoded the ordinary way.
+    const uint32_t n_bulk = host_counters.n_bulk < PTX_MAX_BULK ? host_counters.n_bulk : PTX_MAX_BULK;
+    PtxBulkTable bulk_table;
+    bulk_table.info = bulk_info;
+    bulk_table.n = n_bulk;
+    uint32_t bulk_tokens[PTX_MAX_BULK];     // tokens of each listed statement
+    if (n_bulk) {
+        PtxBulkInfo host_bulk[PTX_MAX_BULK];
+        bk.download(host_bulk, bulk_info, sizeof(PtxBulkInfo) * n_bulk);
+        for (uint32_t j = 0; j < n_bulk; j++) {
+            const uint32_t ts = host_bulk[j].first_tok, te = host_bulk[j].close_tok, nt = te - ts;
+            bulk_tokens[j] = nt;
+            PtxBulkInfo* bi = bulk_info + j;
+            uint32_t* lo_dev = (uint32_t*)bk.alloc(sizeof(uint32_t) * 4);
+            PtxPair* esz = (PtxPair*)bk.alloc(sizeof(PtxPair) * ((size_t)nt + 2));
+            uint32_t* elems = (uint32_t*)bk.alloc(sizeof(uint32_t) * (2 * (size_t)nt + 8));
+            bk.pf("bulk_reset", 1, [=] PTX_HD(size_t) { lo_dev[0] = PTX_ABSENT; lo_dev[1] = 0; });
+            bk.pf("bulk_find_open", nt, [=] PTX_HD(size_t k) {
+                uint32_t i = ts + (uint32_t)k;
+                if (i > ts && PTX_KL_KIND(kinds[i]) == T_LBRACE && PTX_KL_KIND(kinds[i - 1]) == T_EQ) {
+#ifdef __CUDA_ARCH__
+                    atomicMin(&lo_dev[0], i);
+#else
+                    if (i < lo_dev[0]) lo_dev[0] = i;
+#endif
+                }
+            });
+            bk.pf("bulk_measure", nt, [=] PTX_HD(size_t k) {
+                uint32_t i = ts + (uint32_t)k;
+                PtxPair z;
+                z.a = z.b = 0;
+                esz[k] = z;
+                const uint32_t lo = lo_dev[0], hi = te - 2;
+                bool shape_ok = lo != PTX_ABSENT && nt >= 6 && lo + 1 < hi && PTX_KL_KIND(kinds[te - 2]) == T_RBRACE &&
+                                PTX_KL_KIND(kinds[te - 1]) == T_SEMI && PTX_KL_KIND(kinds[hi - 1]) != T_COMMA;
+                if (!shape_ok) { if (k == 0) lo_dev[1] = 1; return; }
+                if (i <= lo || i >= hi) return;
+                uint16_t kd = PTX_KL_KIND(kinds[i]);
+                if (kd == T_LBRACE || kd == T_RBRACE) { lo_dev[1] = 1; return; }
+                if (!(i == lo + 1 || PTX_KL_KIND(kinds[i - 1]) == T_COMMA)) return;
+                // an element starts here: measure it
+                uint32_t mm = ptx_upper_bound_u32(mtb, n_modules, i) - 1;
+                PtxSink sink;
+                PtxResolver res;
+                PtxDecoder d(text, tokens, mtb[mm + 1], layout[mm].text_off + layout[mm].text_len, sink, res);
+                d.pos = i;
+                d.unit_tok0 = i;
+                bool ok = d.reg_or_immediate(true) && sink.ne == 0 && d.pos <= hi;
+                if (ok) {
+                    uint16_t nk = PTX_KL_KIND(kinds[d.pos]);
+                    ok = (d.pos == hi) || nk == T_COMMA;
+                }
+                if (!ok) { lo_dev[1] = 1; return; }
+                z.a = sink.nw;
+                z.b = 1;
+                esz[k] = z;
+            });
+            bk.template scan<PtxPair>("bulk_scan", (size_t)nt, [=] PTX_HD(size_t k) { return esz[k]; }, [=] PTX_HD(size_t k, PtxPair v) {
+                                          PtxPair own = esz[k];
+                                          if (k + 1 == nt) {     // totals, before the entry turns exclusive
+                                              bi->n_words = v.a;
+                                              bi->n_elems = v.b;
+                                          }
+                                          PtxPair ex;
+                                          ex.a = v.a - own.a;
+                                          ex.b = own.b;      // keeps "an element starts here"
+                                          esz[k] = ex;
+                                      },
+                                      PairAddOp(), PtxPair{0, 0});
+            bk.pf("bulk_decode", nt, [=] PTX_HD(size_t k) {
+                if (lo_dev[1] || !esz[k].b) return;
+                uint32_t i = ts + (uint32_t)k;
+                uint32_t mm = ptx_upper_bound_u32(mtb, n_modules, i) - 1;
+                PtxSink sink;
+                sink.words = elems + esz[k].a;
+                PtxResolver res;
+                PtxDecoder d(text, tokens, mtb[mm + 1], layout[mm].text_off + layout[mm].text_len, sink, res);
+                d.pos = i;
+                d.unit_tok0 = i;
+                d.reg_or_immediate(true);
+            });
+            bk.pf("bulk_publish", 1, [=] PTX_HD(size_t) {
+                bi->first_tok = lo_dev[0] + 1;
+                bi->close_tok = te - 2;
+                bi->bad = lo_dev[1];
+                bi->elems = elems;
+                bi->dst = nullptr;
+            });
+        }
+    }
     PtxFnEntry* fn_entries = w.fn_entries = (PtxFnEntry*)bk.alloc(sizeof(PtxFnEntry) * ((size_t)max_funcs + 1));
 
     // T0: class key of every unit (see "unit classes and record templates" above)
@@ -755,6 +876,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         PtxResolver res;
         res.module = m;
         PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
+        d.bulk = bulk_table;
         // the unit's first tokens go to the fast window: the decoder looks at every token many times
         {
             uint32_t avail = mtb[m + 1] - start;
@@ -821,6 +943,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         PtxSink sink;
         PtxResolver res;
         PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
+        d.bulk = bulk_table;
         int st = ptx_decode_module_sequential(d, mtb[m], 0);
         PtxPair sz;
         sz.a = sink.peak;
@@ -904,6 +1027,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
             PtxResolver res;
             res.words = words;
             PtxDecoder d(text, tokens, mtb[m + 1], text_end, sink, res);
+            d.bulk = bulk_table;
             ptx_decode_module_sequential(d, mtb[m], usize[u].a);
             if (sink.peak != usize[u + 1].a - usize[u].a || sink.ne != usize[u + 1].b - usize[u].b) counters->pad = (uint32_t)u + 1;
             sink.pad_to(usize[u + 1].a - usize[u].a);
@@ -917,12 +1041,21 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         res.module = m;
         res.my_dir_ord = udir[u];
         PtxDecoder d(text, tokens, mtb[m + 1], text_end, sink, res);
+        d.bulk = bulk_table;
         uint32_t dp = udepth[u];
         ptx_decode_unit(d, ustart[u], dp & 0x7FFFFFFFu, (dp >> 31) != 0);
         // both passes must agree on the size of every record (a mismatch would overwrite a neighbour's record)
         if (sink.peak != usize[u + 1].a - usize[u].a || sink.ne != usize[u + 1].b - usize[u].b) counters->pad = (uint32_t)u + 1;
         sink.pad_to(usize[u + 1].a - usize[u].a);
     });
+    }
+    // the element runs of the bulk path go where the statements' decoders left room for them
+    for (uint32_t j = 0; j < n_bulk; j++) {
+        const PtxBulkInfo* bi = bulk_info + j;
+        bk.pf("bulk_copy", 2 * (size_t)bulk_tokens[j], [=] PTX_HD(size_t k) {
+            if (bi->bad || !bi->dst || k >= bi->n_words) return;
+            bi->dst[k] = bi->elems[k];
+        });
     }
     bk.pf("module_results_final", n_modules, [=] PTX_HD(size_t m) {
         PtxModuleResult r = results[m];
