@@ -161,3 +161,16 @@ def bulk_cases(n=9000):
     out.append(HEADER + ".global .align 4 .s64 a[%d] = {%s};\n.global .align 4 .u32 b[%d] = {%s};\n" % (n, ", ".join(e), n, ", ".join(e[::-1]))
                + ".visible .entry k()\n{\n" + DECLS + "\nadd.s32 %r1, %r2, %r3;\nret;\n}\n")
     return out
+
+
+def capacity_cases():
+    """More distinct statement classes than the class store holds, and names at the length limits of the packed forms."""
+    many = "\n".join("mov.u32 %%r1, %d;" % i for i in range(270000))      # 270,000 classes (one per immediate)
+    out = [body(many)]
+    longs = []
+    for n in (125, 126, 127, 128, 254, 255, 256, 300, 65534, 65535, 65536, 70000):
+        for ch in "ab":
+            longs.append("add.s32 %%r1, %%%s, %%r3;" % (ch * n))
+            longs.append("L%s: bra L%s;" % (ch * n, ch * n))
+    out.append(body("\n".join(longs)))
+    return out

@@ -68,6 +68,14 @@ def test_bulk_initialisers(oracle, ctx):
     assert_parity(oracle, ctx, cases.bulk_cases(), modes=(0, 2))
 
 
+def test_class_store_capacity_and_long_names(oracle, ctx, monkeypatch):
+    """More classes than the store holds (the rest is decoded the ordinary way), in one slice and across slices."""
+    texts = cases.capacity_cases()
+    assert_parity(oracle, ctx, texts, modes=(0,))
+    monkeypatch.setenv("PTXFE_SLICE_BYTES", "2000000")
+    assert_parity(oracle, ctx, [texts[0][:3000000] + "\nret;\n}\n"] * 3 + texts, modes=(0,))
+
+
 def test_lexer_tokens(oracle, ctx):
     rng = random.Random(7)
     pieces = ["add", ".f32", "%r1", ",", ";", " ", "\n", "// c\n", "/* x */", "/*", "*/", "\"s\"", "\"", "0f3F800000", "0x1F", "1.5e-3",

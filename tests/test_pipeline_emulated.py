@@ -68,6 +68,10 @@ def test_bulk_initialisers(oracle, emu):
     assert stats["bulk"] >= len(texts)      # every module has at least one statement that long
 
 
+def test_class_store_capacity_and_long_names(oracle, emu):
+    assert_parity(oracle, emu, cases.capacity_cases(), modes=(0,))
+
+
 def test_edge_cases_in_reverse_thread_order(oracle, emu, monkeypatch):
     """Every parallel-for of the pipeline run backwards: no step may depend on the order of its threads."""
     monkeypatch.setenv("PTXFE_EMU_ORDER", "reverse")
