@@ -301,6 +301,12 @@ def main():
                 "lexer_segmenter": None}
         lex_ms = sum(prof.get(k, 0.0) for k in ("lex_context_vectors", "scan_context", "lex_tokens", "scan_token_counts",
                                                   "lex_compact_classify", "scan_depth", "scan_unit_index")) / a.steps
+        # whole front end: text read once, records written once (N + O) over the kernel time of a step
+        a_fe = N + 4 * W
+        fe_ms = kernel_ms / a.steps
+        roof["front_end"] = {"ms": fe_ms, "algorithmic_bytes": a_fe, "achieved": a_fe / (fe_ms / 1e3) / 1e9,
+                             "frac": a_fe / (fe_ms / 1e3) / 1e9 / peak}
+        roof["frac_of_nominal_8000"] = ach / 8000.0 if ach else None
         if lex_ms > 0:
             a_lex = N + 8 * T
             roof["lexer_segmenter"] = {"ms": lex_ms, "algorithmic_bytes": a_lex, "achieved": a_lex / (lex_ms / 1e3) / 1e9,

@@ -174,3 +174,23 @@ def capacity_cases():
             longs.append("L%s: bra L%s;" % (ch * n, ch * n))
     out.append(body("\n".join(longs)))
     return out
+
+
+def negative_decimal_side_file(n=1000):
+    """Module-level scalars initialised with NEGATIVE decimal floats and integers: the reference has no rule for '-' in
+    front of a float literal (ptx_parser/src/lib.rs:366-377), so every float directive must be rejected the same way,
+    while negative integers are fine."""
+    import random
+    rng = random.Random(9)
+    lines = []
+    for i in range(n):
+        r = rng.random()
+        if r < 0.4:
+            lines.append(".global .f64 c%d = -%.17g;" % (i, rng.random() * 1e6))
+        elif r < 0.7:
+            lines.append(".global .f32 c%d = -%.9g;" % (i, rng.random() * 100))
+        elif r < 0.85:
+            lines.append(".global .s32 c%d = -%d;" % (i, rng.randrange(1 << 31)))
+        else:
+            lines.append(".global .f64 c%d = %.17g;" % (i, rng.random()))
+    return HEADER + "\n".join(lines) + "\n.visible .entry k()\n{\nret;\n}\n"

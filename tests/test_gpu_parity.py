@@ -63,6 +63,10 @@ def test_statement_classes(oracle, ctx):
     assert_parity(oracle, ctx, texts + texts[::-1], modes=(0,))
 
 
+def test_negative_decimal_side_file(oracle, ctx):
+    assert_parity(oracle, ctx, [cases.negative_decimal_side_file()])
+
+
 def test_bulk_initialisers(oracle, ctx):
     """Initialiser lists long enough for the element-parallel path, regular and irregular."""
     assert_parity(oracle, ctx, cases.bulk_cases(), modes=(0, 2))

@@ -68,6 +68,10 @@ def test_bulk_initialisers(oracle, emu):
     assert stats["bulk"] >= len(texts)      # every module has at least one statement that long
 
 
+def test_negative_decimal_side_file(oracle, emu):
+    assert_parity(oracle, emu, [cases.negative_decimal_side_file()])
+
+
 def test_class_store_capacity_and_long_names(oracle, emu):
     assert_parity(oracle, emu, cases.capacity_cases(), modes=(0,))
 
