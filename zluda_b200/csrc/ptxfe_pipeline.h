@@ -219,6 +219,8 @@ struct PtxCounters {
     uint32_t n_tokens, n_lexerrs, n_units, n_words, n_errs, n_funcs, any_sequential, pad;
     uint32_t n_flagged;         // units whose records are written by the second decode pass
     uint32_t n_bulk;            // statements long enough for the bulk initialiser path
+    uint32_t n_rest;            // units without a template
+    uint32_t n_listed;
 };
 
 PTX_HD inline uint32_t ptx_upper_bound_u32(const uint32_t* a, uint32_t n, uint32_t x) {
@@ -605,10 +607,144 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         bi.dst = nullptr;
         bulk_info[slot] = bi;
     });
+    // T0: class key of every unit (see "unit classes and record templates" above)
+    uint16_t* ukey = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_units + 2));
+    uint32_t* order = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    uint64_t* ckey_of = (uint64_t*)bk.alloc(sizeof(uint64_t) * ((size_t)n_units + 1));
+    bk.pf("unit_class_key", n_units, [=] PTX_HD(size_t u) {
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        uint32_t start = ustart[u];
+        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        uint32_t dp = udepth[u];
+        ckey_of[u] = mod_skip[m] ? 0 : ptx_class_key(text, tokens, kinds, start, end, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
+    });
+
+    // T1: class table (open addressing on the 64-bit key), shared by the slices of a batch; the thread that inserts
+    // a key makes its unit the representative of the class
+    const PtxClassStore cs = bk.class_store(w.first_slice);
+    uint32_t* uclass = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    uint32_t* utmpl = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    uint8_t* uflag = (uint8_t*)bk.alloc((size_t)n_units + 16);
+    bk.pf("reset_flagged", 1, [=] PTX_HD(size_t) {
+        counters->n_flagged = 0;
+        cs.state[2] = cs.state[0] < PTX_MAX_CLASSES ? cs.state[0] : PTX_MAX_CLASSES;
+    });
+    bk.pf("class_insert", n_units, [=] PTX_HD(size_t u) {
+        uclass[u] = PTX_ABSENT;
+        unsigned long long key = ckey_of[u];
+        if (!key) return;
+        uint32_t h = (uint32_t)(key ^ (key >> 29)) & (PTX_CLASS_SLOTS - 1);
+        for (int probe = 0; probe < 64; probe++) {
+#ifdef __CUDA_ARCH__
+            // most units find their class already there: look before competing for the slot
+            unsigned long long old = *(volatile unsigned long long*)&cs.keys[h];
+            if (old == 0) old = atomicCAS(&cs.keys[h], 0ull, key);
+#else
+            unsigned long long old = cs.keys[h];
+            if (old == 0) cs.keys[h] = key;
+#endif
+            if (old == 0) {
+#ifdef __CUDA_ARCH__
+                uint32_t id = atomicAdd(&cs.state[0], 1u);
+#else
+                uint32_t id = cs.state[0]++;
+#endif
+                if (id < PTX_MAX_CLASSES) {
+                    cs.rep_unit[id] = (uint32_t)u;
+                    cs.slot_tmpl[h] = id;
+                } else {
+                    cs.slot_tmpl[h] = PTX_ABSENT;
+                }
+                uclass[u] = h;
+                return;
+            }
+            if (old == key) { uclass[u] = h; return; }
+            h = (h + 1) & (PTX_CLASS_SLOTS - 1);
+        }
+    });
+    // T2: decode the representatives of the classes this slice added, with tagged output, and spell out their signature
+    bk.pf("decode_representatives", PTX_MAX_CLASSES, [=] PTX_HD(size_t k) {
+        size_t id = (size_t)cs.state[2] + k;
+        if (id >= cs.state[0] || id >= PTX_MAX_CLASSES) return;
+        uint32_t u = cs.rep_unit[id];
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, u) - 1;
+        uint32_t start = ustart[u];
+        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        PtxSink sink;
+        sink.words = cs.tmpl_words + id * PTX_TMPL_WORDS;
+        sink.tags = cs.tmpl_tags + id * PTX_TMPL_WORDS;
+        sink.words_cap = PTX_TMPL_WORDS;
+        PtxResolver res;
+        res.module = m;
+        PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
+        uint32_t dp = udepth[u];
+        PtxUnitResult r = ptx_decode_unit(d, start, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
+        PtxTemplateInfo ti;
+        ti.n_words = sink.nw;
+        ti.n_tokens = end - start;
+        ti.depth1 = (dp & 0x7FFFFFFFu) == 1 ? 1u : 0u;
+        ti.ok = (r.status == US_OK && sink.ne == 0 && sink.peak <= PTX_TMPL_WORDS && !sink.poison && r.kind != U_FUNC && r.end == end &&
+                 d.max_seen < end) ? 1u : 0u;
+        if (ti.ok) {
+            uint32_t need = ptx_signature_words(tokens, start, ti.n_tokens);
+#ifdef __CUDA_ARCH__
+            uint32_t at = atomicAdd(&cs.state[1], need);
+#else
+            uint32_t at = cs.state[1];
+            cs.state[1] += need;
+#endif
+            if (at + need <= PTX_SIG_POOL_WORDS) {
+                cs.sig_off[id] = at;
+                ptx_signature_write(cs.sig_pool + at, text, tokens, start, ti.n_tokens, ti.depth1);
+            } else {
+                ti.ok = 0;
+            }
+        }
+        cs.info[id] = ti;
+    });
+    // T3: every unit of a class with a usable template is checked against the class signature and takes its size
+    uint32_t* rest_count = (uint32_t*)bk.alloc(sizeof(uint32_t) * 64);     // striped count of the units left without a template
+    bk.zero(rest_count, sizeof(uint32_t) * 64);
+    bk.pf("apply_templates", n_units, [=] PTX_HD(size_t u) {
+        uflag[u] = PTX_UNIT_UNDECIDED;
+        utmpl[u] = PTX_ABSENT;
+        auto rest = [&]() {      // this unit stays without a template
+#ifdef __CUDA_ARCH__
+            atomicAdd(&rest_count[u & 63], 1u);
+#else
+            rest_count[u & 63]++;
+#endif
+        };
+        uint32_t slot = uclass[u];
+        if (slot == PTX_ABSENT) { rest(); return; }
+        uint32_t id = cs.slot_tmpl[slot];
+        if (id == PTX_ABSENT) { rest(); return; }
+        const PtxTemplateInfo ti = cs.info[id];
+        if (!ti.ok) { rest(); return; }
+        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        uint32_t start = ustart[u];
+        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        uint32_t dp = udepth[u];
+        uint32_t depth1 = (dp & 0x7FFFFFFFu) == 1 ? 1u : 0u;
+        if (end - start != ti.n_tokens || !ptx_signature_matches(cs.sig_pool + cs.sig_off[id], text, tokens, kinds, start, ti.n_tokens, depth1)) { rest(); return; }
+        PtxPair sz;
+        sz.a = ti.n_words;
+        sz.b = 0;
+        usize[u + 1] = sz;
+        if (u == 0) { PtxPair z; z.a = z.b = 0; usize[0] = z; }
+        uend[u] = end;
+        ustatus[u] = US_OK;
+        uflag[u] = PTX_UNIT_TEMPLATED;
+        utmpl[u] = id;
+    });
+
     bk.pf("reset_func_count", 1, [=] PTX_HD(size_t) {
         counters->n_funcs = 0;
         counters->any_sequential = 0;
         counters->pad = n_units ? udir[n_units - 1] : 0;   // number of top-level units: bound for the function table
+        uint32_t rest = 0;
+        for (int i = 0; i < 64; i++) rest += rest_count[i];
+        counters->n_rest = rest;
     });
     bk.download(&host_counters, counters, sizeof(PtxCounters));
     const uint32_t max_funcs = host_counters.pad;
@@ -707,150 +843,46 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     }
     PtxFnEntry* fn_entries = w.fn_entries = (PtxFnEntry*)bk.alloc(sizeof(PtxFnEntry) * ((size_t)max_funcs + 1));
 
-    // T0: class key of every unit (see "unit classes and record templates" above)
-    uint16_t* ukey = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_units + 2));
-    uint32_t* order = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
-    uint64_t* ckey_of = (uint64_t*)bk.alloc(sizeof(uint64_t) * ((size_t)n_units + 1));
-    bk.pf("unit_class_key", n_units, [=] PTX_HD(size_t u) {
-        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
-        uint32_t start = ustart[u];
-        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
-        uint32_t dp = udepth[u];
-        ckey_of[u] = mod_skip[m] ? 0 : ptx_class_key(text, tokens, kinds, start, end, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
-    });
-
-    // T1: class table (open addressing on the 64-bit key), shared by the slices of a batch; the thread that inserts
-    // a key makes its unit the representative of the class
-    const PtxClassStore cs = bk.class_store(w.first_slice);
-    uint32_t* uclass = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
-    uint32_t* utmpl = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
-    uint8_t* uflag = (uint8_t*)bk.alloc((size_t)n_units + 16);
-    bk.pf("reset_flagged", 1, [=] PTX_HD(size_t) {
-        counters->n_flagged = 0;
-        cs.state[2] = cs.state[0] < PTX_MAX_CLASSES ? cs.state[0] : PTX_MAX_CLASSES;
-    });
-    bk.pf("class_insert", n_units, [=] PTX_HD(size_t u) {
-        uclass[u] = PTX_ABSENT;
-        unsigned long long key = ckey_of[u];
-        if (!key) return;
-        uint32_t h = (uint32_t)(key ^ (key >> 29)) & (PTX_CLASS_SLOTS - 1);
-        for (int probe = 0; probe < 64; probe++) {
+    // The units without a template are decoded next.  When they are few (clean input: calls, function headers,
+    // statements whose class was poisoned) they are simply listed; when they are many they are sorted by a "shape key"
+    // (a hash of their token kinds) first: the decoder's control flow depends on token kinds only, so the threads of a
+    // warp then follow the same path.  Results are written at offsets computed in unit order either way, so the order
+    // of processing does not show in the output.  order[0 .. n_rest) = the units to decode.
+    const uint32_t n_rest = host_counters.n_rest;
+    if (n_rest <= 131072) {
+        bk.pf("list_rest_units", n_units, [=] PTX_HD(size_t u) {
+            if (uflag[u] == PTX_UNIT_TEMPLATED) return;
 #ifdef __CUDA_ARCH__
-            // most units find their class already there: look before competing for the slot
-            unsigned long long old = *(volatile unsigned long long*)&cs.keys[h];
-            if (old == 0) old = atomicCAS(&cs.keys[h], 0ull, key);
+            uint32_t slot = atomicAdd(&counters->n_listed, 1u);
 #else
-            unsigned long long old = cs.keys[h];
-            if (old == 0) cs.keys[h] = key;
+            uint32_t slot = counters->n_listed++;
 #endif
-            if (old == 0) {
-#ifdef __CUDA_ARCH__
-                uint32_t id = atomicAdd(&cs.state[0], 1u);
-#else
-                uint32_t id = cs.state[0]++;
-#endif
-                if (id < PTX_MAX_CLASSES) {
-                    cs.rep_unit[id] = (uint32_t)u;
-                    cs.slot_tmpl[h] = id;
-                } else {
-                    cs.slot_tmpl[h] = PTX_ABSENT;
-                }
-                uclass[u] = h;
-                return;
-            }
-            if (old == key) { uclass[u] = h; return; }
-            h = (h + 1) & (PTX_CLASS_SLOTS - 1);
-        }
-    });
-    // T2: decode the representatives of the classes this slice added, with tagged output, and spell out their signature
-    bk.pf("decode_representatives", PTX_MAX_CLASSES, [=] PTX_HD(size_t k) {
-        size_t id = (size_t)cs.state[2] + k;
-        if (id >= cs.state[0] || id >= PTX_MAX_CLASSES) return;
-        uint32_t u = cs.rep_unit[id];
-        uint32_t m = ptx_upper_bound_u32(mub, n_modules, u) - 1;
-        uint32_t start = ustart[u];
-        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
-        PtxSink sink;
-        sink.words = cs.tmpl_words + id * PTX_TMPL_WORDS;
-        sink.tags = cs.tmpl_tags + id * PTX_TMPL_WORDS;
-        sink.words_cap = PTX_TMPL_WORDS;
-        PtxResolver res;
-        res.module = m;
-        PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
-        uint32_t dp = udepth[u];
-        PtxUnitResult r = ptx_decode_unit(d, start, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
-        PtxTemplateInfo ti;
-        ti.n_words = sink.nw;
-        ti.n_tokens = end - start;
-        ti.depth1 = (dp & 0x7FFFFFFFu) == 1 ? 1u : 0u;
-        ti.ok = (r.status == US_OK && sink.ne == 0 && sink.peak <= PTX_TMPL_WORDS && !sink.poison && r.kind != U_FUNC && r.end == end &&
-                 d.max_seen < end) ? 1u : 0u;
-        if (ti.ok) {
-            uint32_t need = ptx_signature_words(tokens, start, ti.n_tokens);
-#ifdef __CUDA_ARCH__
-            uint32_t at = atomicAdd(&cs.state[1], need);
-#else
-            uint32_t at = cs.state[1];
-            cs.state[1] += need;
-#endif
-            if (at + need <= PTX_SIG_POOL_WORDS) {
-                cs.sig_off[id] = at;
-                ptx_signature_write(cs.sig_pool + at, text, tokens, start, ti.n_tokens, ti.depth1);
-            } else {
-                ti.ok = 0;
-            }
-        }
-        cs.info[id] = ti;
-    });
-    // T3: every unit of a class with a usable template is checked against the class signature and takes its size
-    bk.pf("apply_templates", n_units, [=] PTX_HD(size_t u) {
-        uflag[u] = PTX_UNIT_UNDECIDED;
-        utmpl[u] = PTX_ABSENT;
-        uint32_t slot = uclass[u];
-        if (slot == PTX_ABSENT) return;
-        uint32_t id = cs.slot_tmpl[slot];
-        if (id == PTX_ABSENT) return;
-        const PtxTemplateInfo ti = cs.info[id];
-        if (!ti.ok) return;
-        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
-        uint32_t start = ustart[u];
-        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
-        uint32_t dp = udepth[u];
-        uint32_t depth1 = (dp & 0x7FFFFFFFu) == 1 ? 1u : 0u;
-        if (end - start != ti.n_tokens || !ptx_signature_matches(cs.sig_pool + cs.sig_off[id], text, tokens, kinds, start, ti.n_tokens, depth1)) return;
-        PtxPair sz;
-        sz.a = ti.n_words;
-        sz.b = 0;
-        usize[u + 1] = sz;
-        if (u == 0) { PtxPair z; z.a = z.b = 0; usize[0] = z; }
-        uend[u] = end;
-        ustatus[u] = US_OK;
-        uflag[u] = PTX_UNIT_TEMPLATED;
-        utmpl[u] = id;
-    });
-
-    // The units without a template are decoded in the order of a "shape key" (a hash of their token kinds): the
-    // decoder's control flow depends on token kinds only, so the threads of a warp then follow the same path.  Results
-    // are still written at offsets computed in unit order, so the order of processing does not show in the output.
-    bk.pf("unit_shape_key", n_units, [=] PTX_HD(size_t u) {
-        if (uflag[u] == PTX_UNIT_TEMPLATED) { ukey[u] = (uint16_t)(PTX_SORT_BUCKETS - 1); return; }
-        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
-        uint32_t start = ustart[u];
-        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
-        if (end > start + 20) end = start + 20;
-        uint32_t h = 2166136261u ^ (udepth[u] >> 31) ^ ((udepth[u] & 0x7FFFFFFFu) ? 2u : 0u);
-        for (uint32_t i = start; i < end; i++) h = (h ^ PTX_KL_KIND(kinds[i])) * 16777619u;
-        h ^= h >> 15;
-        ukey[u] = (uint16_t)(h & (PTX_SORT_BUCKETS - 1));
-    });
-    bk.sort_by_key("sort_units_by_shape", n_units, ukey, order);
+            order[slot] = (uint32_t)u;
+        });
+    } else {
+        // templated units share the last bucket, so they sort behind all the others
+        bk.pf("unit_shape_key", n_units, [=] PTX_HD(size_t u) {
+            if (uflag[u] == PTX_UNIT_TEMPLATED) { ukey[u] = (uint16_t)(PTX_SORT_BUCKETS - 1); return; }
+            uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+            uint32_t start = ustart[u];
+            uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+            if (end > start + 20) end = start + 20;
+            uint32_t h = 2166136261u ^ (udepth[u] >> 31) ^ ((udepth[u] & 0x7FFFFFFFu) ? 2u : 0u);
+            for (uint32_t i = start; i < end; i++) h = (h ^ PTX_KL_KIND(kinds[i])) * 16777619u;
+            h ^= h >> 15;
+            h &= PTX_SORT_BUCKETS - 1;
+            if (h == PTX_SORT_BUCKETS - 1) h = 0;
+            ukey[u] = (uint16_t)h;
+        });
+        bk.sort_by_key("sort_units_by_shape", n_units, ukey, order);
+    }
 
     // C1: decode every unit once.  The record is built in a small per-thread staging buffer (failed alternatives are
     // rolled back there) and lands in row u of a table; its final place is known only after the sizes are scanned.
     // Units that report errors (every `call` reserves one), or whose record outgrows the buffer, are only measured
     // here and written by the second pass (C6), which also has the function table.
     uint32_t* table = (uint32_t*)bk.alloc(sizeof(uint32_t) * PTX_TMP_STRIDE * ((size_t)n_units + 1));
-    bk.pf_staged("decode_units", n_units, table, PTX_TMP_STRIDE, [=] PTX_HD(size_t idx, const PtxScratch& sc) -> PtxStaged {
+    bk.pf_staged("decode_units", n_rest, table, PTX_TMP_STRIDE, [=] PTX_HD(size_t idx, const PtxScratch& sc) -> PtxStaged {
         PtxStaged ret;
         size_t u = order[idx];
         ret.unit = (uint32_t)u;
@@ -1013,7 +1045,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
             }
         });
         // C6: decode the flagged units again, writing in place
-    bk.pf("decode_emit_flagged", n_units, [=] PTX_HD(size_t idx) {
+    bk.pf("decode_emit_flagged", n_rest, [=] PTX_HD(size_t idx) {
         size_t u = order[idx];
         if (uflag[u] != 1) return;
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
