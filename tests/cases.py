@@ -173,6 +173,9 @@ def capacity_cases():
             longs.append("add.s32 %%r1, %%%s, %%r3;" % (ch * n))
             longs.append("L%s: bra L%s;" % (ch * n, ch * n))
     out.append(body("\n".join(longs)))
+    # more units without a template than the "few" threshold of the decode stage: calls are never templated
+    calls = "\n".join(("call foo, (%%r%d);" % (i % 9)) if i % 3 else "call.uni bar;" for i in range(140000))
+    out.append(HEADER + ".func foo(.param .b32 p)\n{\nret;\n}\n.visible .entry k()\n{\n" + DECLS + "\n" + calls + "\nret;\n}\n")
     return out
 
 
