@@ -36,7 +36,7 @@ UNIT = "GB/s"
 
 
 # (dram__bytes_read.sum + dram__bytes_write.sum) / text bytes, from the ncu captures summarised under profiles/
-NCU_DRAM_BYTES_PER_TEXT_BYTE = {      # profiles/launch_list_config1_64MiB.md
+NCU_DRAM_BYTES_PER_TEXT_BYTE = {      # from the ncu launch list summarised under profiles/ (64 MiB instance)
     "lex_tokens": 4.59, "lex_compact_classify": 6.28, "scan_depth": 1.76, "apply_templates": 3.04, "unit_class_key": 2.67,
     "emit_records": 3.62, "lex_context_vectors": 1.00,
 }

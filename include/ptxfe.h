@@ -2,7 +2,7 @@
  *
  * Drop-in boundary for the three public entry points of ZLUDA's ptx_parser crate.  Those are plain Rust functions
  * (no FFI layer exists in the reference); a binding crate would declare the functions below `extern "C"` and
- * rebuild `ast::Module` from the records.
+ * rebuild `ast::Module` from the records (zluda_b200/csrc/ptx_dump.h is a complete reader of them).
  *
  *   reference (ptx_parser/src/lib.rs)                                  here
  *   parse_module_checked(text)   -> Result<Module, Vec<PtxError>>      ptxfe_parse_batch(.., PTXFE_CHECKED, ..)     lib.rs:428-468
