@@ -79,8 +79,23 @@ struct PtxTemplateInfo {
 #define PTX_KL_LEN(x) ((uint32_t)(x) >> 9)
 #define PTX_KL_LONG 127u
 static_assert(T_COUNT <= 512, "token kinds must fit 9 bits of the kinds array");
+// four bytes of text at any offset (little-endian), bytes at and after `rem` zeroed: two aligned loads and a shift.
+// Reads up to 7 bytes past off: the text buffers of the pipeline have that slack.
+PTX_HD inline uint32_t ptx_text_word(const uint8_t* text, uint32_t off, uint32_t rem) {
+    const uint8_t* a = text + off;
+    const uint32_t mis = (uint32_t)((uintptr_t)a & 3u);
+    const uint32_t* w = (const uint32_t*)(a - mis);
+    uint32_t v = w[0];
+    if (mis) v = (v >> (8u * mis)) | (w[1] << (32u - 8u * mis));
+    if (rem < 4) v &= (1u << (8u * rem)) - 1u;
+    return v;
+}
 PTX_HD inline bool ptx_text_matters(uint16_t k) {
-    return k == T_DECIMAL || k == T_HEX || k == T_F32HEX || k == T_F64HEX || k == T_F64 || k == T_DOTIDENT || k == T_STRING;
+    static_assert(T_DECIMAL < 32 && T_HEX < 32 && T_F32HEX < 32 && T_F64HEX < 32 && T_F64 < 32 && T_DOTIDENT < 32 && T_STRING < 32,
+                  "the literal token kinds are among the first 32");
+    const uint32_t mask = (1u << T_DECIMAL) | (1u << T_HEX) | (1u << T_F32HEX) | (1u << T_F64HEX) | (1u << T_F64) | (1u << T_DOTIDENT) |
+                          (1u << T_STRING);
+    return k < 32 && ((mask >> k) & 1u);
 }
 // 64-bit class key of the tokens [start, end); 0 = this unit gets no template
 PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens, const uint16_t* kinds, uint32_t start, uint32_t end, uint32_t depth,
@@ -97,9 +112,10 @@ PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens
             const PtxToken t = tokens[i];
             if (t.len == 0xFFFF) return 0;
             h2 = (h2 ^ t.len) * 0x85EBCA6Bu;
-            for (uint32_t j = 0; j < t.len; j++) {
-                uint32_t c = text[t.start + j];
+            for (uint32_t j = 0; j < t.len; j += 4) {
+                uint32_t c = ptx_text_word(text, t.start + j, t.len - j);
                 h1 = (h1 ^ c) * 16777619u;
+                h1 ^= h1 >> 13;
                 h2 = (h2 + c) * 0x9E3779B1u;
             }
         } else if (kind == T_IDENT) {
@@ -165,8 +181,7 @@ PTX_HD inline void ptx_signature_write(uint32_t* sig, const uint8_t* text, const
         if (ptx_text_matters(t.kind)) {
             *sig++ = t.kind | ((uint32_t)t.len << 16);
             for (uint32_t j = 0; j < t.len; j += 4) {
-                uint32_t v = 0;
-                for (uint32_t k = 0; k < 4 && j + k < t.len; k++) v |= (uint32_t)text[t.start + j + k] << (8 * k);
+                uint32_t v = ptx_text_word(text, t.start + j, t.len - j);
                 *sig++ = v;
             }
         } else if (t.kind == T_IDENT) {
@@ -190,8 +205,7 @@ PTX_HD inline bool ptx_signature_matches(const uint32_t* sig, const uint8_t* tex
             const PtxToken t = tokens[start + i];
             if ((head >> 16) != t.len || t.len == 0xFFFF) return false;
             for (uint32_t j = 0; j < t.len; j += 4) {
-                uint32_t v = 0;
-                for (uint32_t k = 0; k < 4 && j + k < t.len; k++) v |= (uint32_t)text[t.start + j + k] << (8 * k);
+                uint32_t v = ptx_text_word(text, t.start + j, t.len - j);
                 if (*sig++ != v) return false;
             }
         } else if (kind == T_IDENT) {
