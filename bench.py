@@ -5,8 +5,9 @@
 
 A step is one pass of the whole front end over one batch of synthetic PTX modules: the fatbin-scale configuration
 (4,096 independent modules, ~1 GiB of text, log-normal sizes, mixed sm_80/86/90 targets, 10 % tensor-core tile
-statements).  With N > 1 (torchrun, one rank per GPU) the global module list of N x 4,096 modules is split by
-byte-balanced greedy partitioning; ranks exchange nothing on the data path (weak scaling).
+statements; every statement drawn independently with fresh registers, int32 immediates and normal(0,1) hex floats).
+With N > 1 (torchrun, one rank per GPU) the global module list of N x 4,096 modules is split by byte-balanced greedy
+partitioning; ranks exchange nothing on the data path (weak scaling).
 
 Printed JSON line (rank 0):
   value      front-end GB/s of input text with the text already resident in HBM (all kernels, CUDA-event timed on the
@@ -15,6 +16,8 @@ Printed JSON line (rank 0):
              records inside the timed region
   roofline   the dominant kernel: algorithmic bytes / its CUDA-event time, against the measured HBM copy peak
   cpu_baseline  the CPU restatement of ptx_parser (the oracle) on all host cores, on a bounded sample of the workload
+  parity_checked / parity_ok   outside the timed region: the canonical-dump hash of every 16th module of the timed
+             batch, as produced by the timed call, against the oracle's; the run fails if one differs
 --impl reference times that CPU implementation as the main line (the Rust crate itself cannot be built here).
 """
 import argparse
@@ -94,18 +97,37 @@ class ClockSampler:
                 "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def make_workload(rank, world, n_modules, total_bytes, seed=1001):
-    """The rank's share of world x n_modules modules (byte-balanced greedy partition of the global list)."""
+def workload_selection(rank, world, n_modules, total_bytes, seed=1001):
+    """(module indices of this rank or None for all, modules in the global list, bytes of the global list): the global
+    list has world x n_modules modules and is split by byte-balanced greedy partitioning."""
     from zluda_b200 import corpus
     if world == 1:
-        return corpus.config1(seed=seed, n_modules=n_modules, total_bytes=total_bytes)
+        return None, n_modules, total_bytes
     sizes = corpus.config1_sizes(seed, n_modules * world, total_bytes * world)
-    mine = corpus.greedy_partition(sizes, world)[rank]
-    return corpus.config1(seed=seed, n_modules=n_modules * world, total_bytes=total_bytes * world, indices=mine)
+    return corpus.greedy_partition(sizes, world)[rank], n_modules * world, total_bytes * world
+
+
+def make_workload(rank, world, n_modules, total_bytes, seed=1001):
+    """The rank's share of the global module list as a list of bytes objects (small instances: tests)."""
+    from zluda_b200 import corpus
+    mine, n_all, bytes_all = workload_selection(rank, world, n_modules, total_bytes, seed)
+    return corpus.config1(seed=seed, n_modules=n_all, total_bytes=bytes_all, indices=mine)
+
+
+def make_workload_into(alloc, rank, world, n_modules, total_bytes, seed=1001):
+    """The same, generated back to back straight into one host buffer: `alloc(nbytes)` returns a writable uint8 numpy
+    array (pinned memory for the GPU arm).  Returns (array, [(address, length)] per module)."""
+    from zluda_b200 import corpus
+    mine, n_all, bytes_all = workload_selection(rank, world, n_modules, total_bytes, seed)
+    blob = alloc(corpus.config1_total_bound(seed, n_all, bytes_all, mine))
+    spans = corpus.config1_into(blob, seed, n_all, bytes_all, mine)
+    base = blob.ctypes.data
+    return blob, [(base + o, l) for o, l in spans]
 
 
 def cpu_parse_all_cores(mods, seconds_budget=20.0):
-    """Oracle (CPU restatement of ptx_parser) over `mods` with one thread per core; returns (GB/s, cores, bytes)."""
+    """Oracle (CPU restatement of ptx_parser) over `mods` ((address, length) pairs) with one thread per core; returns
+    (GB/s, cores, bytes, modules)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib
     o = oracle_lib.load()
@@ -114,8 +136,8 @@ def cpu_parse_all_cores(mods, seconds_budget=20.0):
     t0 = time.perf_counter()
     nb = 0
     for m in mods[:4]:
-        o.lib.oracle_parse_only(m, len(m), None, None)
-        nb += len(m)
+        o.lib.oracle_parse_only(m[0], m[1], None, None)
+        nb += m[1]
     rate1 = nb / max(1e-6, time.perf_counter() - t0)
     budget_bytes = rate1 * cores * seconds_budget * 0.6
     sample, total = [], 0
@@ -123,7 +145,7 @@ def cpu_parse_all_cores(mods, seconds_budget=20.0):
         if total > budget_bytes and len(sample) >= cores:
             break
         sample.append(m)
-        total += len(m)
+        total += m[1]
     idx = [0]
     lock = threading.Lock()
     bad = [0]
@@ -135,7 +157,7 @@ def cpu_parse_all_cores(mods, seconds_budget=20.0):
                 idx[0] += 1
             if i >= len(sample):
                 return
-            if o.lib.oracle_parse_only(sample[i], len(sample[i]), None, None) != 0:
+            if o.lib.oracle_parse_only(sample[i][0], sample[i][1], None, None) != 0:
                 bad[0] += 1
 
     t0 = time.perf_counter()
@@ -172,7 +194,7 @@ def main():
     if a.impl == "reference":
         if rank != 0:
             return
-        mods = make_workload(0, 1, a.modules, a.bytes)
+        blob, mods = make_workload_into(lambda n: np.empty(n, dtype=np.uint8), 0, 1, a.modules, a.bytes)
         vals = []
         for _ in range(a.warmup + a.steps):
             gbs, cores, nbytes, nmods = cpu_parse_all_cores(mods, seconds_budget=max(4.0, 60.0 / (a.warmup + a.steps)))
@@ -195,18 +217,17 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     os.environ.setdefault("PTXFE_PROFILE", "1")
-    mods = make_workload(rank, world, a.modules, a.bytes)
-    nbytes = sum(len(m) for m in mods)
-    # pinned host copy of the text: the e2e leg reads it from there
-    blob = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
-    view = blob.numpy()
-    spans, off = [], 0
-    for m in mods:
-        view[off:off + len(m)] = np.frombuffer(m, dtype=np.uint8)
-        spans.append((blob.data_ptr() + off, len(m)))
-        off += len(m)
+    # the text is generated straight into pinned host memory: the e2e leg reads it from there
+    pinned = []
+
+    def alloc_pinned(n):
+        pinned.append(torch.empty(n, dtype=torch.uint8).pin_memory())
+        return pinned[-1].numpy()
+
+    blob, mods = make_workload_into(alloc_pinned, rank, world, a.modules, a.bytes)
+    nbytes = sum(l for _, l in mods)
     ctx = zluda_b200.Context(local_rank)
-    spans = zluda_b200.Texts(spans)      # the (char**, uint64*) arrays of the C call, built once
+    spans = zluda_b200.Texts(mods)       # the (char**, uint64*) arrays of the C call, built once
 
     def barrier():
         torch.cuda.synchronize()
@@ -249,17 +270,33 @@ def main():
         ctx.parse_batch(spans).free()
     barrier()
     t0 = time.perf_counter()
-    for _ in range(a.steps):
+    for step in range(a.steps):
         b = ctx.parse_batch(spans)
         nerr = b.error_count(0)
-        b.free()
+        if step + 1 < a.steps:
+            b.free()
     barrier()
     e2e_ms = (time.perf_counter() - t0) * 1e3
     e2e_stats = ctx.stats()
     sampler.stop_flag = True
     sampler.join()
+    # ---- outside the timed region: what the last timed call returned, against the oracle, on every 16th module
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib
+    from concurrent.futures import ThreadPoolExecutor
+    check = list(range(0, len(mods), 16))
+    t_par = time.perf_counter()
+    with ThreadPoolExecutor(min(32, os.cpu_count() or 1)) as ex:
+        ours = list(ex.map(b.dump_hash, check))
+    theirs = oracle_lib.load().dump_hashes([mods[i] for i in check])
+    n_errors = sum(b.error_count(i) for i in range(len(mods)))
+    b.free()
+    parity_bad = [i for i, x, y in zip(check, ours, theirs) if x != y]
+    parity_s = time.perf_counter() - t_par
+    if parity_bad:
+        raise SystemExit("bench: parity FAILED: the dumps of modules %s of the timed batch differ from the oracle's" % parity_bad[:8])
 
-    times = torch.tensor([kernel_ms, e2e_ms, float(nbytes), float(e2e_stats["h2d_bytes"]), float(e2e_stats["d2h_bytes"])],
+    times = torch.tensor([kernel_ms, e2e_ms, float(nbytes), float(e2e_stats["h2d_bytes"]), float(e2e_stats["d2h_bytes"]), float(len(check))],
                          dtype=torch.float64, device="cuda")
     if world > 1:
         tmax = times.clone()
@@ -268,7 +305,9 @@ def main():
         dist.all_reduce(tsum, op=dist.ReduceOp.SUM)
         kernel_ms, e2e_ms, total_bytes = float(tmax[0]), float(tmax[1]), float(tsum[2])
         h2d_bytes, d2h_bytes = int(tsum[3]), int(tsum[4])      # whole job: all ranks
+        n_checked = int(tsum[5])                               # a rank whose check failed has left with an error
     else:
+        n_checked = len(check)
         total_bytes = float(nbytes)
         h2d_bytes, d2h_bytes = int(e2e_stats["h2d_bytes"]), int(e2e_stats["d2h_bytes"])
     if rank != 0:
@@ -326,8 +365,14 @@ def main():
         "clocks": sampler.summary(),
         "stages_ms": {"lex": stats["lex_ms"], "structure": stats["structure_ms"], "decode": stats["decode_ms"]},
         "kernels_ms": {k: v / a.steps for k, v in sorted(prof.items(), key=lambda kv: -kv[1])},
+        "parity_checked": n_checked, "parity_ok": True, "parity_seconds": parity_s,
         "counts": {"text_bytes": nbytes, "tokens": int(T), "units": int(stats["n_units"]), "result_words": int(W),
-                   "sequential_modules": int(e2e_stats["n_sequential"]), "errors_module0": int(nerr)},
+                   "sequential_modules": int(e2e_stats["n_sequential"]), "errors_all_modules": int(n_errors),
+                   "classes": int(e2e_stats["n_classes"]), "class_capacity": int(e2e_stats["n_class_capacity"]),
+                   "units_templated": int(e2e_stats["n_units"] - e2e_stats["n_untemplated"]),
+                   "units_decoded_one_by_one": int(e2e_stats["n_untemplated"]),
+                   "signature_words": int(e2e_stats["n_signature_words"]), "signature_capacity": int(e2e_stats["n_signature_capacity"]),
+                   "classes_resident_run": int(stats["n_classes"]), "units_decoded_one_by_one_resident_run": int(stats["n_untemplated"])},
         "wall_ms_kernel_loop": wall_ms,
     }
     print(json.dumps(line))

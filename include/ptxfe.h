@@ -45,7 +45,10 @@ enum {
 enum {
     PTXFE_MODULE_OK = 0,        /* checked: Ok(module); unchecked: a module was returned */
     PTXFE_MODULE_ERR = 1,       /* checked: Err(errors); unchecked: Module::empty() (ptx_parser/src/ast.rs:2008-2016) */
-    PTXFE_MODULE_REF_PANICS = 2 /* input on which the reference unwraps an empty slice (lib.rs:939) */
+    PTXFE_MODULE_REF_PANICS = 2, /* input on which the reference unwraps an empty slice (lib.rs:939) */
+    PTXFE_MODULE_REF_DIVERGES = 3 /* damage below deeply nested blocks: the reference's statement recovery re-parses the
+                                     contents of every enclosing block and doubles its work per level (lib.rs:858-880,
+                                     921-951); given up after 4 * tokens + 1024 statement attempts, no module, no errors */
 };
 
 typedef struct ptxfe_stats {
@@ -56,6 +59,11 @@ typedef struct ptxfe_stats {
     uint64_t h2d_bytes, d2h_bytes;
     float h2d_ms, kernel_ms, d2h_ms;   /* CUDA-event times of the three phases of the last call */
     float lex_ms, structure_ms, decode_ms;   /* kernel_ms split by stage */
+    /* statement classes: units of one class share the grammar work through a record template */
+    uint64_t n_classes;          /* classes in the batch's class store after the last slice */
+    uint64_t n_class_capacity;   /* templates the store holds; classes beyond it are decoded unit by unit */
+    uint64_t n_untemplated;      /* units that were decoded one by one */
+    uint64_t n_signature_words, n_signature_capacity;
 } ptxfe_stats;
 
 /* Create a context on CUDA device `device` (one stream, reusable device arenas, pinned result buffers). */

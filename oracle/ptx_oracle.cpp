@@ -1069,6 +1069,11 @@ struct Parser {
     }
     // returns false when neither the statement nor its recovery matches (the enclosing repeat stops)
     bool statement(std::vector<Statement>* out) {
+        // Work budget.  A block that fails to parse is recovered from its '{' and its contents are then parsed again as
+        // statements of the enclosing block (lib.rs:858-880, 921-951): damage below d levels of nesting multiplies the
+        // work (and the appended errors) by 2^d, and winnow does not memoise.  Where the reference would in practice
+        // not come back, parsing stops after 4 * tokens + 1024 statement attempts with the verdict ReferenceDiverges.
+        if (diverged || ++attempts > 4 * (uint64_t)t.size() + 1024) { diverged = true; return false; }
         size_t save = pos;
         Statement st;
         // label
@@ -1125,6 +1130,8 @@ struct Parser {
         return true;
     }
     bool panicked = false;
+    bool diverged = false;
+    uint64_t attempts = 0;
 
     // ---- directives, lib.rs:579-856
     static bool directive_start(uint16_t k) {
@@ -1321,7 +1328,7 @@ struct Parser {
         for (;;) {
             Directive d;
             int r = directive(&d);
-            if (r == 0) break;
+            if (r == 0 || diverged) break;
             if (r == 1) m->directives.push_back(std::move(d));
             else if (r == 3) m->invalid++;
         }
@@ -1675,6 +1682,11 @@ std::string run(const char* text, size_t n, int mode, int* status) {
         Parser p(text, n, lx.toks, errors);
         bool ok = p.module(&m);
         panicked = p.panicked;
+        if (p.diverged) {
+            o.putf("mode: %s\nstatus: ReferenceDiverges\nerrors: 0\n", mode == MODE_CHECKED ? "checked" : mode == MODE_UNCHECKED ? "unchecked" : "errors");
+            *status = 1;
+            return std::move(o.s);
+        }
         if (!ok) errors.push_back({E_PARSER, 0, 0, 0});
         if (mode == MODE_CHECKED) {
             have_module = ok && errors.empty() && m.invalid == 0;
@@ -1710,6 +1722,16 @@ char* oracle_parse(const char* text, uint64_t len, int mode, uint64_t* out_len, 
     if (out_len) *out_len = s.size();
     if (status) *status = st;
     return r;
+}
+
+// 64-bit FNV-1a of the canonical dump (parity checks over many large modules: the dump itself stays on this side).
+uint64_t oracle_dump_hash(const char* text, uint64_t len, int mode, int* status) {
+    int st = 0;
+    std::string s = run(text, len, mode, &st);
+    if (status) *status = st;
+    uint64_t h = 1469598103934665603ull;
+    for (unsigned char c : s) h = (h ^ c) * 1099511628211ull;
+    return h;
 }
 
 // Parse without producing the dump (the timed CPU baseline).  Returns 0 when parse_module_checked would be Ok.

@@ -82,16 +82,31 @@ def all_cases():
 
 
 def class_cases():
-    """Statements of one shape that must NOT share a record: the decoder's result depends on a token's text (numbers,
-    dot-identifiers, %envreg names) or on its surroundings, and statements of one shape that must (only names differ).
+    """Statements of one shape that must NOT share a record template: the decoder's path depends on a token's text
+    (dot-identifiers, %envreg names), on what kind of number a literal is (suffix, radix errors, which limits its
+    magnitude exceeds) or on its surroundings; and statements of one shape that must share one: only names and the
+    digits of literals differ, and the template is instantiated with each statement's own values.
     Every module repeats each statement, so that all but the first meet an existing class."""
     groups = [
         # same kinds, different identifier spellings and lengths: one class, records differ in offsets and lengths only
         ["add.s32 %r1, %r2, %r3;", "add.s32 %rd10, %a, %bb;", "add.s32 %r1,%r2,%r3;", "add.s32   %x ,\n %yy , %zzz ;"],
-        # the spelling of a number is part of the class
-        ["mov.u32 %r1, 1;", "mov.u32 %r1, 2;", "mov.u32 %r1, 0x2;", "mov.u32 %r1, 02;", "mov.u32 %r1, 2U;", "mov.u32 %r1, 99999999999;"],
-        ["mov.f32 %f1, 0f3F800000;", "mov.f32 %f1, 0f40000000;", "mov.f64 %fd1, 1.5;", "mov.f64 %fd1, 1.5e3;", "mov.f64 %fd1, 0d3FF0000000000000;"],
-        ["ld.global.u32 %r1, [%rd1+4];", "ld.global.u32 %r1, [%rd1+8];", "ld.global.u32 %r1, [%rd1+-4];", "ld.global.u32 %r1, [%rd1];"],
+        # the digits of a number are not part of the class, the facts the grammar can learn from them are: one template
+        # serves 1, 2, 0x2, 02 and 077; the suffix, the limits and conversion errors make classes of their own
+        ["mov.u32 %r1, 1;", "mov.u32 %r1, 2;", "mov.u32 %r1, 0x2;", "mov.u32 %r1, 02;", "mov.u32 %r1, 077;", "mov.u32 %r1, 2U;",
+         "mov.u32 %r1, 99999999999;", "mov.u32 %r1, 2147483647;", "mov.u32 %r1, 2147483648;", "mov.u32 %r1, 4294967295;",
+         "mov.u32 %r1, 4294967296;", "mov.u64 %rd1, 9223372036854775807;", "mov.u64 %rd1, 9223372036854775808;",
+         "mov.u64 %rd1, 18446744073709551615;", "mov.u64 %rd1, 18446744073709551616;", "mov.u64 %rd1, 18446744073709551615U;",
+         "mov.u64 %rd1, 0xFFFFFFFFFFFFFFFF;", "mov.u64 %rd1, 0x1FFFFFFFFFFFFFFFF;", "mov.u32 %r1, 09;", "mov.u32 %r1, 0xG;", "mov.u32 %r1, 0xU;",
+         "mov.s64 %rd1, -1;", "mov.s64 %rd1, -9223372036854775807;", "mov.s64 %rd1, -9223372036854775808;", "mov.s64 %rd1, -9223372036854775809;",
+         "mov.s64 %rd1, -0x10;", "mov.s64 %rd1, -5U;", "mov.s64 %rd1, -18446744073709551616;", "mov.u32 %r1, WARP_SZ;"],
+        ["mov.f32 %f1, 0f3F800000;", "mov.f32 %f1, 0f40000000;", "mov.f32 %f1, 0fBF80000a;", "mov.f32 %f1, 0f3F80000G;", "mov.f64 %fd1, 1.5;",
+         "mov.f64 %fd1, 1.5e3;", "mov.f64 %fd1, 2.5e-3;", "mov.f64 %fd1, .5;", "mov.f64 %fd1, 8.98846567431158e307;", "mov.f64 %fd1, 1.0e400;",
+         "mov.f64 %fd1, 0d3FF0000000000000;", "mov.f64 %fd1, 0dBFF000000000000Z;", "mov.f64 %fd1, 0d4000000000000000;", "mov.f64 %fd1, -1.5;"],
+        ["ld.global.u32 %r1, [%rd1+4];", "ld.global.u32 %r1, [%rd1+8];", "ld.global.u32 %r1, [%rd1+-4];", "ld.global.u32 %r1, [%rd1+-8];",
+         "ld.global.u32 %r1, [%rd1];", "ld.global.u32 %r1, [%rd1+0x7FFFFFFF];", "ld.global.u32 %r1, [%rd1+2147483648];",
+         "ld.global.u32 %r1, [%rd1+-2147483647];", "ld.global.u32 %r1, [%rd1+-2147483648];", "ld.global.u32 %r1, [%rd1+010];",
+         "ld.global.u32 %r1, [%rd1+16U];", "st.shared.v2.f32 [%rd2+64], {%f1, 0f3F800000};", "st.shared.v2.f32 [%rd2+128], {%f1, 0f40000000};",
+         "shfl.sync.bfly.b32 %r1|%p1, %r2, 1, 31, -1;", "shfl.sync.bfly.b32 %r1|%p1, %r2, 16, 0x1f, -2;", "bar.sync 0;", "bar.sync 15;"],
         # vector members and unknown dot words
         ["mov.u32 %r1, %tid.x;", "mov.u32 %r1, %tid.y;", "mov.u32 %r1, %tid.z;", "mov.u32 %r1, %tid.w;", "mov.u32 %r1, %tid.q;"],
         # %envreg names raise an error, other names of the same length do not
@@ -165,7 +180,8 @@ def bulk_cases(n=9000):
 
 def capacity_cases():
     """More distinct statement classes than the class store holds, and names at the length limits of the packed forms."""
-    many = "\n".join("mov.u32 %%r1, %d;" % i for i in range(270000))      # 270,000 classes (one per immediate)
+    # 270,000 classes: the text of a string is part of its statement's class; and as many immediates, which are one class
+    many = "\n".join(".pragma \"n%d\";\nmov.u32 %%r1, %d;" % (i, i) for i in range(270000))
     out = [body(many)]
     longs = []
     for n in (125, 126, 127, 128, 254, 255, 256, 300, 65534, 65535, 65536, 70000):
@@ -176,6 +192,26 @@ def capacity_cases():
     # more units without a template than the "few" threshold of the decode stage: calls are never templated
     calls = "\n".join(("call foo, (%%r%d);" % (i % 9)) if i % 3 else "call.uni bar;" for i in range(140000))
     out.append(HEADER + ".func foo(.param .b32 p)\n{\nret;\n}\n.visible .entry k()\n{\n" + DECLS + "\n" + calls + "\nret;\n}\n")
+    return out
+
+
+def nested_damage_cases():
+    """A stray token in front of a '}' below d levels of nested blocks.  The reference recovers a failed block from its
+    '{' and parses its contents again as statements of the enclosing block, at every level: 2^d times the work and as
+    many appended errors.  Shallow damage must come out identical (errors repeated as the reference repeats them); deep
+    damage must end with the verdict ReferenceDiverges on both sides, after the same number of statement attempts."""
+    out = []
+    for depth in (1, 2, 3, 5, 8, 12, 16, 28, 32):
+        lines = []
+        for d in range(depth):
+            lines.append("\t" * d + "{")
+            lines.append("\t" * (d + 1) + ".reg .b32 %%t%d;" % d)
+            lines.append("\t" * (d + 1) + "add.s32 %r1, %r2, %r3;")
+        lines.append("\t" * depth + ".bar")
+        for d in reversed(range(depth)):
+            lines.append("\t" * d + "}")
+        out.append(body("\n".join(lines)))
+        out.append(body("\n".join(lines)) + ".global .u32 after;\n.visible .entry k2()\n{\nret;\n}\n")
     return out
 
 

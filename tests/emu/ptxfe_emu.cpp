@@ -141,6 +141,8 @@ char* emu_parse(const char* const* texts, const uint64_t* lens, uint32_t n, uint
         stats[4] = seq;
         stats[5] = hc.pad;
         stats[6] = hc.n_bulk;
+        stats[7] = hc.n_rest;
+        stats[8] = hc.n_classes;
     }
     char* r = (char*)malloc(all.size() + 1);
     memcpy(r, all.data(), all.size());

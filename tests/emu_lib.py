@@ -28,12 +28,12 @@ class Emu:
         arr = (ctypes.c_char_p * n)(*texts)
         lens = (ctypes.c_uint64 * n)(*[len(t) for t in texts])
         ol = ctypes.c_uint64()
-        st = (ctypes.c_uint64 * 8)()
+        st = (ctypes.c_uint64 * 16)()
         p = self.lib.emu_parse(arr, lens, n, mode, ctypes.byref(ol), st)
         s = ctypes.string_at(p, ol.value)
         self.lib.emu_free(p)
         dumps = [x.decode("utf-8", "replace") for x in s.split(b"\0")[:-1]]
-        return dumps, dict(tokens=st[0], units=st[1], words=st[2], errors=st[3], sequential=st[4], pass_mismatch=st[5], bulk=st[6])
+        return dumps, dict(tokens=st[0], units=st[1], words=st[2], errors=st[3], sequential=st[4], pass_mismatch=st[5], bulk=st[6], untemplated=st[7], classes=st[8])
 
     def lex(self, text):
         if isinstance(text, str):

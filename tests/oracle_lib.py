@@ -18,8 +18,11 @@ class Oracle:
         lib.oracle_lex.restype = ctypes.c_void_p
         lib.oracle_lex.argtypes = [ctypes.c_char_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_uint64),
                                    ctypes.POINTER(ctypes.c_uint64)]
-        lib.oracle_parse_only.argtypes = [ctypes.c_char_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_uint64),
+        # text as an address: bytes objects and raw buffers (pinned host memory) are both accepted
+        lib.oracle_parse_only.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_uint64),
                                           ctypes.POINTER(ctypes.c_uint64)]
+        lib.oracle_dump_hash.restype = ctypes.c_uint64
+        lib.oracle_dump_hash.argtypes = [ctypes.c_void_p, ctypes.c_uint64, ctypes.c_int, ctypes.POINTER(ctypes.c_int)]
         lib.oracle_free.argtypes = [ctypes.c_void_p]
         lib.oracle_token_text.restype = ctypes.c_char_p
 
@@ -33,6 +36,20 @@ class Oracle:
         s = ctypes.string_at(p, n.value).decode("utf-8", "replace")
         self.lib.oracle_free(p)
         return st.value, s
+
+    def dump_hash(self, text, mode=CHECKED):
+        """64-bit FNV-1a of the dump of `text` (bytes, or an (address, length) pair)."""
+        if isinstance(text, tuple):
+            return self.lib.oracle_dump_hash(text[0], text[1], mode, None)
+        if isinstance(text, str):
+            text = text.encode()
+        return self.lib.oracle_dump_hash(ctypes.cast(ctypes.c_char_p(text), ctypes.c_void_p), len(text), mode, None)
+
+    def dump_hashes(self, texts, mode=CHECKED, threads=None):
+        """The same for many modules, one per task over a thread pool (the library call releases the GIL)."""
+        from concurrent.futures import ThreadPoolExecutor
+        with ThreadPoolExecutor(threads or min(32, os.cpu_count() or 1)) as ex:
+            return list(ex.map(lambda t: self.dump_hash(t, mode), texts))
 
     def errors(self, text, mode=CHECKED):
         dump = self.parse(text, mode)[1]

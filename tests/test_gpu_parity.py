@@ -63,6 +63,16 @@ def test_statement_classes(oracle, ctx):
     assert_parity(oracle, ctx, texts + texts[::-1], modes=(0,))
 
 
+def test_nested_damage_and_divergence(oracle, ctx):
+    """Damage below nested blocks: identical while the reference's doubling recovery stays within its work budget,
+    the verdict ReferenceDiverges (PTXFE_MODULE_REF_DIVERGES) beyond it; the kernel that parses such a module returns."""
+    texts = cases.nested_damage_cases()
+    assert_parity(oracle, ctx, texts)
+    b = ctx.parse_batch(texts, 0)
+    assert b.status(len(texts) - 1) == 3 and b.status(0) == 1
+    b.free()
+
+
 def test_negative_decimal_side_file(oracle, ctx):
     assert_parity(oracle, ctx, [cases.negative_decimal_side_file()])
 

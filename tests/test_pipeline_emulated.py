@@ -59,6 +59,18 @@ def test_edge_cases(oracle, emu):
 def test_statement_classes(oracle, emu):
     """Record templates: statements of one shape share the grammar work; what must stay different does."""
     assert_parity(oracle, emu, cases.class_cases())
+    # literal digits are not part of a class: 3,000 statements with fresh immediates, offsets and hex floats are a
+    # handful of classes, and all but their representatives are instantiated from templates
+    rng = random.Random(3)
+    stmts = []
+    for i in range(1000):
+        stmts.append("mov.u32 %%r%d, %d;" % (i % 7, rng.randrange(-2**31, 2**31)))
+        stmts.append("ld.global.f32 %%f%d, [%%rd%d+%d];" % (i % 5, i % 3, 4 * rng.randrange(1024)))
+        stmts.append("fma.rn.f32 %%f1, %%f2, %%f3, 0f%08X;" % rng.randrange(2**32))
+    text = cases.body("\n".join(stmts))
+    stats = assert_parity(oracle, emu, [text], modes=(0,))
+    assert stats["classes"] < 40, stats
+    assert stats["untemplated"] < 60, stats
 
 
 def test_bulk_initialisers(oracle, emu):
@@ -66,6 +78,13 @@ def test_bulk_initialisers(oracle, emu):
     texts = cases.bulk_cases()
     stats = assert_parity(oracle, emu, texts, modes=(0, 2))
     assert stats["bulk"] >= len(texts)      # every module has at least one statement that long
+
+
+def test_nested_damage_and_divergence(oracle, emu):
+    texts = cases.nested_damage_cases()
+    assert_parity(oracle, emu, texts)
+    verdicts = [oracle.parse(t, 0)[1].split("\n")[1] for t in texts]
+    assert verdicts[0] == "status: Err" and verdicts[-1] == "status: ReferenceDiverges", verdicts
 
 
 def test_negative_decimal_side_file(oracle, emu):

@@ -12,6 +12,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libptxfe.so")
+CORPUS_LIB = os.path.join(PKG, "libptxcorpus.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--extended-lambda",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
@@ -53,6 +54,13 @@ def build_library(force=False):
     return log
 
 
+def build_corpus_generator(force=False):
+    """The synthetic-corpus generator (plain C, host only): used by the benchmark, the smoke run and the tests."""
+    src = os.path.join(CSRC, "ptx_corpus.c")
+    if force or _newer(CORPUS_LIB, [src]):
+        _run(["gcc", "-O2", "-fPIC", "-shared", "-o", CORPUS_LIB, src, "-lm"])
+
+
 def build_test_helpers(force=False):
     _run(["make", "-C", os.path.join(ROOT, "oracle")] + (["-B"] if force else []))
     emu_src = os.path.join(ROOT, "tests", "emu", "ptxfe_emu.cpp")
@@ -66,6 +74,7 @@ def build_test_helpers(force=False):
 def build(force=False):
     generate()
     log = build_library(force)
+    build_corpus_generator(force)
     build_test_helpers(force)
     return log
 

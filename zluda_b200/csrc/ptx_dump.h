@@ -478,6 +478,11 @@ inline std::string dump_module(const PtxBatchView& v, uint32_t m, int* status_ou
         else if (d.kind == U_FUNC || d.kind == U_MODVAR) kept++;
     }
     bool panicked = res.sequential && res.status == US_PANIC;
+    if (res.sequential && res.status == US_DIVERGE && !skip_parse) {
+        o.putf("mode: %s\nstatus: ReferenceDiverges\nerrors: 0\n", mode_name);
+        if (status_out) *status_out = 1;
+        return std::move(o.s);
+    }
     if (skip_parse) verdict = v.mode == 0 ? "Err" : "Empty";
     else if (v.mode == 0) {
         have_module = parsed_ok && n_parse_errs == 0 && invalid == 0 && n_lex == 0;

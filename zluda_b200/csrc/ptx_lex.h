@@ -466,6 +466,69 @@ PTX_HD inline uint16_t lx_classify(const uint8_t* g, uint32_t start, uint32_t le
     return k == T_ERROR ? kind : k;
 }
 
+// ------------------------------------------------------------------------------------------------ numeric literals
+// What the parser does with a numeric literal depends on its digits only through a few facts: whether it carries the
+// 'U' suffix, whether it converts at all, and which of the limits the grammar applies it exceeds (i32 for address
+// offsets, u32 for counts, i63 / 2^63 for the S64-or-U64 choice and for negated literals; ptx_parser/src/lib.rs:263-350).
+// Those facts are the literal's CODE.  Two statements whose tokens have the same kinds and the same codes take the same
+// path through the decoder and differ only in the converted values.
+#define PTX_LC_UNS 1u        // 'U' suffix
+#define PTX_LC_ERR 2u        // does not convert to 64 bits: invalid digit for its radix, overflow, or no digits
+#define PTX_LC_GT_I32 4u     // magnitude > 0x7FFFFFFF
+#define PTX_LC_GT_U32 8u     // magnitude > 0xFFFFFFFF
+#define PTX_LC_GT_I63 16u    // magnitude > 2^63 - 1
+#define PTX_LC_GT_2P63 32u   // magnitude > 2^63
+#define PTX_LC_LONG 64u      // a token of 65535 bytes or more: not looked at
+PTX_HD inline bool ptx_is_numeric_kind(uint16_t k) {
+    static_assert(T_F32HEX == 18 && T_DECIMAL == 22, "the five numeric literal kinds are consecutive");
+    return (uint32_t)(k - T_F32HEX) <= (uint32_t)(T_DECIMAL - T_F32HEX);
+}
+// Magnitude (DECIMAL, HEX: radix 8 / 10 / 16 by prefix, 'U' stripped) or bit pattern (F32HEX, F64HEX) of a literal of
+// `len` < 65535 bytes, and its code.  T_F64 (decimal floating point) has code 0 and is converted elsewhere.
+PTX_HD inline uint32_t ptx_literal_scan(const uint8_t* s, uint32_t len, uint16_t kind, uint64_t* mag) {
+    *mag = 0;
+    if (kind == T_F64) return 0;
+    uint32_t code = 0, i = 0, radix = 16;
+    if (kind == T_DECIMAL || kind == T_HEX) {
+        if (s[len - 1] == 'U') { code |= PTX_LC_UNS; len--; }
+        if (kind == T_HEX) i = 2;
+        else radix = s[0] == '0' ? 8 : 10;
+    } else {
+        i = 2;
+    }
+    if (i >= len) return code | PTX_LC_ERR;
+    uint64_t v = 0;
+    for (; i < len; i++) {
+        uint32_t ch = s[i], d;
+        if (ch - '0' < 10u) d = ch - '0';
+        else if ((ch | 32u) - 'a' < 26u) d = (ch | 32u) - 'a' + 10;
+        else return code | PTX_LC_ERR;
+        if (d >= radix) return code | PTX_LC_ERR;
+        if (v > (~0ull - d) / radix) return code | PTX_LC_ERR;
+        v = v * radix + d;
+    }
+    *mag = v;
+    if (kind == T_DECIMAL || kind == T_HEX) {
+        if (v > 0x7FFFFFFFull) code |= PTX_LC_GT_I32;
+        if (v > 0xFFFFFFFFull) code |= PTX_LC_GT_U32;
+        if (v > 0x7FFFFFFFFFFFFFFFull) code |= PTX_LC_GT_I63;
+        if (v > 0x8000000000000000ull) code |= PTX_LC_GT_2P63;
+    }
+    return code;
+}
+// the entry of the per-token side array `kinds`: kind in the low 9 bits; above them the literal code of a numeric
+// literal, min(length, 127) of every other token
+PTX_HD inline uint16_t ptx_kind_entry(const uint8_t* text, uint32_t start, uint32_t len, uint16_t kind) {
+    uint32_t aux;
+    if (ptx_is_numeric_kind(kind)) {
+        uint64_t mag;
+        aux = len >= 0xFFFFu ? PTX_LC_LONG : ptx_literal_scan(text + start, len, kind, &mag);
+    } else {
+        aux = len < 127u ? len : 127u;
+    }
+    return (uint16_t)(kind | (aux << 9));
+}
+
 PTX_HD inline uint32_t ptx_token_len(const uint8_t* s, const PtxToken& t, uint64_t me) {
     if (t.len != 0xFFFF) return t.len;
     if (t.kind == T_STRING) {

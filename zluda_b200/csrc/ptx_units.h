@@ -3,7 +3,7 @@
 #pragma once
 #include "ptx_decode.h"
 
-enum PtxUnitStatus { US_OK = 0, US_FAIL = 1, US_PANIC = 2 };
+enum PtxUnitStatus { US_OK = 0, US_FAIL = 1, US_PANIC = 2, US_DIVERGE = 3 };
 
 struct PtxUnitResult {
     uint32_t end;        // token index where the unit stopped
@@ -64,8 +64,15 @@ PTX_HD PTX_NOINLINE inline PtxUnitResult ptx_decode_unit(PtxDecoder& d, uint32_t
 
 // Whole module, sequentially, exactly as the reference's `module` parser would (lib.rs:503-526, 579-617, 847-880).
 // `tb` = first token of the module.  `base` = global word offset of the sink's first word (write mode).
-// Returns US_OK, or US_PANIC where the reference would panic.
+// Returns US_OK, US_PANIC where the reference would panic, or US_DIVERGE: a block that fails to parse is recovered from
+// its '{' and its contents are parsed again as statements of the enclosing block, so damage below d levels of nesting
+// costs the reference 2^d times the work (it does not memoise) and appends as many errors.  After 4 * tokens + 1024
+// statement attempts the module is given up with the verdict ReferenceDiverges; this also bounds the running time of
+// the one thread that parses it.
 PTX_HD PTX_NOINLINE inline int ptx_decode_module_sequential(PtxDecoder& d, uint32_t tb, uint32_t base) {
+    d.stmt_attempts = 0;
+    d.stmt_budget = 4ull * (uint64_t)(d.te - tb) + 1024ull;
+    d.diverged = false;
     d.pos = tb;
     d.unit_off = tb < d.te ? d.tk(tb).start : 0;
     uint32_t m;
@@ -90,6 +97,7 @@ PTX_HD PTX_NOINLINE inline int ptx_decode_module_sequential(PtxDecoder& d, uint3
             bool body_ok = false, failed = false;
             while (!failed) {
                 uint16_t tk = d.kind();
+                if ((tk == T_LBRACE || tk == T_RBRACE) && ++d.stmt_attempts > d.stmt_budget) return US_DIVERGE;
                 if (tk == T_LBRACE) {
                     if (sp == PTX_SEQ_MAX_DEPTH) { d.push(E_PARSER, 1, 0, 0); failed = true; break; }
                     blk_pos[sp] = d.pos;
@@ -109,6 +117,7 @@ PTX_HD PTX_NOINLINE inline int ptx_decode_module_sequential(PtxDecoder& d, uint3
                     continue;
                 }
                 int s = d.statement();
+                if (d.diverged) return US_DIVERGE;
                 if (s == -2) s = d.recover_statement();
                 if (s == 1) continue;
                 if (s < 0) return US_PANIC;

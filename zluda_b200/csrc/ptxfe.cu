@@ -759,6 +759,11 @@ int ptxfe_run(ptxfe_ctx* ctx, uint32_t mode) {
     s.n_lex_errors = ctx->counters.n_lexerrs;
     s.n_kernel_launches = ctx->launches;
     s.n_sequential = 0;
+    s.n_classes = ctx->counters.n_classes;
+    s.n_class_capacity = PTX_MAX_CLASSES;
+    s.n_untemplated = ctx->counters.n_rest;
+    s.n_signature_words = ctx->counters.n_sig_words;
+    s.n_signature_capacity = PTX_SIG_POOL_WORDS;
     ctx->ran = true;
     collect_profile(ctx);
     return PTXFE_OK;
@@ -945,6 +950,9 @@ int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* 
     std::vector<size_t> base_w(ns), base_e(ns), base_l(ns);
     ptxfe_stats& s = ctx->stats;
     s.n_tokens = s.n_units = s.n_result_words = s.n_errors = s.n_lex_errors = 0;
+    s.n_classes = s.n_untemplated = s.n_signature_words = 0;
+    s.n_class_capacity = PTX_MAX_CLASSES;
+    s.n_signature_capacity = PTX_SIG_POOL_WORDS;
     for (size_t k = 0; k < ns; k++) {
         const Slice& sl = slices[k];
         ctx->cur = (int)(k & 1);
@@ -988,6 +996,9 @@ int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* 
         s.n_result_words += nw;
         s.n_errors += ne;
         s.n_lex_errors += nl;
+        s.n_untemplated += c.n_rest;
+        s.n_classes = c.n_classes;
+        s.n_signature_words = c.n_sig_words;
     }
     CUDA_TRY(cudaStreamSynchronize(ctx->s_out));
     CUDA_TRY(cudaStreamSynchronize(ctx->s_in));
@@ -1083,6 +1094,7 @@ int ptxfe_module_status(const ptxfe_batch* b, uint32_t i) {
     int status = 0;
     std::string s = ptxfe_dump_module_impl(view_of(b), i, &status);
     if (b->results[i].sequential && b->results[i].status == US_PANIC) return PTXFE_MODULE_REF_PANICS;
+    if (b->results[i].sequential && b->results[i].status == US_DIVERGE) return PTXFE_MODULE_REF_DIVERGES;
     return status ? PTXFE_MODULE_ERR : PTXFE_MODULE_OK;
 }
 

@@ -61,9 +61,11 @@ struct PtxScratch {
 };
 
 // ---- unit classes and record templates
-// Two units are in the same class when they have the same token kinds, the same text in every token whose text the
-// decoder reads (numbers, dot-identifiers, strings, `%envreg` names) and the same depth class.  The decoder then takes
-// the same path for both, and their records differ only in words copied from tokens (offsets, lengths).  One
+// Two units are in the same class when they have the same token kinds, the same literal codes (ptx_lex.h: what the
+// decoder's control flow can learn from a number), the same text in every other token whose text the decoder reads
+// (dot-identifiers that are no keyword, strings, `%envreg` names) and the same depth class.  The decoder then takes
+// the same path for both, and their records differ only in words taken from tokens (offsets, lengths, converted
+// literal values).  One
 // representative per class is decoded with tagged output (PtxSink::tags); every other unit is compared with its
 // representative token by token and its record is instantiated from the template.
 #define PTX_TMPL_WORDS 40u            // longest record that gets a template
@@ -73,8 +75,9 @@ enum { PTX_UNIT_STAGED = 0, PTX_UNIT_FLAGGED = 1, PTX_UNIT_NOTHING = 2, PTX_UNIT
 struct PtxTemplateInfo {
     uint32_t n_words, n_tokens, ok, depth1;
 };
-// The per-token side array `kinds` holds kind | min(length, 127) << 9: most passes want the kind alone, and the class
-// passes can tell from the length whether they have to look at the token itself.
+// The per-token side array `kinds` holds kind | aux << 9 (ptx_kind_entry): aux is the literal code of a numeric literal
+// and min(length, 127) of any other token.  Most passes want the kind alone; the class passes need the token itself
+// only for dot-identifiers, strings and identifiers of 8 or 9 bytes.
 #define PTX_KL_KIND(x) ((uint16_t)((x) & 0x1FFu))
 #define PTX_KL_LEN(x) ((uint32_t)(x) >> 9)
 #define PTX_KL_LONG 127u
@@ -90,13 +93,7 @@ PTX_HD inline uint32_t ptx_text_word(const uint8_t* text, uint32_t off, uint32_t
     if (rem < 4) v &= (1u << (8u * rem)) - 1u;
     return v;
 }
-PTX_HD inline bool ptx_text_matters(uint16_t k) {
-    static_assert(T_DECIMAL < 32 && T_HEX < 32 && T_F32HEX < 32 && T_F64HEX < 32 && T_F64 < 32 && T_DOTIDENT < 32 && T_STRING < 32,
-                  "the literal token kinds are among the first 32");
-    const uint32_t mask = (1u << T_DECIMAL) | (1u << T_HEX) | (1u << T_F32HEX) | (1u << T_F64HEX) | (1u << T_F64) | (1u << T_DOTIDENT) |
-                          (1u << T_STRING);
-    return k < 32 && ((mask >> k) & 1u);
-}
+PTX_HD inline bool ptx_text_matters(uint16_t k) { return k == T_DOTIDENT || k == T_STRING; }
 // 64-bit class key of the tokens [start, end); 0 = this unit gets no template
 PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens, const uint16_t* kinds, uint32_t start, uint32_t end, uint32_t depth,
                                      bool module_first) {
@@ -108,7 +105,12 @@ PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens
         h1 = (h1 ^ kind) * 16777619u;
         h2 = (h2 + kind) * 0x9E3779B1u;
         h2 ^= h2 >> 15;
-        if (ptx_text_matters(kind)) {
+        if (ptx_is_numeric_kind(kind)) {
+            const uint32_t code = PTX_KL_LEN(kl);
+            if (code & PTX_LC_LONG) return 0;
+            h1 = (h1 ^ code) * 16777619u;
+            h2 = (h2 + code) * 0x85EBCA6Bu;
+        } else if (ptx_text_matters(kind)) {
             const PtxToken t = tokens[i];
             if (t.len == 0xFFFF) return 0;
             h2 = (h2 ^ t.len) * 0x85EBCA6Bu;
@@ -133,8 +135,9 @@ PTX_HD inline uint64_t ptx_class_key(const uint8_t* text, const PtxToken* tokens
 // The class store lives as long as a batch: the slices of one ptxfe_parse_batch call share it, so a class met in
 // slice 3 is not decoded again in slice 4.  A class keeps a SIGNATURE (what ptx_class_key hashed, spelled out), so that
 // membership can be checked exactly without the representative's tokens, which are gone when its slice is.
-//   signature = [n_tokens | depth1 << 31, then per token: kind | len << 16, and for tokens whose text matters
-//                ceil(len / 4) words of text; for identifiers: kind | envreg << 16]
+//   signature = [n_tokens | depth1 << 31, then per token: kind | x << 16 with x = the literal code of a numeric literal,
+//                the envreg flag of an identifier, the length of a token whose text matters, which is followed by
+//                ceil(len / 4) words of text]
 #define PTX_CLASS_SLOTS (1u << 20)          // hash slots (power of two)
 #define PTX_SIG_POOL_WORDS (16u << 20)      // 64 MiB of signatures
 struct PtxClassStore {
@@ -174,11 +177,14 @@ PTX_HD inline uint32_t ptx_signature_words(const PtxToken* tokens, uint32_t star
     }
     return w;
 }
-PTX_HD inline void ptx_signature_write(uint32_t* sig, const uint8_t* text, const PtxToken* tokens, uint32_t start, uint32_t n, uint32_t depth1) {
+PTX_HD inline void ptx_signature_write(uint32_t* sig, const uint8_t* text, const PtxToken* tokens, const uint16_t* kinds, uint32_t start, uint32_t n,
+                                       uint32_t depth1) {
     *sig++ = n | (depth1 << 31);
     for (uint32_t i = 0; i < n; i++) {
         const PtxToken t = tokens[start + i];
-        if (ptx_text_matters(t.kind)) {
+        if (ptx_is_numeric_kind(t.kind)) {
+            *sig++ = t.kind | (PTX_KL_LEN(kinds[start + i]) << 16);
+        } else if (ptx_text_matters(t.kind)) {
             *sig++ = t.kind | ((uint32_t)t.len << 16);
             for (uint32_t j = 0; j < t.len; j += 4) {
                 uint32_t v = ptx_text_word(text, t.start + j, t.len - j);
@@ -201,7 +207,9 @@ PTX_HD inline bool ptx_signature_matches(const uint32_t* sig, const uint8_t* tex
         const uint16_t kind = PTX_KL_KIND(kl);
         uint32_t head = *sig++;
         if ((head & 0xFFFFu) != kind) return false;
-        if (ptx_text_matters(kind)) {
+        if (ptx_is_numeric_kind(kind)) {
+            if ((head >> 16) != PTX_KL_LEN(kl)) return false;
+        } else if (ptx_text_matters(kind)) {
             const PtxToken t = tokens[start + i];
             if ((head >> 16) != t.len || t.len == 0xFFFF) return false;
             for (uint32_t j = 0; j < t.len; j += 4) {
@@ -235,6 +243,8 @@ struct PtxCounters {
     uint32_t n_bulk;            // statements long enough for the bulk initialiser path
     uint32_t n_rest;            // units without a template
     uint32_t n_listed;
+    uint32_t n_classes;         // statement classes met so far in this batch (all slices)
+    uint32_t n_sig_words;       // words of the signature pool in use
 };
 
 PTX_HD inline uint32_t ptx_upper_bound_u32(const uint32_t* a, uint32_t n, uint32_t x) {
@@ -424,7 +434,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         PtxToken t = slots[c * PTX_CHUNK + i];
         t.kind = lx_classify8(text, t.start, t.len, t.kind);
         tokens[j] = t;
-        kinds[j] = (uint16_t)(t.kind | ((t.len < PTX_KL_LONG ? t.len : PTX_KL_LONG) << 9));
+        kinds[j] = ptx_kind_entry(text, t.start, t.len, t.kind);
     });
     // A6: lexer errors are rare: a second walk, only when there are any, and only over the chunks that have one
     if (n_lexerrs) bk.pf_text("lex_emit_errors", n_chunks, text, PtxLexErrorsStep{info, text, vec, cnt, lexerrs});
@@ -709,7 +719,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
 #endif
             if (at + need <= PTX_SIG_POOL_WORDS) {
                 cs.sig_off[id] = at;
-                ptx_signature_write(cs.sig_pool + at, text, tokens, start, ti.n_tokens, ti.depth1);
+                ptx_signature_write(cs.sig_pool + at, text, tokens, kinds, start, ti.n_tokens, ti.depth1);
             } else {
                 ti.ok = 0;
             }
@@ -759,6 +769,8 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         uint32_t rest = 0;
         for (int i = 0; i < 64; i++) rest += rest_count[i];
         counters->n_rest = rest;
+        counters->n_classes = cs.state[0];
+        counters->n_sig_words = cs.state[1];
     });
     bk.download(&host_counters, counters, sizeof(PtxCounters));
     const uint32_t max_funcs = host_counters.pad;
@@ -1032,7 +1044,13 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         if (g) {
             const PtxToken t = tokens[ustart[u] + (g & 0xFFu)];
             uint32_t type = g >> 8;
-            x = type == PTX_TAG_START ? t.start : type == PTX_TAG_LEN ? (uint32_t)t.len : ((x & 0xFFu) | ((uint32_t)t.len << 8));
+            if (type >= PTX_TAG_VAL_LO) {
+                uint64_t v = ptx_literal_value(text, t.start, t.len, t.kind);
+                if (type >= PTX_TAG_NEG_LO) v = 0 - v;
+                x = (type & 1u) ? (uint32_t)(v >> 32) : (uint32_t)v;
+            } else {
+                x = type == PTX_TAG_START ? t.start : type == PTX_TAG_LEN ? (uint32_t)t.len : ((x & 0xFFu) | ((uint32_t)t.len << 8));
+            }
         }
         words[j] = x;
     });
