@@ -1339,7 +1339,16 @@ struct Parser {
 // =============================================================================================== canonical dump
 struct Out {
     std::string s;
-    void put(sv x) { s.append(x); }
+    // hash-only mode: the text is folded into a 64-bit FNV-1a hash as it grows and is not kept (a module with millions of
+    // initialisers dumps to gigabytes)
+    bool hashing = false;
+    uint64_t h = 1469598103934665603ull;
+    void fold() {
+        for (unsigned char c : s) h = (h ^ c) * 1099511628211ull;
+        s.clear();
+    }
+    void tick() { if (hashing && s.size() > (1u << 16)) fold(); }
+    void put(sv x) { s.append(x); tick(); }
     void putf(const char* fmt, ...) __attribute__((format(printf, 2, 3))) {
         char buf[128];
         va_list ap;
@@ -1667,11 +1676,13 @@ void dump_errors(Out& o, const std::vector<Error>& errs, const char* text) {
 enum { MODE_CHECKED = 0, MODE_UNCHECKED = 1, MODE_ERRORS_ONLY = 2 };
 
 // lib.rs:392-501.  The dump has a fixed layout: mode line, status line, the module (when one is returned), the errors.
-std::string run(const char* text, size_t n, int mode, int* status) {
+// With `hash_out` the dump is not kept: its FNV-1a hash is returned there and the string comes back empty.
+std::string run(const char* text, size_t n, int mode, int* status, uint64_t* hash_out = nullptr) {
     LexResult lx = lex(text, n);
     std::vector<Error> errors;
     for (const Tok& e : lx.errors) errors.push_back({E_LEXER, 0, e.start, e.end - e.start});
     Out o;
+    o.hashing = hash_out != nullptr;
     Module m;
     bool have_module = false;
     const char* verdict;
@@ -1685,6 +1696,7 @@ std::string run(const char* text, size_t n, int mode, int* status) {
         if (p.diverged) {
             o.putf("mode: %s\nstatus: ReferenceDiverges\nerrors: 0\n", mode == MODE_CHECKED ? "checked" : mode == MODE_UNCHECKED ? "unchecked" : "errors");
             *status = 1;
+            if (hash_out) { o.fold(); *hash_out = o.h; }
             return std::move(o.s);
         }
         if (!ok) errors.push_back({E_PARSER, 0, 0, 0});
@@ -1705,6 +1717,7 @@ std::string run(const char* text, size_t n, int mode, int* status) {
         o.put("Module { ptx_version: (1, 0), sm_version: 0, address_size: 64, invalid_directives: 18446744073709551615, directives: 0 }\n");
     dump_errors(o, errors, text);
     *status = have_module ? 0 : 1;
+    if (hash_out) { o.fold(); *hash_out = o.h; }
     return std::move(o.s);
 }
 
@@ -1727,10 +1740,9 @@ char* oracle_parse(const char* text, uint64_t len, int mode, uint64_t* out_len, 
 // 64-bit FNV-1a of the canonical dump (parity checks over many large modules: the dump itself stays on this side).
 uint64_t oracle_dump_hash(const char* text, uint64_t len, int mode, int* status) {
     int st = 0;
-    std::string s = run(text, len, mode, &st);
+    uint64_t h = 0;
+    run(text, len, mode, &st, &h);
     if (status) *status = st;
-    uint64_t h = 1469598103934665603ull;
-    for (unsigned char c : s) h = (h ^ c) * 1099511628211ull;
     return h;
 }
 

@@ -351,7 +351,7 @@ size_t ptx_corpus_config3(uint64_t seed, uint64_t total_bytes, uint32_t n_funcs,
                 gen_statement(&o, &r, name, 1, 0);    /* its rare branches go to the kernel's first generated label */
             }
             line_no++;
-            if (rng_unit(&r) < 0.75) {
+            if (rng_unit(&r) < 0.95) {
                 uint32_t i = rng_below(&r, 512);
                 if (rng_below(&r, 2)) {
                     put(&o, "\t// inlined from helper_"); put_u64(&o, i); put(&o, " at line "); put_u64(&o, i * 7 % 1000);

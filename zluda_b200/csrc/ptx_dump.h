@@ -18,8 +18,17 @@ namespace ptxdump {
 
 struct Out {
     std::string s;
-    void put(const char* x) { s.append(x); }
-    void putn(const char* x, size_t n) { s.append(x, n); }
+    // hash-only mode: the text is folded into a 64-bit FNV-1a hash as it grows and is not kept (a module with millions of
+    // initialisers dumps to gigabytes)
+    bool hashing = false;
+    uint64_t h = 1469598103934665603ull;
+    void fold() {
+        for (unsigned char c : s) h = (h ^ c) * 1099511628211ull;
+        s.clear();
+    }
+    void tick() { if (hashing && s.size() > (1u << 16)) fold(); }
+    void put(const char* x) { s.append(x); tick(); }
+    void putn(const char* x, size_t n) { s.append(x, n); tick(); }
     void putf(const char* fmt, ...) __attribute__((format(printf, 2, 3))) {
         char buf[160];
         va_list ap;
@@ -404,10 +413,12 @@ struct Directive {
     uint32_t n_errors = 0;
 };
 
-inline std::string dump_module(const PtxBatchView& v, uint32_t m, int* status_out) {
+// With `hash_out` the dump is not kept: its FNV-1a hash is returned there and the string comes back empty.
+inline std::string dump_module(const PtxBatchView& v, uint32_t m, int* status_out, uint64_t* hash_out = nullptr) {
     Reader r(v, m);
     const PtxModuleResult& res = v.results[m];
     Out o;
+    o.hashing = hash_out != nullptr;
     const char* mode_name = v.mode == 0 ? "checked" : v.mode == 1 ? "unchecked" : "errors";
     uint32_t n_lex = res.lexerr_end - res.lexerr_begin;
     uint64_t base = v.layout[m].text_off;
@@ -481,6 +492,7 @@ inline std::string dump_module(const PtxBatchView& v, uint32_t m, int* status_ou
     if (res.sequential && res.status == US_DIVERGE && !skip_parse) {
         o.putf("mode: %s\nstatus: ReferenceDiverges\nerrors: 0\n", mode_name);
         if (status_out) *status_out = 1;
+        if (hash_out) { o.fold(); *hash_out = o.h; }
         return std::move(o.s);
     }
     if (skip_parse) verdict = v.mode == 0 ? "Err" : "Empty";
@@ -577,6 +589,7 @@ inline std::string dump_module(const PtxBatchView& v, uint32_t m, int* status_ou
         if (!parsed_ok && res.word_begin == res.word_end) o.put("Parser(ContextError)\n");
     }
     if (status_out) *status_out = have_module ? 0 : 1;
+    if (hash_out) { o.fold(); *hash_out = o.h; }
     return std::move(o.s);
 }
 

@@ -20,6 +20,7 @@
 
 // host side (ptxfe_dump.cpp)
 std::string ptxfe_dump_module_impl(const PtxBatchView& v, uint32_t m, int* status);
+uint64_t ptxfe_dump_hash_impl(const PtxBatchView& v, uint32_t m, int* status);
 
 #define CUDA_TRY(call)                                                                      \
     do {                                                                                    \
@@ -1082,10 +1083,7 @@ int ptxfe_module_dump(const ptxfe_batch* b, uint32_t i, char** out, uint64_t* ou
 int ptxfe_module_dump_hash(const ptxfe_batch* b, uint32_t i, uint64_t* out_hash) {
     if (!b || !b->ctx || i >= b->n || !out_hash) return PTXFE_ERR_BAD_ARG;
     int status = 0;
-    std::string s = ptxfe_dump_module_impl(view_of(b), i, &status);
-    uint64_t h = 1469598103934665603ull;
-    for (unsigned char c : s) h = (h ^ c) * 1099511628211ull;
-    *out_hash = h;
+    *out_hash = ptxfe_dump_hash_impl(view_of(b), i, &status);
     return PTXFE_OK;
 }
 
