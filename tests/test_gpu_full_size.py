@@ -89,7 +89,7 @@ def test_config2_literal_heavy(oracle, ctx):
     """16 arrays x 4 Mi initialisers (hex and decimal) + 1 Mi scalar constants (0d / 0f hex, 9- and 17-digit decimals):
     ~400 MB in one module."""
     mods = corpus.config2()
-    assert 3.5e8 < len(mods[0]) < 5.5e8
+    assert 3.5e8 < len(mods[0]) < 7.0e8      # the stated counts give ~620 MB; the configuration text says "~400 MB"
     expect = {}
     t = threading.Thread(target=lambda: expect.setdefault("h", oracle.dump_hash(mods[0])))
     t.start()
