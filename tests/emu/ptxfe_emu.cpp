@@ -50,6 +50,41 @@ struct HostBackend {
         }
         return cs;
     }
+    // the block-cooperative lexer steps, phase by phase with one "thread" after the other (a small thread count, so
+    // that the strided loops of every phase take several rounds)
+    void lex_mark(const char*, size_t n_tiles, const PtxLexTileArgs& a) {
+        const uint32_t nt = 24;
+        std::vector<PtxLexMarkShared> shv(1);
+        PtxLexMarkShared& sh = shv[0];
+        auto phase = [&](auto f) {
+            if (reverse) { for (uint32_t t = nt; t-- > 0;) f(t); } else { for (uint32_t t = 0; t < nt; t++) f(t); }
+        };
+        for (size_t tile = 0; tile < n_tiles; tile++) {
+            phase([&](uint32_t t) { lt_mark_init(sh, a, (uint32_t)tile, t, nt); });
+            phase([&](uint32_t t) { lt_mark_simple(sh, a, (uint32_t)tile, t, nt); });
+            phase([&](uint32_t t) { lt_mark_special(sh, a, (uint32_t)tile, t, nt); });
+            phase([&](uint32_t t) { lt_mark_triggers(sh, a, (uint32_t)tile, t, nt); });
+            phase([&](uint32_t t) { lt_mark_finish(sh, a, (uint32_t)tile, t, nt); });
+        }
+    }
+    void lex_emit(const char*, size_t n_tiles, const PtxLexTileArgs& a) {
+        const uint32_t nt = 24;
+        std::vector<PtxLexEmitShared> shv(1);
+        PtxLexEmitShared& sh = shv[0];
+        auto phase = [&](auto f) {
+            if (reverse) { for (uint32_t t = nt; t-- > 0;) f(t); } else { for (uint32_t t = 0; t < nt; t++) f(t); }
+        };
+        for (size_t tile = 0; tile < n_tiles; tile++) {
+            phase([&](uint32_t t) { lt_emit_init(sh, a, (uint32_t)tile, t, nt); });
+            phase([&](uint32_t t) { lt_emit_list(sh, t, nt); });
+            const uint32_t n_tok = sh.chunk_rank[LT_CHUNKS];
+            for (uint32_t t0 = 0; t0 < n_tok; t0 += LT_BATCH) {
+                phase([&](uint32_t t) { lt_emit_first(sh, a, (uint32_t)tile, t0, t, nt); });
+                phase([&](uint32_t t) { lt_emit_second(sh, a, (uint32_t)tile, t0, t, nt); });
+                phase([&](uint32_t t) { lt_emit_reset(sh, t); });
+            }
+        }
+    }
     template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f) {
         const uint32_t cap = 40, win_cap = 5;   // a small window, so that decoders cross its end
         std::vector<uint32_t> stage(cap);

@@ -342,7 +342,10 @@ PTX_HD inline void lx_chunk(const TX& tx, const uint8_t* g, uint32_t ms, uint32_
         }
         break;
     }
-    while (p <= me && (p < ce || (lx_state_open(st) && tstart >= cs))) {
+    // Past the end of the chunk the walk goes on while a token that started inside it is open - and, for a few bytes,
+    // while any token is open: a token that fails late backs up by at most 18 bytes ("0d" + 16 digits), and where it
+    // backs up to a byte of this chunk the tokens from there on are this chunk's.
+    while (p <= me && (p < ce || (lx_state_open(st) && (tstart >= cs || p < ce + 32u)))) {
         const unsigned c = p < me ? tx[p] : ' ';
         const uint32_t e = tx.lookup(st, c);
         const int prev = st;

@@ -87,6 +87,38 @@ __global__ void __launch_bounds__(256) lex_tile_kernel(uint32_t n_chunks, const 
     if (c < n_chunks) f((size_t)c, PtxTileReader{tile, fused, text, c0 * PTX_CHUNK});
 }
 
+// ---- the two block-cooperative lexer steps (ptx_lex_tile.h): one block per tile, a barrier between the phases
+__global__ void __launch_bounds__(256) lex_mark_kernel(PtxLexTileArgs a) {
+    __shared__ PtxLexMarkShared sh;
+    const uint32_t tile = blockIdx.x, tid = threadIdx.x;
+    lt_mark_init(sh, a, tile, tid, 256);
+    __syncthreads();
+    lt_mark_simple(sh, a, tile, tid, 256);
+    __syncthreads();
+    lt_mark_special(sh, a, tile, tid, 256);
+    __syncthreads();
+    lt_mark_triggers(sh, a, tile, tid, 256);
+    __syncthreads();
+    lt_mark_finish(sh, a, tile, tid, 256);
+}
+__global__ void __launch_bounds__(256) lex_emit_kernel(PtxLexTileArgs a) {
+    __shared__ PtxLexEmitShared sh;
+    const uint32_t tile = blockIdx.x, tid = threadIdx.x;
+    lt_emit_init(sh, a, tile, tid, 256);
+    __syncthreads();
+    lt_emit_list(sh, tid, 256);
+    __syncthreads();
+    const uint32_t n_tok = sh.chunk_rank[LT_CHUNKS];
+    for (uint32_t t0 = 0; t0 < n_tok; t0 += LT_BATCH) {
+        lt_emit_first(sh, a, tile, t0, tid, 256);
+        __syncthreads();
+        lt_emit_second(sh, a, tile, t0, tid, 256);
+        __syncthreads();
+        lt_emit_reset(sh, tid);
+        __syncthreads();
+    }
+}
+
 // ---- first decode pass: every thread builds its record in shared memory, then each warp copies its 32 records to
 // their rows of the staging table with coalesced stores.  Word k of thread t lives at stage[k * STAGE_STRIDE + t]:
 // threads of a warp decode units of the same shape in lockstep, so they write the same k at the same time (32
@@ -495,6 +527,20 @@ struct CudaBackend {
             cudaFuncSetAttribute(lex_tile_kernel<true, F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(LEX_TILE_BYTES + LEX_TABLE_BYTES));
             lex_tile_kernel<true><<<blocks, 256, LEX_TILE_BYTES + LEX_TABLE_BYTES, ctx->stream>>>((uint32_t)n, text, f);
         }
+        prof_end();
+        ctx->launches++;
+    }
+    void lex_mark(const char* name, size_t n_tiles, const PtxLexTileArgs& a) {
+        if (ctx->failed || n_tiles == 0) return;
+        prof_begin(name);
+        lex_mark_kernel<<<(unsigned)n_tiles, 256, 0, ctx->stream>>>(a);
+        prof_end();
+        ctx->launches++;
+    }
+    void lex_emit(const char* name, size_t n_tiles, const PtxLexTileArgs& a) {
+        if (ctx->failed || n_tiles == 0) return;
+        prof_begin(name);
+        lex_emit_kernel<<<(unsigned)n_tiles, 256, 0, ctx->stream>>>(a);
         prof_end();
         ctx->launches++;
     }

@@ -326,6 +326,8 @@ struct SegDepthOp {
 //   template <class F> void pf_segments(const char* name, size_t n, const PtxPair* off, F f);
 //        segment s owns the items [off[s].a, off[s + 1].a): f(s, i, off[s].a + i) for every s < n and every item i of s
 //   PtxClassStore class_store(bool reset);   the batch's class store (device memory that outlives the arena), emptied if asked
+//   void lex_mark(const char* name, size_t n_tiles, const PtxLexTileArgs& a);   the phases of ptx_lex_tile.h's mark step, one block per tile
+//   void lex_emit(const char* name, size_t n_tiles, const PtxLexTileArgs& a);   the phases of its emit step
 //   void* alloc(size_t bytes); void zero(void* p, size_t bytes);
 //   void download(void* host, const void* dev, size_t bytes);   (synchronises the stream)
 // The pipeline allocates through the backend and never frees: the backend's arena is reset per batch.
@@ -344,6 +346,7 @@ struct PtxLexChunkInfo {
         first = c == mcb[m];
     }
 };
+#include "ptx_lex_tile.h"
 struct PtxLexVectorsStep {
     PtxLexChunkInfo info;
     uint32_t* vec;
@@ -413,9 +416,15 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     // A2: inclusive scan with composition; chunk c starts in state (prefix[c-1])[CODE]
     bk.template scan<uint32_t>("scan_context", n_chunks, [=] PTX_HD(size_t i) { return vec[i]; }, [=] PTX_HD(size_t i, uint32_t v) { vec[i] = v; },
                                ComposeOp(), CX_IDENTITY);
-    // A3: the token pass.  Every chunk writes its tokens into its own row of PTX_CHUNK slots
-    PtxToken* slots = (PtxToken*)bk.alloc(sizeof(PtxToken) * PTX_CHUNK * ((size_t)n_chunks + 1));
-    bk.pf_text("lex_tokens", n_chunks, text, PtxLexTokensStep{info, text, vec, cnt, slots});
+    // A3: token boundaries, byte-parallel: one bit per text byte and the token / error count of every chunk
+    const size_t n_tiles = ((size_t)n_chunks + LT_CHUNKS - 1) / LT_CHUNKS;
+    uint32_t* start_bits = (uint32_t*)bk.alloc(sizeof(uint32_t) * LT_WORDS * (n_tiles + 1));
+    uint32_t* mod_flag = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 1));
+    bk.zero(mod_flag, sizeof(uint32_t) * (n_modules + 1));
+    PtxLexTileArgs la{info, text, vec, n_chunks, start_bits, cnt, mod_flag, nullptr, nullptr};
+    bk.lex_mark("lex_mark", n_tiles, la);
+    // modules with a run of soft bytes too long for the look-back of the parallel step: one thread each (rare)
+    bk.pf("lex_serial_modules", n_modules, [=] PTX_HD(size_t m) { lt_lex_module_serial(la, (uint32_t)m); });
     // A4: exclusive offsets (cnt[c] = tokens before chunk c; cnt[n_chunks] = total)
     bk.template scan<PtxPair>("scan_token_counts", n_chunks + 1, [=] PTX_HD(size_t i) { return cnt[i]; }, [=] PTX_HD(size_t i, PtxPair v) { cnt[i] = v; },
                               PairAddOp(), PtxPair{0, 0});
@@ -428,14 +437,11 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     PtxToken* tokens = w.tokens = (PtxToken*)bk.alloc(sizeof(PtxToken) * (size_t)(n_tokens + 1));
     uint16_t* kinds = w.kinds = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_tokens + 8));   // the kinds alone, for the passes that read nothing else
     uint32_t* lexerrs = w.lexerrs = (uint32_t*)bk.alloc(sizeof(uint32_t) * 2 * (size_t)(n_lexerrs + 1));
-    // A5: tokens to their final places, one thread per token; identifiers that spell an opcode, modifier or directive
-    // word get that kind on the way
-    bk.pf_segments("lex_compact_classify", n_chunks, cnt, [=] PTX_HD(size_t c, uint32_t i, uint32_t j) {
-        PtxToken t = slots[c * PTX_CHUNK + i];
-        t.kind = lx_classify8(text, t.start, t.len, t.kind);
-        tokens[j] = t;
-        kinds[j] = ptx_kind_entry(text, t.start, t.len, t.kind);
-    });
+    // A5: one thread per token: length, kind (identifiers that spell an opcode, modifier or directive word get that
+    // kind), literal code; written to the token's final place
+    la.tokens = tokens;
+    la.kinds = kinds;
+    bk.lex_emit("lex_emit", n_tiles, la);
     // A6: lexer errors are rare: a second walk, only when there are any, and only over the chunks that have one
     if (n_lexerrs) bk.pf_text("lex_emit_errors", n_chunks, text, PtxLexErrorsStep{info, text, vec, cnt, lexerrs});
     uint32_t* mtb = w.mod_tok_begin;
