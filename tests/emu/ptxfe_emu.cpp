@@ -52,6 +52,12 @@ struct HostBackend {
     }
     // the block-cooperative lexer steps, phase by phase with one "thread" after the other (a small thread count, so
     // that the strided loops of every phase take several rounds)
+    PtxLexTables tables;
+    bool tables_filled = false;
+    const PtxLexTables* lex_tables() {
+        if (!tables_filled) { lt_fill_tables(&tables, 0, 1); tables_filled = true; }
+        return &tables;
+    }
     void lex_mark(const char*, size_t n_tiles, const PtxLexTileArgs& a) {
         const uint32_t nt = 24;
         std::vector<PtxLexMarkShared> shv(1);

@@ -8,14 +8,14 @@
 // Step 1, lex_mark (one tile = 64 chunks = 8 KiB): one bit per text byte, "a token starts here".
 //   In code, outside comments and strings, whether a token starts at byte c depends on c and the byte p in front of it
 //   only (ptx_parser/src/lib.rs:1930-2030: single-character tokens, '.'-led and sigil-led words, maximal munch over
-//   [A-Za-z0-9_$]) - except around numbers, lone sigils and the few literals with "::" inside.  So every thread
-//   classifies 16 bytes through a 256-entry class table and a (class of p, class of c) table, and the exceptions are
-//   collected as TRIGGERS and settled afterwards, one thread per trigger, by lexing forward from a known token start
-//   with the exact per-token rules (lx_one):
-//     T1  a digit that does not continue a word: the run of "soft" bytes around it (word characters and % . : + -)
-//         can hold one number (1.5e-3) or several tokens (12Ux, 0f3F800000z);
-//     T3  "::": .shared::cta and its like are single tokens, and what follows them starts a new one;
-//         a run with a T1 or T3 in it is lexed from its first byte by the thread of its first trigger;
+//   [A-Za-z0-9_$]) - except around numbers that are more than a run of digits, lone sigils and the few literals with
+//   "::" inside.  So every thread takes 16 bytes through a 256-entry class table and a small transition table
+//   (state = what the bytes in front amount to: nothing, a word, a run of digits that started a token, a dot, a
+//   word-starting sigil, a colon), and the exceptions are collected as TRIGGERS and settled afterwards, one thread per
+//   trigger, by lexing forward from a known token start with the exact per-token rules (lx_one):
+//     T1  a word character behind a number (12U, 0x1F, 1e5, 0f3F800000) or a digit behind a dot (.5, 1.5e-3): the run
+//         of "soft" bytes around it (word characters and % . : + -) is lexed from its first byte, a token start;
+//     T3  "::": .shared::cta and its like are single tokens, and what follows them starts a new one; same treatment;
 //     T2  a sigil (_ $ %) that starts a word and is followed by no word character: a lexer error, not a token.
 //   Chunks that contain a comment or string character (/ * ") or start inside a comment or string take the proven
 //   byte-serial walk (lx_chunk), one thread per chunk.  Every writer of the second round sets bits to the true lexing,
@@ -36,7 +36,7 @@
 #define LT_BATCH 2048u             // tokens classified per round of the emit step
 
 enum { TC_WS = 0, TC_ALPHA = 1, TC_DIGIT = 2, TC_SIGIL = 3, TC_PCT = 4, TC_DOT = 5, TC_COLON = 6, TC_PM = 7, TC_PUNCT = 8, TC_SPECIAL = 9, TC_BAD = 10 };
-enum { LP_START = 1, LP_ERR = 2, LP_T1 = 4, LP_T2 = 8, LP_T3 = 16, LP_SPECIAL = 32 };
+enum { LP_START = 1, LP_ERR = 2, LP_WORD = 4, LP_T1 = 8, LP_T2 = 16, LP_T3 = 32, LP_SPECIAL = 64 };
 
 PTX_HD inline uint32_t lt_class(unsigned c) {
     if (lx_alpha(c)) return TC_ALPHA;
@@ -55,29 +55,82 @@ PTX_HD inline uint32_t lt_class(unsigned c) {
     }
 }
 PTX_HD inline bool lt_word(uint32_t cls) { return cls == TC_ALPHA || cls == TC_DIGIT || cls == TC_SIGIL; }
-// what byte class cc does behind byte class pc (TC_WS stands for "nothing in front": start of a module)
-PTX_HD inline uint32_t lt_pair(uint32_t pc, uint32_t cc) {
-    const bool continues = lt_word(pc) || pc == TC_PCT || pc == TC_DOT;     // a word character here continues a word
-    uint32_t e = 0;
+// what the bytes in front of a byte amount to
+enum { TS_OTHER = 0, TS_WORD = 1, TS_NUM = 2, TS_DOT = 3, TS_SIGIL = 4, TS_COLON = 5, TS_COUNT = 8 };
+// byte class cc in state st: flags in the low byte, next state << 8
+PTX_HD inline uint32_t lt_step(uint32_t st, uint32_t cc) {
+    uint32_t e = 0, nx = TS_OTHER;
     switch (cc) {
-    case TC_ALPHA: case TC_SIGIL: if (!continues) e |= LP_START; break;
-    case TC_DIGIT:
-        if (!continues) e |= LP_START;
-        if (!(lt_word(pc) || pc == TC_PCT)) e |= LP_T1;
+    case TC_ALPHA:
+        nx = TS_WORD;
+        if (st == TS_NUM) e |= LP_T1;
+        else if (!(st == TS_WORD || st == TS_SIGIL || st == TS_DOT)) e |= LP_START;
         break;
-    case TC_PCT: if (pc != TC_DOT) e |= LP_START; break;
-    case TC_DOT: case TC_PM: case TC_PUNCT: e |= LP_START; break;
+    case TC_DIGIT:
+        nx = TS_WORD;
+        if (st == TS_DOT) e |= LP_T1;
+        else if (st == TS_NUM) nx = TS_NUM;
+        else if (!(st == TS_WORD || st == TS_SIGIL)) { e |= LP_START; nx = TS_NUM; }
+        break;
+    case TC_SIGIL:
+        nx = TS_WORD;
+        if (st == TS_NUM) e |= LP_T1;
+        else if (st == TS_DOT) nx = TS_SIGIL;
+        else if (!(st == TS_WORD || st == TS_SIGIL)) { e |= LP_START; nx = TS_SIGIL; }
+        break;
+    case TC_PCT:
+        nx = TS_SIGIL;
+        if (st != TS_DOT) e |= LP_START;
+        break;
+    case TC_DOT: e |= LP_START; nx = TS_DOT; break;
+    case TC_PM: case TC_PUNCT: e |= LP_START; break;
     case TC_COLON:
         e |= LP_START;
-        if (pc == TC_COLON) e |= LP_T3;
+        nx = TS_COLON;
+        if (st == TS_COLON) e |= LP_T3;
         break;
     case TC_SPECIAL: e |= LP_SPECIAL; break;
     case TC_BAD: e |= LP_ERR; break;
     default: break;
     }
-    if (!lt_word(cc) && (pc == TC_SIGIL || pc == TC_PCT)) e |= LP_T2;      // the sigil in front of this byte may stand alone
-    return e;
+    if (!lt_word(cc) && st == TS_SIGIL) e |= LP_T2;      // the sigil in front of this byte stands alone
+    if (lt_word(cc)) e |= LP_WORD;
+    return e | (nx << 8);
 }
+// state in front of text[pos] (pos > ms), from the bytes before it; false: the look-back outgrew its cap
+PTX_HD inline bool lt_state_before(const uint8_t* text, uint32_t pos, uint32_t ms, uint32_t* st) {
+    const unsigned p = text[pos - 1];
+    const uint32_t pc = lt_class(p);
+    *st = TS_OTHER;
+    switch (pc) {
+    case TC_ALPHA: *st = TS_WORD; break;
+    case TC_DOT: *st = TS_DOT; break;
+    case TC_COLON: *st = TS_COLON; break;
+    case TC_PCT: *st = TS_SIGIL; break;
+    case TC_SIGIL: {
+        const unsigned q = pos - 1 > ms ? text[pos - 2] : ' ';
+        *st = (lx_identc(q) || q == '%') ? TS_WORD : TS_SIGIL;
+        break;
+    }
+    case TC_DIGIT: {
+        // digits inside a word, behind a dot, or a number of their own?
+        uint32_t j = pos - 1;
+        while (j > ms && pos - j <= LT_BACK_CAP && lx_digit(text[j - 1])) j--;
+        if (pos - j > LT_BACK_CAP) return false;
+        const unsigned q = j > ms ? text[j - 1] : ' ';
+        *st = (lx_identc(q) || q == '%' || q == '.') ? TS_WORD : TS_NUM;
+        break;
+    }
+    default: break;
+    }
+    return true;
+}
+// the constant tables of both steps, filled once per context
+struct PtxLexTables {
+    uint8_t cls[256];
+    uint16_t step[TS_COUNT * 16];
+    uint16_t first[256];       // emit step: what a token's first byte says about it (FK_* flags)
+};
 
 #ifdef __CUDA_ARCH__
 #define LT_ATOMIC_OR(p, v) atomicOr((p), (v))
@@ -94,7 +147,10 @@ struct PtxLexTileArgs {
     const uint8_t* text;
     const uint32_t* vec;        // scanned context vectors per chunk
     uint32_t n_chunks;
+    const PtxLexTables* tables;
+    const uint32_t* tile_mod;   // [n_tiles] module of the tile's first chunk
     uint32_t* start_bits;       // [n_chunks * 4]: bit b of word w = a token starts at text byte 32 w + b
+    uint32_t* word_bits;        // the same shape: the byte is a word character [A-Za-z0-9_$]
     PtxPair* cnt;               // [n_chunks + 1]: mark step: tokens / errors of chunk c at [c + 1]; emit step: their exclusive prefix
     uint32_t* mod_flag;         // [n_modules] 1 = a run of soft bytes outgrew the look-back: the module is lexed by one thread
     PtxToken* tokens;           // emit step
@@ -104,8 +160,8 @@ struct PtxLexTileArgs {
 // working memory of one tile (shared memory on the GPU)
 struct PtxLexMarkShared {
     uint8_t cls[256];
-    uint8_t pair[256];
-    uint32_t start[LT_WORDS], err[LT_WORDS];
+    uint16_t step[TS_COUNT * 16];
+    uint32_t start[LT_WORDS], err[LT_WORDS], word[LT_WORDS];
     uint32_t chunk_ms[LT_CHUNKS], chunk_me[LT_CHUNKS];
     uint8_t chunk_cx[LT_CHUNKS], chunk_special[LT_CHUNKS];
     uint32_t chunk_errs[LT_CHUNKS];      // errors of a chunk lexed by the serial walk
@@ -114,12 +170,18 @@ struct PtxLexMarkShared {
 };
 
 // ---- mark step, phase 0: tables, chunk geometry
+// module bounds of the chunks of a tile: the tile's first module is known, the others follow in order
+PTX_HD inline void lt_locate(const PtxLexTileArgs& a, uint32_t tile, uint32_t c, uint32_t* ms, uint32_t* me, bool* first) {
+    uint32_t m = a.tile_mod[tile];
+    while (m + 1 < a.info.n_modules && a.info.mcb[m + 1] <= c) m++;
+    *ms = (uint32_t)a.info.layout[m].text_off;
+    *me = *ms + (uint32_t)a.info.layout[m].text_len;
+    *first = c == a.info.mcb[m];
+}
 PTX_HD inline void lt_mark_init(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
-    for (uint32_t i = tid; i < 256; i += nt) {
-        sh.cls[i] = (uint8_t)lt_class(i);
-        sh.pair[i] = (uint8_t)lt_pair(i >> 4, i & 15u);
-    }
-    for (uint32_t i = tid; i < LT_WORDS; i += nt) sh.start[i] = sh.err[i] = 0;
+    for (uint32_t i = tid; i < 256; i += nt) sh.cls[i] = a.tables->cls[i];
+    for (uint32_t i = tid; i < TS_COUNT * 16; i += nt) sh.step[i] = a.tables->step[i];
+    for (uint32_t i = tid; i < LT_WORDS; i += nt) sh.start[i] = sh.err[i] = sh.word[i] = 0;
     for (uint32_t k = tid; k < LT_CHUNKS; k += nt) {
         uint32_t c = tile * LT_CHUNKS + k;
         sh.chunk_special[k] = 0;
@@ -127,7 +189,7 @@ PTX_HD inline void lt_mark_init(PtxLexMarkShared& sh, const PtxLexTileArgs& a, u
         if (c >= a.n_chunks) { sh.chunk_ms[k] = sh.chunk_me[k] = 0; sh.chunk_cx[k] = CX_CODE; continue; }
         uint32_t ms, me;
         bool first;
-        a.info.locate(c, ms, me, first);
+        lt_locate(a, tile, c, &ms, &me, &first);
         sh.chunk_ms[k] = ms;
         sh.chunk_me[k] = me;
         int cx = first ? CX_CODE : (int)(a.vec[c - 1] & 7u);
@@ -136,6 +198,8 @@ PTX_HD inline void lt_mark_init(PtxLexMarkShared& sh, const PtxLexTileArgs& a, u
     }
     if (tid == 0) sh.n_trig = 0;
 }
+// fills the constant tables (one block of 256 threads on the GPU)
+PTX_HD inline void lt_fill_tables(PtxLexTables* t, uint32_t tid, uint32_t nt);
 
 // ---- phase 1: 16 bytes per thread through the two tables
 PTX_HD inline void lt_mark_simple(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
@@ -146,38 +210,44 @@ PTX_HD inline void lt_mark_simple(PtxLexMarkShared& sh, const PtxLexTileArgs& a,
         const uint32_t pos0 = c * PTX_CHUNK + (piece & 7u) * 16u;
         if (pos0 >= me) continue;
         const uint32_t* w = (const uint32_t*)(a.text + pos0);
-        uint32_t words[4] = {w[0], w[1], w[2], w[3]};
-        uint32_t pc = pos0 > ms ? sh.cls[a.text[pos0 - 1]] : (uint32_t)TC_WS;
-        uint32_t n = me - pos0 < 16u ? me - pos0 : 16u;
-        uint32_t acc = 0, any = 0;
-        for (uint32_t i = 0; i < n; i++) {
-            const uint32_t ch = (words[i >> 2] >> (8u * (i & 3u))) & 0xFFu;
+        const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3];
+        uint32_t st = TS_OTHER;
+        if (pos0 > ms && !lt_state_before(a.text, pos0, ms, &st)) {
+            // the module goes to the one-thread path, which rewrites its token starts; the word bits below stay valid
+            a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, c) - 1] = 1;
+            st = TS_WORD;
+        }
+        const uint32_t n = me - pos0 < 16u ? me - pos0 : 16u;
+        uint32_t sm = 0, em = 0, wm = 0, any = 0;
+#pragma unroll
+        for (uint32_t i = 0; i < 16; i++) {
+            const uint32_t wd = i < 4 ? w0 : i < 8 ? w1 : i < 12 ? w2 : w3;
+            const uint32_t ch = (wd >> (8u * (i & 3u))) & 0xFFu;
             const uint32_t cc = sh.cls[ch];
-            const uint32_t e = sh.pair[(pc << 4) | cc];
-            acc |= (e & 3u) << (2u * i);
+            const uint32_t e = i < n ? (uint32_t)sh.step[(st << 4) | cc] : 0u;
+            sm |= (e & 1u) << i;
+            em |= ((e >> 1) & 1u) << i;
+            wm |= ((e >> 2) & 1u) << i;
             any |= e;
             if (e & (LP_T1 | LP_T2 | LP_T3)) {
                 uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
                 if (slot < LT_TRIG_CAP) sh.trig[slot] = (piece * 16u + i) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
             }
-            pc = cc;
+            if (i < n) st = e >> 8;
         }
         // the triggers that look one byte back also fire behind the last byte of the tile and behind the last byte of
         // the module (where nothing follows)
         if ((piece == LT_PIECES - 1 && n == 16 && pos0 + 16 < me) || pos0 + n == me) {
-            const uint32_t e = sh.pair[(pc << 4) | (pos0 + n == me ? (uint32_t)TC_WS : (uint32_t)sh.cls[a.text[pos0 + 16]])];
-            if (e & (LP_T2 | LP_T3)) {
+            const uint32_t e = sh.step[(st << 4) | (pos0 + n == me ? (uint32_t)TC_WS : (uint32_t)sh.cls[a.text[pos0 + 16]])];
+            if (e & (LP_T1 | LP_T2 | LP_T3)) {
                 uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
-                if (slot < LT_TRIG_CAP) sh.trig[slot] = (piece * 16u + n) | ((e & (LP_T2 | LP_T3)) << 16);
+                if (slot < LT_TRIG_CAP) sh.trig[slot] = (piece * 16u + n) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
             }
         }
-        // even bits of acc: starts, odd bits: errors
-        uint32_t s = acc & 0x55555555u, r = (acc >> 1) & 0x55555555u;
-        s = (s | (s >> 1)) & 0x33333333u; s = (s | (s >> 2)) & 0x0F0F0F0Fu; s = (s | (s >> 4)) & 0x00FF00FFu; s = (s | (s >> 8)) & 0xFFFFu;
-        r = (r | (r >> 1)) & 0x33333333u; r = (r | (r >> 2)) & 0x0F0F0F0Fu; r = (r | (r >> 4)) & 0x00FF00FFu; r = (r | (r >> 8)) & 0xFFFFu;
         const uint32_t sft = 16u * (piece & 1u);
-        if (s) LT_ATOMIC_OR(&sh.start[piece >> 1], s << sft);
-        if (r) LT_ATOMIC_OR(&sh.err[piece >> 1], r << sft);
+        if (sm) LT_ATOMIC_OR(&sh.start[piece >> 1], sm << sft);
+        if (em) LT_ATOMIC_OR(&sh.err[piece >> 1], em << sft);
+        if (wm) LT_ATOMIC_OR(&sh.word[piece >> 1], wm << sft);
         if (any & LP_SPECIAL) sh.chunk_special[k] = 1;
     }
 }
@@ -212,14 +282,15 @@ PTX_HD inline void lt_chain(PtxLexMarkShared& sh, const uint8_t* text, uint32_t 
         pos += len;
     }
 }
-// a digit that does not continue a word, or the first colon of "::"
-PTX_HD inline bool lt_is_trigger(const uint8_t* text, uint32_t j, uint32_t ms, uint32_t me) {
-    const unsigned c = text[j];
-    if (c == ':') return j + 1 < me && text[j + 1] == ':';
-    if (!lx_digit(c)) return false;
-    if (j == ms) return true;
-    const unsigned p = text[j - 1];
-    return !(lx_identc(p) || p == '%');
+// does the run of soft bytes [q, end), which begins at a token start, hold a T1 or T3 trigger?
+PTX_HD inline bool lt_run_has_trigger(const uint8_t* text, uint32_t q, uint32_t end) {
+    uint32_t st = TS_OTHER;
+    for (uint32_t j = q; j < end; j++) {
+        const uint32_t e = lt_step(st, lt_class(text[j]));
+        if (e & (LP_T1 | LP_T3)) return true;
+        st = e >> 8;
+    }
+    return false;
 }
 // token sink of the serial walk over one chunk
 struct LexMarkSink {
@@ -248,10 +319,12 @@ PTX_HD inline void lt_mark_special(PtxLexMarkShared& sh, const PtxLexTileArgs& a
         for (uint32_t w = 0; w < 4; w++) sh.start[k * 4 + w] = sh.err[k * 4 + w] = 0;
         if (cs >= me) continue;
         // the walk looks back over one run of soft bytes; a run longer than the cap goes to the one-thread path
+        uint32_t run_start = cs;
         if (sh.chunk_cx[k] == CX_CODE && cs > ms && lx_soft(a.text[cs - 1]) && lx_soft(a.text[cs])) {
             uint32_t q = cs - 1;
             while (q > ms && cs - q <= LT_BACK_CAP && lx_soft(a.text[q - 1])) q--;
             if (cs - q > LT_BACK_CAP) { a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, c) - 1] = 1; continue; }
+            run_start = q;
         }
         LexMarkSink sink;
         sink.sh = &sh;
@@ -260,6 +333,9 @@ PTX_HD inline void lt_mark_special(PtxLexMarkShared& sh, const PtxLexTileArgs& a
         sh.chunk_errs[k] = sink.n_errors;
         // the bytes behind the last token that belong to the same run of soft bytes, in the chunks that follow
         if (sink.last_end >= cs + PTX_CHUNK) lt_chain(sh, a.text, tile_base, sink.last_end, me);
+        // a run of soft bytes that reaches into the chunk from the chunk in front is code: its triggers may lie in this
+        // chunk, where nobody else answers them, and can change a token start in front of the chunk
+        if (run_start < cs) lt_chain(sh, a.text, tile_base, run_start, me);
     }
 }
 
@@ -275,44 +351,28 @@ PTX_HD inline void lt_mark_triggers(PtxLexMarkShared& sh, const PtxLexTileArgs& 
             const uint32_t ms = sh.chunk_ms[0], me = sh.chunk_me[0];
             if (tile_base >= me || tile_base <= ms || !lx_soft(a.text[tile_base]) || !lx_soft(a.text[tile_base - 1])) continue;
             uint32_t q = tile_base - 1;
-            bool any = false;
             while (q > ms && tile_base - q <= LT_BACK_CAP && lx_soft(a.text[q - 1])) q--;
             if (tile_base - q > LT_BACK_CAP) { a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, c) - 1] = 1; continue; }
-            for (uint32_t j = q; j < tile_base && !any; j++) any = lt_is_trigger(a.text, j, ms, me);
-            if (any) lt_chain(sh, a.text, tile_base, q, me);
+            // one byte past the tile's first: a trigger there (a digit behind a dot, the second colon) looks back into the run
+            if (lt_run_has_trigger(a.text, q, tile_base + 1 < me ? tile_base + 1 : me)) lt_chain(sh, a.text, tile_base, q, me);
             continue;
         }
         const uint32_t off = sh.trig[t] & 0xFFFFu, kind = sh.trig[t] >> 16;
         const uint32_t pos = tile_base + off;
         // T1 sits on its digit; T2 and T3 sit one byte behind the sigil / the first colon they are about
-        const uint32_t at = (kind & LP_T1) ? off : (off ? off - 1 : 0u);
+        const uint32_t at = ((kind & LP_T1) && off < LT_BYTES) ? off : (off ? off - 1 : 0u);
         const uint32_t k = at >> 7;
         if (sh.chunk_special[k]) continue;        // lexed by the serial walk
         const uint32_t ms = sh.chunk_ms[k], me = sh.chunk_me[k];
         if (kind & (LP_T1 | LP_T3)) {
-            // A run of soft bytes with a number or a "::" in it is lexed from its first byte, which is a token start, by
-            // the thread of its first trigger (T3 sits one byte behind the first colon).
-            const uint32_t own = (kind & LP_T1) ? pos : pos - 1;
-            uint32_t j = own;
-            bool earlier = false;
-            while (j > ms && own - j <= LT_BACK_CAP && lx_soft(a.text[j - 1])) {
-                j--;
-                if (lt_is_trigger(a.text, j, ms, me)) { earlier = true; break; }
-            }
-            if (own - j > LT_BACK_CAP) { a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, tile * LT_CHUNKS + k) - 1] = 1; continue; }
-            if (!earlier) lt_chain(sh, a.text, tile_base, j, me);
+            // the run of soft bytes around the trigger is lexed from its first byte, which is a token start (several
+            // triggers in one run do the same work and write the same bits)
+            uint32_t j = pos < me ? pos : me - 1;
+            while (j > ms && pos - j <= LT_BACK_CAP && lx_soft(a.text[j - 1])) j--;
+            if (pos - j > LT_BACK_CAP) { a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, tile * LT_CHUNKS + k) - 1] = 1; continue; }
+            lt_chain(sh, a.text, tile_base, j, me);
         }
-        if (kind & LP_T2) {
-            // the sigil at pos - 1, followed by no word character: alone unless it continues a word
-            const uint32_t s = pos - 1;
-            const unsigned ch = a.text[s];
-            bool alone = ch == '%' || s == ms;
-            if (!alone) {
-                unsigned p = a.text[s - 1];
-                alone = !(lx_identc(p) || p == '%');
-            }
-            if (alone) lt_truth(sh, tile_base, s, 1, true);
-        }
+        if (kind & LP_T2) lt_truth(sh, tile_base, pos - 1, 1, true);      // the sigil at pos - 1 stands alone: an error, no token
     }
 }
 
@@ -338,7 +398,10 @@ PTX_HD inline void lt_mark_finish(PtxLexMarkShared& sh, const PtxLexTileArgs& a,
         if (c == 0) { PtxPair z; z.a = z.b = 0; a.cnt[0] = z; }
     }
     for (uint32_t w = tid; w < LT_WORDS; w += nt)
-        if (tile * LT_CHUNKS + (w >> 2) < a.n_chunks) a.start_bits[(size_t)tile * LT_WORDS + w] = sh.start[w];
+        if (tile * LT_CHUNKS + (w >> 2) < a.n_chunks) {
+            a.start_bits[(size_t)tile * LT_WORDS + w] = sh.start[w];
+            a.word_bits[(size_t)tile * LT_WORDS + w] = sh.word[w];
+        }
 }
 
 // ---- modules whose soft runs outgrew the look-back: one thread lexes the whole module and rewrites its bits and counts
@@ -373,35 +436,65 @@ PTX_HD inline void lt_lex_module_serial(const PtxLexTileArgs& a, uint32_t m) {
 }
 
 // =============================================================================================== emit step
+// what a token's first byte says about it: provisional kind in the low 9 bits, then
+enum { FK_WORD = 0x200,      // a word: length 1 + the run of word characters behind the first byte
+       FK_KW = 0x400,        // may spell a keyword
+       FK_EXACT = 0x800,     // numbers, strings, anything unusual: the exact per-token rules
+       FK_DOT = 0x1000 };    // '.': depends on the next byte
 struct PtxLexEmitShared {
     uint8_t cls[256];
-    uint32_t bits[LT_WORDS];
+    uint16_t first[256];
+    uint32_t bits[LT_WORDS], word[LT_WORDS + 2];
     uint32_t chunk_me[LT_CHUNKS], chunk_rank[LT_CHUNKS + 1];     // rank of the chunk's first token inside the tile
     uint16_t list[LT_BYTES];            // tile offset of every token, in order
-    uint16_t len[LT_BATCH];             // length found by the first round (capped), for the second
-    uint16_t kw[LT_BATCH], num[LT_BATCH];
-    uint32_t n_kw, n_num;
+    uint16_t work[LT_BATCH];            // tokens left to the second round: keyword candidates from the front, exact ones from the back
+    uint32_t n_kw, n_exact;
     uint32_t text[LT_BYTES / 4 + 4];
 };
 
+// slot in a shared list for every thread with `pred`; one atomic per warp on the GPU
+PTX_HD inline uint32_t lt_append(uint32_t* counter, bool pred) {
+#ifdef __CUDA_ARCH__
+    const unsigned active = __activemask();
+    const unsigned m = __ballot_sync(active, pred);
+    if (!m) return 0;
+    const unsigned lane = threadIdx.x & 31u;
+    const int leader = __ffs(m) - 1;
+    uint32_t base = 0;
+    if ((int)lane == leader) base = atomicAdd(counter, (uint32_t)__popc(m));
+    base = __shfl_sync(active, base, leader);
+    return base + (uint32_t)__popc(m & ((1u << lane) - 1u));
+#else
+    if (!pred) return 0;
+    return (*counter)++;
+#endif
+}
+
 PTX_HD inline void lt_emit_init(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
-    for (uint32_t i = tid; i < 256; i += nt) sh.cls[i] = (uint8_t)lt_class(i);
+    for (uint32_t i = tid; i < 256; i += nt) {
+        sh.cls[i] = a.tables->cls[i];
+        sh.first[i] = a.tables->first[i];
+    }
     const uint32_t c0 = tile * LT_CHUNKS;
-    for (uint32_t w = tid; w < LT_WORDS; w += nt) sh.bits[w] = c0 + (w >> 2) < a.n_chunks ? a.start_bits[(size_t)tile * LT_WORDS + w] : 0u;
+    for (uint32_t w = tid; w < LT_WORDS + 2; w += nt) {
+        const bool in = w < LT_WORDS && c0 + (w >> 2) < a.n_chunks;
+        if (w < LT_WORDS) sh.bits[w] = in ? a.start_bits[(size_t)tile * LT_WORDS + w] : 0u;
+        sh.word[w] = in ? a.word_bits[(size_t)tile * LT_WORDS + w] : 0u;
+    }
     for (uint32_t k = tid; k <= LT_CHUNKS; k += nt) {
         uint32_t c = c0 + k < a.n_chunks ? c0 + k : a.n_chunks;
         sh.chunk_rank[k] = a.cnt[c].a - a.cnt[c0].a;
         if (k < LT_CHUNKS) {
             uint32_t ms = 0, me = 0;
             bool first;
-            if (c0 + k < a.n_chunks) a.info.locate(c0 + k, ms, me, first);
+            if (c0 + k < a.n_chunks) lt_locate(a, tile, c0 + k, &ms, &me, &first);
             sh.chunk_me[k] = me;
         }
     }
     const uint32_t n_words = (c0 + LT_CHUNKS <= a.n_chunks ? LT_CHUNKS : a.n_chunks - c0) * (PTX_CHUNK / 4);
     const uint32_t* src = (const uint32_t*)(a.text + (size_t)tile * LT_BYTES);
     for (uint32_t i = tid; i < LT_BYTES / 4 + 4; i += nt) sh.text[i] = i < n_words ? src[i] : 0u;
-    if (tid == 0) sh.n_kw = sh.n_num = 0;
+    if (tid == 0) sh.n_kw = sh.n_exact = 0;
 }
 // positions of the set bits, window by window
 PTX_HD inline void lt_emit_list(PtxLexEmitShared& sh, uint32_t tid, uint32_t nt) {
@@ -426,16 +519,19 @@ PTX_HD inline void lt_emit_list(PtxLexEmitShared& sh, uint32_t tid, uint32_t nt)
         }
     }
 }
-struct PtxLexEmitReader {      // text of the tile from shared memory, everything else from global memory
-    const PtxLexEmitShared& sh;
-    const uint8_t* g;
-    uint32_t base;
-    PTX_HD unsigned operator[](uint32_t p) const {
-        uint32_t o = p - base;
-        if (o < LT_BYTES) return ((const uint8_t*)sh.text)[o];
-        return g[p];
-    }
-};
+// length of the run of word characters that starts at tile offset o (at most 32; the bits behind the tile are zero)
+PTX_HD inline uint32_t lt_word_run(const PtxLexEmitShared& sh, uint32_t o) {
+    const uint32_t w = o >> 5, b = o & 31u;
+#ifdef __CUDA_ARCH__
+    const uint32_t win = __funnelshift_r(sh.word[w], sh.word[w + 1], b);
+    const uint32_t inv = ~win;
+    return inv ? (uint32_t)(__ffs(inv) - 1) : 32u;
+#else
+    const uint64_t both = ((uint64_t)sh.word[w + 1] << 32) | sh.word[w];
+    const uint32_t inv = ~(uint32_t)(both >> b);
+    return inv ? (uint32_t)__builtin_ctz(inv) : 32u;
+#endif
+}
 PTX_HD inline void lt_put_token(const PtxLexTileArgs& a, uint32_t j, uint32_t start, uint32_t len, uint16_t kind) {
     PtxTokenWord t;
     t.x = start;
@@ -443,77 +539,131 @@ PTX_HD inline void lt_put_token(const PtxLexTileArgs& a, uint32_t j, uint32_t st
     ((PtxTokenWord*)a.tokens)[j] = t;
     a.kinds[j] = ptx_kind_entry(a.text, start, len, kind);
 }
-// first round over the tokens [t0, t0 + LT_BATCH) of the tile: lengths; punctuation and sigil-led words are finished
+// a token that is no numeric literal: the kinds entry is kind and capped length
+PTX_HD inline void lt_put_plain(const PtxLexTileArgs& a, uint32_t j, uint32_t start, uint32_t len, uint32_t kind) {
+    PtxTokenWord t;
+    t.x = start;
+    t.y = len | (kind << 16);
+    ((PtxTokenWord*)a.tokens)[j] = t;
+    a.kinds[j] = (uint16_t)(kind | ((len < 127u ? len : 127u) << 9));
+}
+// First round over the tokens [t0, t0 + LT_BATCH) of the tile, the same few steps for every token: first byte, length
+// from the word-character bits, provisional kind.  Punctuation and sigil-led words are finished here.
 PTX_HD inline void lt_emit_first(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t t0, uint32_t tid, uint32_t nt) {
     const uint32_t n_tok = sh.chunk_rank[LT_CHUNKS], tile_base = tile * LT_BYTES;
     const uint32_t j0 = a.cnt[tile * LT_CHUNKS].a;
-    const PtxLexEmitReader rd{sh, a.text, tile_base};
-    for (uint32_t i = tid; i < LT_BATCH && t0 + i < n_tok; i += nt) {
-        const uint32_t off = sh.list[t0 + i], pos = tile_base + off, me = sh.chunk_me[off >> 7];
-        const unsigned c = rd[pos];
-        const uint32_t cc = sh.cls[c];
-        uint32_t q = pos + 1;
-        if (cc == TC_PUNCT || cc == TC_PM || cc == TC_COLON) {
-            lt_put_token(a, j0 + t0 + i, pos, 1, ptx_lex_single[c]);
-            continue;
-        }
-        if (cc == TC_ALPHA || cc == TC_SIGIL || cc == TC_PCT) {
-            while (q < me && lx_identc(rd[q])) q++;
-            if (cc != TC_ALPHA) { lt_put_token(a, j0 + t0 + i, pos, q - pos, T_IDENT); continue; }
-            sh.len[i] = (uint16_t)(q - pos < 0xFFFFu ? q - pos : 0xFFFFu);
-            sh.kw[LT_ATOMIC_ADD(&sh.n_kw, 1u)] = (uint16_t)i;
-            continue;
-        }
-        if (cc == TC_DOT) {
-            const unsigned d = q < me ? rd[q] : 0;
-            const uint32_t dc = sh.cls[d];
-            if (dc == TC_ALPHA || dc == TC_SIGIL || dc == TC_PCT) {
-                q++;
-                while (q < me && lx_identc(rd[q])) q++;
-                const bool colons = q + 1 < me && rd[q] == ':' && rd[q + 1] == ':';
-                if ((dc != TC_ALPHA && q == pos + 2) || colons) {
-                    sh.num[LT_ATOMIC_ADD(&sh.n_num, 1u)] = (uint16_t)i;      // a lone sigil behind the dot, or a "::" literal: exact rules
-                } else {
-                    sh.len[i] = (uint16_t)(q - pos < 0xFFFFu ? q - pos : 0xFFFFu);
-                    sh.kw[LT_ATOMIC_ADD(&sh.n_kw, 1u)] = (uint16_t)i;
+    const uint8_t* tb = (const uint8_t*)sh.text;
+    for (uint32_t i0 = 0; i0 < LT_BATCH && t0 + i0 < n_tok; i0 += nt) {
+        const uint32_t i = i0 + tid;
+        const bool live = i < LT_BATCH && t0 + i < n_tok;
+        uint32_t off = 0, f = 0, len = 1, kind = 0;
+        bool kw = false, exact = false;
+        if (live) {
+            off = sh.list[t0 + i];
+            f = sh.first[tb[off]];
+            const uint32_t run = lt_word_run(sh, off + 1);
+            kind = f & 0x1FFu;
+            kw = (f & FK_KW) != 0;
+            exact = (f & FK_EXACT) != 0;
+            if (f & FK_DOT) {
+                const uint32_t dc = sh.cls[tb[off + 1]];          // the byte behind the tile reads as 0: not a word character
+                if (dc == TC_ALPHA || dc == TC_SIGIL) {
+                    kind = T_DOTIDENT;
+                    kw = true;
+                    f |= FK_WORD;
+                    // a lone sigil behind the dot, or "::" behind the word: exact rules
+                    const uint32_t e = off + 1 + run;
+                    exact = (dc == TC_SIGIL && run == 1) || (tb[e] == ':' && tb[e + 1] == ':') || e + 1 >= LT_BYTES;
+                } else if (dc == TC_DIGIT || dc == TC_PCT || off + 1 >= LT_BYTES) {
+                    exact = true;
                 }
-                continue;
             }
-            if (dc != TC_DIGIT) { lt_put_token(a, j0 + t0 + i, pos, 1, T_DOT); continue; }
+            if (f & FK_WORD) {
+                len = 1 + run;
+                if (run >= 32u || off + len >= LT_BYTES) exact = true;       // a long word, or one that may go on behind the tile
+            }
+            if (exact) kw = false;
+            if (!kw && !exact) lt_put_plain(a, j0 + t0 + i, tile_base + off, len, kind);
         }
-        if (c == '"') {
-            while (q < me && rd[q] != '"') q++;
-            lt_put_token(a, j0 + t0 + i, pos, q + 1 - pos, T_STRING);
-            continue;
-        }
-        sh.num[LT_ATOMIC_ADD(&sh.n_num, 1u)] = (uint16_t)i;      // numbers and whatever else: the exact per-token rules
+        const uint32_t sk = lt_append(&sh.n_kw, kw);
+        if (kw) sh.work[sk] = (uint16_t)i;
+        const uint32_t se = lt_append(&sh.n_exact, exact);
+        if (exact) sh.work[LT_BATCH - 1 - se] = (uint16_t)i;
     }
 }
-// second round: keyword lookups and numbers, each with full warps
+// the keyword table through the tile's text in shared memory: the token lies inside the tile
+PTX_HD inline uint16_t lt_keyword8(const PtxLexEmitShared& sh, uint32_t off, uint32_t len) {
+    if (len > PTX_KW_MAXLEN) return T_ERROR;
+    const uint32_t shft = (off & 3u) * 8u;
+    const uint32_t* w = sh.text + (off >> 2);
+    const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+    uint32_t lo = shft ? (w0 >> shft) | (w1 << (32u - shft)) : w0;
+    uint32_t hi = shft ? (w1 >> shft) | (w2 << (32u - shft)) : w1;
+    if (len < 4) { lo &= (1u << (8u * len)) - 1u; hi = 0; }
+    else if (len < 8) hi &= (1u << (8u * (len - 4u))) - 1u;
+    uint32_t h = (lo ^ hi) * 0x9E3779B1u;
+    h ^= len * 0x85EBCA6Bu;
+    h ^= h >> 15;
+    h *= 0x2C1B3C6Du;
+    h ^= h >> 12;
+    h &= PTX_KW8_SIZE - 1;
+    const uint8_t* tb = (const uint8_t*)sh.text;
+    for (;;) {
+        const PtxKw8Entry e = ptx_kw8_table[h];
+        if (e.kind == 0xFFFF) return T_ERROR;
+        if (e.lo == lo && e.hi == hi && e.len == len) {
+            bool same = true;
+            for (uint32_t i = 8; i < len; i++)
+                if ((uint8_t)ptx_kw_pool[e.off + i] != tb[off + i]) { same = false; break; }
+            if (same) return e.kind;
+        }
+        h = (h + 1) & (PTX_KW8_SIZE - 1);
+    }
+}
+// second round: keyword lookups, then the exact rules, each with full warps
 PTX_HD inline void lt_emit_second(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t t0, uint32_t tid, uint32_t nt) {
     const uint32_t tile_base = tile * LT_BYTES, j0 = a.cnt[tile * LT_CHUNKS].a;
-    const uint32_t n_kw = sh.n_kw, n_num = sh.n_num;
-    for (uint32_t x = tid; x < n_kw + n_num; x += nt) {
-        if (x < n_kw) {
-            const uint32_t i = sh.kw[x], pos = tile_base + sh.list[t0 + i];
-            uint32_t len = sh.len[i];
-            const bool dot = ((const uint8_t*)sh.text)[pos - tile_base] == '.';
-            if (len == 0xFFFFu) {       // re-measure a very long word
-                uint32_t me = sh.chunk_me[(pos - tile_base) >> 7], q = pos + 1;
-                while (q < me && lx_identc(a.text[q])) q++;
-                len = q - pos;
-            }
-            uint16_t k = lx_keyword8(a.text, pos, len);
-            if (k == T_ERROR) k = dot ? (uint16_t)T_DOTIDENT : (uint16_t)T_IDENT;
-            lt_put_token(a, j0 + t0 + i, pos, len, k);
+    const uint32_t n_kw = sh.n_kw, n_exact = sh.n_exact;
+    const uint8_t* tb = (const uint8_t*)sh.text;
+    for (uint32_t x = tid; x < n_kw; x += nt) {
+        const uint32_t i = sh.work[x], off = sh.list[t0 + i];
+        const uint32_t len = 1 + lt_word_run(sh, off + 1);
+        uint32_t k = lt_keyword8(sh, off, len);
+        if (k == T_ERROR) k = tb[off] == '.' ? (uint32_t)T_DOTIDENT : (uint32_t)T_IDENT;
+        lt_put_plain(a, j0 + t0 + i, tile_base + off, len, k);
+    }
+    for (uint32_t x = tid; x < n_exact; x += nt) {
+        const uint32_t i = sh.work[LT_BATCH - 1 - x], off = sh.list[t0 + i], pos = tile_base + off, me = sh.chunk_me[off >> 7];
+        uint32_t len;
+        uint16_t k;
+        if (a.text[pos] == '"') {
+            uint32_t q = pos + 1;
+            while (q < me && a.text[q] != '"') q++;
+            len = q + 1 - pos;
+            k = T_STRING;
         } else {
-            const uint32_t i = sh.num[x - n_kw], off = sh.list[t0 + i], pos = tile_base + off;
-            uint32_t len;
-            uint16_t k = lx_one(a.text, pos, sh.chunk_me[off >> 7], &len);
-            lt_put_token(a, j0 + t0 + i, pos, len, k);
+            k = lx_one(a.text, pos, me, &len);
         }
+        lt_put_token(a, j0 + t0 + i, pos, len, k);
     }
 }
 PTX_HD inline void lt_emit_reset(PtxLexEmitShared& sh, uint32_t tid) {
-    if (tid == 0) sh.n_kw = sh.n_num = 0;
+    if (tid == 0) sh.n_kw = sh.n_exact = 0;
+}
+
+PTX_HD inline void lt_fill_tables(PtxLexTables* t, uint32_t tid, uint32_t nt) {
+    for (uint32_t i = tid; i < 256; i += nt) {
+        const uint32_t cc = lt_class(i);
+        t->cls[i] = (uint8_t)cc;
+        uint32_t f;
+        switch (cc) {
+        case TC_ALPHA: f = T_IDENT | FK_WORD | FK_KW; break;
+        case TC_SIGIL: case TC_PCT: f = T_IDENT | FK_WORD; break;
+        case TC_DOT: f = T_DOT | FK_DOT; break;
+        case TC_COLON: case TC_PM: case TC_PUNCT: f = ptx_lex_single[i]; break;
+        default: f = FK_EXACT; break;
+        }
+        t->first[i] = (uint16_t)f;
+    }
+    for (uint32_t i = tid; i < TS_COUNT * 16; i += nt) t->step[i] = (uint16_t)lt_step(i >> 4, i & 15u);
 }

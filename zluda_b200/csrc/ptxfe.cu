@@ -88,6 +88,7 @@ __global__ void __launch_bounds__(256) lex_tile_kernel(uint32_t n_chunks, const 
 }
 
 // ---- the two block-cooperative lexer steps (ptx_lex_tile.h): one block per tile, a barrier between the phases
+__global__ void lex_fill_tables_kernel(PtxLexTables* t) { lt_fill_tables(t, threadIdx.x, blockDim.x); }
 __global__ void __launch_bounds__(256) lex_mark_kernel(PtxLexTileArgs a) {
     __shared__ PtxLexMarkShared sh;
     const uint32_t tile = blockIdx.x, tid = threadIdx.x;
@@ -387,6 +388,7 @@ struct ptxfe_ctx {
     uint8_t* d_text = nullptr;
     size_t d_text_cap = 0;
     void* d_class_store = nullptr;        // PtxClassStore arrays (one allocation, made at the first parse)
+    PtxLexTables* d_lex_tables = nullptr; // constant tables of the lexer steps (filled at the first parse)
     uint8_t* d_raw = nullptr;             // host-contiguous runs land here before they are repacked into d_text
     size_t d_raw_cap = 0;
     PtxWork work;
@@ -530,6 +532,19 @@ struct CudaBackend {
         prof_end();
         ctx->launches++;
     }
+    const PtxLexTables* lex_tables() {
+        if (!ctx->d_lex_tables && !ctx->failed) {
+            if (cudaMalloc((void**)&ctx->d_lex_tables, sizeof(PtxLexTables)) != cudaSuccess) {
+                snprintf(ctx->err, sizeof ctx->err, "cudaMalloc of the lexer tables failed");
+                ctx->failed = true;
+                cudaGetLastError();
+                ctx->d_lex_tables = nullptr;
+                return nullptr;
+            }
+            lex_fill_tables_kernel<<<1, 256, 0, ctx->stream>>>(ctx->d_lex_tables);
+        }
+        return ctx->d_lex_tables;
+    }
     void lex_mark(const char* name, size_t n_tiles, const PtxLexTileArgs& a) {
         if (ctx->failed || n_tiles == 0) return;
         prof_begin(name);
@@ -641,6 +656,7 @@ void ptxfe_destroy(ptxfe_ctx* ctx) {
     if (ctx->d_text) cudaFree(ctx->d_text);
     if (ctx->d_raw) cudaFree(ctx->d_raw);
     if (ctx->d_class_store) cudaFree(ctx->d_class_store);
+    if (ctx->d_lex_tables) cudaFree(ctx->d_lex_tables);
     if (ctx->h_words) cudaFreeHost(ctx->h_words);
     if (ctx->h_errs) cudaFreeHost(ctx->h_errs);
     if (ctx->h_lexerrs) cudaFreeHost(ctx->h_lexerrs);

@@ -326,6 +326,7 @@ struct SegDepthOp {
 //   template <class F> void pf_segments(const char* name, size_t n, const PtxPair* off, F f);
 //        segment s owns the items [off[s].a, off[s + 1].a): f(s, i, off[s].a + i) for every s < n and every item i of s
 //   PtxClassStore class_store(bool reset);   the batch's class store (device memory that outlives the arena), emptied if asked
+//   const PtxLexTables* lex_tables();   the constant tables of ptx_lex_tile.h where the steps can read them (filled by lt_fill_tables)
 //   void lex_mark(const char* name, size_t n_tiles, const PtxLexTileArgs& a);   the phases of ptx_lex_tile.h's mark step, one block per tile
 //   void lex_emit(const char* name, size_t n_tiles, const PtxLexTileArgs& a);   the phases of its emit step
 //   void* alloc(size_t bytes); void zero(void* p, size_t bytes);
@@ -421,7 +422,10 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     uint32_t* start_bits = (uint32_t*)bk.alloc(sizeof(uint32_t) * LT_WORDS * (n_tiles + 1));
     uint32_t* mod_flag = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 1));
     bk.zero(mod_flag, sizeof(uint32_t) * (n_modules + 1));
-    PtxLexTileArgs la{info, text, vec, n_chunks, start_bits, cnt, mod_flag, nullptr, nullptr};
+    uint32_t* word_bits = (uint32_t*)bk.alloc(sizeof(uint32_t) * LT_WORDS * (n_tiles + 1));
+    uint32_t* tile_mod = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_tiles + 1));
+    bk.pf("lex_tile_modules", n_tiles, [=] PTX_HD(size_t t) { tile_mod[t] = ptx_upper_bound_u32(mcb, n_modules, (uint32_t)t * LT_CHUNKS) - 1; });
+    PtxLexTileArgs la{info, text, vec, n_chunks, bk.lex_tables(), tile_mod, start_bits, word_bits, cnt, mod_flag, nullptr, nullptr};
     bk.lex_mark("lex_mark", n_tiles, la);
     // modules with a run of soft bytes too long for the look-back of the parallel step: one thread each (rare)
     bk.pf("lex_serial_modules", n_modules, [=] PTX_HD(size_t m) { lt_lex_module_serial(la, (uint32_t)m); });
