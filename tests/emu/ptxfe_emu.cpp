@@ -65,6 +65,7 @@ struct HostBackend {
         auto phase = [&](auto f) {
             if (reverse) { for (uint32_t t = nt; t-- > 0;) f(t); } else { for (uint32_t t = 0; t < nt; t++) f(t); }
         };
+        phase([&](uint32_t t) { lt_mark_tables(sh, a, t, nt); });
         for (size_t tile = 0; tile < n_tiles; tile++) {
             phase([&](uint32_t t) { lt_mark_init(sh, a, (uint32_t)tile, t, nt); });
             phase([&](uint32_t t) { lt_mark_simple(sh, a, (uint32_t)tile, t, nt); });
@@ -80,15 +81,11 @@ struct HostBackend {
         auto phase = [&](auto f) {
             if (reverse) { for (uint32_t t = nt; t-- > 0;) f(t); } else { for (uint32_t t = 0; t < nt; t++) f(t); }
         };
+        phase([&](uint32_t t) { lt_emit_tables(sh, a, t, nt); });
         for (size_t tile = 0; tile < n_tiles; tile++) {
             phase([&](uint32_t t) { lt_emit_init(sh, a, (uint32_t)tile, t, nt); });
-            phase([&](uint32_t t) { lt_emit_list(sh, t, nt); });
-            const uint32_t n_tok = sh.chunk_rank[LT_CHUNKS];
-            for (uint32_t t0 = 0; t0 < n_tok; t0 += LT_BATCH) {
-                phase([&](uint32_t t) { lt_emit_first(sh, a, (uint32_t)tile, t0, t, nt); });
-                phase([&](uint32_t t) { lt_emit_second(sh, a, (uint32_t)tile, t0, t, nt); });
-                phase([&](uint32_t t) { lt_emit_reset(sh, t); });
-            }
+            phase([&](uint32_t t) { lt_emit_first(sh, a, (uint32_t)tile, t, nt); });
+            phase([&](uint32_t t) { lt_emit_second(sh, a, (uint32_t)tile, t, nt); });
         }
     }
     template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f) {

@@ -33,7 +33,7 @@
 #define LT_WORDS (LT_BYTES / 32u)
 #define LT_TRIG_CAP 6144u          // triggers per tile; a tile with more is lexed chunk by chunk by the serial walk
 #define LT_BACK_CAP 2048u          // longest look-back over a run of soft bytes; beyond it the module is lexed by one thread
-#define LT_BATCH 2048u             // tokens classified per round of the emit step
+#define LT_EXACT_CAP 2048u         // tokens of a tile the emit step leaves to its second round (more are settled on the spot)
 
 enum { TC_WS = 0, TC_ALPHA = 1, TC_DIGIT = 2, TC_SIGIL = 3, TC_PCT = 4, TC_DOT = 5, TC_COLON = 6, TC_PM = 7, TC_PUNCT = 8, TC_SPECIAL = 9, TC_BAD = 10 };
 enum { LP_START = 1, LP_ERR = 2, LP_WORD = 4, LP_T1 = 8, LP_T2 = 16, LP_T3 = 32, LP_SPECIAL = 64 };
@@ -98,9 +98,9 @@ PTX_HD inline uint32_t lt_step(uint32_t st, uint32_t cc) {
     return e | (nx << 8);
 }
 // state in front of text[pos] (pos > ms), from the bytes before it; false: the look-back outgrew its cap
-PTX_HD inline bool lt_state_before(const uint8_t* text, uint32_t pos, uint32_t ms, uint32_t* st) {
+PTX_HD inline bool lt_state_before(const uint8_t* cls, const uint8_t* text, uint32_t pos, uint32_t ms, uint32_t* st) {
     const unsigned p = text[pos - 1];
-    const uint32_t pc = lt_class(p);
+    const uint32_t pc = cls[p];
     *st = TS_OTHER;
     switch (pc) {
     case TC_ALPHA: *st = TS_WORD; break;
@@ -178,10 +178,12 @@ PTX_HD inline void lt_locate(const PtxLexTileArgs& a, uint32_t tile, uint32_t c,
     *me = *ms + (uint32_t)a.info.layout[m].text_len;
     *first = c == a.info.mcb[m];
 }
-PTX_HD inline void lt_mark_init(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
+// once per block: the constant tables
+PTX_HD inline void lt_mark_tables(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tid, uint32_t nt) {
     for (uint32_t i = tid; i < 256; i += nt) sh.cls[i] = a.tables->cls[i];
     for (uint32_t i = tid; i < TS_COUNT * 16; i += nt) sh.step[i] = a.tables->step[i];
-    for (uint32_t i = tid; i < LT_WORDS; i += nt) sh.start[i] = sh.err[i] = sh.word[i] = 0;
+}
+PTX_HD inline void lt_mark_init(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
     for (uint32_t k = tid; k < LT_CHUNKS; k += nt) {
         uint32_t c = tile * LT_CHUNKS + k;
         sh.chunk_special[k] = 0;
@@ -201,53 +203,55 @@ PTX_HD inline void lt_mark_init(PtxLexMarkShared& sh, const PtxLexTileArgs& a, u
 // fills the constant tables (one block of 256 threads on the GPU)
 PTX_HD inline void lt_fill_tables(PtxLexTables* t, uint32_t tid, uint32_t nt);
 
-// ---- phase 1: 16 bytes per thread through the two tables
+struct alignas(16) LtWord4 {
+    uint32_t x, y, z, w;
+};
+// ---- phase 1: 32 bytes per thread through the two tables; the thread owns one word of each bit map
 PTX_HD inline void lt_mark_simple(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
-    for (uint32_t piece = tid; piece < LT_PIECES; piece += nt) {
-        const uint32_t k = piece >> 3, c = tile * LT_CHUNKS + k;
-        if (c >= a.n_chunks) continue;
-        const uint32_t ms = sh.chunk_ms[k], me = sh.chunk_me[k];
-        const uint32_t pos0 = c * PTX_CHUNK + (piece & 7u) * 16u;
-        if (pos0 >= me) continue;
-        const uint32_t* w = (const uint32_t*)(a.text + pos0);
-        const uint32_t w0 = w[0], w1 = w[1], w2 = w[2], w3 = w[3];
-        uint32_t st = TS_OTHER;
-        if (pos0 > ms && !lt_state_before(a.text, pos0, ms, &st)) {
-            // the module goes to the one-thread path, which rewrites its token starts; the word bits below stay valid
-            a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, c) - 1] = 1;
-            st = TS_WORD;
-        }
-        const uint32_t n = me - pos0 < 16u ? me - pos0 : 16u;
+    for (uint32_t win = tid; win < LT_WORDS; win += nt) {
+        const uint32_t k = win >> 2, c = tile * LT_CHUNKS + k;
         uint32_t sm = 0, em = 0, wm = 0, any = 0;
+        const uint32_t ms = sh.chunk_ms[k], me = sh.chunk_me[k];
+        const uint32_t pos0 = c * PTX_CHUNK + (win & 3u) * 32u;
+        if (c < a.n_chunks && pos0 < me) {
+            const LtWord4* w = (const LtWord4*)(a.text + pos0);
+            const LtWord4 lo = w[0], hi = w[1];
+            uint32_t st = TS_OTHER;
+            if (pos0 > ms && !lt_state_before(sh.cls, a.text, pos0, ms, &st)) {
+                // the module goes to the one-thread path, which rewrites its token starts; the word bits below stay valid
+                a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, c) - 1] = 1;
+                st = TS_WORD;
+            }
+            const uint32_t n = me - pos0 < 32u ? me - pos0 : 32u;
 #pragma unroll
-        for (uint32_t i = 0; i < 16; i++) {
-            const uint32_t wd = i < 4 ? w0 : i < 8 ? w1 : i < 12 ? w2 : w3;
-            const uint32_t ch = (wd >> (8u * (i & 3u))) & 0xFFu;
-            const uint32_t cc = sh.cls[ch];
-            const uint32_t e = i < n ? (uint32_t)sh.step[(st << 4) | cc] : 0u;
-            sm |= (e & 1u) << i;
-            em |= ((e >> 1) & 1u) << i;
-            wm |= ((e >> 2) & 1u) << i;
-            any |= e;
-            if (e & (LP_T1 | LP_T2 | LP_T3)) {
-                uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
-                if (slot < LT_TRIG_CAP) sh.trig[slot] = (piece * 16u + i) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
+            for (uint32_t i = 0; i < 32; i++) {
+                const uint32_t wd = i < 4 ? lo.x : i < 8 ? lo.y : i < 12 ? lo.z : i < 16 ? lo.w : i < 20 ? hi.x : i < 24 ? hi.y : i < 28 ? hi.z : hi.w;
+                const uint32_t ch = (wd >> (8u * (i & 3u))) & 0xFFu;
+                const uint32_t cc = sh.cls[ch];
+                const uint32_t e = i < n ? (uint32_t)sh.step[(st << 4) | cc] : 0u;
+                sm |= (e & 1u) << i;
+                em |= ((e >> 1) & 1u) << i;
+                wm |= ((e >> 2) & 1u) << i;
+                any |= e;
+                if (e & (LP_T1 | LP_T2 | LP_T3)) {
+                    uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
+                    if (slot < LT_TRIG_CAP) sh.trig[slot] = (win * 32u + i) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
+                }
+                if (i < n) st = e >> 8;
             }
-            if (i < n) st = e >> 8;
-        }
-        // the triggers that look one byte back also fire behind the last byte of the tile and behind the last byte of
-        // the module (where nothing follows)
-        if ((piece == LT_PIECES - 1 && n == 16 && pos0 + 16 < me) || pos0 + n == me) {
-            const uint32_t e = sh.step[(st << 4) | (pos0 + n == me ? (uint32_t)TC_WS : (uint32_t)sh.cls[a.text[pos0 + 16]])];
-            if (e & (LP_T1 | LP_T2 | LP_T3)) {
-                uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
-                if (slot < LT_TRIG_CAP) sh.trig[slot] = (piece * 16u + n) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
+            // the triggers that look one byte back also fire behind the last byte of the tile and behind the last byte of
+            // the module (where nothing follows)
+            if ((win == LT_WORDS - 1 && n == 32 && pos0 + 32 < me) || pos0 + n == me) {
+                const uint32_t e = sh.step[(st << 4) | (pos0 + n == me ? (uint32_t)TC_WS : (uint32_t)sh.cls[a.text[pos0 + 32]])];
+                if (e & (LP_T1 | LP_T2 | LP_T3)) {
+                    uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
+                    if (slot < LT_TRIG_CAP) sh.trig[slot] = (win * 32u + n) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
+                }
             }
         }
-        const uint32_t sft = 16u * (piece & 1u);
-        if (sm) LT_ATOMIC_OR(&sh.start[piece >> 1], sm << sft);
-        if (em) LT_ATOMIC_OR(&sh.err[piece >> 1], em << sft);
-        if (wm) LT_ATOMIC_OR(&sh.word[piece >> 1], wm << sft);
+        sh.start[win] = sm;
+        sh.err[win] = em;
+        sh.word[win] = wm;
         if (any & LP_SPECIAL) sh.chunk_special[k] = 1;
     }
 }
@@ -444,37 +448,23 @@ enum { FK_WORD = 0x200,      // a word: length 1 + the run of word characters be
 struct PtxLexEmitShared {
     uint8_t cls[256];
     uint16_t first[256];
+    PtxKw8Entry kw[PTX_KW8_SIZE];       // the keyword table
     uint32_t bits[LT_WORDS], word[LT_WORDS + 2];
     uint32_t chunk_me[LT_CHUNKS], chunk_rank[LT_CHUNKS + 1];     // rank of the chunk's first token inside the tile
-    uint16_t list[LT_BYTES];            // tile offset of every token, in order
-    uint16_t work[LT_BATCH];            // tokens left to the second round: keyword candidates from the front, exact ones from the back
-    uint32_t n_kw, n_exact;
+    uint32_t exact[LT_EXACT_CAP];       // tokens left to the second round: tile offset | rank in the tile << 13
+    uint32_t n_exact;
     uint32_t text[LT_BYTES / 4 + 4];
 };
 
-// slot in a shared list for every thread with `pred`; one atomic per warp on the GPU
-PTX_HD inline uint32_t lt_append(uint32_t* counter, bool pred) {
-#ifdef __CUDA_ARCH__
-    const unsigned active = __activemask();
-    const unsigned m = __ballot_sync(active, pred);
-    if (!m) return 0;
-    const unsigned lane = threadIdx.x & 31u;
-    const int leader = __ffs(m) - 1;
-    uint32_t base = 0;
-    if ((int)lane == leader) base = atomicAdd(counter, (uint32_t)__popc(m));
-    base = __shfl_sync(active, base, leader);
-    return base + (uint32_t)__popc(m & ((1u << lane) - 1u));
-#else
-    if (!pred) return 0;
-    return (*counter)++;
-#endif
-}
-
-PTX_HD inline void lt_emit_init(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
+// once per block: the constant tables
+PTX_HD inline void lt_emit_tables(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tid, uint32_t nt) {
     for (uint32_t i = tid; i < 256; i += nt) {
         sh.cls[i] = a.tables->cls[i];
         sh.first[i] = a.tables->first[i];
     }
+    for (uint32_t i = tid; i < PTX_KW8_SIZE; i += nt) sh.kw[i] = ptx_kw8_table[i];
+}
+PTX_HD inline void lt_emit_init(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
     const uint32_t c0 = tile * LT_CHUNKS;
     for (uint32_t w = tid; w < LT_WORDS + 2; w += nt) {
         const bool in = w < LT_WORDS && c0 + (w >> 2) < a.n_chunks;
@@ -494,30 +484,7 @@ PTX_HD inline void lt_emit_init(PtxLexEmitShared& sh, const PtxLexTileArgs& a, u
     const uint32_t n_words = (c0 + LT_CHUNKS <= a.n_chunks ? LT_CHUNKS : a.n_chunks - c0) * (PTX_CHUNK / 4);
     const uint32_t* src = (const uint32_t*)(a.text + (size_t)tile * LT_BYTES);
     for (uint32_t i = tid; i < LT_BYTES / 4 + 4; i += nt) sh.text[i] = i < n_words ? src[i] : 0u;
-    if (tid == 0) sh.n_kw = sh.n_exact = 0;
-}
-// positions of the set bits, window by window
-PTX_HD inline void lt_emit_list(PtxLexEmitShared& sh, uint32_t tid, uint32_t nt) {
-    for (uint32_t w = tid; w < LT_WORDS; w += nt) {
-        uint32_t r = sh.chunk_rank[w >> 2];
-        for (uint32_t v = w & ~3u; v < w; v++) {
-#ifdef __CUDA_ARCH__
-            r += __popc(sh.bits[v]);
-#else
-            r += (uint32_t)__builtin_popcount(sh.bits[v]);
-#endif
-        }
-        uint32_t b = sh.bits[w];
-        while (b) {
-#ifdef __CUDA_ARCH__
-            uint32_t i = __ffs(b) - 1;
-#else
-            uint32_t i = (uint32_t)__builtin_ctz(b);
-#endif
-            b &= b - 1;
-            sh.list[r++] = (uint16_t)(w * 32u + i);
-        }
-    }
+    if (tid == 0) sh.n_exact = 0;
 }
 // length of the run of word characters that starts at tile offset o (at most 32; the bits behind the tile are zero)
 PTX_HD inline uint32_t lt_word_run(const PtxLexEmitShared& sh, uint32_t o) {
@@ -547,24 +514,82 @@ PTX_HD inline void lt_put_plain(const PtxLexTileArgs& a, uint32_t j, uint32_t st
     ((PtxTokenWord*)a.tokens)[j] = t;
     a.kinds[j] = (uint16_t)(kind | ((len < 127u ? len : 127u) << 9));
 }
-// First round over the tokens [t0, t0 + LT_BATCH) of the tile, the same few steps for every token: first byte, length
-// from the word-character bits, provisional kind.  Punctuation and sigil-led words are finished here.
-PTX_HD inline void lt_emit_first(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t t0, uint32_t tid, uint32_t nt) {
-    const uint32_t n_tok = sh.chunk_rank[LT_CHUNKS], tile_base = tile * LT_BYTES;
+// the keyword table through the tile's text in shared memory: the token lies inside the tile
+PTX_HD inline uint32_t lt_keyword8(const PtxLexEmitShared& sh, uint32_t off, uint32_t len) {
+    if (len > PTX_KW_MAXLEN) return T_ERROR;
+    const uint32_t shft = (off & 3u) * 8u;
+    const uint32_t* w = sh.text + (off >> 2);
+    const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+#ifdef __CUDA_ARCH__
+    uint32_t lo = __funnelshift_r(w0, w1, shft), hi = __funnelshift_r(w1, w2, shft);
+#else
+    uint32_t lo = shft ? (w0 >> shft) | (w1 << (32u - shft)) : w0;
+    uint32_t hi = shft ? (w1 >> shft) | (w2 << (32u - shft)) : w1;
+#endif
+    if (len < 4) { lo &= (1u << (8u * len)) - 1u; hi = 0; }
+    else if (len < 8) hi &= (1u << (8u * (len - 4u))) - 1u;
+    uint32_t h = (lo ^ hi) * 0x9E3779B1u;
+    h ^= len * 0x85EBCA6Bu;
+    h ^= h >> 15;
+    h *= 0x2C1B3C6Du;
+    h ^= h >> 12;
+    h &= PTX_KW8_SIZE - 1;
+    const uint8_t* tb = (const uint8_t*)sh.text;
+    for (;;) {
+        const PtxKw8Entry e = sh.kw[h];
+        if (e.kind == 0xFFFF) return T_ERROR;
+        if (e.lo == lo && e.hi == hi && e.len == len) {
+            bool same = true;
+            for (uint32_t i = 8; i < len; i++)
+                if ((uint8_t)ptx_kw_pool[e.off + i] != tb[off + i]) { same = false; break; }
+            if (same) return e.kind;
+        }
+        h = (h + 1) & (PTX_KW8_SIZE - 1);
+    }
+}
+// the exact rules for one token
+PTX_HD inline void lt_emit_exact(const PtxLexTileArgs& a, uint32_t j, uint32_t pos, uint32_t me) {
+    uint32_t len;
+    uint16_t k;
+    if (a.text[pos] == '"') {
+        uint32_t q = pos + 1;
+        while (q < me && a.text[q] != '"') q++;
+        len = q + 1 - pos;
+        k = T_STRING;
+    } else {
+        k = lx_one(a.text, pos, me, &len);
+    }
+    lt_put_token(a, j, pos, len, k);
+}
+// First round: one thread per 32-byte window walks its set bits in order.  The same few steps for every token: first
+// byte, length from the word-character bits, kind (words that may spell a keyword go through the keyword table);
+// numbers, strings and the unusual are left to the second round.
+PTX_HD inline void lt_emit_first(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
+    const uint32_t tile_base = tile * LT_BYTES;
     const uint32_t j0 = a.cnt[tile * LT_CHUNKS].a;
     const uint8_t* tb = (const uint8_t*)sh.text;
-    for (uint32_t i0 = 0; i0 < LT_BATCH && t0 + i0 < n_tok; i0 += nt) {
-        const uint32_t i = i0 + tid;
-        const bool live = i < LT_BATCH && t0 + i < n_tok;
-        uint32_t off = 0, f = 0, len = 1, kind = 0;
-        bool kw = false, exact = false;
-        if (live) {
-            off = sh.list[t0 + i];
-            f = sh.first[tb[off]];
+    for (uint32_t w = tid; w < LT_WORDS; w += nt) {
+        uint32_t bits = sh.bits[w];
+        if (!bits) continue;
+        uint32_t rank = sh.chunk_rank[w >> 2];
+        for (uint32_t v = w & ~3u; v < w; v++) {
+#ifdef __CUDA_ARCH__
+            rank += __popc(sh.bits[v]);
+#else
+            rank += (uint32_t)__builtin_popcount(sh.bits[v]);
+#endif
+        }
+        while (bits) {
+#ifdef __CUDA_ARCH__
+            const uint32_t off = w * 32u + (uint32_t)(__ffs(bits) - 1);
+#else
+            const uint32_t off = w * 32u + (uint32_t)__builtin_ctz(bits);
+#endif
+            bits &= bits - 1;
+            uint32_t f = sh.first[tb[off]];
             const uint32_t run = lt_word_run(sh, off + 1);
-            kind = f & 0x1FFu;
-            kw = (f & FK_KW) != 0;
-            exact = (f & FK_EXACT) != 0;
+            uint32_t kind = f & 0x1FFu, len = 1;
+            bool kw = (f & FK_KW) != 0, exact = (f & FK_EXACT) != 0;
             if (f & FK_DOT) {
                 const uint32_t dc = sh.cls[tb[off + 1]];          // the byte behind the tile reads as 0: not a word character
                 if (dc == TC_ALPHA || dc == TC_SIGIL) {
@@ -582,73 +607,29 @@ PTX_HD inline void lt_emit_first(PtxLexEmitShared& sh, const PtxLexTileArgs& a, 
                 len = 1 + run;
                 if (run >= 32u || off + len >= LT_BYTES) exact = true;       // a long word, or one that may go on behind the tile
             }
-            if (exact) kw = false;
-            if (!kw && !exact) lt_put_plain(a, j0 + t0 + i, tile_base + off, len, kind);
+            if (exact) {
+                const uint32_t slot = LT_ATOMIC_ADD(&sh.n_exact, 1u);
+                if (slot < LT_EXACT_CAP) sh.exact[slot] = off | (rank << 13);
+                else lt_emit_exact(a, j0 + rank, tile_base + off, sh.chunk_me[off >> 7]);       // no room in the list (a tile of numbers)
+            } else {
+                if (kw) {
+                    const uint32_t k = lt_keyword8(sh, off, len);
+                    if (k != T_ERROR) kind = k;
+                }
+                lt_put_plain(a, j0 + rank, tile_base + off, len, kind);
+            }
+            rank++;
         }
-        const uint32_t sk = lt_append(&sh.n_kw, kw);
-        if (kw) sh.work[sk] = (uint16_t)i;
-        const uint32_t se = lt_append(&sh.n_exact, exact);
-        if (exact) sh.work[LT_BATCH - 1 - se] = (uint16_t)i;
     }
 }
-// the keyword table through the tile's text in shared memory: the token lies inside the tile
-PTX_HD inline uint16_t lt_keyword8(const PtxLexEmitShared& sh, uint32_t off, uint32_t len) {
-    if (len > PTX_KW_MAXLEN) return T_ERROR;
-    const uint32_t shft = (off & 3u) * 8u;
-    const uint32_t* w = sh.text + (off >> 2);
-    const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
-    uint32_t lo = shft ? (w0 >> shft) | (w1 << (32u - shft)) : w0;
-    uint32_t hi = shft ? (w1 >> shft) | (w2 << (32u - shft)) : w1;
-    if (len < 4) { lo &= (1u << (8u * len)) - 1u; hi = 0; }
-    else if (len < 8) hi &= (1u << (8u * (len - 4u))) - 1u;
-    uint32_t h = (lo ^ hi) * 0x9E3779B1u;
-    h ^= len * 0x85EBCA6Bu;
-    h ^= h >> 15;
-    h *= 0x2C1B3C6Du;
-    h ^= h >> 12;
-    h &= PTX_KW8_SIZE - 1;
-    const uint8_t* tb = (const uint8_t*)sh.text;
-    for (;;) {
-        const PtxKw8Entry e = ptx_kw8_table[h];
-        if (e.kind == 0xFFFF) return T_ERROR;
-        if (e.lo == lo && e.hi == hi && e.len == len) {
-            bool same = true;
-            for (uint32_t i = 8; i < len; i++)
-                if ((uint8_t)ptx_kw_pool[e.off + i] != tb[off + i]) { same = false; break; }
-            if (same) return e.kind;
-        }
-        h = (h + 1) & (PTX_KW8_SIZE - 1);
-    }
-}
-// second round: keyword lookups, then the exact rules, each with full warps
-PTX_HD inline void lt_emit_second(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t t0, uint32_t tid, uint32_t nt) {
+// second round: the exact rules, one thread per token left over
+PTX_HD inline void lt_emit_second(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
     const uint32_t tile_base = tile * LT_BYTES, j0 = a.cnt[tile * LT_CHUNKS].a;
-    const uint32_t n_kw = sh.n_kw, n_exact = sh.n_exact;
-    const uint8_t* tb = (const uint8_t*)sh.text;
-    for (uint32_t x = tid; x < n_kw; x += nt) {
-        const uint32_t i = sh.work[x], off = sh.list[t0 + i];
-        const uint32_t len = 1 + lt_word_run(sh, off + 1);
-        uint32_t k = lt_keyword8(sh, off, len);
-        if (k == T_ERROR) k = tb[off] == '.' ? (uint32_t)T_DOTIDENT : (uint32_t)T_IDENT;
-        lt_put_plain(a, j0 + t0 + i, tile_base + off, len, k);
-    }
+    const uint32_t n_exact = sh.n_exact < LT_EXACT_CAP ? sh.n_exact : LT_EXACT_CAP;
     for (uint32_t x = tid; x < n_exact; x += nt) {
-        const uint32_t i = sh.work[LT_BATCH - 1 - x], off = sh.list[t0 + i], pos = tile_base + off, me = sh.chunk_me[off >> 7];
-        uint32_t len;
-        uint16_t k;
-        if (a.text[pos] == '"') {
-            uint32_t q = pos + 1;
-            while (q < me && a.text[q] != '"') q++;
-            len = q + 1 - pos;
-            k = T_STRING;
-        } else {
-            k = lx_one(a.text, pos, me, &len);
-        }
-        lt_put_token(a, j0 + t0 + i, pos, len, k);
+        const uint32_t off = sh.exact[x] & 0x1FFFu, rank = sh.exact[x] >> 13;
+        lt_emit_exact(a, j0 + rank, tile_base + off, sh.chunk_me[off >> 7]);
     }
-}
-PTX_HD inline void lt_emit_reset(PtxLexEmitShared& sh, uint32_t tid) {
-    if (tid == 0) sh.n_kw = sh.n_exact = 0;
 }
 
 PTX_HD inline void lt_fill_tables(PtxLexTables* t, uint32_t tid, uint32_t nt) {

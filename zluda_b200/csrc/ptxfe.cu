@@ -89,34 +89,36 @@ __global__ void __launch_bounds__(256) lex_tile_kernel(uint32_t n_chunks, const 
 
 // ---- the two block-cooperative lexer steps (ptx_lex_tile.h): one block per tile, a barrier between the phases
 __global__ void lex_fill_tables_kernel(PtxLexTables* t) { lt_fill_tables(t, threadIdx.x, blockDim.x); }
-__global__ void __launch_bounds__(256) lex_mark_kernel(PtxLexTileArgs a) {
+// Persistent blocks: the tables are loaded once, then the block takes every gridDim.x-th tile.
+__global__ void __launch_bounds__(256) lex_mark_kernel(PtxLexTileArgs a, uint32_t n_tiles) {
     __shared__ PtxLexMarkShared sh;
-    const uint32_t tile = blockIdx.x, tid = threadIdx.x;
-    lt_mark_init(sh, a, tile, tid, 256);
-    __syncthreads();
-    lt_mark_simple(sh, a, tile, tid, 256);
-    __syncthreads();
-    lt_mark_special(sh, a, tile, tid, 256);
-    __syncthreads();
-    lt_mark_triggers(sh, a, tile, tid, 256);
-    __syncthreads();
-    lt_mark_finish(sh, a, tile, tid, 256);
+    const uint32_t tid = threadIdx.x;
+    lt_mark_tables(sh, a, tid, 256);
+    for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+        __syncthreads();
+        lt_mark_init(sh, a, tile, tid, 256);
+        __syncthreads();
+        lt_mark_simple(sh, a, tile, tid, 256);
+        __syncthreads();
+        lt_mark_special(sh, a, tile, tid, 256);
+        __syncthreads();
+        lt_mark_triggers(sh, a, tile, tid, 256);
+        __syncthreads();
+        lt_mark_finish(sh, a, tile, tid, 256);
+    }
 }
-__global__ void __launch_bounds__(256) lex_emit_kernel(PtxLexTileArgs a) {
-    __shared__ PtxLexEmitShared sh;
-    const uint32_t tile = blockIdx.x, tid = threadIdx.x;
-    lt_emit_init(sh, a, tile, tid, 256);
-    __syncthreads();
-    lt_emit_list(sh, tid, 256);
-    __syncthreads();
-    const uint32_t n_tok = sh.chunk_rank[LT_CHUNKS];
-    for (uint32_t t0 = 0; t0 < n_tok; t0 += LT_BATCH) {
-        lt_emit_first(sh, a, tile, t0, tid, 256);
+__global__ void __launch_bounds__(256) lex_emit_kernel(PtxLexTileArgs a, uint32_t n_tiles) {
+    extern __shared__ __align__(16) unsigned char lex_emit_smem[];
+    PtxLexEmitShared& sh = *(PtxLexEmitShared*)lex_emit_smem;
+    const uint32_t tid = threadIdx.x;
+    lt_emit_tables(sh, a, tid, 256);
+    for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
         __syncthreads();
-        lt_emit_second(sh, a, tile, t0, tid, 256);
+        lt_emit_init(sh, a, tile, tid, 256);
         __syncthreads();
-        lt_emit_reset(sh, tid);
+        lt_emit_first(sh, a, tile, tid, 256);
         __syncthreads();
+        lt_emit_second(sh, a, tile, tid, 256);
     }
 }
 
@@ -545,17 +547,26 @@ struct CudaBackend {
         }
         return ctx->d_lex_tables;
     }
+    // persistent grids: as many blocks as the device holds at once
+    unsigned resident_blocks(const void* kernel, size_t smem, size_t n_tiles) {
+        int per_sm = 0, sms = 0;
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, smem);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, ctx->device);
+        size_t g = (size_t)(per_sm > 0 ? per_sm : 1) * (size_t)(sms > 0 ? sms : 1);
+        return (unsigned)(g < n_tiles ? g : n_tiles);
+    }
     void lex_mark(const char* name, size_t n_tiles, const PtxLexTileArgs& a) {
         if (ctx->failed || n_tiles == 0) return;
         prof_begin(name);
-        lex_mark_kernel<<<(unsigned)n_tiles, 256, 0, ctx->stream>>>(a);
+        lex_mark_kernel<<<resident_blocks((const void*)lex_mark_kernel, 0, n_tiles), 256, 0, ctx->stream>>>(a, (uint32_t)n_tiles);
         prof_end();
         ctx->launches++;
     }
     void lex_emit(const char* name, size_t n_tiles, const PtxLexTileArgs& a) {
         if (ctx->failed || n_tiles == 0) return;
         prof_begin(name);
-        lex_emit_kernel<<<(unsigned)n_tiles, 256, 0, ctx->stream>>>(a);
+        cudaFuncSetAttribute(lex_emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PtxLexEmitShared));
+        lex_emit_kernel<<<resident_blocks((const void*)lex_emit_kernel, sizeof(PtxLexEmitShared), n_tiles), 256, sizeof(PtxLexEmitShared), ctx->stream>>>(a, (uint32_t)n_tiles);
         prof_end();
         ctx->launches++;
     }
