@@ -321,7 +321,7 @@ def main():
     T, W, N = stats["n_tokens"], stats["n_result_words"], nbytes
     U = stats["n_units"]
     algo = {   # algorithmic bytes per launch: text read once, tokens / records read or written once
-        "lex_context_vectors": N, "lex_tokens": N + 8 * T, "lex_compact_classify": 18 * T + N,
+        "lex_context_vectors": N, "lex_mark": N + N // 4, "lex_emit": N + N // 4 + 10 * T,
         "scan_depth": 8 * T, "scan_unit_index": 4 * T + 8 * U,
         "unit_shape_key": 2 * T + 10 * U, "apply_templates": 2 * T + 16 * U, "class_insert": 12 * U,
         "emit_records": 4 * W + 9 * U, "decode_units": N + 8 * T + 4 * W, "decode_emit_flagged": 5 * U,
@@ -338,8 +338,10 @@ def main():
         roof = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                 "frac": ach / peak if ach else None, "traffic": tpb * N if tpb else None, "ms_per_launch": ms, "algorithmic_bytes": ab,
                 "lexer_segmenter": None}
-        lex_ms = sum(prof.get(k, 0.0) for k in ("lex_context_vectors", "scan_context", "lex_tokens", "scan_token_counts",
-                                                  "lex_compact_classify", "scan_depth", "scan_unit_index")) / a.steps
+        lex_ms = sum(prof.get(k, 0.0) for k in ("lex_context_vectors", "scan_context", "lex_tile_modules", "lex_mark", "lex_serial_modules",
+                                                  "scan_token_counts", "set_token_total", "lex_emit", "module_token_ranges",
+                                                  "module_results_init", "mark_module_first", "scan_depth", "reset_unit_total",
+                                                  "scan_unit_index", "module_unit_ranges", "module_unit_ranges_fill")) / a.steps
         # whole front end: text read once, records written once (N + O) over the kernel time of a step
         a_fe = N + 4 * W
         fe_ms = kernel_ms / a.steps

@@ -103,6 +103,14 @@ struct HostBackend {
             for (uint32_t i = 0, cnt = off[s + 1].a - off[s].a; i < cnt; i++) f(s, i, off[s].a + i);
         });
     }
+    template <class F, class G> void pf_segments2(const char* name, size_t n, const PtxPair* off, F f, G g) {
+        std::vector<std::pair<size_t, uint32_t>> later;
+        pf(name, n, [&](size_t s) {
+            for (uint32_t i = 0, cnt = off[s + 1].a - off[s].a; i < cnt; i++)
+                if (f(s, i, off[s].a + i)) later.push_back({s, i});
+        });
+        for (auto& it : later) g(it.first, it.second, off[it.first].a + it.second);
+    }
     void sort_by_key(const char*, size_t n, const uint16_t* key, uint32_t* order) {
         std::vector<uint32_t> cursor(PTX_SORT_BUCKETS + 1, 0);
         for (size_t i = 0; i < n; i++) cursor[key[i] + 1]++;

@@ -152,6 +152,40 @@ __global__ void __launch_bounds__(256) staged_kernel(size_t n, uint32_t* table, 
 
 // ---- one thread per item of a segmented range: a block takes 256 consecutive segments, whose items are contiguous,
 // and every thread finds the segment of its item by binary search over the block's offsets in shared memory
+// Two rounds: f(segment, item, global index) handles an item or returns true to put it off; the items put off are
+// collected and handled by g with full warps (work that only a few scattered items need: literal conversion).
+#define SEG_DEFER_CAP 2048u
+template <class F, class G>
+__global__ void __launch_bounds__(256) segments2_kernel(uint32_t n_units, const PtxPair* off, F f, G g) {
+    __shared__ uint32_t so[257];
+    __shared__ uint32_t later[SEG_DEFER_CAP];
+    __shared__ uint32_t n_later;
+    const uint32_t u0 = blockIdx.x * 256;
+    const uint32_t nu = n_units - u0 < 256u ? n_units - u0 : 256u;
+    for (uint32_t k = threadIdx.x; k <= nu; k += 256) so[k] = off[u0 + k].a;
+    if (threadIdx.x == 0) n_later = 0;
+    __syncthreads();
+    const uint32_t first = so[0], total = so[nu] - so[0];
+    for (uint32_t j = threadIdx.x; j < total; j += 256) {
+        uint32_t o = first + j;
+        uint32_t lo = 0, hi = nu;          // last k with so[k] <= o
+        while (hi - lo > 1) {
+            uint32_t mid = (lo + hi) >> 1;
+            if (so[mid] <= o) lo = mid; else hi = mid;
+        }
+        if (f((size_t)(u0 + lo), o - so[lo], o)) {
+            uint32_t slot = atomicAdd(&n_later, 1u);
+            if (slot < SEG_DEFER_CAP && j < (1u << 24)) later[slot] = j | (lo << 24);
+            else g((size_t)(u0 + lo), o - so[lo], o);
+        }
+    }
+    __syncthreads();
+    const uint32_t nl = n_later < SEG_DEFER_CAP ? n_later : SEG_DEFER_CAP;
+    for (uint32_t x = threadIdx.x; x < nl; x += 256) {
+        const uint32_t j = later[x] & 0xFFFFFFu, lo = later[x] >> 24, o = first + j;
+        g((size_t)(u0 + lo), o - so[lo], o);
+    }
+}
 template <class F>
 __global__ void __launch_bounds__(256) segments_kernel(uint32_t n_units, const PtxPair* off, F f) {
     __shared__ uint32_t so[257];
@@ -516,6 +550,13 @@ struct CudaBackend {
         if (ctx->failed || n == 0) return;
         prof_begin(name);
         segments_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>((uint32_t)n, off, f);
+        prof_end();
+        ctx->launches++;
+    }
+    template <class F, class G> void pf_segments2(const char* name, size_t n, const PtxPair* off, F f, G g) {
+        if (ctx->failed || n == 0) return;
+        prof_begin(name);
+        segments2_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>((uint32_t)n, off, f, g);
         prof_end();
         ctx->launches++;
     }

@@ -325,6 +325,9 @@ struct SegDepthOp {
 //        afterwards the backend copies the first r.n staged words to table[r.unit * row_words ...]
 //   template <class F> void pf_segments(const char* name, size_t n, const PtxPair* off, F f);
 //        segment s owns the items [off[s].a, off[s + 1].a): f(s, i, off[s].a + i) for every s < n and every item i of s
+//   template <class F, class G> void pf_segments2(const char* name, size_t n, const PtxPair* off, F f, G g);
+//        the same in two rounds: an item for which f returns true is handled by g(s, i, off[s].a + i) afterwards, the
+//        items put off packed together (work that few scattered items need)
 //   PtxClassStore class_store(bool reset);   the batch's class store (device memory that outlives the arena), emptied if asked
 //   const PtxLexTables* lex_tables();   the constant tables of ptx_lex_tile.h where the steps can read them (filled by lt_fill_tables)
 //   void lex_mark(const char* name, size_t n_tiles, const PtxLexTileArgs& a);   the phases of ptx_lex_tile.h's mark step, one block per tile
@@ -1042,28 +1045,43 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     // C5: records of the units that were staged go to their final place
     // one thread per output word (the backend maps words to units): staged records come from their table row,
     // templated ones are instantiated from the class template and the unit's own tokens
-    bk.pf_segments("emit_records", n_units, usize, [=] PTX_HD(size_t u, uint32_t i, uint32_t j) {
-        uint8_t fl = uflag[u];
-        if (fl == PTX_UNIT_STAGED) {
-            words[j] = table[u * PTX_TMP_STRIDE + i];
-            return;
-        }
-        if (fl != PTX_UNIT_TEMPLATED) return;
-        size_t at = (size_t)utmpl[u] * PTX_TMPL_WORDS + i;
-        uint32_t x = cs.tmpl_words[at], g = cs.tmpl_tags[at];
-        if (g) {
-            const PtxToken t = tokens[ustart[u] + (g & 0xFFu)];
-            uint32_t type = g >> 8;
-            if (type >= PTX_TAG_VAL_LO) {
-                uint64_t v = ptx_literal_value(text, t.start, t.len, t.kind);
-                if (type >= PTX_TAG_NEG_LO) v = 0 - v;
-                x = (type & 1u) ? (uint32_t)(v >> 32) : (uint32_t)v;
-            } else {
+    // Literal values are converted in a second round, one thread per literal with the warps full: the low-word thread
+    // also writes the high word when the template has it next (the two value words of an immediate)
+    bk.pf_segments2(
+        "emit_records", n_units, usize,
+        [=] PTX_HD(size_t u, uint32_t i, uint32_t j) -> bool {
+            uint8_t fl = uflag[u];
+            if (fl == PTX_UNIT_STAGED) {
+                words[j] = table[u * PTX_TMP_STRIDE + i];
+                return false;
+            }
+            if (fl != PTX_UNIT_TEMPLATED) return false;
+            size_t at = (size_t)utmpl[u] * PTX_TMPL_WORDS + i;
+            uint32_t x = cs.tmpl_words[at], g = cs.tmpl_tags[at];
+            if (g) {
+                const uint32_t type = g >> 8;
+                if (type >= PTX_TAG_VAL_LO) {
+                    if (!(type & 1u)) return true;      // low word: second round
+                    // high word: written by the low-word thread in front of it, unless it stands alone
+                    if (i > 0 && cs.tmpl_tags[at - 1] == (uint16_t)(g - 0x100u)) return false;
+                    return true;
+                }
+                const PtxToken t = tokens[ustart[u] + (g & 0xFFu)];
                 x = type == PTX_TAG_START ? t.start : type == PTX_TAG_LEN ? (uint32_t)t.len : ((x & 0xFFu) | ((uint32_t)t.len << 8));
             }
-        }
-        words[j] = x;
-    });
+            words[j] = x;
+            return false;
+        },
+        [=] PTX_HD(size_t u, uint32_t i, uint32_t j) {
+            size_t at = (size_t)utmpl[u] * PTX_TMPL_WORDS + i;
+            const uint32_t g = cs.tmpl_tags[at], type = g >> 8;
+            const PtxToken t = tokens[ustart[u] + (g & 0xFFu)];
+            uint64_t v = ptx_literal_value(text, t.start, t.len, t.kind);
+            if (type >= PTX_TAG_NEG_LO) v = 0 - v;
+            if (type & 1u) { words[j] = (uint32_t)(v >> 32); return; }
+            words[j] = (uint32_t)v;
+            if (i + 1 < cs.info[utmpl[u]].n_words && cs.tmpl_tags[at + 1] == (uint16_t)(g + 0x100u)) words[j + 1] = (uint32_t)(v >> 32);
+        });
     if (host_counters.n_flagged) {
         // function table for `call`
         uint32_t mask = 1;
