@@ -85,6 +85,7 @@ struct HostBackend {
         for (size_t tile = 0; tile < n_tiles; tile++) {
             phase([&](uint32_t t) { lt_emit_init(sh, a, (uint32_t)tile, t, nt); });
             phase([&](uint32_t t) { lt_emit_first(sh, a, (uint32_t)tile, t, nt); });
+            phase([&](uint32_t t) { lt_emit_keywords(sh, a, (uint32_t)tile, t, nt); });
             phase([&](uint32_t t) { lt_emit_second(sh, a, (uint32_t)tile, t, nt); });
         }
     }

@@ -31,7 +31,7 @@
 #define LT_BYTES (LT_CHUNKS * PTX_CHUNK)
 #define LT_PIECES (LT_BYTES / 16u)
 #define LT_WORDS (LT_BYTES / 32u)
-#define LT_TRIG_CAP 6144u          // triggers per tile; a tile with more is lexed chunk by chunk by the serial walk
+#define LT_TRIG_CAP 1536u          // triggers per tile; a tile with more is lexed chunk by chunk by the serial walk
 #define LT_BACK_CAP 2048u          // longest look-back over a run of soft bytes; beyond it the module is lexed by one thread
 #define LT_EXACT_CAP 2048u         // tokens of a tile the emit step leaves to its second round (more are settled on the spot)
 
@@ -95,7 +95,7 @@ PTX_HD inline uint32_t lt_step(uint32_t st, uint32_t cc) {
     }
     if (!lt_word(cc) && st == TS_SIGIL) e |= LP_T2;      // the sigil in front of this byte stands alone
     if (lt_word(cc)) e |= LP_WORD;
-    return e | (nx << 8);
+    return e | (nx << 12);      // entry >> 8 = next state << 4: the next table index without its class
 }
 // state in front of text[pos] (pos > ms), from the bytes before it; false: the look-back outgrew its cap
 PTX_HD inline bool lt_state_before(const uint8_t* cls, const uint8_t* text, uint32_t pos, uint32_t ms, uint32_t* st) {
@@ -223,22 +223,38 @@ PTX_HD inline void lt_mark_simple(PtxLexMarkShared& sh, const PtxLexTileArgs& a,
                 st = TS_WORD;
             }
             const uint32_t n = me - pos0 < 32u ? me - pos0 : 32u;
+            uint32_t st4 = st << 4;      // the table entries carry the next state shifted the same way
+            if (n == 32u) {
 #pragma unroll
-            for (uint32_t i = 0; i < 32; i++) {
-                const uint32_t wd = i < 4 ? lo.x : i < 8 ? lo.y : i < 12 ? lo.z : i < 16 ? lo.w : i < 20 ? hi.x : i < 24 ? hi.y : i < 28 ? hi.z : hi.w;
-                const uint32_t ch = (wd >> (8u * (i & 3u))) & 0xFFu;
-                const uint32_t cc = sh.cls[ch];
-                const uint32_t e = i < n ? (uint32_t)sh.step[(st << 4) | cc] : 0u;
-                sm |= (e & 1u) << i;
-                em |= ((e >> 1) & 1u) << i;
-                wm |= ((e >> 2) & 1u) << i;
-                any |= e;
-                if (e & (LP_T1 | LP_T2 | LP_T3)) {
-                    uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
-                    if (slot < LT_TRIG_CAP) sh.trig[slot] = (win * 32u + i) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
+                for (uint32_t i = 0; i < 32; i++) {
+                    const uint32_t wd = i < 4 ? lo.x : i < 8 ? lo.y : i < 12 ? lo.z : i < 16 ? lo.w : i < 20 ? hi.x : i < 24 ? hi.y : i < 28 ? hi.z : hi.w;
+                    const uint32_t ch = (wd >> (8u * (i & 3u))) & 0xFFu;
+                    const uint32_t e = sh.step[st4 | sh.cls[ch]];
+                    sm |= (e & 1u) << i;
+                    em |= ((e >> 1) & 1u) << i;
+                    wm |= ((e >> 2) & 1u) << i;
+                    any |= e;
+                    if (e & (LP_T1 | LP_T2 | LP_T3)) {
+                        uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
+                        if (slot < LT_TRIG_CAP) sh.trig[slot] = (win * 32u + i) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
+                    }
+                    st4 = e >> 8;
                 }
-                if (i < n) st = e >> 8;
+            } else {
+                for (uint32_t i = 0; i < n; i++) {
+                    const uint32_t e = sh.step[st4 | sh.cls[a.text[pos0 + i]]];
+                    sm |= (e & 1u) << i;
+                    em |= ((e >> 1) & 1u) << i;
+                    wm |= ((e >> 2) & 1u) << i;
+                    any |= e;
+                    if (e & (LP_T1 | LP_T2 | LP_T3)) {
+                        uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
+                        if (slot < LT_TRIG_CAP) sh.trig[slot] = (win * 32u + i) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
+                    }
+                    st4 = e >> 8;
+                }
             }
+            st = st4 >> 4;
             // the triggers that look one byte back also fire behind the last byte of the tile and behind the last byte of
             // the module (where nothing follows)
             if ((win == LT_WORDS - 1 && n == 32 && pos0 + 32 < me) || pos0 + n == me) {
@@ -292,7 +308,7 @@ PTX_HD inline bool lt_run_has_trigger(const uint8_t* text, uint32_t q, uint32_t 
     for (uint32_t j = q; j < end; j++) {
         const uint32_t e = lt_step(st, lt_class(text[j]));
         if (e & (LP_T1 | LP_T3)) return true;
-        st = e >> 8;
+        st = e >> 12;
     }
     return false;
 }
@@ -450,11 +466,17 @@ struct PtxLexEmitShared {
     uint16_t first[256];
     PtxKw8Entry kw[PTX_KW8_SIZE];       // the keyword table
     uint32_t bits[LT_WORDS], word[LT_WORDS + 2];
+    uint32_t kwbits[LT_WORDS];          // first round -> keyword round: the tokens that may spell a keyword
     uint32_t chunk_me[LT_CHUNKS], chunk_rank[LT_CHUNKS + 1];     // rank of the chunk's first token inside the tile
     uint32_t exact[LT_EXACT_CAP];       // tokens left to the second round: tile offset | rank in the tile << 13
     uint32_t n_exact;
-    uint32_t text[LT_BYTES / 4 + 4];
+    // The tile's text, one spare word behind every 32 bytes: the threads of a warp work on consecutive 32-byte windows,
+    // and with a stride of nine words instead of eight their byte reads fall into different banks.
+    uint32_t text[LT_BYTES / 4 + LT_WORDS + 16];
 };
+// byte `o` of the tile (o may run a few bytes past the tile: zeros), and text word `i`, in the skewed layout
+PTX_HD inline unsigned lt_tb(const PtxLexEmitShared& sh, uint32_t o) { return ((const uint8_t*)sh.text)[o + ((o >> 5) << 2)]; }
+PTX_HD inline uint32_t lt_tw(const PtxLexEmitShared& sh, uint32_t i) { return sh.text[i + (i >> 3)]; }
 
 // once per block: the constant tables
 PTX_HD inline void lt_emit_tables(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tid, uint32_t nt) {
@@ -483,7 +505,7 @@ PTX_HD inline void lt_emit_init(PtxLexEmitShared& sh, const PtxLexTileArgs& a, u
     }
     const uint32_t n_words = (c0 + LT_CHUNKS <= a.n_chunks ? LT_CHUNKS : a.n_chunks - c0) * (PTX_CHUNK / 4);
     const uint32_t* src = (const uint32_t*)(a.text + (size_t)tile * LT_BYTES);
-    for (uint32_t i = tid; i < LT_BYTES / 4 + 4; i += nt) sh.text[i] = i < n_words ? src[i] : 0u;
+    for (uint32_t i = tid; i < LT_BYTES / 4 + 12; i += nt) sh.text[i + (i >> 3)] = i < n_words ? src[i] : 0u;
     if (tid == 0) sh.n_exact = 0;
 }
 // length of the run of word characters that starts at tile offset o (at most 32; the bits behind the tile are zero)
@@ -518,8 +540,8 @@ PTX_HD inline void lt_put_plain(const PtxLexTileArgs& a, uint32_t j, uint32_t st
 PTX_HD inline uint32_t lt_keyword8(const PtxLexEmitShared& sh, uint32_t off, uint32_t len) {
     if (len > PTX_KW_MAXLEN) return T_ERROR;
     const uint32_t shft = (off & 3u) * 8u;
-    const uint32_t* w = sh.text + (off >> 2);
-    const uint32_t w0 = w[0], w1 = w[1], w2 = w[2];
+    const uint32_t wi = off >> 2;
+    const uint32_t w0 = lt_tw(sh, wi), w1 = lt_tw(sh, wi + 1), w2 = lt_tw(sh, wi + 2);
 #ifdef __CUDA_ARCH__
     uint32_t lo = __funnelshift_r(w0, w1, shft), hi = __funnelshift_r(w1, w2, shft);
 #else
@@ -534,14 +556,13 @@ PTX_HD inline uint32_t lt_keyword8(const PtxLexEmitShared& sh, uint32_t off, uin
     h *= 0x2C1B3C6Du;
     h ^= h >> 12;
     h &= PTX_KW8_SIZE - 1;
-    const uint8_t* tb = (const uint8_t*)sh.text;
     for (;;) {
         const PtxKw8Entry e = sh.kw[h];
         if (e.kind == 0xFFFF) return T_ERROR;
         if (e.lo == lo && e.hi == hi && e.len == len) {
             bool same = true;
             for (uint32_t i = 8; i < len; i++)
-                if ((uint8_t)ptx_kw_pool[e.off + i] != tb[off + i]) { same = false; break; }
+                if ((uint8_t)ptx_kw_pool[e.off + i] != lt_tb(sh, off + i)) { same = false; break; }
             if (same) return e.kind;
         }
         h = (h + 1) & (PTX_KW8_SIZE - 1);
@@ -561,64 +582,105 @@ PTX_HD inline void lt_emit_exact(const PtxLexTileArgs& a, uint32_t j, uint32_t p
     }
     lt_put_token(a, j, pos, len, k);
 }
-// First round: one thread per 32-byte window walks its set bits in order.  The same few steps for every token: first
-// byte, length from the word-character bits, kind (words that may spell a keyword go through the keyword table);
-// numbers, strings and the unusual are left to the second round.
+PTX_HD inline uint32_t lt_window_rank(const PtxLexEmitShared& sh, uint32_t w) {
+    uint32_t rank = sh.chunk_rank[w >> 2];
+    for (uint32_t v = w & ~3u; v < w; v++) {
+#ifdef __CUDA_ARCH__
+        rank += __popc(sh.bits[v]);
+#else
+        rank += (uint32_t)__builtin_popcount(sh.bits[v]);
+#endif
+    }
+    return rank;
+}
+// First round: one thread per 32-byte window walks its set bits in order, the same few steps for every token: first
+// byte, length from the word-character bits, kind by the first byte.  Every token but the numbers, strings and the
+// unusual (second round: exact rules) is written here; words that may spell a keyword are written as plain words and
+// marked for the keyword round, so that no thread looks up a keyword while its neighbours wait.
+// one token of the first round: returns its bit for the keyword round (0: not a keyword candidate)
+PTX_HD inline uint32_t lt_emit_one(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile_base, uint32_t j, uint32_t rank, uint32_t w, uint32_t bit) {
+    // straight-line on purpose (bitwise logic, no short-circuit): the tokens of a warp's 32 windows are of all sorts, and
+    // every branch taken by some of them would be paid by all
+    const uint32_t off = w * 32u + bit;
+    const uint32_t f = sh.first[lt_tb(sh, off)];
+    const uint32_t dc = sh.cls[lt_tb(sh, off + 1)];        // the bytes behind the tile read as 0: no word characters
+    const uint32_t run = lt_word_run(sh, off + 1);
+    const uint32_t e = off + 1 + run;
+    const uint32_t colons = (uint32_t)(lt_tb(sh, e) == ':') & (uint32_t)(lt_tb(sh, e + 1) == ':');
+    const uint32_t isdot = (f >> 12) & 1u;                                                // FK_DOT
+    const uint32_t dotword = isdot & ((uint32_t)(dc == TC_ALPHA) | (uint32_t)(dc == TC_SIGIL));
+    const uint32_t word = ((f >> 9) & 1u) | dotword;                                        // FK_WORD
+    const uint32_t len = 1u + (word ? run : 0u);
+    const uint32_t kind = dotword ? (uint32_t)T_DOTIDENT : (f & 0x1FFu);
+    const uint32_t kw = ((f >> 10) & 1u) | dotword;                                         // FK_KW
+    // exact rules: numbers, strings, the unusual; a dot in front of a digit or '%'; a lone sigil behind a dot or "::"
+    // behind a dot-word; a long word, or one that may go on behind the tile
+    const uint32_t exact = ((f >> 11) & 1u) |
+                           (isdot & ((uint32_t)(dc == TC_DIGIT) | (uint32_t)(dc == TC_PCT) | (uint32_t)(off + 1 >= LT_BYTES))) |
+                           (dotword & (((uint32_t)(dc == TC_SIGIL) & (uint32_t)(run == 1u)) | colons | (uint32_t)(e + 1 >= LT_BYTES))) |
+                           (word & ((uint32_t)(run >= 32u) | (uint32_t)(off + len >= LT_BYTES)));
+    if (exact) {
+        const uint32_t slot = LT_ATOMIC_ADD(&sh.n_exact, 1u);
+        if (slot < LT_EXACT_CAP) sh.exact[slot] = off | (rank << 13);
+        else lt_emit_exact(a, j, tile_base + off, sh.chunk_me[off >> 7]);       // no room in the list (a tile of numbers)
+        return 0;
+    }
+    lt_put_plain(a, j, tile_base + off, len, kind);
+    return (kw & (uint32_t)(len <= PTX_KW_MAXLEN)) << bit;
+}
 PTX_HD inline void lt_emit_first(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
     const uint32_t tile_base = tile * LT_BYTES;
     const uint32_t j0 = a.cnt[tile * LT_CHUNKS].a;
-    const uint8_t* tb = (const uint8_t*)sh.text;
     for (uint32_t w = tid; w < LT_WORDS; w += nt) {
-        uint32_t bits = sh.bits[w];
-        if (!bits) continue;
-        uint32_t rank = sh.chunk_rank[w >> 2];
-        for (uint32_t v = w & ~3u; v < w; v++) {
-#ifdef __CUDA_ARCH__
-            rank += __popc(sh.bits[v]);
-#else
-            rank += (uint32_t)__builtin_popcount(sh.bits[v]);
-#endif
-        }
+        uint32_t bits = sh.bits[w], kwb = 0;
+        uint32_t rank = bits ? lt_window_rank(sh, w) : 0u;
+        // two tokens per turn: their steps do not depend on one another and overlap
         while (bits) {
 #ifdef __CUDA_ARCH__
-            const uint32_t off = w * 32u + (uint32_t)(__ffs(bits) - 1);
+            const uint32_t b0 = (uint32_t)(__ffs(bits) - 1);
 #else
-            const uint32_t off = w * 32u + (uint32_t)__builtin_ctz(bits);
+            const uint32_t b0 = (uint32_t)__builtin_ctz(bits);
 #endif
             bits &= bits - 1;
-            uint32_t f = sh.first[tb[off]];
-            const uint32_t run = lt_word_run(sh, off + 1);
-            uint32_t kind = f & 0x1FFu, len = 1;
-            bool kw = (f & FK_KW) != 0, exact = (f & FK_EXACT) != 0;
-            if (f & FK_DOT) {
-                const uint32_t dc = sh.cls[tb[off + 1]];          // the byte behind the tile reads as 0: not a word character
-                if (dc == TC_ALPHA || dc == TC_SIGIL) {
-                    kind = T_DOTIDENT;
-                    kw = true;
-                    f |= FK_WORD;
-                    // a lone sigil behind the dot, or "::" behind the word: exact rules
-                    const uint32_t e = off + 1 + run;
-                    exact = (dc == TC_SIGIL && run == 1) || (tb[e] == ':' && tb[e + 1] == ':') || e + 1 >= LT_BYTES;
-                } else if (dc == TC_DIGIT || dc == TC_PCT || off + 1 >= LT_BYTES) {
-                    exact = true;
-                }
+            const uint32_t more = bits;
+#ifdef __CUDA_ARCH__
+            const uint32_t b1 = more ? (uint32_t)(__ffs(more) - 1) : b0;
+#else
+            const uint32_t b1 = more ? (uint32_t)__builtin_ctz(more) : b0;
+#endif
+            bits &= bits - 1;       // 0 stays 0
+            const uint32_t k0 = lt_emit_one(sh, a, tile_base, j0 + rank, rank, w, b0);
+            uint32_t k1 = 0;
+            if (more) k1 = lt_emit_one(sh, a, tile_base, j0 + rank + 1, rank + 1, w, b1);
+            kwb |= k0 | k1;
+            rank += more ? 2u : 1u;
+        }
+        sh.kwbits[w] = kwb;
+    }
+}
+// keyword round: the marked words through the keyword table; a word that spells one gets that kind
+PTX_HD inline void lt_emit_keywords(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
+    const uint32_t j0 = a.cnt[tile * LT_CHUNKS].a;
+    for (uint32_t w = tid; w < LT_WORDS; w += nt) {
+        uint32_t kwb = sh.kwbits[w];
+        if (!kwb) continue;
+        const uint32_t all = sh.bits[w], rank0 = lt_window_rank(sh, w);
+        while (kwb) {
+#ifdef __CUDA_ARCH__
+            const uint32_t bit = (uint32_t)(__ffs(kwb) - 1);
+            const uint32_t rank = rank0 + (uint32_t)__popc(all & ((1u << bit) - 1u));
+#else
+            const uint32_t bit = (uint32_t)__builtin_ctz(kwb);
+            const uint32_t rank = rank0 + (uint32_t)__builtin_popcount(all & ((1u << bit) - 1u));
+#endif
+            kwb &= kwb - 1;
+            const uint32_t off = w * 32u + bit;
+            const uint32_t len = 1 + lt_word_run(sh, off + 1);
+            const uint32_t k = lt_keyword8(sh, off, len);
+            if (k != T_ERROR) {
+                a.tokens[j0 + rank].kind = (uint16_t)k;
+                a.kinds[j0 + rank] = (uint16_t)(k | (len << 9));      // a keyword is at most 20 bytes long
             }
-            if (f & FK_WORD) {
-                len = 1 + run;
-                if (run >= 32u || off + len >= LT_BYTES) exact = true;       // a long word, or one that may go on behind the tile
-            }
-            if (exact) {
-                const uint32_t slot = LT_ATOMIC_ADD(&sh.n_exact, 1u);
-                if (slot < LT_EXACT_CAP) sh.exact[slot] = off | (rank << 13);
-                else lt_emit_exact(a, j0 + rank, tile_base + off, sh.chunk_me[off >> 7]);       // no room in the list (a tile of numbers)
-            } else {
-                if (kw) {
-                    const uint32_t k = lt_keyword8(sh, off, len);
-                    if (k != T_ERROR) kind = k;
-                }
-                lt_put_plain(a, j0 + rank, tile_base + off, len, kind);
-            }
-            rank++;
         }
     }
 }
