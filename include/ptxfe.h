@@ -118,8 +118,8 @@ int ptxfe_lex_module(ptxfe_ctx* ctx, const char* text, uint64_t len, uint32_t** 
 /* Lexer without any allocation.  It has no counterpart in the reference, which lexes on the CPU into a Vec.
  *
  * For callers that are not allowed to call cudaMalloc (or anything that might): code running while another component
- * owns the device's memory budget, inside a region where the allocator may not be entered (a capture or a callback),
- * or in a process whose device heap is exhausted or fragmented.  The usual entry points grow a per-context arena and
+ * owns the device's memory budget, inside a region where the allocator may not be entered (a stream callback, a
+ * library's own hook), or in a process whose device heap is exhausted or fragmented.  The usual entry points grow a per-context arena and
  * pinned buffers on demand; this one touches only memory the caller passes in plus a fixed 2 MiB working array that is
  * part of the library image (each GPU that loads the library carries that array until the process exits).
  *
@@ -128,11 +128,14 @@ int ptxfe_lex_module(ptxfe_ctx* ctx, const char* text, uint64_t len, uint32_t** 
  *   d_tokens   device pointer to room for `token_capacity` 8-byte token records {start:u32, len:u16, kind:u16}
  *              (same records as ptxfe_lex_module; len 0xFFFF = 65535 or longer); tokens beyond the capacity are
  *              dropped but still counted
- *   d_counts   device pointer to two uint32: number of tokens, number of lex errors
+ *   d_counts   device pointer to two uint32: number of tokens, number of lex errors; both 0xFFFFFFFF when the text was
+ *              refused because one run of word characters and . : + - % is longer than 64 KiB (no real PTX has one;
+ *              lexing it chunk by chunk would walk that run once per chunk)
  *   stream     cudaStream_t to launch on (0 = default stream).  The call only enqueues kernels.
  *
- * The first call on a device looks up the device address of the working array (cudaGetSymbolAddress); make that first
- * call outside any stream capture.  All calls on one GPU share the working array: two calls whose kernels can overlap
+ * The call makes `device` current while it works and puts the caller's current device back before it returns.  The
+ * first call on a device looks up the device address of the working array (cudaGetSymbolAddress; any thread may make
+ * it, concurrent first calls look up the same address); make that first call outside any stream capture.  All calls on one GPU share the working array: two calls whose kernels can overlap
  * on the device (different streams, different threads) race - serialise them.  Nothing in the array has to survive
  * between calls and nothing needs clearing by the caller. */
 int ptxfe_lex_device_noalloc(int device, const void* d_text, uint64_t len, void* d_tokens, uint64_t token_capacity,

@@ -39,6 +39,12 @@ def assert_parity(oracle, ctx, texts, modes=(0, 1, 2)):
             d = b.dump(i)
             assert o == d, (mode, i, first_difference(o, d))
             assert (b.status(i) == 0) == (st == 0)
+            # the verdict and the error count are read off the module's result row, not off the dump
+            n_err = [int(l.split()[1]) for l in d.split("\n") if l.startswith("errors: ")][-1]
+            assert b.error_count(i) == n_err, (mode, i, b.error_count(i), n_err)
+            verdict = d.split("\n")[1]
+            assert (b.status(i) == 3) == (verdict == "status: ReferenceDiverges")
+            assert (b.status(i) == 2) == (verdict == "status: ReferencePanics")
         b.free()
     return ctx.stats()
 

@@ -50,6 +50,28 @@ def test_allocation_free_lexer_matches_the_ordinary_one():
     # a table that is too small is filled up to its capacity and the full count is still reported
     got, n_tok, _ = _lex_noalloc(lib, torch, second, 100)
     assert len(got) == 100 and n_tok == len(ctx.lex(second)[0]) and got == ctx.lex(second)[0][:100]
+    # the claim in the name: device memory in use is the same before and after calls (the buffers are the test's own)
+    edge = (b"add.s32 %r1, %r2, 0x1F; // c\n" * ((16 << 20) // 29 + 1))
+    for n in ((16 << 20) - 1, 16 << 20):
+        text = edge[:n]
+        want_toks, want_errs = ctx.lex(text)
+        raw = torch.from_numpy(np.frombuffer(text, dtype=np.uint8).copy()).cuda()
+        d_tokens = torch.zeros((len(want_toks) + 16) * 2, dtype=torch.int32, device="cuda")
+        d_counts = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        st = lib.ptxfe_lex_device_noalloc(0, ctypes.c_void_p(raw.data_ptr()), ctypes.c_uint64(n), ctypes.c_void_p(d_tokens.data_ptr()),
+                                          ctypes.c_uint64(len(want_toks) + 16), ctypes.c_void_p(d_counts.data_ptr()), ctypes.c_void_p(0))
+        torch.cuda.synchronize()
+        assert st == 0 and torch.cuda.mem_get_info()[0] == free_before
+        assert [int(x) for x in d_counts.cpu().numpy().astype(np.uint32)] == [len(want_toks), len(want_errs)]
+        words = d_tokens.cpu().numpy().view(np.uint32)[: 2 * len(want_toks)].reshape(-1, 2)
+        step = max(1, len(want_toks) // 5000)
+        assert [(int(w[1] >> 16), int(w[0]), int(w[1] & 0xFFFF)) for w in words[::step]] == want_toks[::step]
+    # one run of word characters longer than the look-back bound: refused through the counts, quickly
+    long_run = b"mov.u32 %r1, " + b"a" * (200 << 10) + b";"
+    got, n_tok, n_err = _lex_noalloc(lib, torch, long_run, 64)
+    assert n_tok == 0xFFFFFFFF and n_err == 0xFFFFFFFF
     # inputs beyond the fixed working memory are refused
     big = torch.zeros(8, dtype=torch.uint8, device="cuda")
     st = lib.ptxfe_lex_device_noalloc(0, ctypes.c_void_p(big.data_ptr()), ctypes.c_uint64((16 << 20) + 1),

@@ -4,6 +4,8 @@
 #include "ptx_decode.h"
 
 enum PtxUnitStatus { US_OK = 0, US_FAIL = 1, US_PANIC = 2, US_DIVERGE = 3 };
+#define US_MASK 0xFu
+#define US_MODULE_FAILED 0x10u     // sequential path: the module-level parse failed (a U_MODULE_FAIL record was written)
 
 struct PtxUnitResult {
     uint32_t end;        // token index where the unit stopped
@@ -80,7 +82,7 @@ PTX_HD PTX_NOINLINE inline int ptx_decode_module_sequential(PtxDecoder& d, uint3
         d.push(E_PARSER, 0, 0, 0);
         d.begin_record(&m);
         d.end_record(m, U_MODULE_FAIL);
-        return US_OK;
+        return US_OK | US_MODULE_FAILED;
     }
     for (;;) {
         uint32_t save = d.pos;
@@ -148,6 +150,7 @@ PTX_HD PTX_NOINLINE inline int ptx_decode_module_sequential(PtxDecoder& d, uint3
         d.push(E_PARSER, 0, 0, 0);
         d.begin_record(&m);
         d.end_record(m, U_MODULE_FAIL);
+        return US_OK | US_MODULE_FAILED;
     }
     return US_OK;
 }

@@ -9,6 +9,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <atomic>
 #include <string>
 #include <type_traits>
 #include <vector>
@@ -1056,12 +1057,28 @@ int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* 
         if (k + 1 == ns) CUDA_TRY(cudaEventRecord(ctx->ev[1], ctx->s_in));
         return PTXFE_OK;
     };
+    // From here on copies may be in flight that read the caller's text and write the pinned result buffers: every error
+    // exit waits for all three streams first, so that the caller may free `texts` as soon as the call returns.
+    auto drain = [&](int code) -> int {
+        cudaStreamSynchronize(ctx->s_in);
+        cudaStreamSynchronize(ctx->s_out);
+        cudaStreamSynchronize(ctx->stream);
+        return code;
+    };
+#define DRAIN_TRY(call)                                                                     \
+    do {                                                                                    \
+        cudaError_t e_ = (call);                                                            \
+        if (e_ != cudaSuccess) {                                                            \
+            snprintf(ctx->err, sizeof ctx->err, "%s: %s", #call, cudaGetErrorString(e_));   \
+            return drain(PTXFE_ERR_CUDA);                                                   \
+        }                                                                                   \
+    } while (0)
     for (size_t k = 0; k < ns && k < 2; k++)
-        if ((st = submit_text(k)) != PTXFE_OK) return st;
+        if ((st = submit_text(k)) != PTXFE_OK) return drain(st);
     // ---- host result buffers: sized from the text; grown (after the copies in flight have landed) if a slice needs more
     int rc;
-    if ((rc = grow_pinned(ctx, &ctx->h_results, &ctx->h_results_cap, sizeof(PtxModuleResult) * (size_t)n + 16, 0)) != PTXFE_OK) return rc;
-    if ((rc = grow_pinned(ctx, &ctx->h_words, &ctx->h_words_cap, (size_t)(total * 2) + 4096, 0)) != PTXFE_OK) return rc;
+    if ((rc = grow_pinned(ctx, &ctx->h_results, &ctx->h_results_cap, sizeof(PtxModuleResult) * (size_t)n + 16, 0)) != PTXFE_OK) return drain(rc);
+    if ((rc = grow_pinned(ctx, &ctx->h_words, &ctx->h_words_cap, (size_t)(total * 2) + 4096, 0)) != PTXFE_OK) return drain(rc);
     size_t words_done = 0, errs_done = 0, lexerrs_done = 0;
     std::vector<size_t> base_w(ns), base_e(ns), base_l(ns);
     ptxfe_stats& s = ctx->stats;
@@ -1073,38 +1090,34 @@ int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* 
         const Slice& sl = slices[k];
         ctx->cur = (int)(k & 1);
         // this arena held the results of slice k-2: wait until they have left the device
-        if (k >= 2) CUDA_TRY(cudaEventSynchronize(ctx->slice_ev[5 * (k - 2) + 4]));
-        CUDA_TRY(cudaStreamWaitEvent(ctx->stream, ctx->slice_ev[5 * k], 0));
-        if (k + 2 < ns && (rc = submit_text(k + 2)) != PTXFE_OK) return rc;
+        if (k >= 2) DRAIN_TRY(cudaEventSynchronize(ctx->slice_ev[5 * (k - 2) + 4]));
+        DRAIN_TRY(cudaStreamWaitEvent(ctx->stream, ctx->slice_ev[5 * k], 0));
+        if (k + 2 < ns && (rc = submit_text(k + 2)) != PTXFE_OK) return drain(rc);
         rc = run_pipeline(ctx, ctx->d_text + sl.text_off, ctx->layout.data() + sl.m0, sl.m1 - sl.m0, mode,
                           ctx->slice_ev[5 * k + 1], nullptr, nullptr, ctx->slice_ev[5 * k + 2],
                           use_raw[k] ? repack.data() + sl.m0 : nullptr, ctx->d_raw + raw_base[k], k == 0);
-        if (rc != PTXFE_OK) {
-            cudaStreamSynchronize(ctx->s_in);
-            cudaStreamSynchronize(ctx->s_out);
-            return rc;
-        }
+        if (rc != PTXFE_OK) return drain(rc);
         const PtxCounters& c = ctx->counters;
         size_t nw = c.n_words, ne = c.n_errs, nl = c.n_lexerrs, nm = sl.m1 - sl.m0;
         if ((words_done + nw) * sizeof(uint32_t) + 16 > ctx->h_words_cap || (errs_done + ne) * sizeof(PtxErrRec) + 16 > ctx->h_errs_cap ||
             (lexerrs_done + nl) * 8 + 16 > ctx->h_lexerrs_cap) {
-            CUDA_TRY(cudaStreamSynchronize(ctx->s_out));
+            DRAIN_TRY(cudaStreamSynchronize(ctx->s_out));
             // extrapolate from what the slices so far produced
             double done_bytes = 0;
             for (size_t j = 0; j <= k; j++) done_bytes += (double)slices[j].bytes;
             double scale = done_bytes > 0 ? (double)total / done_bytes * 1.1 : 1.0;
-            if ((rc = grow_pinned(ctx, &ctx->h_words, &ctx->h_words_cap, (size_t)((words_done + nw) * scale) * 4 + 4096, words_done * 4)) != PTXFE_OK) return rc;
-            if ((rc = grow_pinned(ctx, &ctx->h_errs, &ctx->h_errs_cap, (size_t)((errs_done + ne) * scale) * sizeof(PtxErrRec) + 4096, errs_done * sizeof(PtxErrRec))) != PTXFE_OK) return rc;
-            if ((rc = grow_pinned(ctx, &ctx->h_lexerrs, &ctx->h_lexerrs_cap, (size_t)((lexerrs_done + nl) * scale) * 8 + 4096, lexerrs_done * 8)) != PTXFE_OK) return rc;
+            if ((rc = grow_pinned(ctx, &ctx->h_words, &ctx->h_words_cap, (size_t)((words_done + nw) * scale) * 4 + 4096, words_done * 4)) != PTXFE_OK) return drain(rc);
+            if ((rc = grow_pinned(ctx, &ctx->h_errs, &ctx->h_errs_cap, (size_t)((errs_done + ne) * scale) * sizeof(PtxErrRec) + 4096, errs_done * sizeof(PtxErrRec))) != PTXFE_OK) return drain(rc);
+            if ((rc = grow_pinned(ctx, &ctx->h_lexerrs, &ctx->h_lexerrs_cap, (size_t)((lexerrs_done + nl) * scale) * 8 + 4096, lexerrs_done * 8)) != PTXFE_OK) return drain(rc);
         }
         // the kernels of this slice have finished (run_pipeline waits for them)
-        CUDA_TRY(cudaEventRecord(ctx->slice_ev[5 * k + 3], ctx->s_out));
-        if (nw) CUDA_TRY(cudaMemcpyAsync((uint32_t*)ctx->h_words + words_done, ctx->work.words, nw * 4, cudaMemcpyDeviceToHost, ctx->s_out));
-        if (ne) CUDA_TRY(cudaMemcpyAsync((PtxErrRec*)ctx->h_errs + errs_done, ctx->work.errs, ne * sizeof(PtxErrRec), cudaMemcpyDeviceToHost, ctx->s_out));
-        if (nl) CUDA_TRY(cudaMemcpyAsync((uint32_t*)ctx->h_lexerrs + 2 * lexerrs_done, ctx->work.lexerrs, nl * 8, cudaMemcpyDeviceToHost, ctx->s_out));
-        if (nm) CUDA_TRY(cudaMemcpyAsync((PtxModuleResult*)ctx->h_results + sl.m0, ctx->work.results, nm * sizeof(PtxModuleResult), cudaMemcpyDeviceToHost, ctx->s_out));
-        CUDA_TRY(cudaEventRecord(ctx->slice_ev[5 * k + 4], ctx->s_out));
-        if (words_done + nw > 0xFFFFFFFFull) return PTXFE_ERR_TOO_LARGE;   // module results index words with 32 bits
+        DRAIN_TRY(cudaEventRecord(ctx->slice_ev[5 * k + 3], ctx->s_out));
+        if (nw) DRAIN_TRY(cudaMemcpyAsync((uint32_t*)ctx->h_words + words_done, ctx->work.words, nw * 4, cudaMemcpyDeviceToHost, ctx->s_out));
+        if (ne) DRAIN_TRY(cudaMemcpyAsync((PtxErrRec*)ctx->h_errs + errs_done, ctx->work.errs, ne * sizeof(PtxErrRec), cudaMemcpyDeviceToHost, ctx->s_out));
+        if (nl) DRAIN_TRY(cudaMemcpyAsync((uint32_t*)ctx->h_lexerrs + 2 * lexerrs_done, ctx->work.lexerrs, nl * 8, cudaMemcpyDeviceToHost, ctx->s_out));
+        if (nm) DRAIN_TRY(cudaMemcpyAsync((PtxModuleResult*)ctx->h_results + sl.m0, ctx->work.results, nm * sizeof(PtxModuleResult), cudaMemcpyDeviceToHost, ctx->s_out));
+        DRAIN_TRY(cudaEventRecord(ctx->slice_ev[5 * k + 4], ctx->s_out));
+        if (words_done + nw > 0xFFFFFFFFull) return drain(PTXFE_ERR_TOO_LARGE);   // module results index words with 32 bits
         base_w[k] = words_done; base_e[k] = errs_done; base_l[k] = lexerrs_done;
         words_done += nw; errs_done += ne; lexerrs_done += nl;
         s.n_tokens += c.n_tokens;
@@ -1116,8 +1129,9 @@ int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* 
         s.n_classes = c.n_classes;
         s.n_signature_words = c.n_sig_words;
     }
-    CUDA_TRY(cudaStreamSynchronize(ctx->s_out));
-    CUDA_TRY(cudaStreamSynchronize(ctx->s_in));
+    DRAIN_TRY(cudaStreamSynchronize(ctx->s_out));
+    DRAIN_TRY(cudaStreamSynchronize(ctx->s_in));
+#undef DRAIN_TRY
     // ---- module results index the batch-wide host arrays
     PtxModuleResult* res = (PtxModuleResult*)ctx->h_results;
     uint64_t seq = 0;
@@ -1202,23 +1216,28 @@ int ptxfe_module_dump_hash(const ptxfe_batch* b, uint32_t i, uint64_t* out_hash)
     return PTXFE_OK;
 }
 
+// The verdict and the error count come from the module's result row (filled on the device): no record is read.
 int ptxfe_module_status(const ptxfe_batch* b, uint32_t i) {
     if (!b || !b->ctx || i >= b->n) return PTXFE_MODULE_ERR;
-    int status = 0;
-    std::string s = ptxfe_dump_module_impl(view_of(b), i, &status);
-    if (b->results[i].sequential && b->results[i].status == US_PANIC) return PTXFE_MODULE_REF_PANICS;
-    if (b->results[i].sequential && b->results[i].status == US_DIVERGE) return PTXFE_MODULE_REF_DIVERGES;
-    return status ? PTXFE_MODULE_ERR : PTXFE_MODULE_OK;
+    const PtxModuleResult& r = b->results[i];
+    const uint32_t n_lex = r.lexerr_end - r.lexerr_begin;
+    if (n_lex && b->mode != PTXFE_ERRORS_ONLY) return PTXFE_MODULE_ERR;      // not parsed (lib.rs:447-449, 487-489)
+    if (r.sequential && (r.status & US_MASK) == US_DIVERGE) return PTXFE_MODULE_REF_DIVERGES;
+    if (r.sequential && (r.status & US_MASK) == US_PANIC) return PTXFE_MODULE_REF_PANICS;
+    if (b->mode == PTXFE_ERRORS_ONLY) return PTXFE_MODULE_ERR;               // no module is returned in this mode
+    const bool parsed_ok = r.word_end > r.word_begin && !(r.status & US_MODULE_FAILED);
+    if (b->mode == PTXFE_UNCHECKED) return parsed_ok ? PTXFE_MODULE_OK : PTXFE_MODULE_ERR;
+    return (parsed_ok && r.n_errors == 0 && n_lex == 0) ? PTXFE_MODULE_OK : PTXFE_MODULE_ERR;
 }
 
 uint32_t ptxfe_module_error_count(const ptxfe_batch* b, uint32_t i) {
     if (!b || !b->ctx || i >= b->n) return 0;
     const PtxModuleResult& r = b->results[i];
-    uint32_t n = r.lexerr_end - r.lexerr_begin;
-    if (n && b->mode != PTXFE_ERRORS_ONLY) return n;
-    for (uint32_t e = r.err_begin; e < r.err_end; e++)
-        if ((b->errs[e].w0 & 0xFFFF) != E_NONE) n++;
-    return n;
+    const uint32_t n_lex = r.lexerr_end - r.lexerr_begin;
+    if (n_lex && b->mode != PTXFE_ERRORS_ONLY) return n_lex;
+    if (r.sequential && (r.status & US_MASK) == US_DIVERGE) return 0;
+    // a module without tokens: the implicit Parser error of the reference (the header does not parse)
+    return n_lex + r.n_errors + (r.word_end == r.word_begin ? 1u : 0u);
 }
 
 int ptxfe_module_records(const ptxfe_batch* b, uint32_t i, const uint32_t** words, uint64_t* n_words, uint64_t* text_base) {
@@ -1286,6 +1305,7 @@ int ptxfe_lex_module(ptxfe_ctx* ctx, const char* text, uint64_t len, uint32_t** 
 #define PTXFE_NOALLOC_MAX_TEXT (16u << 20)
 #define PTXFE_NOALLOC_MAX_CHUNKS (PTXFE_NOALLOC_MAX_TEXT / PTX_CHUNK)
 #define PTXFE_NOALLOC_SCRATCH_BYTES (2u << 20)
+#define PTXFE_NOALLOC_MAX_BACK (64u << 10)
 static __device__ __align__(256) unsigned char ptxfe_noalloc_scratch[PTXFE_NOALLOC_SCRATCH_BYTES];
 
 // inclusive scan of at most SCAN_TILE * SCAN_TILE elements with caller-provided room for the tile totals
@@ -1306,33 +1326,43 @@ extern "C" int ptxfe_lex_device_noalloc(int device, const void* d_text_v, uint64
                              uint32_t* d_counts, void* stream_v) {
     // Device addresses of the scratch array, looked up once per device.  The array's name is only a host-side handle:
     // kernels must be given the address that cudaGetSymbolAddress returns while that device is current.
-    static unsigned char* scratch_addr[64] = {nullptr};
+    static std::atomic<unsigned char*> scratch_addr[64];
     if (!d_text_v || !d_tokens_v || !d_counts || device < 0 || device >= 64) return PTXFE_ERR_BAD_ARG;
     if (len > PTXFE_NOALLOC_MAX_TEXT) {
         fprintf(stderr, "ptxfe_lex_device_noalloc: %llu bytes of text exceed the fixed working memory (limit %u bytes)\n",
                 (unsigned long long)len, PTXFE_NOALLOC_MAX_TEXT);
         return PTXFE_ERR_TOO_LARGE;
     }
-    if (cudaSetDevice(device) != cudaSuccess) return PTXFE_ERR_CUDA;
-    if (!scratch_addr[device]) {
+    // the device is made current for the look-up and the launches and the caller's current device is put back on return
+    int caller_device = -1;
+    if (cudaGetDevice(&caller_device) != cudaSuccess) return PTXFE_ERR_CUDA;
+    struct RestoreDevice {
+        int dev;
+        ~RestoreDevice() { if (dev >= 0) cudaSetDevice(dev); }
+    } restore{caller_device != device ? caller_device : -1};
+    if (caller_device != device && cudaSetDevice(device) != cudaSuccess) return PTXFE_ERR_CUDA;
+    unsigned char* scratch = scratch_addr[device].load(std::memory_order_acquire);
+    if (!scratch) {
         void* p = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&p, ptxfe_noalloc_scratch);
         if (e != cudaSuccess || !p) {
             fprintf(stderr, "ptxfe_lex_device_noalloc: cudaGetSymbolAddress failed: %s\n", cudaGetErrorString(e));
             return PTXFE_ERR_CUDA;
         }
-        scratch_addr[device] = (unsigned char*)p;
+        scratch = (unsigned char*)p;
+        scratch_addr[device].store(scratch, std::memory_order_release);      // every thread that looks it up stores the same address
     }
     cudaStream_t stream = (cudaStream_t)stream_v;
     const uint8_t* text = (const uint8_t*)d_text_v;
     PtxToken* tokens = (PtxToken*)d_tokens_v;
     const uint32_t n_chunks = (uint32_t)((len + PTX_CHUNK - 1) / PTX_CHUNK);
-    unsigned char* base = scratch_addr[device];
+    unsigned char* base = scratch;
     uint32_t* vec = (uint32_t*)base;                                                    // n_chunks + 1
     PtxPair* cnt = (PtxPair*)(base + sizeof(uint32_t) * (PTXFE_NOALLOC_MAX_CHUNKS + 64));   // n_chunks + 2
     unsigned char* tail = (unsigned char*)(cnt + PTXFE_NOALLOC_MAX_CHUNKS + 64);
     uint32_t* partial_u32 = (uint32_t*)tail;                                            // <= 64 + 1 tile totals
     PtxPair* partial_pair = (PtxPair*)(tail + 4096);
+    uint32_t* refused = (uint32_t*)(tail + 8192);                                       // 1 = a run of soft bytes outgrew the look-back
     if (n_chunks == 0) {
         if (cudaMemsetAsync(d_counts, 0, 2 * sizeof(uint32_t), stream) != cudaSuccess) return PTXFE_ERR_CUDA;
         return PTXFE_OK;
@@ -1345,13 +1375,23 @@ extern "C" int ptxfe_lex_device_noalloc(int device, const void* d_text_v, uint64
         uint64_t ce = cs + PTX_CHUNK < me ? cs + PTX_CHUNK : me;
         uint32_t v = cx_chunk_vector(PtxGlobalReader{text, (uint32_t)me}, (uint32_t)cs, (uint32_t)ce);
         vec[c] = c == 0 ? cx_restart(v) : v;
+        if (c == 0) *refused = 0;
     });
+    // The byte walk of a chunk that begins inside a run of soft bytes starts over at the head of that run: bounded
+    // here, so that a module made of one enormous run cannot keep the kernels busy for hours
+    auto run_too_long = [=] __device__(uint32_t cs) -> bool {
+        if (cs == 0 || cs >= (uint32_t)me || !lx_soft(text[cs - 1]) || !lx_soft(text[cs])) return false;
+        uint32_t q = cs - 1;
+        while (q > 0 && cs - q <= PTXFE_NOALLOC_MAX_BACK && lx_soft(text[q - 1])) q--;
+        return cs - q > PTXFE_NOALLOC_MAX_BACK;
+    };
     scan_in_scratch<uint32_t>(stream, n_chunks, ArrayLoad<uint32_t>{vec}, ArrayStore<uint32_t>{vec}, ComposeOp(), CX_IDENTITY, partial_u32);
     pf_kernel<<<(n_chunks + 255) / 256, 256, 0, stream>>>((size_t)n_chunks, [=] __device__(size_t c) {
         uint64_t cs = (uint64_t)c * PTX_CHUNK;
         int state = c == 0 ? CX_CODE : (int)(vec[c - 1] & 7u);
         LexCountSink sink;
-        lx_chunk(PtxGlobalReader{text, (uint32_t)me}, text, 0u, (uint32_t)me, (uint32_t)cs, (uint32_t)cs + PTX_CHUNK, state, sink);
+        if (state == CX_CODE && run_too_long((uint32_t)cs)) *refused = 1;
+        else lx_chunk(PtxGlobalReader{text, (uint32_t)me}, text, 0u, (uint32_t)me, (uint32_t)cs, (uint32_t)cs + PTX_CHUNK, state, sink);
         PtxPair p;
         p.a = sink.n_tokens;
         p.b = sink.n_errors;
@@ -1367,10 +1407,10 @@ extern "C" int ptxfe_lex_device_noalloc(int device, const void* d_text_v, uint64
         sink.text = text;
         sink.next = cnt[c].a;
         sink.capacity = token_capacity;
-        lx_chunk(PtxGlobalReader{text, (uint32_t)me}, text, 0u, (uint32_t)me, (uint32_t)cs, (uint32_t)cs + PTX_CHUNK, state, sink);
+        if (!*refused) lx_chunk(PtxGlobalReader{text, (uint32_t)me}, text, 0u, (uint32_t)me, (uint32_t)cs, (uint32_t)cs + PTX_CHUNK, state, sink);
         if (c == 0) {
-            d_counts[0] = cnt[n_chunks].a;
-            d_counts[1] = cnt[n_chunks].b;
+            d_counts[0] = *refused ? 0xFFFFFFFFu : cnt[n_chunks].a;
+            d_counts[1] = *refused ? 0xFFFFFFFFu : cnt[n_chunks].b;
         }
     });
     cudaError_t e = cudaGetLastError();

@@ -24,7 +24,9 @@ struct PtxModuleResult {
     uint32_t word_begin, word_end;
     uint32_t err_begin, err_end;
     uint32_t sequential;   // 1 = parsed by the sequential path
-    uint32_t status;       // PtxUnitStatus of the sequential path
+    uint32_t status;       // sequential path: PtxUnitStatus | US_MODULE_FAILED
+    uint32_t n_errors;     // parser errors raised (reserved slots that stayed unused not counted)
+    uint32_t pad;
 };
 
 // host view of one fetched batch (input of the dump)
@@ -465,7 +467,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         r.lexerr_begin = mod_lexerr_begin[m];
         r.lexerr_end = mod_lexerr_begin[m + 1];
         r.unit_begin = r.unit_end = r.word_begin = r.word_end = r.err_begin = r.err_end = 0;
-        r.sequential = r.status = 0;
+        r.sequential = r.status = r.n_errors = r.pad = 0;
         results[m] = r;
     });
 }
@@ -1149,8 +1151,25 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
             bi->dst[k] = bi->elems[k];
         });
     }
+    // parser errors per module, so that a module's verdict can be read off its result row
+    uint32_t* mod_nerr = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 1));
+    bk.zero(mod_nerr, sizeof(uint32_t) * (n_modules + 1));
+    bk.pf("count_module_errors", n_errs, [=] PTX_HD(size_t e) {
+        if ((errs[e].w0 & 0xFFFFu) == E_NONE) return;
+        uint32_t lo = 0, hi = n_modules;       // last module whose errors begin at or before e
+        while (hi - lo > 1) {
+            uint32_t mid = (lo + hi) >> 1;
+            if (usize[mub[mid]].b <= (uint32_t)e) lo = mid; else hi = mid;
+        }
+#ifdef __CUDA_ARCH__
+        atomicAdd(&mod_nerr[lo], 1u);
+#else
+        mod_nerr[lo]++;
+#endif
+    });
     bk.pf("module_results_final", n_modules, [=] PTX_HD(size_t m) {
         PtxModuleResult r = results[m];
+        r.n_errors = mod_nerr[m];
         r.unit_begin = mub[m];
         r.unit_end = mub[m + 1];
         r.word_begin = n_units ? usize[mub[m]].a : 0;
