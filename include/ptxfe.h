@@ -90,6 +90,25 @@ int ptxfe_stage(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, 
 int ptxfe_run(ptxfe_ctx* ctx, uint32_t mode);
 int ptxfe_fetch(ptxfe_ctx* ctx, ptxfe_batch** out);
 
+/* Several GPUs of one machine.  Modules are independent, so a batch is sharded by module with byte-balanced greedy
+ * partitioning (largest module first onto the device with the fewest bytes so far) and nothing is exchanged between
+ * the devices.  The reference's counterpart is its one fan-out caller, which hands modules to a thread pool
+ * (zluda_precompile/src/main.rs:57-64).  ptxfe_multi_create makes one context per entry of `devices` (a device may be
+ * named more than once: each entry gets its own context, streams and arenas); ptxfe_parse_batch_multi splits the
+ * batch, runs ptxfe_parse_batch on every shard from a host thread of its own, and returns ONE batch whose modules are
+ * indexed as the caller passed them: every ptxfe_module_* function below works on it unchanged.
+ * ptxfe_multi_part_stats reports the statistics of shard `part` of the last call, ptxfe_multi_part_of the shard a
+ * module went to. */
+typedef struct ptxfe_multi ptxfe_multi;
+int ptxfe_multi_create(const int* devices, uint32_t n_devices, ptxfe_multi** out);
+void ptxfe_multi_destroy(ptxfe_multi* m);
+const char* ptxfe_multi_last_error(const ptxfe_multi* m);
+int ptxfe_parse_batch_multi(ptxfe_multi* m, const char* const* texts, const uint64_t* lens, uint32_t n, uint32_t mode,
+                            ptxfe_batch** out);
+uint32_t ptxfe_multi_parts(const ptxfe_multi* m);
+void ptxfe_multi_part_stats(const ptxfe_multi* m, uint32_t part, ptxfe_stats* out);
+int ptxfe_multi_part_of(const ptxfe_batch* batch, uint32_t i);
+
 void ptxfe_batch_free(ptxfe_batch* batch);
 uint32_t ptxfe_batch_size(const ptxfe_batch* batch);
 int ptxfe_module_status(const ptxfe_batch* batch, uint32_t i);

@@ -13,6 +13,8 @@
 #define PTX_HD
 #define PTX_TABLE static const
 #include "../../zluda_b200/csrc/ptx_dump.h"
+#include "../../zluda_b200/csrc/ptx_partition.h"
+#include <thread>
 
 struct HostBackend {
     std::vector<void*> blocks;
@@ -191,6 +193,43 @@ char* emu_parse(const char* const* texts, const uint64_t* lens, uint32_t n, uint
         stats[7] = hc.n_rest;
         stats[8] = hc.n_classes;
     }
+    char* r = (char*)malloc(all.size() + 1);
+    memcpy(r, all.data(), all.size());
+    *out_len = all.size();
+    return r;
+}
+
+// The sharded form: the product's partitioner splits the batch into n_parts shards, every shard runs through the
+// pipeline on a host thread of its own, and the dumps come back in the caller's module order.  part_of[i] = shard of
+// module i.
+char* emu_parse_multi(const char* const* texts, const uint64_t* lens, uint32_t n, uint32_t n_parts, uint32_t mode, uint64_t* out_len,
+                      uint32_t* part_of, uint64_t* part_bytes) {
+    PtxPartition part = ptx_partition_greedy(lens, n, n_parts);
+    std::vector<std::vector<std::string>> dumps(part.members.size());
+    std::vector<std::thread> threads;
+    for (size_t k = 0; k < part.members.size(); k++)
+        threads.emplace_back([&, k]() {
+            std::vector<const char*> t;
+            std::vector<uint64_t> l;
+            for (uint32_t i : part.members[k]) { t.push_back(texts[i]); l.push_back(lens[i]); }
+            uint64_t ol = 0;
+            char* r = emu_parse(t.data(), l.data(), (uint32_t)t.size(), mode, &ol, nullptr);
+            const char* p = r;
+            for (size_t j = 0; j < t.size(); j++) {
+                dumps[k].push_back(std::string(p));
+                p += dumps[k].back().size() + 1;
+            }
+            free(r);
+        });
+    for (std::thread& th : threads) th.join();
+    std::string all;
+    for (uint32_t i = 0; i < n; i++) {
+        all += dumps[part.where[i].first][part.where[i].second];
+        all.push_back('\0');
+        if (part_of) part_of[i] = part.where[i].first;
+    }
+    if (part_bytes)
+        for (size_t k = 0; k < part.bytes.size(); k++) part_bytes[k] = part.bytes[k];
     char* r = (char*)malloc(all.size() + 1);
     memcpy(r, all.data(), all.size());
     *out_len = all.size();

@@ -15,6 +15,10 @@ class Emu:
         lib.emu_parse.restype = ctypes.c_void_p
         lib.emu_parse.argtypes = [ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_uint64), ctypes.c_uint32,
                                   ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
+        lib.emu_parse_multi.restype = ctypes.c_void_p
+        lib.emu_parse_multi.argtypes = [ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(ctypes.c_uint64), ctypes.c_uint32, ctypes.c_uint32,
+                                        ctypes.c_uint32, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint32),
+                                        ctypes.POINTER(ctypes.c_uint64)]
         lib.emu_lex.restype = ctypes.c_void_p
         lib.emu_lex.argtypes = [ctypes.c_char_p, ctypes.c_uint64, ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_uint64)]
         lib.emu_free.argtypes = [ctypes.c_void_p]
@@ -34,6 +38,21 @@ class Emu:
         self.lib.emu_free(p)
         dumps = [x.decode("utf-8", "replace") for x in s.split(b"\0")[:-1]]
         return dumps, dict(tokens=st[0], units=st[1], words=st[2], errors=st[3], sequential=st[4], pass_mismatch=st[5], bulk=st[6], untemplated=st[7], classes=st[8])
+
+    def parse_multi(self, texts, n_parts, mode=0):
+        """Sharded over n_parts host threads with the product's partitioner -> (dumps in the caller's order, shard of
+        every module, bytes per shard)."""
+        texts = [t.encode() if isinstance(t, str) else t for t in texts]
+        n = len(texts)
+        arr = (ctypes.c_char_p * n)(*texts)
+        lens = (ctypes.c_uint64 * n)(*[len(t) for t in texts])
+        ol = ctypes.c_uint64()
+        part_of = (ctypes.c_uint32 * max(1, n))()
+        part_bytes = (ctypes.c_uint64 * n_parts)()
+        p = self.lib.emu_parse_multi(arr, lens, n, n_parts, mode, ctypes.byref(ol), part_of, part_bytes)
+        s = ctypes.string_at(p, ol.value)
+        self.lib.emu_free(p)
+        return [x.decode("utf-8", "replace") for x in s.split(b"\0")[:-1]], list(part_of)[:n], list(part_bytes)
 
     def lex(self, text):
         if isinstance(text, str):
@@ -59,6 +78,6 @@ def load():
         deps = [src] + [os.path.join(csrc, f) for f in os.listdir(csrc) if f.endswith(".h")]
         deps += [os.path.join(csrc, "gen", f) for f in os.listdir(os.path.join(csrc, "gen"))]
         if not os.path.exists(SO) or any(os.path.getmtime(d) > os.path.getmtime(SO) for d in deps):
-            subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-o", SO, src])
+            subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", SO, src])
         _cached = Emu(ctypes.CDLL(SO))
     return _cached

@@ -192,6 +192,37 @@ def test_full_size_properties(ctx):
     assert h1 == h2
 
 
+def test_multi_device_entry_point(oracle):
+    """ptxfe_parse_batch_multi: the batch split over a device list inside the library, one host thread and context per
+    entry, results in the caller's module order.  With one GPU visible the list names it twice (two contexts, two
+    threads); with more, the first two or four devices."""
+    import torch
+    n_dev = torch.cuda.device_count()
+    devices = [0, 0] if n_dev < 2 else list(range(min(n_dev, 4)))
+    texts = cases.all_cases()[:80] + corpus.config1(n_modules=64, total_bytes=8 << 20) + cases.nested_damage_cases()[:4]
+    mc = zluda_b200.MultiContext(devices)
+    for mode in (0, 2):
+        b = mc.parse_batch(texts, mode)
+        assert len(b) == len(texts)
+        for i, t in enumerate(texts):
+            st, o = oracle.parse(t, mode)
+            assert b.dump(i) == o, (mode, i)
+            assert (b.status(i) == 0) == (st == 0)
+        parts = [b.part_of(i) for i in range(len(texts))]
+        assert set(parts) == set(range(len(devices)))
+        stats = mc.part_stats()
+        assert sum(s["n_modules"] for s in stats) == len(texts)
+        loads = [s["text_bytes"] for s in stats]
+        assert max(loads) - min(loads) <= max(len(t) for t in texts)
+        b.free()
+    # a second batch through the same contexts, and an empty one
+    b = mc.parse_batch(texts[:3], 0)
+    assert [b.dump(i) for i in range(3)] == [oracle.parse(t, 0)[1] for t in texts[:3]]
+    b.free()
+    assert len(mc.parse_batch([], 0)) == 0
+    mc.close()
+
+
 def test_public_api(oracle):
     text = cases.body("add.s32 %r1, %r2, %r3;")
     r = zluda_b200.parse_module_checked(text)

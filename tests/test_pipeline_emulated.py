@@ -87,6 +87,24 @@ def test_nested_damage_and_divergence(oracle, emu):
     assert verdicts[0] == "status: Err" and verdicts[-1] == "status: ReferenceDiverges", verdicts
 
 
+def test_sharded_over_two_host_threads(oracle, emu):
+    """The library's multi-device entry point splits a batch with byte-balanced greedy partitioning, parses every shard
+    on a host thread of its own and hands the modules back in the caller's order: the same partitioner and the same
+    gather on two (and three) host threads here, every dump against the oracle's."""
+    texts = cases.all_cases()[:60] + [t.decode() for t in corpus.config1(n_modules=24, total_bytes=1 << 20)] + cases.nested_damage_cases()[:6]
+    for n_parts in (2, 3):
+        dumps, part_of, part_bytes = emu.parse_multi(texts, n_parts)
+        assert len(dumps) == len(texts)
+        for t, d in zip(texts, dumps):
+            assert oracle.parse(t, 0)[1] == d
+        assert set(part_of) == set(range(n_parts))
+        sizes = [len(t.encode()) for t in texts]
+        assert sum(part_bytes) == sum(sizes)
+        assert max(part_bytes) - min(part_bytes) <= max(sizes)      # greedy: no part is more than one module above another
+    assert emu.parse_multi([], 2)[0] == []
+    assert emu.parse_multi(texts[:1], 4)[1] == [0]
+
+
 def test_negative_decimal_side_file(oracle, emu):
     assert_parity(oracle, emu, [cases.negative_decimal_side_file()])
 

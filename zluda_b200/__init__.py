@@ -73,6 +73,15 @@ def lib():
         L.ptxfe_module_dump_hash.argtypes = [vp, u32, ctypes.POINTER(u64)]
         L.ptxfe_free.argtypes = [vp]
         L.ptxfe_lex_module.argtypes = [vp, ctypes.c_char_p, u64, ctypes.POINTER(vp), ctypes.POINTER(u64), ctypes.POINTER(u64)]
+        L.ptxfe_multi_create.argtypes = [ctypes.POINTER(ctypes.c_int), u32, ctypes.POINTER(vp)]
+        L.ptxfe_multi_destroy.argtypes = [vp]
+        L.ptxfe_multi_last_error.argtypes = [vp]
+        L.ptxfe_multi_last_error.restype = ctypes.c_char_p
+        L.ptxfe_parse_batch_multi.argtypes = [vp, ctypes.POINTER(ctypes.c_char_p), ctypes.POINTER(u64), u32, u32, ctypes.POINTER(vp)]
+        L.ptxfe_multi_parts.argtypes = [vp]
+        L.ptxfe_multi_parts.restype = u32
+        L.ptxfe_multi_part_stats.argtypes = [vp, u32, ctypes.POINTER(Stats)]
+        L.ptxfe_multi_part_of.argtypes = [vp, u32]
         _lib = L
     return _lib
 
@@ -128,6 +137,10 @@ class Batch:
 
     def status(self, i):
         return lib().ptxfe_module_status(self._h, i)
+
+    def part_of(self, i):
+        """The shard (index into the device list) that parsed module i; 0 for a single-device batch."""
+        return lib().ptxfe_multi_part_of(self._h, i)
 
     def error_count(self, i):
         return lib().ptxfe_module_error_count(self._h, i)
@@ -242,6 +255,48 @@ class Context:
         errs = [(arr[nt.value * 3 + 2 * i], arr[nt.value * 3 + 2 * i + 1]) for i in range(ne.value)]
         lib().ptxfe_free(p)
         return toks, errs
+
+
+class MultiContext:
+    """Several CUDA devices of one machine (ptxfe_multi): a batch is sharded by module, byte-balanced, one host thread
+    and one context per device; the returned Batch indexes modules as they were passed."""
+
+    def __init__(self, devices):
+        self._h = ctypes.c_void_p()
+        arr = (ctypes.c_int * len(devices))(*devices)
+        st = lib().ptxfe_multi_create(arr, len(devices), ctypes.byref(self._h))
+        if st != 0:
+            self._h = None
+            raise PtxfeError("ptxfe_multi_create(%s) failed: %s" % (list(devices), lib().ptxfe_status_str(st).decode()))
+
+    def close(self):
+        if self._h:
+            lib().ptxfe_multi_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, st):
+        if st != 0:
+            raise PtxfeError("%s: %s" % (lib().ptxfe_status_str(st).decode(), lib().ptxfe_multi_last_error(self._h).decode()))
+
+    def parse_batch(self, texts, mode=CHECKED):
+        keep, ptrs, lens = _as_buffers(texts)
+        h = ctypes.c_void_p()
+        self._check(lib().ptxfe_parse_batch_multi(self._h, ptrs, lens, len(ptrs), mode, ctypes.byref(h)))
+        return Batch(self, h, (keep, ptrs, lens))
+
+    def part_stats(self):
+        out = []
+        for k in range(lib().ptxfe_multi_parts(self._h)):
+            s = Stats()
+            lib().ptxfe_multi_part_stats(self._h, k, ctypes.byref(s))
+            out.append(s.as_dict())
+        return out
 
 
 class ParseResult:

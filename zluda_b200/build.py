@@ -68,7 +68,7 @@ def build_test_helpers(force=False):
     deps = [emu_src] + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".h")] + \
            [os.path.join(CSRC, "gen", f) for f in os.listdir(os.path.join(CSRC, "gen"))]
     if force or _newer(emu, deps):
-        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-o", emu, emu_src])
+        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", emu, emu_src])
 
 
 def build(force=False):

@@ -18,6 +18,8 @@
 #define PTX_TABLE static __device__ const
 #include "../../include/ptxfe.h"
 #include "ptxfe_pipeline.h"
+#include "ptx_partition.h"
+#include <thread>
 
 // host side (ptxfe_dump.cpp)
 std::string ptxfe_dump_module_impl(const PtxBatchView& v, uint32_t m, int* status);
@@ -395,6 +397,9 @@ struct ArenaBlock {
 };
 
 struct ptxfe_batch {
+    // a batch parsed on several devices is a list of per-device batches and a map from the caller's module index
+    std::vector<ptxfe_batch*> parts;
+    std::vector<std::pair<uint32_t, uint32_t>> where;
     ptxfe_ctx* ctx;
     uint32_t n, mode;
     std::vector<const char*> texts;
@@ -1176,10 +1181,17 @@ int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* 
 
 void ptxfe_batch_free(ptxfe_batch* b) {
     if (!b) return;
+    for (ptxfe_batch* p : b->parts) ptxfe_batch_free(p);
     if (b->ctx && b->ctx->live == b) b->ctx->live = nullptr;
     delete b;
 }
 uint32_t ptxfe_batch_size(const ptxfe_batch* b) { return b ? b->n : 0; }
+// module i of a batch that was parsed on several devices lives in one of its parts
+#define PTXFE_ROUTE(b, i, fn, ...)                                                                   \
+    if ((b) && !(b)->parts.empty()) {                                                                \
+        if ((i) >= (b)->n) return PTXFE_ERR_BAD_ARG;                                                 \
+        return fn((b)->parts[(b)->where[(i)].first], (b)->where[(i)].second, ##__VA_ARGS__);         \
+    }
 void ptxfe_get_stats(const ptxfe_ctx* ctx, ptxfe_stats* out) {
     if (ctx && out) *out = ctx->stats;
 }
@@ -1198,6 +1210,7 @@ static PtxBatchView view_of(const ptxfe_batch* b) {
 }
 
 int ptxfe_module_dump(const ptxfe_batch* b, uint32_t i, char** out, uint64_t* out_len) {
+    PTXFE_ROUTE(b, i, ptxfe_module_dump, out, out_len)
     if (!b || !b->ctx || i >= b->n || !out) return PTXFE_ERR_BAD_ARG;
     int status = 0;
     std::string s = ptxfe_dump_module_impl(view_of(b), i, &status);
@@ -1210,6 +1223,7 @@ int ptxfe_module_dump(const ptxfe_batch* b, uint32_t i, char** out, uint64_t* ou
 }
 
 int ptxfe_module_dump_hash(const ptxfe_batch* b, uint32_t i, uint64_t* out_hash) {
+    PTXFE_ROUTE(b, i, ptxfe_module_dump_hash, out_hash)
     if (!b || !b->ctx || i >= b->n || !out_hash) return PTXFE_ERR_BAD_ARG;
     int status = 0;
     *out_hash = ptxfe_dump_hash_impl(view_of(b), i, &status);
@@ -1218,6 +1232,7 @@ int ptxfe_module_dump_hash(const ptxfe_batch* b, uint32_t i, uint64_t* out_hash)
 
 // The verdict and the error count come from the module's result row (filled on the device): no record is read.
 int ptxfe_module_status(const ptxfe_batch* b, uint32_t i) {
+    if (b && !b->parts.empty()) return i < b->n ? ptxfe_module_status(b->parts[b->where[i].first], b->where[i].second) : PTXFE_MODULE_ERR;
     if (!b || !b->ctx || i >= b->n) return PTXFE_MODULE_ERR;
     const PtxModuleResult& r = b->results[i];
     const uint32_t n_lex = r.lexerr_end - r.lexerr_begin;
@@ -1231,6 +1246,7 @@ int ptxfe_module_status(const ptxfe_batch* b, uint32_t i) {
 }
 
 uint32_t ptxfe_module_error_count(const ptxfe_batch* b, uint32_t i) {
+    if (b && !b->parts.empty()) return i < b->n ? ptxfe_module_error_count(b->parts[b->where[i].first], b->where[i].second) : 0u;
     if (!b || !b->ctx || i >= b->n) return 0;
     const PtxModuleResult& r = b->results[i];
     const uint32_t n_lex = r.lexerr_end - r.lexerr_begin;
@@ -1241,6 +1257,7 @@ uint32_t ptxfe_module_error_count(const ptxfe_batch* b, uint32_t i) {
 }
 
 int ptxfe_module_records(const ptxfe_batch* b, uint32_t i, const uint32_t** words, uint64_t* n_words, uint64_t* text_base) {
+    PTXFE_ROUTE(b, i, ptxfe_module_records, words, n_words, text_base)
     if (!b || !b->ctx || i >= b->n) return PTXFE_ERR_BAD_ARG;
     if (words) *words = b->words + b->results[i].word_begin;
     if (n_words) *n_words = b->results[i].word_end - b->results[i].word_begin;
@@ -1249,6 +1266,94 @@ int ptxfe_module_records(const ptxfe_batch* b, uint32_t i, const uint32_t** word
 }
 
 void ptxfe_free(void* p) { free(p); }
+
+// ------------------------------------------------------------------------------------------------ several devices
+struct ptxfe_multi {
+    std::vector<ptxfe_ctx*> ctxs;
+    std::vector<ptxfe_stats> stats;
+    char err[512] = {0};
+};
+
+int ptxfe_multi_create(const int* devices, uint32_t n_devices, ptxfe_multi** out) {
+    if (!out || !devices || n_devices == 0) return PTXFE_ERR_BAD_ARG;
+    *out = nullptr;
+    ptxfe_multi* m = new ptxfe_multi();
+    for (uint32_t k = 0; k < n_devices; k++) {
+        ptxfe_ctx* c = nullptr;
+        int st = ptxfe_create(devices[k], &c);
+        if (st != PTXFE_OK) {
+            ptxfe_multi_destroy(m);
+            return st;
+        }
+        m->ctxs.push_back(c);
+    }
+    m->stats.resize(n_devices);
+    memset(m->stats.data(), 0, sizeof(ptxfe_stats) * n_devices);
+    *out = m;
+    return PTXFE_OK;
+}
+void ptxfe_multi_destroy(ptxfe_multi* m) {
+    if (!m) return;
+    for (ptxfe_ctx* c : m->ctxs) ptxfe_destroy(c);
+    delete m;
+}
+const char* ptxfe_multi_last_error(const ptxfe_multi* m) { return m ? m->err : "no context"; }
+uint32_t ptxfe_multi_parts(const ptxfe_multi* m) { return m ? (uint32_t)m->ctxs.size() : 0; }
+void ptxfe_multi_part_stats(const ptxfe_multi* m, uint32_t part, ptxfe_stats* out) {
+    if (m && out && part < m->stats.size()) *out = m->stats[part];
+}
+int ptxfe_multi_part_of(const ptxfe_batch* b, uint32_t i) {
+    if (!b || i >= b->n) return -1;
+    return b->parts.empty() ? 0 : (int)b->where[i].first;
+}
+
+int ptxfe_parse_batch_multi(ptxfe_multi* m, const char* const* texts, const uint64_t* lens, uint32_t n, uint32_t mode, ptxfe_batch** out) {
+    if (!out) return PTXFE_ERR_BAD_ARG;
+    *out = nullptr;
+    if (!m || m->ctxs.empty() || (n && (!texts || !lens)) || mode > 2) return PTXFE_ERR_BAD_ARG;
+    const uint32_t n_parts = (uint32_t)m->ctxs.size();
+    PtxPartition part = ptx_partition_greedy(lens, n, n_parts);
+    // every shard gets its own (char**, uint64*) arrays and its own host thread; a thread makes its context's device
+    // current (ptxfe_parse_batch does) and touches nothing of the others
+    std::vector<std::vector<const char*>> ptexts(n_parts);
+    std::vector<std::vector<uint64_t>> plens(n_parts);
+    for (uint32_t k = 0; k < n_parts; k++)
+        for (uint32_t i : part.members[k]) {
+            ptexts[k].push_back(texts[i]);
+            plens[k].push_back(lens[i]);
+        }
+    std::vector<ptxfe_batch*> batches(n_parts, nullptr);
+    std::vector<int> status(n_parts, PTXFE_OK);
+    std::vector<std::thread> threads;
+    for (uint32_t k = 0; k < n_parts; k++)
+        threads.emplace_back([&, k]() {
+            status[k] = ptxfe_parse_batch(m->ctxs[k], ptexts[k].data(), plens[k].data(), (uint32_t)ptexts[k].size(), mode, &batches[k]);
+        });
+    for (std::thread& t : threads) t.join();
+    int rc = PTXFE_OK;
+    for (uint32_t k = 0; k < n_parts; k++) {
+        ptxfe_get_stats(m->ctxs[k], &m->stats[k]);
+        if (status[k] != PTXFE_OK && rc == PTXFE_OK) {
+            rc = status[k];
+            snprintf(m->err, sizeof m->err, "device part %u: %s", k, ptxfe_last_error(m->ctxs[k]));
+        }
+    }
+    if (rc != PTXFE_OK) {
+        for (ptxfe_batch* b : batches) ptxfe_batch_free(b);
+        return rc;
+    }
+    ptxfe_batch* b = new ptxfe_batch();
+    b->ctx = nullptr;
+    b->n = n;
+    b->mode = mode;
+    b->words = nullptr;
+    b->errs = nullptr;
+    b->lexerrs = nullptr;
+    b->parts = batches;
+    b->where = part.where;
+    *out = b;
+    return PTXFE_OK;
+}
 
 int ptxfe_lex_module(ptxfe_ctx* ctx, const char* text, uint64_t len, uint32_t** out, uint64_t* n_tokens, uint64_t* n_errors) {
     if (!ctx || !out || !n_tokens || !n_errors) return PTXFE_ERR_BAD_ARG;
