@@ -126,6 +126,12 @@ int ptxfe_module_records(const ptxfe_batch* batch, uint32_t i, const uint32_t** 
 /* Canonical text dump of module i: the tree printed as if every ptx_parser AST type derived Debug (floats as bit
  * patterns), followed by the ordered error list.  malloc'ed; release with ptxfe_free. */
 int ptxfe_module_dump(const ptxfe_batch* batch, uint32_t i, char** out, uint64_t* out_len);
+/* Materialiser: builds, for every module of the batch, the tree a caller of the reference holds - module, directives,
+ * functions, statements with nested blocks, variables with their padded initialisers, instructions with typed data and
+ * operands, names as slices of the caller's text (zluda_b200/csrc/ptx_ast.h mirrors ptx_parser/src/ast.rs:14-19,
+ * 1216-1240, 1922-2005) - on n_threads host threads, and drops it again; *n_nodes = nodes built.  ptxfe_module_dump
+ * prints from the same tree.  This is what a binding pays on top of ptxfe_parse_batch to hand out ast-like values. */
+int ptxfe_batch_materialize(const ptxfe_batch* batch, uint32_t n_threads, uint64_t* n_nodes);
 /* 64-bit FNV-1a of the same dump, without materialising it beyond one module at a time. */
 int ptxfe_module_dump_hash(const ptxfe_batch* batch, uint32_t i, uint64_t* out_hash);
 void ptxfe_free(void* p);

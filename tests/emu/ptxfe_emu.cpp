@@ -12,7 +12,7 @@
 
 #define PTX_HD
 #define PTX_TABLE static const
-#include "../../zluda_b200/csrc/ptx_dump.h"
+#include "../../zluda_b200/csrc/ptx_ast.h"
 #include "../../zluda_b200/csrc/ptx_partition.h"
 #include <thread>
 
@@ -178,7 +178,15 @@ char* emu_parse(const char* const* texts, const uint64_t* lens, uint32_t n, uint
     uint64_t seq = 0;
     for (uint32_t m = 0; m < n; m++) {
         int st;
-        all += ptxdump::dump_module(v, m, &st);
+        std::string by_records = ptxdump::dump_module(v, m, &st);
+        if (getenv("PTXFE_EMU_TREE")) {
+            // the materialiser's way: records -> tree -> text; must be the same text
+            ptxast::Module mod;
+            ptxast::materialize(v, m, &mod);
+            std::string by_tree = ptxast::print(v, m, mod);
+            if (by_tree != by_records) by_records = "TREE DUMP DIFFERS\n" + by_tree;
+        }
+        all += by_records;
         all.push_back('\0');
         seq += w.results[m].sequential;
     }

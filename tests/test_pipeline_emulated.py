@@ -87,6 +87,17 @@ def test_nested_damage_and_divergence(oracle, emu):
     assert verdicts[0] == "status: Err" and verdicts[-1] == "status: ReferenceDiverges", verdicts
 
 
+def test_materialised_tree_prints_the_same_text(oracle, emu, monkeypatch):
+    """The materialiser (records -> tree) and its printer against the record reader and the oracle, on every edge case
+    in all three modes, the class cases, nested damage and small corpora."""
+    monkeypatch.setenv("PTXFE_EMU_TREE", "1")
+    assert_parity(oracle, emu, cases.all_cases())
+    assert_parity(oracle, emu, cases.class_cases() + cases.nested_damage_cases() + [cases.negative_decimal_side_file()], modes=(0, 1))
+    mods = corpus.config3(total_bytes=200 << 10, n_funcs=8, n_labels=100) + corpus.config1(n_modules=8, total_bytes=256 << 10) + \
+        corpus.config2(n_arrays=2, n_init=3000, n_consts=500)
+    assert_parity(oracle, emu, mods, modes=(0,))
+
+
 def test_sharded_over_two_host_threads(oracle, emu):
     """The library's multi-device entry point splits a batch with byte-balanced greedy partitioning, parses every shard
     on a host thread of its own and hands the modules back in the caller's order: the same partitioner and the same

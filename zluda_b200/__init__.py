@@ -73,6 +73,7 @@ def lib():
         L.ptxfe_module_dump_hash.argtypes = [vp, u32, ctypes.POINTER(u64)]
         L.ptxfe_free.argtypes = [vp]
         L.ptxfe_lex_module.argtypes = [vp, ctypes.c_char_p, u64, ctypes.POINTER(vp), ctypes.POINTER(u64), ctypes.POINTER(u64)]
+        L.ptxfe_batch_materialize.argtypes = [vp, u32, ctypes.POINTER(u64)]
         L.ptxfe_multi_create.argtypes = [ctypes.POINTER(ctypes.c_int), u32, ctypes.POINTER(vp)]
         L.ptxfe_multi_destroy.argtypes = [vp]
         L.ptxfe_multi_last_error.argtypes = [vp]
@@ -137,6 +138,14 @@ class Batch:
 
     def status(self, i):
         return lib().ptxfe_module_status(self._h, i)
+
+    def materialize(self, threads=None):
+        """Build (and drop) the tree of every module on `threads` host threads; returns the number of nodes built."""
+        n = ctypes.c_uint64()
+        st = lib().ptxfe_batch_materialize(self._h, threads or (os.cpu_count() or 1), ctypes.byref(n))
+        if st != 0:
+            raise PtxfeError("ptxfe_batch_materialize failed")
+        return n.value
 
     def part_of(self, i):
         """The shard (index into the device list) that parsed module i; 0 for a single-device batch."""

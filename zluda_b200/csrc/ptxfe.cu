@@ -24,6 +24,8 @@
 // host side (ptxfe_dump.cpp)
 std::string ptxfe_dump_module_impl(const PtxBatchView& v, uint32_t m, int* status);
 uint64_t ptxfe_dump_hash_impl(const PtxBatchView& v, uint32_t m, int* status);
+std::string ptxfe_dump_module_tree_impl(const PtxBatchView& v, uint32_t m, int* status);
+uint64_t ptxfe_materialize_impl(const PtxBatchView& v, uint32_t m);
 
 #define CUDA_TRY(call)                                                                      \
     do {                                                                                    \
@@ -1213,7 +1215,8 @@ int ptxfe_module_dump(const ptxfe_batch* b, uint32_t i, char** out, uint64_t* ou
     PTXFE_ROUTE(b, i, ptxfe_module_dump, out, out_len)
     if (!b || !b->ctx || i >= b->n || !out) return PTXFE_ERR_BAD_ARG;
     int status = 0;
-    std::string s = ptxfe_dump_module_impl(view_of(b), i, &status);
+    // records -> tree -> text (the hash below walks the records directly: both readers must tell the same story)
+    std::string s = ptxfe_dump_module_tree_impl(view_of(b), i, &status);
     char* r = (char*)malloc(s.size() + 1);
     if (!r) return PTXFE_ERR_OOM;
     memcpy(r, s.data(), s.size() + 1);
@@ -1262,6 +1265,31 @@ int ptxfe_module_records(const ptxfe_batch* b, uint32_t i, const uint32_t** word
     if (words) *words = b->words + b->results[i].word_begin;
     if (n_words) *n_words = b->results[i].word_end - b->results[i].word_begin;
     if (text_base) *text_base = b->layout[i].text_off;
+    return PTXFE_OK;
+}
+
+// Builds the tree of every module of the batch (and drops it again), modules spread over n_threads host threads: the
+// cost a caller pays after the parse call to hold ast-like structures instead of flat records.
+int ptxfe_batch_materialize(const ptxfe_batch* b, uint32_t n_threads, uint64_t* n_nodes) {
+    if (!b) return PTXFE_ERR_BAD_ARG;
+    if (n_threads == 0) n_threads = 1;
+    std::vector<uint64_t> nodes(n_threads, 0);
+    std::vector<std::thread> threads;
+    std::atomic<uint32_t> next{0};
+    for (uint32_t t = 0; t < n_threads; t++)
+        threads.emplace_back([&, t]() {
+            for (;;) {
+                const uint32_t i = next.fetch_add(1);
+                if (i >= b->n) return;
+                const ptxfe_batch* part = b->parts.empty() ? b : b->parts[b->where[i].first];
+                const uint32_t j = b->parts.empty() ? i : b->where[i].second;
+                nodes[t] += ptxfe_materialize_impl(view_of(part), j);
+            }
+        });
+    for (std::thread& t : threads) t.join();
+    uint64_t total = 0;
+    for (uint64_t x : nodes) total += x;
+    if (n_nodes) *n_nodes = total;
     return PTXFE_OK;
 }
 
