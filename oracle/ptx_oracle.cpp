@@ -333,6 +333,8 @@ struct Error {
 };
 
 // =============================================================================================== parser
+static unsigned char g_pattern_hits[PTX_N_PATTERNS];   // not thread-safe by design: read by single-threaded tests only
+
 struct Parser {
     const char* text;
     size_t text_len;
@@ -924,6 +926,7 @@ struct Parser {
         ins.variant = pt.instr;
         Builder b{*this, ins};
         ptx_build(pattern, b, mv, av, aneg, auni);
+        g_pattern_hits[pattern] = 1;      // test coverage: which patterns the inputs so far have exercised
         return true;
     }
 
@@ -1775,6 +1778,15 @@ uint32_t* oracle_lex(const char* text, uint64_t len, uint64_t* n_tokens, uint64_
 }
 
 int oracle_schema_ok() { return g_schema_ok ? 1 : 0; }
+// Coverage of the instruction patterns by everything parsed since the last reset: out[i] = 1 if pattern i matched.
+int oracle_pattern_count() { return PTX_N_PATTERNS; }
+const char* oracle_pattern_head(int i) { return i >= 0 && i < PTX_N_PATTERNS ? ptx_pattern_heads[i] : ""; }
+void oracle_pattern_hits(unsigned char* out, int reset) {
+    for (int i = 0; i < PTX_N_PATTERNS; i++) {
+        if (out) out[i] = g_pattern_hits[i];
+        if (reset) g_pattern_hits[i] = 0;
+    }
+}
 const char* oracle_token_text(int kind) { return kind >= 0 && kind < T_COUNT ? ptx_tok_text[kind] : ""; }
 int oracle_token_count() { return T_COUNT; }
 void oracle_free(void* p) { free(p); }

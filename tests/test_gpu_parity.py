@@ -192,6 +192,20 @@ def test_full_size_properties(ctx):
     assert h1 == h2
 
 
+def test_pattern_pins_on_the_device(ctx):
+    """Every instruction pattern through the CUDA path: the frozen line per statement (tests/golden/pattern_pins.json) and
+    the sweeps of cvt / setp / atom / ldmatrix against their re-derivations from the reference (test_pattern_pins.py)."""
+    import test_pattern_pins as pins
+
+    def parse(texts, mode):
+        b = ctx.parse_batch(texts, mode)
+        dumps = [b.dump(i) for i in range(len(texts))]
+        b.free()
+        return dumps
+    pins.check_pins(parse)
+    assert pins.check_sweep(parse) > 2500
+
+
 def test_multi_device_entry_point(oracle):
     """ptxfe_parse_batch_multi: the batch split over a device list inside the library, one host thread and context per
     entry, results in the caller's module order.  With one GPU visible the list names it twice (two contexts, two
