@@ -3,6 +3,7 @@
 // decoders and the record format can be checked against the oracle on a machine without a GPU.  It is not linked
 // into the product library and is never a fallback for it.
 #include <stdint.h>
+#include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -89,6 +90,47 @@ struct HostBackend {
             phase([&](uint32_t t) { lt_emit_first(sh, a, (uint32_t)tile, t, nt); });
             phase([&](uint32_t t) { lt_emit_keywords(sh, a, (uint32_t)tile, t, nt); });
             phase([&](uint32_t t) { lt_emit_second(sh, a, (uint32_t)tile, t, nt); });
+        }
+    }
+    // stage B: the per-thread bodies of the device kernel, tile after tile; the prefix of the earlier tiles is a running
+    // value here (the device finds it by looking back along the tiles)
+    void fail(const char* why) {
+        fprintf(stderr, "ptxfe_emu: %s\n", why);
+        abort();
+    }
+    void structure(const char*, const PtxStructArgs& a) {
+        const size_t n_tiles = ((size_t)a.n_tokens + SX_TILE - 1) / SX_TILE;
+        std::vector<SxThread> th(SX_THREADS);
+        std::vector<PtxSeg3> before(SX_THREADS);
+        std::vector<uint32_t> ubefore(SX_THREADS), starts(SX_THREADS);
+        uint8_t table[512];
+        for (uint32_t k = 0; k < 512; k++) table[k] = (uint8_t)sx_flags(k);
+        PtxSeg3 run{0, 0, 0};
+        uint32_t units = 0;
+        SegDepthOp op;
+        auto phase = [&](auto f) {
+            if (reverse) { for (uint32_t t = SX_THREADS; t-- > 0;) f(t); } else { for (uint32_t t = 0; t < SX_THREADS; t++) f(t); }
+        };
+        for (size_t tile = 0; tile < n_tiles; tile++) {
+            std::vector<PtxSeg3> agg(SX_THREADS);
+            const bool has_first = sx_tile_has_first(a, (uint32_t)(tile * SX_TILE));
+            phase([&](uint32_t t) {
+                sx_load(a, (uint32_t)(tile * SX_TILE + t * SX_ITEMS), th[t], table, has_first);
+                agg[t] = sx_aggregate(th[t]);
+            });
+            for (uint32_t t = 0; t < SX_THREADS; t++) { before[t] = run; run = op(run, agg[t]); }
+            phase([&](uint32_t t) { starts[t] = sx_decide(a, th[t], before[t]); });
+            // the bitwise case against the token-by-token case, thread by thread
+            for (uint32_t t = 0; t < SX_THREADS; t++) {
+                if (!th[t].fast) continue;
+                SxThread slow;
+                sx_load(a, th[t].tb, slow, table, true, false);
+                PtxSeg3 x = sx_aggregate(slow);
+                if (x.scope != agg[t].scope || x.paren != agg[t].paren || x.flag != agg[t].flag || sx_decide(a, slow, before[t]) != starts[t])
+                    fail("structure: the bitwise case and the token-by-token case disagree");
+            }
+            for (uint32_t t = 0; t < SX_THREADS; t++) { ubefore[t] = units; units += sx_popc(starts[t]); }
+            phase([&](uint32_t t) { sx_write(a, th[t], before[t], starts[t], ubefore[t]); });
         }
     }
     template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f) {

@@ -1,0 +1,293 @@
+// Stage B in one pass over the token kinds: scope / parenthesis depth (a segmented scan that restarts at every
+// module), the decision "a parse unit starts at this token", the numbering of the unit starts, and the unit table
+// (start token, depth in front of it, first unit of every module, scope depth behind every module's last token).
+//
+// The work is cut into tiles of SX_TILE tokens; a tile is SX_THREADS threads with SX_ITEMS consecutive tokens each.
+// Everything a thread needs of its tokens sits in registers: the 16 kinds, the three kinds in front of them (a brace is
+// classified by two tokens of left context, and a unit start looks at the class of the token before it), and one bit
+// per token for "first token of a module" (found by a binary search of the module table, not stored per token).
+// Per tile: thread aggregates -> ordered scan over the tile's threads -> the prefix of the tiles before (the backend's
+// business: a look-back chain on the device, a running value in the host emulation) -> the start decisions -> their
+// count, scanned the same way -> the unit table rows.  The functions here are the per-thread bodies of those steps.
+#pragma once
+// (included by ptxfe_pipeline.h after the token kinds, PtxSeg3 and the brace rules are defined)
+
+constexpr uint32_t SX_THREADS = 256, SX_ITEMS = 16, SX_TILE = SX_THREADS * SX_ITEMS;
+
+struct PtxStructArgs {
+    const uint16_t* kinds;        // [n_tokens + 32] readable
+    uint32_t n_tokens;
+    const uint32_t* mtb;          // [n_modules + 1] first token of every module (empty modules repeat the next begin)
+    uint32_t n_modules;
+    int32_t* mod_final_scope;     // [n_modules] out: scope depth behind the module's last token
+    uint32_t* ustart;             // out: start token of unit u
+    uint32_t* udepth;             // out: scope depth in front of unit u, bit 31 = first unit of a module
+    uint32_t* mub;                // out: first unit of module m (modules with tokens only)
+    PtxCounters* counters;        // out: n_units
+};
+
+// ---- flags of a token kind, one byte: what the structure pass wants to know of a token
+enum : uint32_t { SXF_L = 1, SXF_R = 2, SXF_OPENS = 4, SXF_LP = 8, SXF_RP = 16, SXF_S = 32, SXF_DIR = 64, SXF_SECTION = 128 };
+PTX_HD inline uint32_t sx_flags(uint32_t k) {
+    uint32_t f = 0;
+    if (k == T_LBRACE) f |= SXF_L;
+    if (k == T_RBRACE) f |= SXF_R;
+    if (ptx_opens_operand((uint16_t)k)) f |= SXF_OPENS;
+    if (k == T_LPAREN) f |= SXF_LP;
+    if (k == T_RPAREN) f |= SXF_RP;
+    if (k == T_SEMI || k == T_COLON) f |= SXF_S;
+    if (ptx_is_directive_start((uint16_t)k)) f |= SXF_DIR;
+    if (k == T_DOT_SECTION) f |= SXF_SECTION;
+    return f;
+}
+PTX_HD inline uint32_t sx_popc(uint32_t x) {
+#ifdef __CUDA_ARCH__
+    return (uint32_t)__popc(x);
+#else
+    return (uint32_t)__builtin_popcount(x);
+#endif
+}
+PTX_HD inline uint32_t sx_lowest(uint32_t x) {     // x != 0
+#ifdef __CUDA_ARCH__
+    return (uint32_t)(__ffs(x) - 1);
+#else
+    return (uint32_t)__builtin_ctz(x);
+#endif
+}
+
+// A thread's 16 tokens.  The common case ("fast": no module begins among the tokens or the three in front, and the
+// batch does not end here) never looks at a kind again after the table look-up: the flag bytes go into four words,
+// token i in byte i / 4 of word i % 4, so that the token before the tokens of word r are the same bytes of word r - 1,
+// and four tokens are judged by one bitwise operation.  One-bit-per-token results are kept as "spread" masks: token i
+// at bit 8 * (i / 4) + i % 4, which keeps the tokens in order (so "the tokens before i" is a mask of lower bits) and
+// leaves the upper half of every byte for a second mask:
+//   braces: scope-opening '{' (low halves) and scope-closing '}' (high halves);  parens: '(' and ')';
+//   marks: previous token is ';' or ':' (low halves) and directive keywords (high halves).
+// Threads of the other case keep the kinds in w[] and go token by token.
+struct SxThread {
+    uint32_t tb, n_valid;
+    uint32_t first;               // bit i: token tb - 3 + i is the first token of a module
+    bool fast;
+    uint32_t braces, parens, marks;
+    uint32_t brace_before;        // the token in front of the thread's first is a scope brace
+    uint16_t w[SX_ITEMS + 3];     // slow case only: w[3 + k] is the kind of token tb + k, w[0..2] the three before
+};
+constexpr uint32_t SX_LOW = 0x0F0F0F0Fu, SX_ONES = 0x01010101u;
+// spread position of token i, and the tokens of a spread mask moved one place up (token i's bit to token i + 1)
+PTX_HD inline uint32_t sx_pos(uint32_t i) { return 8u * (i >> 2) + (i & 3u); }
+PTX_HD inline uint32_t sx_up(uint32_t m) { return ((m & 0x07070707u) << 1) | ((m & 0x08080808u) << 5); }
+
+// does a module begin in the tile that starts at token tile_base, or in the three tokens in front of it
+PTX_HD inline bool sx_tile_has_first(const PtxStructArgs& a, uint32_t tile_base) {
+    uint32_t lowest = tile_base >= 3 ? tile_base - 3 : 0;
+    uint32_t lo = 0, hi = a.n_modules;
+    while (lo < hi) {
+        uint32_t mid = (lo + hi) >> 1;
+        if (a.mtb[mid] < lowest) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo < a.n_modules && (uint64_t)a.mtb[lo] < (uint64_t)tile_base + SX_TILE;
+}
+
+// table: flags of every kind (512 entries; the caller's copy in fast memory); has_first: a module begins somewhere in
+// the tile or in the three tokens in front of it
+PTX_HD inline void sx_load(const PtxStructArgs& a, uint32_t tb, SxThread& t, const uint8_t* table, bool has_first, bool allow_fast = true) {
+    t.tb = tb;
+    t.n_valid = tb >= a.n_tokens ? 0u : (a.n_tokens - tb < SX_ITEMS ? a.n_tokens - tb : SX_ITEMS);
+    t.first = 0;
+    t.fast = false;
+    t.braces = t.parens = t.marks = t.brace_before = 0;
+    if (!t.n_valid) return;
+    if (has_first) {
+        // module begins inside [tb - 3, tb + 16)
+        uint32_t lowest = tb >= 3 ? tb - 3 : 0;
+        uint32_t lo = 0, hi = a.n_modules;
+        while (lo < hi) {
+            uint32_t mid = (lo + hi) >> 1;
+            if (a.mtb[mid] < lowest) lo = mid + 1;
+            else hi = mid;
+        }
+        for (uint32_t m = lo; m < a.n_modules; m++) {
+            uint32_t b = a.mtb[m];
+            if (b >= tb + SX_ITEMS) break;
+            t.first |= 1u << (b + 3 - tb);
+        }
+    }
+    // tb is a multiple of 16: two aligned 16-byte loads, and one of 8 bytes for the tokens in front
+    union { LtWord4 q[2]; uint16_t h[16]; uint32_t u[8]; } own;
+    own.q[0] = ((const LtWord4*)(a.kinds + tb))[0];
+    own.q[1] = ((const LtWord4*)(a.kinds + tb))[1];
+    union { unsigned long long q; uint16_t h[4]; } halo;
+    halo.q = tb ? *(const unsigned long long*)(a.kinds + tb - 4) : 0ull;
+    t.fast = allow_fast && t.first == 0 && (uint64_t)tb + SX_ITEMS < a.n_tokens;
+    if (!t.fast) {
+#pragma unroll
+        for (uint32_t k = 0; k < SX_ITEMS; k++) t.w[3 + k] = PTX_KL_KIND(own.h[k]);
+        t.w[0] = tb ? PTX_KL_KIND(halo.h[1]) : 0; t.w[1] = tb ? PTX_KL_KIND(halo.h[2]) : 0; t.w[2] = tb ? PTX_KL_KIND(halo.h[3]) : 0;
+        return;
+    }
+    uint32_t F[4] = {0, 0, 0, 0};
+#pragma unroll
+    for (uint32_t i = 0; i < 8; i++) {      // word i: tokens 2i and 2i + 1 -> byte i / 2 of words (i % 2) * 2 and + 1
+        const uint32_t lo = table[own.u[i] & 0x1FFu], hi = table[(own.u[i] >> 16) & 0x1FFu];
+        F[(i & 1u) * 2u] |= lo << (8u * (i >> 1));
+        F[(i & 1u) * 2u + 1u] |= hi << (8u * (i >> 1));
+    }
+    // without tokens in front (tb == 0 cannot be fast: token 0 begins a module) the three flag bytes are read anyway
+    const uint32_t h1 = table[PTX_KL_KIND(halo.h[1])], h2 = table[PTX_KL_KIND(halo.h[2])], h3 = table[PTX_KL_KIND(halo.h[3])];
+    const uint32_t P1[4] = {(F[3] << 8) | h3, F[0], F[1], F[2]};          // the token before
+    const uint32_t P2[4] = {(F[2] << 8) | h2, P1[0], F[0], F[1]};         // the token two before
+    uint32_t braces = 0, parens = 0, marks = 0;
+#pragma unroll
+    for (uint32_t r = 0; r < 4; r++) {
+        const uint32_t f = F[r], p1 = P1[r], p2 = P2[r];
+        const uint32_t plus = f & ~(p1 >> 2) & ~(p2 >> 7) & SX_ONES;                   // '{' not after an operand opener or .section x
+        const uint32_t minus = (f >> 1) & (p1 | (p1 >> 1) | (p1 >> 5)) & SX_ONES;      // '}' after ';' ':' '{' '}'
+        braces |= (plus << r) | (minus << (4u + r));
+        parens |= (((f >> 3) & SX_ONES) << r) | (((f >> 4) & SX_ONES) << (4u + r));
+        marks |= (((p1 >> 5) & SX_ONES) << r) | (((f >> 6) & SX_ONES) << (4u + r));
+    }
+    t.braces = braces; t.parens = parens; t.marks = marks;
+    const uint32_t plus_h = h3 & ~(h2 >> 2) & ~(h1 >> 7) & 1u, minus_h = (h3 >> 1) & (h2 | (h2 >> 1) | (h2 >> 5)) & 1u;
+    t.brace_before = plus_h | minus_h;
+}
+
+// scope delta of the token at window index x (x >= 3): see ptx_brace_class
+PTX_HD inline int sx_brace(const SxThread& t, uint32_t x) {
+    uint16_t k = t.w[x];
+    if (k != T_LBRACE && k != T_RBRACE) return 0;
+    bool first = (t.first >> x) & 1u;
+    uint16_t prev = first ? (uint16_t)0xFFFE : t.w[x - 1];
+    if (k == T_LBRACE) {
+        bool section = false;
+        if (!first && !((t.first >> (x - 1)) & 1u) && t.tb + x >= 5) section = t.w[x - 2] == T_DOT_SECTION;
+        return (!ptx_opens_operand(prev) && !section) ? 1 : 0;
+    }
+    return (prev == T_SEMI || prev == T_COLON || prev == T_LBRACE || prev == T_RBRACE) ? -1 : 0;
+}
+// the same for the token just in front of the thread's first (window index 2), whose own left context is w[0..1]
+PTX_HD inline int sx_brace_before(const SxThread& t) {
+    return t.tb ? sx_brace(t, 2) : 0;
+}
+
+// step 1: the thread's aggregate (flag = a module begins among its tokens; depths counted from the last such begin)
+PTX_HD inline PtxSeg3 sx_aggregate(const SxThread& t) {
+    if (t.fast)
+        return PtxSeg3{(int32_t)sx_popc(t.braces & SX_LOW) - (int32_t)sx_popc(t.braces & ~SX_LOW),
+                       (int32_t)sx_popc(t.parens & SX_LOW) - (int32_t)sx_popc(t.parens & ~SX_LOW), 0};
+    PtxSeg3 v{0, 0, 0};
+#pragma unroll
+    for (uint32_t k = 0; k < SX_ITEMS; k++) {
+        if (k >= t.n_valid) break;
+        uint32_t x = 3 + k;
+        if ((t.first >> x) & 1u) v = PtxSeg3{0, 0, 1};
+        v.scope += sx_brace(t, x);
+        v.paren += t.w[x] == T_LPAREN ? 1 : t.w[x] == T_RPAREN ? -1 : 0;
+    }
+    return v;
+}
+
+// step 2: with the depths in front of the thread's first token: where units start, as a spread mask; the scope depth
+// behind a module's last token goes to mod_final_scope.  The rule, for a token that does not begin a module: at the
+// top level (scope depth 0, outside parentheses) a directive keyword that does not continue a run of linking keywords;
+// inside a scope, the token after ';', ':' or a scope brace, and a scope brace itself.
+PTX_HD inline uint32_t sx_decide_slow(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before, uint16_t* codes);
+PTX_HD inline uint32_t sx_decide(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before) {
+    if (!t.fast) {
+        uint16_t codes[SX_ITEMS];
+        sx_decide_slow(a, t, before, codes);
+        uint32_t starts = 0;
+#pragma unroll
+        for (uint32_t k = 0; k < SX_ITEMS; k++) starts |= (codes[k] ? 1u : 0u) << sx_pos(k);
+        return starts;
+    }
+    const uint32_t plus = t.braces & SX_LOW, minus = (t.braces >> 4) & SX_LOW;
+    const uint32_t in_scope = (t.marks & SX_LOW) | plus | minus | sx_up(plus | minus) | t.brace_before;
+    if (before.scope - (int32_t)sx_popc(minus) > 0) return in_scope;                        // inside a scope all the way
+    const uint32_t dirs = (t.marks >> 4) & SX_LOW;
+    if (before.scope <= 0 && !plus && !dirs) return 0;                                     // top level all the way, no directive keyword
+    // a bit of both: token by token
+    int32_t sd = before.scope, pd = before.paren;
+    uint32_t starts = 0;
+#pragma unroll
+    for (uint32_t k = 0; k < SX_ITEMS; k++) {
+        const uint32_t bit = 1u << sx_pos(k);
+        if (sd > 0) {
+            starts |= in_scope & bit;
+        } else if (sd == 0 && pd == 0 && (dirs & bit)) {
+            const uint16_t prev = PTX_KL_KIND(a.kinds[t.tb + k - 1]);       // fast threads have tb > 0
+            if (!(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak)) starts |= bit;
+        }
+        sd += (int32_t)((plus >> sx_pos(k)) & 1u) - (int32_t)((minus >> sx_pos(k)) & 1u);
+        pd += (int32_t)((t.parens >> sx_pos(k)) & 1u) - (int32_t)((t.parens >> (sx_pos(k) + 4u)) & 1u);
+    }
+    return starts;
+}
+
+// the same token by token from the kinds: the code of every token (0 = no unit starts here, else 1 + clamped scope
+// depth in front of it, bit 15 = first token of a module)
+PTX_HD inline uint32_t sx_decide_slow(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before, uint16_t* codes) {
+    int32_t sd = before.scope, pd = before.paren;
+    uint32_t count = 0;
+    int bc_prev = sx_brace_before(t);
+#pragma unroll
+    for (uint32_t k = 0; k < SX_ITEMS; k++) {
+        codes[k] = 0;
+        if (k >= t.n_valid) continue;
+        uint32_t x = 3 + k, j = t.tb + k;
+        int bc = sx_brace(t, x);
+        if ((t.first >> x) & 1u) {
+            if (j) a.mod_final_scope[ptx_upper_bound_u32(a.mtb, a.n_modules, j - 1) - 1] = sd;
+            codes[k] = (uint16_t)(1u | 0x8000u);
+            sd = pd = 0;
+        } else {
+            uint16_t kk = t.w[x], prev = t.w[x - 1];
+            bool start;
+            if (sd <= 0) {
+                // top level: a directive keyword outside parentheses that does not continue a run of linking keywords
+                start = sd == 0 && pd == 0 && ptx_is_directive_start(kk) && !(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak);
+            } else {
+                start = prev == T_SEMI || prev == T_COLON || bc != 0 || bc_prev != 0;
+            }
+            uint32_t clamped = sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
+            codes[k] = start ? (uint16_t)(1u + clamped) : (uint16_t)0;
+        }
+        count += codes[k] ? 1u : 0u;
+        sd += bc;
+        pd += t.w[x] == T_LPAREN ? 1 : t.w[x] == T_RPAREN ? -1 : 0;
+        bc_prev = bc;
+        if (j + 1 == a.n_tokens) a.mod_final_scope[ptx_upper_bound_u32(a.mtb, a.n_modules, j) - 1] = sd;
+    }
+    return count;
+}
+
+// step 3: with the number of unit starts in front of the thread's first token: the rows of the unit table
+PTX_HD inline void sx_write(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before, uint32_t starts, uint32_t units_before) {
+    uint32_t u = units_before;
+    if (t.fast) {
+        const uint32_t plus = t.braces & SX_LOW, minus = (t.braces >> 4) & SX_LOW;
+        while (starts) {
+            const uint32_t pos = sx_lowest(starts), below = (1u << pos) - 1u;
+            starts &= starts - 1u;
+            const int32_t sd = before.scope + (int32_t)sx_popc(plus & below) - (int32_t)sx_popc(minus & below);
+            a.ustart[u] = t.tb + (pos >> 3) * 4u + (pos & 3u);
+            a.udepth[u] = sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
+            u++;
+        }
+        return;
+    }
+    if (!t.n_valid) return;
+    uint16_t codes[SX_ITEMS];
+    sx_decide_slow(a, t, before, codes);
+#pragma unroll
+    for (uint32_t k = 0; k < SX_ITEMS; k++) {
+        uint32_t code = codes[k];
+        if (!code) continue;
+        uint32_t j = t.tb + k;
+        a.ustart[u] = j;
+        a.udepth[u] = ((code & 0x7FFFu) - 1u) | ((code & 0x8000u) ? 0x80000000u : 0u);
+        if (code & 0x8000u) a.mub[ptx_upper_bound_u32(a.mtb, a.n_modules, j) - 1] = u;
+        u++;
+    }
+    if (t.tb + t.n_valid == a.n_tokens) a.counters->n_units = u;
+}

@@ -257,6 +257,22 @@ __device__ inline T shfl_up_words(T v, int d) {
     for (size_t i = 0; i < sizeof(T) / 4; i++) b.w[i] = __shfl_up_sync(0xFFFFFFFFu, a.w[i], d);
     return b.t;
 }
+template <class T>
+__device__ inline T shfl_down_words(T v, int d) {
+    union { T t; uint32_t w[sizeof(T) / 4]; } a, b;
+    a.t = v;
+#pragma unroll
+    for (size_t i = 0; i < sizeof(T) / 4; i++) b.w[i] = __shfl_down_sync(0xFFFFFFFFu, a.w[i], d);
+    return b.t;
+}
+template <class T>
+__device__ inline T shfl_words(T v, int src) {
+    union { T t; uint32_t w[sizeof(T) / 4]; } a, b;
+    a.t = v;
+#pragma unroll
+    for (size_t i = 0; i < sizeof(T) / 4; i++) b.w[i] = __shfl_sync(0xFFFFFFFFu, a.w[i], src);
+    return b.t;
+}
 template <class T, class Op>
 __device__ inline void block_scan(T v, Op op, T identity, T* warp_tot, T& incl, T& excl) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -307,6 +323,163 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_apply_kernel(size_t n, Ld l
 #pragma unroll
     for (int k = 0; k < SCAN_ITEMS; k++)
         if (base + k < n) st(base + k, op(prefix, vals[k]));
+}
+
+// ---- stage B in one pass (ptx_struct_tile.h).  Tiles are handed out in order by an atomic counter, so a tile only
+// ever waits for tiles that are already running or done.  Every tile publishes the aggregate of its tokens, then looks
+// back along the tiles before it until it meets one whose whole prefix is known (or, for the depths, one in which a
+// module begins: nothing before that matters), and publishes its own prefix.  A published value is self-contained:
+// 64-bit words with the state in the top two bits (0 nothing yet, 1 the tile's own aggregate, 2 the prefix up to
+// and including the tile); the depths take two words, which a reader accepts only when both carry the same state.
+// Waiting is bounded: a tile that waits too long sets the abort word, every other waiter sees it and leaves, and the
+// host reads struct_abort with the counters.
+struct StructDesc {
+    unsigned long long depth0, depth1, count, pad;
+};
+constexpr unsigned long long SXD_AGG = 1ull << 62, SXD_PREFIX = 2ull << 62, SXD_STATE = 3ull << 62;
+constexpr uint32_t SX_WAIT_LIMIT = 1u << 22;
+
+__device__ inline unsigned long long sx_ld(const unsigned long long* p) { return *(const volatile unsigned long long*)p; }
+__device__ inline void sx_st(unsigned long long* p, unsigned long long v) { *(volatile unsigned long long*)p = v; }
+__device__ inline void sx_publish_depth(StructDesc* d, unsigned long long state, PtxSeg3 v) {
+    sx_st(&d->depth0, state | ((unsigned long long)(v.flag ? 1u : 0u) << 32) | (uint32_t)v.scope);
+    sx_st(&d->depth1, state | (uint32_t)v.paren);
+}
+// false = gave up (abort set by this or another tile)
+__device__ inline bool sx_read_depth(const StructDesc* d, uint32_t* ctl, unsigned long long& state, PtxSeg3& v) {
+    for (uint32_t spin = 0;; spin++) {
+        unsigned long long a = sx_ld(&d->depth0), b = sx_ld(&d->depth1);
+        if ((a & SXD_STATE) && (a & SXD_STATE) == (b & SXD_STATE)) {
+            state = a & SXD_STATE;
+            v.scope = (int32_t)(uint32_t)a;
+            v.flag = (int32_t)((a >> 32) & 1u);
+            v.paren = (int32_t)(uint32_t)b;
+            return true;
+        }
+        if ((spin & 63u) == 63u && *(volatile uint32_t*)&ctl[1]) return false;
+        if (spin >= SX_WAIT_LIMIT) { atomicExch(&ctl[1], 1u); return false; }
+        __nanosleep(40);
+    }
+}
+__device__ inline bool sx_read_count(const StructDesc* d, uint32_t* ctl, unsigned long long& state, uint32_t& v) {
+    for (uint32_t spin = 0;; spin++) {
+        unsigned long long a = sx_ld(&d->count);
+        if (a & SXD_STATE) { state = a & SXD_STATE; v = (uint32_t)a; return true; }
+        if ((spin & 63u) == 63u && *(volatile uint32_t*)&ctl[1]) return false;
+        if (spin >= SX_WAIT_LIMIT) { atomicExch(&ctl[1], 1u); return false; }
+        __nanosleep(40);
+    }
+}
+
+__global__ void __launch_bounds__(SX_THREADS) structure_kernel(PtxStructArgs a, uint32_t n_tiles, StructDesc* desc, uint32_t* ctl) {
+    __shared__ PtxSeg3 warp_depth[SX_THREADS / 32];
+    __shared__ uint32_t warp_count[SX_THREADS / 32];
+    __shared__ uint32_t s_tile, s_units_before, s_ok, s_has_first;
+    __shared__ PtxSeg3 s_before;
+    __shared__ uint8_t s_table[512];
+    const int lane = threadIdx.x & 31;
+    const SegDepthOp op;
+    for (uint32_t k = threadIdx.x; k < 512; k += SX_THREADS) s_table[k] = (uint8_t)sx_flags(k);
+    for (;;) {
+        __syncthreads();                                   // the shared words of the tile before are no longer read
+        if (threadIdx.x == 0) {
+            const uint32_t tile = atomicAdd(&ctl[0], 1u);
+            s_tile = tile;
+            s_ok = *(volatile uint32_t*)&ctl[1] ? 0u : 1u;  // aborted: later tiles do nothing
+            s_has_first = tile < n_tiles && sx_tile_has_first(a, tile * SX_TILE) ? 1u : 0u;
+        }
+        __syncthreads();
+        const uint32_t tile = s_tile;
+        if (tile >= n_tiles) return;
+        if (!s_ok) {
+            if (threadIdx.x == 0) a.counters->struct_abort = 1;
+            return;
+        }
+        SxThread t;
+        sx_load(a, tile * SX_TILE + threadIdx.x * SX_ITEMS, t, s_table, s_has_first != 0);
+        PtxSeg3 incl, excl;
+        block_scan(sx_aggregate(t), op, PtxSeg3{0, 0, 0}, warp_depth, incl, excl);
+        if (threadIdx.x == SX_THREADS - 1) s_before = incl;         // the tile's aggregate, for warp 0
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            const PtxSeg3 agg = s_before;
+            __syncwarp();
+            PtxSeg3 before{0, 0, 0};
+            bool ok = true;
+            if (tile == 0) {
+                if (lane == 0) sx_publish_depth(&desc[0], SXD_PREFIX, agg);
+            } else {
+                if (lane == 0) sx_publish_depth(&desc[tile], SXD_AGG, agg);
+                // windows of 32 earlier tiles, nearest first; lane 0 holds the nearest tile of the window
+                for (int64_t back = (int64_t)tile - 1; ok;) {
+                    int64_t mine = back - lane;
+                    unsigned long long state = SXD_PREFIX;
+                    PtxSeg3 v{0, 0, 0};
+                    bool got = mine < 0 ? true : sx_read_depth(&desc[mine], ctl, state, v);
+                    if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
+                    // the chain ends at the nearest tile with a known prefix or a module begin (or before tile 0)
+                    unsigned ends = __ballot_sync(0xFFFFFFFFu, mine < 0 || state == SXD_PREFIX || v.flag);
+                    int last = ends ? __ffs(ends) - 1 : 31;
+                    if (lane > last || mine < 0) v = PtxSeg3{0, 0, 0};
+                    // ordered reduction: lane 0 ends up with op(v[last], ..., v[1], v[0])
+#pragma unroll
+                    for (int d = 1; d < 32; d <<= 1) {
+                        PtxSeg3 y = shfl_down_words(v, d);
+                        if (lane + d < 32) v = op(y, v);
+                    }
+                    v = shfl_words(v, 0);
+                    before = op(v, before);
+                    if (ends) break;
+                    back -= 32;
+                }
+                if (ok && lane == 0) sx_publish_depth(&desc[tile], SXD_PREFIX, op(before, agg));
+            }
+            if (lane == 0) { s_before = before; if (!ok) s_ok = 0; }
+        }
+        __syncthreads();
+        if (!s_ok) {
+            if (threadIdx.x == 0) a.counters->struct_abort = 1;
+            return;
+        }
+        const PtxSeg3 before = op(s_before, excl);
+        const uint32_t starts = sx_decide(a, t, before);
+        uint32_t cincl, cexcl;
+        block_scan((uint32_t)__popc(starts), AddOp(), 0u, warp_count, cincl, cexcl);
+        if (threadIdx.x == SX_THREADS - 1) s_units_before = cincl;
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            const uint32_t agg = s_units_before;
+            __syncwarp();
+            uint32_t before = 0;
+            bool ok = true;
+            if (tile == 0) {
+                if (lane == 0) sx_st(&desc[0].count, SXD_PREFIX | agg);
+            } else {
+                if (lane == 0) sx_st(&desc[tile].count, SXD_AGG | agg);
+                for (int64_t back = (int64_t)tile - 1; ok;) {
+                    int64_t mine = back - lane;
+                    unsigned long long state = SXD_PREFIX;
+                    uint32_t v = 0;
+                    bool got = mine < 0 ? true : sx_read_count(&desc[mine], ctl, state, v);
+                    if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
+                    unsigned ends = __ballot_sync(0xFFFFFFFFu, mine < 0 || state == SXD_PREFIX);
+                    int last = ends ? __ffs(ends) - 1 : 31;
+                    if (lane > last || mine < 0) v = 0;
+                    before += __reduce_add_sync(0xFFFFFFFFu, v);
+                    if (ends) break;
+                    back -= 32;
+                }
+                if (ok && lane == 0) sx_st(&desc[tile].count, SXD_PREFIX | (uint32_t)(before + agg));
+            }
+            if (lane == 0) { s_units_before = before; if (!ok) s_ok = 0; }
+        }
+        __syncthreads();
+        if (!s_ok) {
+            if (threadIdx.x == 0) a.counters->struct_abort = 1;
+            return;
+        }
+        sx_write(a, t, before, starts, s_units_before + cexcl);
+    }
 }
 
 // ---- counting sort of unit indices by a 12-bit key: block-local histograms / ranks in shared memory, one global
@@ -617,6 +790,22 @@ struct CudaBackend {
         prof_begin(name);
         cudaFuncSetAttribute(lex_emit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sizeof(PtxLexEmitShared));
         lex_emit_kernel<<<resident_blocks((const void*)lex_emit_kernel, sizeof(PtxLexEmitShared), n_tiles), 256, sizeof(PtxLexEmitShared), ctx->stream>>>(a, (uint32_t)n_tiles);
+        prof_end();
+        ctx->launches++;
+    }
+    void fail(const char* why) {
+        if (!ctx->failed) snprintf(ctx->err, sizeof ctx->err, "%s", why);
+        ctx->failed = true;
+    }
+    void structure(const char* name, const PtxStructArgs& a) {
+        if (ctx->failed || a.n_tokens == 0) return;
+        const size_t n_tiles = ((size_t)a.n_tokens + SX_TILE - 1) / SX_TILE;
+        StructDesc* desc = (StructDesc*)alloc(sizeof(StructDesc) * n_tiles + 256);
+        if (!desc) return;
+        uint32_t* ctl = (uint32_t*)(desc + n_tiles);      // [0] next tile, [1] abort
+        prof_begin(name);
+        cudaMemsetAsync(desc, 0, sizeof(StructDesc) * n_tiles + 256, ctx->stream);
+        structure_kernel<<<resident_blocks((const void*)structure_kernel, 0, n_tiles), SX_THREADS, 0, ctx->stream>>>(a, (uint32_t)n_tiles, desc, ctl);
         prof_end();
         ctx->launches++;
     }

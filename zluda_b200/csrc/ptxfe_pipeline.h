@@ -247,6 +247,7 @@ struct PtxCounters {
     uint32_t n_listed;
     uint32_t n_classes;         // statement classes met so far in this batch (all slices)
     uint32_t n_sig_words;       // words of the signature pool in use
+    uint32_t struct_abort;      // the structure pass ran into its wait limit (its results are void)
 };
 
 PTX_HD inline uint32_t ptx_upper_bound_u32(const uint32_t* a, uint32_t n, uint32_t x) {
@@ -273,7 +274,6 @@ struct PtxWork {
     uint32_t* mod_tok_begin = nullptr;     // [n_modules + 1]
     bool first_slice = true;               // the class store is emptied before the first slice of a batch
     uint16_t* kinds = nullptr;             // [n_tokens] tokens[i].kind | min(tokens[i].len, 127) << 9
-    uint8_t* tfirst = nullptr;             // [n_tokens] 1 = first token of a module
     int32_t* mod_final_scope = nullptr;    // [n_modules] scope depth behind the module's last token
     uint32_t* unit_start = nullptr;        // [n_units + 1]
     uint32_t* unit_depth = nullptr;        // [n_units]  scope depth in front of the unit | module-first << 31
@@ -319,6 +319,8 @@ struct SegDepthOp {
 //   template <class F> void pf(const char* name, size_t n, F f);                f(i) for i in [0, n)
 //   template <class T, class Op, class Ld, class St> void scan(const char* name, size_t n, Ld ld, St st, Op op, T identity);
 //        inclusive scan: st(i, op(ld(0), ..., ld(i)))
+//   void structure(const char* name, const PtxStructArgs& a);                    stage B in one pass (ptx_struct_tile.h)
+//   void fail(const char* why);                                                  the batch cannot be finished
 //   void sort_by_key(const char* name, size_t n, const uint16_t* key, uint32_t* order);
 //        order = a permutation of 0..n-1 that puts equal keys next to each other, either over the whole range or
 //        inside consecutive segments of the backend's choice (keys < PTX_SORT_BUCKETS; order inside a group is free)
@@ -444,7 +446,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     bk.download(&host_counters, counters, sizeof(PtxCounters));
     const uint32_t n_tokens = host_counters.n_tokens, n_lexerrs = host_counters.n_lexerrs;
     PtxToken* tokens = w.tokens = (PtxToken*)bk.alloc(sizeof(PtxToken) * (size_t)(n_tokens + 1));
-    uint16_t* kinds = w.kinds = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_tokens + 8));   // the kinds alone, for the passes that read nothing else
+    uint16_t* kinds = w.kinds = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_tokens + 32));   // the kinds alone, for the passes that read nothing else
     uint32_t* lexerrs = w.lexerrs = (uint32_t*)bk.alloc(sizeof(uint32_t) * 2 * (size_t)(n_lexerrs + 1));
     // A5: one thread per token: length, kind (identifiers that spell an opcode, modifier or directive word get that
     // kind), literal code; written to the token's final place
@@ -482,20 +484,9 @@ PTX_HD inline bool ptx_is_directive_start(uint16_t k) {
            k == T_MOD_global || k == T_MOD_const || k == T_MOD_shared || k == T_DOT_FILE || k == T_DOT_SECTION;
 }
 
-// scope delta of token i: +1 for a '{' that opens a scope, -1 for a '}' that closes one, 0 otherwise (also for the
-// braces of vector operands, initialisers and .section bodies, told apart by two tokens of left context)
-PTX_HD inline int ptx_brace_class(const uint16_t* kinds, const uint8_t* tfirst, size_t i) {
-    uint16_t k = PTX_KL_KIND(kinds[i]);
-    if (k != T_LBRACE && k != T_RBRACE) return 0;
-    bool first = tfirst[i] != 0;
-    uint16_t prev = first ? (uint16_t)0xFFFE : PTX_KL_KIND(kinds[i - 1]);
-    if (k == T_LBRACE) {
-        bool section = false;
-        if (!first && i >= 2 && !tfirst[i - 1]) section = PTX_KL_KIND(kinds[i - 2]) == T_DOT_SECTION;
-        return (!ptx_opens_operand(prev) && !section) ? 1 : 0;
-    }
-    return (prev == T_SEMI || prev == T_COLON || prev == T_LBRACE || prev == T_RBRACE) ? -1 : 0;
-}
+// Scope delta of a token: +1 for a '{' that opens a scope, -1 for a '}' that closes one, 0 otherwise (also for the
+// braces of vector operands, initialisers and .section bodies, told apart by two tokens of left context): sx_brace.
+#include "ptx_struct_tile.h"
 
 template <class BK>
 inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, uint32_t mode) {
@@ -503,77 +494,29 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
     const uint16_t* kinds = w.kinds;
     const uint32_t* mtb = w.mod_tok_begin;
     const PtxModuleResult* results = w.results;
-    uint8_t* tfirst = w.tfirst = (uint8_t*)bk.alloc((size_t)n_tokens + 16);
-    // per token: 0 = no unit starts here; else 1 + scope depth in front of it (clamped), bit 15 = first token of a module
-    uint16_t* sd16 = (uint16_t*)bk.alloc(sizeof(uint16_t) * ((size_t)n_tokens + 2));
     int32_t* mod_final_scope = w.mod_final_scope = (int32_t*)bk.alloc(sizeof(int32_t) * (n_modules + 1));
     w.mod_unit_begin = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 2));
     PtxCounters* counters = w.counters;
     uint32_t* mod_skip = w.mod_skip = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 1));
-    bk.zero(tfirst, (size_t)n_tokens + 16);
     bk.zero(mod_final_scope, sizeof(int32_t) * (n_modules + 1));
-    // B0: mark the first token of every module.  A module with a lex error is not parsed unless only its errors
+    // B0: a module with a lex error is not parsed unless only its errors
     // are wanted (lib.rs:392-411 vs 447-449, 487-489)
-    bk.pf("mark_module_first", n_modules, [=] PTX_HD(size_t m) {
-        if (mtb[m] < mtb[m + 1]) tfirst[mtb[m]] = 1;
+    bk.pf("mark_module_skip", n_modules, [=] PTX_HD(size_t m) {
         bool lexerr = results[m].lexerr_end > results[m].lexerr_begin;
         mod_skip[m] = (mtb[m] == mtb[m + 1] || (lexerr && mode != 2)) ? 1u : 0u;
     });
-    // B1: one segmented scan of (scope, paren) depth, restarting at every module.  Nothing per token is kept of it:
-    // as soon as the depth behind token i is known, the scan decides whether a unit starts at token i + 1 and
-    // leaves two bytes for it; the depth behind a module's last token goes to mod_final_scope.
-    bk.template scan<PtxSeg3>(
-        "scan_depth", n_tokens,
-        [=] PTX_HD(size_t i) {
-            PtxSeg3 v;
-            uint16_t k = PTX_KL_KIND(kinds[i]);
-            v.scope = ptx_brace_class(kinds, tfirst, i);
-            v.paren = k == T_LPAREN ? 1 : k == T_RPAREN ? -1 : 0;
-            v.flag = tfirst[i] ? 1 : 0;
-            return v;
-        },
-        [=] PTX_HD(size_t i, PtxSeg3 v) {
-            if (i == 0) sd16[0] = (uint16_t)(1u | 0x8000u);     // token 0 is the first token of a module
-            size_t j = i + 1;
-            bool last_of_module = j == n_tokens || tfirst[j] != 0;
-            if (last_of_module) mod_final_scope[ptx_upper_bound_u32(mtb, n_modules, (uint32_t)i) - 1] = v.scope;
-            if (j == n_tokens) return;
-            if (tfirst[j]) { sd16[j] = (uint16_t)(1u | 0x8000u); return; }
-            int32_t sd = v.scope, pd = v.paren;
-            uint16_t k = PTX_KL_KIND(kinds[j]), prev = PTX_KL_KIND(kinds[i]);
-            bool start;
-            if (sd <= 0) {
-                // top level: a directive keyword outside parentheses that does not continue a run of linking keywords
-                // (the token after a function's closing brace or after a directive's terminator is not a start by
-                // itself: a well-formed module continues with a directive keyword there)
-                start = sd == 0 && pd == 0 && ptx_is_directive_start(k) &&
-                        !(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak);
-            } else {
-                start = prev == T_SEMI || prev == T_COLON || ptx_brace_class(kinds, tfirst, j) != 0 || ptx_brace_class(kinds, tfirst, i) != 0;
-            }
-            uint32_t clamped = sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
-            sd16[j] = start ? (uint16_t)(1u + clamped) : (uint16_t)0;
-        },
-        SegDepthOp(), PtxSeg3{0, 0, 0});
-    // B2: number the unit starts; the scan itself writes each unit's start token and depth (no per-token index is
-    // kept), the first unit of every module, and the total
-    uint32_t* ustart = w.unit_start = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_tokens + 2));   // at most one unit per token
+    // B1: one pass over the token kinds: (scope, paren) depth restarting at every module, the unit starts, their
+    // numbering and the unit table (at most one unit per token); nothing per token is kept of it
+    uint32_t* ustart = w.unit_start = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_tokens + 2));
     uint32_t* udepth = w.unit_depth = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_tokens + 2));
     uint32_t* mub = w.mod_unit_begin;
-    bk.pf("reset_unit_total", 1, [=] PTX_HD(size_t) { counters->n_units = 0; });
-    bk.template scan<uint32_t>("scan_unit_index", n_tokens, [=] PTX_HD(size_t i) { return sd16[i] ? 1u : 0u; },
-                               [=] PTX_HD(size_t i, uint32_t v) {
-                                   uint32_t code = sd16[i];
-                                   if (code) {
-                                       uint32_t u = v - 1;
-                                       ustart[u] = (uint32_t)i;
-                                       udepth[u] = ((code & 0x7FFFu) - 1u) | ((code & 0x8000u) ? 0x80000000u : 0u);
-                                       if (code & 0x8000u) mub[ptx_upper_bound_u32(mtb, n_modules, (uint32_t)i) - 1] = u;
-                                   }
-                                   if (i + 1 == n_tokens) counters->n_units = v;
-                               },
-                               AddOp(), 0u);
+    bk.pf("reset_unit_total", 1, [=] PTX_HD(size_t) { counters->n_units = 0; counters->struct_abort = 0; });
+    bk.structure("structure", PtxStructArgs{kinds, n_tokens, mtb, n_modules, mod_final_scope, ustart, udepth, mub, counters});
     bk.download(&host_counters, counters, sizeof(PtxCounters));
+    if (host_counters.struct_abort) {
+        bk.fail("the structure pass gave up waiting for an earlier tile");
+        host_counters.n_units = 0;
+    }
     const uint32_t n_units = host_counters.n_units;
     // modules without tokens begin where the next module with tokens begins; mub[n_modules] = n_units
     bk.pf("module_unit_ranges", n_modules + 1, [=] PTX_HD(size_t m) {
