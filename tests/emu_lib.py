@@ -73,11 +73,7 @@ class Emu:
 def load():
     global _cached
     if _cached is None:
-        src = os.path.join(ROOT, "tests", "emu", "ptxfe_emu.cpp")
-        csrc = os.path.join(ROOT, "zluda_b200", "csrc")
-        deps = [src] + [os.path.join(csrc, f) for f in os.listdir(csrc) if f.endswith(".h")]
-        deps += [os.path.join(csrc, "gen", f) for f in os.listdir(os.path.join(csrc, "gen"))]
-        if not os.path.exists(SO) or any(os.path.getmtime(d) > os.path.getmtime(SO) for d in deps):
-            subprocess.check_call(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", SO, src])
+        import build_helpers
+        build_helpers.build()       # only what is out of date
         _cached = Emu(ctypes.CDLL(SO))
     return _cached

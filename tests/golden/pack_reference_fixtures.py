@@ -6,7 +6,7 @@ Every `ptx` test of the reference enters through parse_module_checked(text).unwr
 files are test vectors (inputs), not source code.  The pass tests hold input and expected output in one file, split at
 "// %%% output %%%": only the input part is a parser input.  Packed form: zlib(JSON list of {name, text (latin-1),
 sha256 of the oracle's dump per mode}).  Run from the repository root with the reference mounted:
-    python tests/golden/pack_reference_fixtures.py [/root/reference]
+    python tests/golden/pack_reference_fixtures.py <path of the reference checkout>
 """
 import glob
 import hashlib
@@ -21,7 +21,9 @@ import oracle_lib  # noqa: E402
 
 
 def main():
-    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("PTXFE_REFERENCE", "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    ref = sys.argv[1]
     o = oracle_lib.load()
     rows = []
     for f in sorted(glob.glob(os.path.join(ref, "**", "*.ptx"), recursive=True)):

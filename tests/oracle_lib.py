@@ -84,8 +84,7 @@ _cached = None
 def load():
     global _cached
     if _cached is None:
-        src = os.path.join(ROOT, "oracle", "ptx_oracle.cpp")
-        if not os.path.exists(SO) or (os.path.exists(src) and os.path.getmtime(src) > os.path.getmtime(SO)):
-            subprocess.check_call(["make", "-C", os.path.join(ROOT, "oracle")], stdout=subprocess.DEVNULL)
+        import build_helpers
+        build_helpers.build()       # only what is out of date
         _cached = Oracle(ctypes.CDLL(SO))
     return _cached

@@ -14,7 +14,7 @@ import pytest
 
 from oracle_lib import CHECKED, ERRORS_ONLY, UNCHECKED
 
-REFERENCE = os.environ.get("PTXFE_REFERENCE", "/root/reference")
+import reference_fixtures
 
 HEADER = ".version 6.5\n.target sm_30\n.address_size 64\n"
 
@@ -301,36 +301,32 @@ def test_lexer_longest_match(oracle):
 
 
 # ------------------------------------------------------------------ the reference's accept corpus
-def _fixtures():
-    if not os.path.isdir(REFERENCE):
-        return []
-    files = sorted(glob.glob(os.path.join(REFERENCE, "**", "*.ptx"), recursive=True))
-    # spirv_fail/ and spirv_build/ are not referenced by any reference test
-    return [f for f in files if "spirv_fail" not in f and "spirv_build" not in f]
-
-
-@pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="reference checkout not mounted")
 def test_every_reference_fixture_is_accepted(oracle):
-    files = _fixtures()
-    assert len(files) >= 240
-    for f in files:
-        text = open(f, "rb").read()
-        if "/pass/test/" in f:
-            # the pass tests parse the part before this marker (ptx/src/pass/test/mod.rs:14-36)
-            text = text.split(b"// %%% output %%%")[0].strip()
+    """Every `ptx` test of the reference feeds its input to parse_module_checked(..).unwrap() (ptx/src/test/mod.rs:32-75;
+    the pass tests parse the part before their output marker, ptx/src/pass/test/mod.rs:14-36).  spirv_fail/ and
+    spirv_build/ are not referenced by any reference test."""
+    import hashlib
+    rows = reference_fixtures.rows()
+    assert len(rows) >= 240
+    for r in rows:
+        text = r["text"].encode("latin-1")
         st, dump = oracle.parse(text, CHECKED)
-        assert st == 0, (f, dump[-600:])
+        if "spirv_fail" not in r["name"] and "spirv_build" not in r["name"]:
+            assert st == 0, (r["name"], dump[-600:])
+        assert (st == 0) == r["accepted"], r["name"]
+        assert hashlib.sha256(dump.encode()).hexdigest() == r["sha256"][0], r["name"]
     assert oracle.schema_ok()
 
 
-@pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="reference checkout not mounted")
 def test_reference_fixture_values(oracle):
     """Spot values that the reference's LLVM goldens depend on (ptx/src/test/ll/*.ll)."""
+    texts = reference_fixtures.texts()
+
     def dump_of(name):
-        return oracle.parse(open(os.path.join(REFERENCE, "ptx/src/test/spirv_run", name), "rb").read())[1]
+        return oracle.parse(texts["ptx/src/test/spirv_run/" + name])[1]
     assert "Imm(S64(-" in dump_of("constant_negative.ptx")
     assert "Imm(F32(bits=0x" in dump_of("constant_f32.ptx")
     d = dump_of("global_array_f32.ptx")
     assert "Array(None, F32, [" in d and "Imm(F32(bits=0x" in d
     assert "CreatePolicyFractional" in dump_of("createpolicy.ptx")
-    assert 'VecMember("%ntid", 0)' in oracle.parse(open(os.path.join(REFERENCE, "ptx/src/test/operands.ptx"), "rb").read())[1]
+    assert 'VecMember("%ntid", 0)' in oracle.parse(texts["ptx/src/test/operands.ptx"])[1]

@@ -15,7 +15,7 @@ import cases
 import emu_lib
 from zluda_b200 import corpus
 
-REFERENCE = os.environ.get("PTXFE_REFERENCE", "/root/reference")
+import reference_fixtures
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
@@ -193,14 +193,8 @@ def test_mutated_modules(oracle, emu):
     assert_parity(oracle, emu, texts)
 
 
-@pytest.mark.skipif(not os.path.isdir(REFERENCE), reason="reference checkout not mounted")
 def test_reference_fixtures(oracle, emu):
-    texts = []
-    for f in sorted(glob.glob(os.path.join(REFERENCE, "**", "*.ptx"), recursive=True)):
-        t = open(f, "rb").read()
-        if "/pass/test/" in f:
-            t = t.split(b"// %%% output %%%")[0].strip()
-        texts.append(t)
+    texts = list(reference_fixtures.texts().values())
     assert len(texts) >= 240
     assert_parity(oracle, emu, texts)
 

@@ -1,5 +1,6 @@
-"""Build step of the package: generate the tables, compile the CUDA library for sm_100a (in-tree), and the test-side
-helpers (CPU oracle, host emulation backend).  nvcc cross-compiles without a GPU.
+"""Build step of the package: generate the tables, compile the CUDA library for sm_100a (in-tree) and the synthetic
+corpus generator.  nvcc cross-compiles without a GPU.  (The test-side helpers, the CPU oracle and the host emulation
+backend, are built by tests/build_helpers.py.)
 
     python -m zluda_b200.build            build everything that is out of date
     python -m zluda_b200.build --force
@@ -35,7 +36,7 @@ def _run(cmd, **kw):
 
 def generate():
     g = os.path.join(PKG, "grammar")
-    _run([sys.executable, os.path.join(g, "gen_tables.py"), "--out", os.path.join(CSRC, "gen"), "--out", os.path.join(ROOT, "oracle", "gen")])
+    _run([sys.executable, os.path.join(g, "gen_tables.py"), "--out", os.path.join(CSRC, "gen")])
     _run([sys.executable, os.path.join(g, "gen_pow5.py"), "--out", os.path.join(CSRC, "gen")])
     _run([sys.executable, os.path.join(g, "gen_lex_tables.py"), "--out", os.path.join(CSRC, "gen")])
 
@@ -61,21 +62,10 @@ def build_corpus_generator(force=False):
         _run(["gcc", "-O2", "-fPIC", "-shared", "-o", CORPUS_LIB, src, "-lm"])
 
 
-def build_test_helpers(force=False):
-    _run(["make", "-C", os.path.join(ROOT, "oracle")] + (["-B"] if force else []))
-    emu_src = os.path.join(ROOT, "tests", "emu", "ptxfe_emu.cpp")
-    emu = os.path.join(ROOT, "tests", "emu", "libptxfe_emu.so")
-    deps = [emu_src] + [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".h")] + \
-           [os.path.join(CSRC, "gen", f) for f in os.listdir(os.path.join(CSRC, "gen"))]
-    if force or _newer(emu, deps):
-        _run(["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-pthread", "-o", emu, emu_src])
-
-
 def build(force=False):
     generate()
     log = build_library(force)
     build_corpus_generator(force)
-    build_test_helpers(force)
     return log
 
 
