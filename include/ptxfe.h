@@ -64,6 +64,9 @@ typedef struct ptxfe_stats {
     uint64_t n_class_capacity;   /* templates the store holds; classes beyond it are decoded unit by unit */
     uint64_t n_untemplated;      /* units that were decoded one by one */
     uint64_t n_signature_words, n_signature_capacity;
+    /* tokens that went through the single-thread recovery path: only the part of a damaged module from the top-level
+     * directive with the first damage to the module's end does */
+    uint64_t n_sequential_tokens;
 } ptxfe_stats;
 
 /* Create a context on CUDA device `device` (one stream, reusable device arenas, pinned result buffers). */

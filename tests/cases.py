@@ -215,6 +215,39 @@ def nested_damage_cases():
     return out
 
 
+def confined_damage_cases(n_funcs=12, n_instr=60):
+    """Modules of several functions that call one another, damaged in one place: everything in front of the damaged
+    top-level directive must keep its speculated units, only the tail goes through the sequential parser (some of the
+    damage is recovered inside its statement and needs no sequential parse at all).  Returns (text, fraction of the
+    text in front of the damaged directive) pairs."""
+    def func(i, extra=""):
+        lines = [".func (.param .b32 r) f%d(.param .b32 a)" % i, "{", ".reg .b32 %r<8>;", ".reg .pred %p<2>;", ".param .b32 pa;", ".param .b32 pr;"]
+        for k in range(n_instr):
+            lines.append("add.s32 %%r%d, %%r%d, %d;" % (k % 7 + 1, (k + 1) % 7 + 1, k))
+            if k % 17 == 5 and i > 0:
+                # a call of an earlier function (declared in front of the damage or behind it) and of an unknown one
+                lines.append("st.param.b32 [pa], %r1;")
+                lines.append("call (pr), f%d, (pa);" % (i // 2))
+                lines.append("call (pr), nowhere%d, (pa);" % i)
+            if k == n_instr // 2:
+                lines.append(extra)
+        lines += ["ret;", "}"]
+        return "\n".join(l for l in lines if l)
+    out = []
+    for damage in ("{", "(", ".reg .b32 %dup<2>; { add.s32 %r1, %r2, %r3;", "}", "} }", "foo bar {"):
+        for where in (0, n_funcs // 2, n_funcs - 1):
+            funcs = [func(i, damage if i == where else "") for i in range(n_funcs)]
+            text = HEADER + "\n".join(funcs) + "\n.global .u32 after;\n"
+            front = len(HEADER + "\n".join(funcs[:where]))
+            out.append((text, front / len(text)))
+    # a module cut off in the middle of its last function
+    funcs = [func(i) for i in range(n_funcs)]
+    text = HEADER + "\n".join(funcs)
+    cut = len(text) - len(funcs[-1]) // 2
+    out.append((text[:cut], len(HEADER + "\n".join(funcs[:-1])) / cut))
+    return out
+
+
 def negative_decimal_side_file(n=1000):
     """Module-level scalars initialised with NEGATIVE decimal floats and integers: the reference has no rule for '-' in
     front of a float literal (ptx_parser/src/lib.rs:366-377), so every float directive must be rejected the same way,

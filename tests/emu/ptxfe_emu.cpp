@@ -111,12 +111,16 @@ struct HostBackend {
         auto phase = [&](auto f) {
             if (reverse) { for (uint32_t t = SX_THREADS; t-- > 0;) f(t); } else { for (uint32_t t = 0; t < SX_THREADS; t++) f(t); }
         };
+        std::vector<uint32_t> marks(n_tiles + 1, 0);
+        pf("structure_mark", a.n_modules, [&](size_t m) { sx_mark_tiles(a, (uint32_t)m, marks.data(), 1); });
+        if (marks[n_tiles]) fail("structure: a mark behind the last tile");
         for (size_t tile = 0; tile < n_tiles; tile++) {
             std::vector<PtxSeg3> agg(SX_THREADS);
-            const bool has_first = sx_tile_has_first(a, (uint32_t)(tile * SX_TILE));
+            const bool has_first = marks[tile] != 0;
+            if (has_first != sx_tile_has_first(a, (uint32_t)(tile * SX_TILE))) fail("structure: tile marks and module table disagree");
             phase([&](uint32_t t) {
                 sx_load(a, (uint32_t)(tile * SX_TILE + t * SX_ITEMS), th[t], table, has_first);
-                agg[t] = sx_aggregate(th[t]);
+                agg[t] = sx_aggregate(a, th[t]);
             });
             for (uint32_t t = 0; t < SX_THREADS; t++) { before[t] = run; run = op(run, agg[t]); }
             phase([&](uint32_t t) { starts[t] = sx_decide(a, th[t], before[t]); });
@@ -125,7 +129,7 @@ struct HostBackend {
                 if (!th[t].fast) continue;
                 SxThread slow;
                 sx_load(a, th[t].tb, slow, table, true, false);
-                PtxSeg3 x = sx_aggregate(slow);
+                PtxSeg3 x = sx_aggregate(a, slow);
                 if (x.scope != agg[t].scope || x.paren != agg[t].paren || x.flag != agg[t].flag || sx_decide(a, slow, before[t]) != starts[t])
                     fail("structure: the bitwise case and the token-by-token case disagree");
             }
@@ -148,13 +152,18 @@ struct HostBackend {
             for (uint32_t i = 0, cnt = off[s + 1].a - off[s].a; i < cnt; i++) f(s, i, off[s].a + i);
         });
     }
-    template <class F, class G> void pf_segments2(const char* name, size_t n, const PtxPair* off, F f, G g) {
+    void emit_records(const char* name, size_t n, const PtxPair* off, const PtxEmitStep& e) {
         std::vector<std::pair<size_t, uint32_t>> later;
-        pf(name, n, [&](size_t s) {
-            for (uint32_t i = 0, cnt = off[s + 1].a - off[s].a; i < cnt; i++)
-                if (f(s, i, off[s].a + i)) later.push_back({s, i});
+        pf(name, n, [&](size_t u) {
+            const PtxEmitUnit info = e.unit(u);
+            for (uint32_t i = 0, cnt = off[u + 1].a - off[u].a; i < cnt; i++) {
+                uint32_t x = 0;
+                const int what = e.word(info, u, i, x);
+                if (what == PtxEmitStep::WRITE) e.words[off[u].a + i] = x;
+                else if (what == PtxEmitStep::SECOND_ROUND) later.push_back({u, i});
+            }
         });
-        for (auto& it : later) g(it.first, it.second, off[it.first].a + it.second);
+        for (auto& it : later) e.literal(e.unit(it.first), it.second, off[it.first].a + it.second);
     }
     void sort_by_key(const char*, size_t n, const uint16_t* key, uint32_t* order) {
         std::vector<uint32_t> cursor(PTX_SORT_BUCKETS + 1, 0);
@@ -217,7 +226,7 @@ char* emu_parse(const char* const* texts, const uint64_t* lens, uint32_t n, uint
     v.lexerrs = w.lexerrs;
     v.texts = texts;
     std::string all;
-    uint64_t seq = 0;
+    uint64_t seq = 0, seq_tokens = 0;
     for (uint32_t m = 0; m < n; m++) {
         int st;
         std::string by_records = ptxdump::dump_module(v, m, &st);
@@ -231,6 +240,7 @@ char* emu_parse(const char* const* texts, const uint64_t* lens, uint32_t n, uint
         all += by_records;
         all.push_back('\0');
         seq += w.results[m].sequential;
+        seq_tokens += w.results[m].seq_tokens;
     }
     if (stats) {
         stats[0] = hc.n_tokens;
@@ -242,6 +252,7 @@ char* emu_parse(const char* const* texts, const uint64_t* lens, uint32_t n, uint
         stats[6] = hc.n_bulk;
         stats[7] = hc.n_rest;
         stats[8] = hc.n_classes;
+        stats[9] = seq_tokens;
     }
     char* r = (char*)malloc(all.size() + 1);
     memcpy(r, all.data(), all.size());

@@ -37,7 +37,7 @@ class Emu:
         s = ctypes.string_at(p, ol.value)
         self.lib.emu_free(p)
         dumps = [x.decode("utf-8", "replace") for x in s.split(b"\0")[:-1]]
-        return dumps, dict(tokens=st[0], units=st[1], words=st[2], errors=st[3], sequential=st[4], pass_mismatch=st[5], bulk=st[6], untemplated=st[7], classes=st[8])
+        return dumps, dict(tokens=st[0], units=st[1], words=st[2], errors=st[3], sequential=st[4], pass_mismatch=st[5], bulk=st[6], untemplated=st[7], classes=st[8], sequential_tokens=st[9])
 
     def parse_multi(self, texts, n_parts, mode=0):
         """Sharded over n_parts host threads with the product's partitioner -> (dumps in the caller's order, shard of

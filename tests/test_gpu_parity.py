@@ -192,6 +192,46 @@ def test_full_size_properties(ctx):
     assert h1 == h2
 
 
+def test_damage_is_confined_to_the_tail(oracle, ctx):
+    """Damage in one top-level directive: the directives in front of it keep their speculated units, the sequential
+    parser (one thread) takes over from that directive to the end of the module."""
+    n_sequential = 0
+    for text, front in cases.confined_damage_cases():
+        for mode in (0, 1, 2):
+            b = ctx.parse_batch([text], mode)
+            assert b.dump(0) == oracle.parse(text, mode)[1], (text[-300:], mode)
+            b.free()
+            st = ctx.stats()
+            assert st["n_sequential_tokens"] <= (1.0 - front) * st["n_tokens"] + 64, (front, st)
+            n_sequential += st["n_sequential"]
+    assert n_sequential >= 30
+
+
+def test_large_truncated_module(oracle, ctx):
+    """A 4 MB module cut off in the middle of its last function (what a dump of a crashed process looks like): only
+    that function goes through the one-thread parser, and the module costs milliseconds, not seconds."""
+    text = corpus.config1(n_modules=1, total_bytes=4 << 20)[0]
+    last = text.rfind(b".visible .entry")
+    assert last > 0.8 * len(text)
+    cut = text[:last + (len(text) - last) // 2]
+    b = ctx.parse_batch([cut], 1)
+    st = ctx.stats()
+    assert b.dump_hash(0) == oracle.dump_hash(cut, 1)
+    assert b.error_count(0) >= 1
+    b.free()
+    assert st["n_sequential"] == 1
+    assert st["n_sequential_tokens"] < 0.2 * st["n_tokens"], st
+    assert st["kernel_ms"] < 100, st          # the whole module through the one-thread parser: 4.4 s
+    # a stray '{' in the last tenth of the module: the sequential tail is that tenth
+    at = text.find(b"\n", int(0.9 * len(text))) + 1
+    damaged = text[:at] + b"{\n" + text[at:]
+    b = ctx.parse_batch([damaged], 1)
+    st = ctx.stats()
+    assert b.dump_hash(0) == oracle.dump_hash(damaged, 1)
+    b.free()
+    assert st["n_sequential"] == 1 and st["n_sequential_tokens"] < 0.3 * st["n_tokens"], st
+
+
 def test_pattern_pins_on_the_device(ctx):
     """Every instruction pattern through the CUDA path: the frozen line per statement (tests/golden/pattern_pins.json) and
     the sweeps of cvt / setp / atom / ldmatrix against their re-derivations from the reference (test_pattern_pins.py)."""

@@ -193,6 +193,18 @@ def test_mutated_modules(oracle, emu):
     assert_parity(oracle, emu, texts)
 
 
+def test_damage_is_confined_to_the_tail(oracle, emu):
+    """The sequential parser takes over at the top-level directive with the first damage, not at the module's header."""
+    n_sequential = 0
+    for text, front in cases.confined_damage_cases():
+        for mode in (0, 1, 2):
+            dumps, st = emu.parse([text], mode)
+            assert dumps[0] == oracle.parse(text, mode)[1], (text[-300:], mode)
+            assert st["sequential_tokens"] <= (1.0 - front) * st["tokens"] + 64, (front, st)
+            n_sequential += st["sequential"]
+    assert n_sequential >= 30
+
+
 def test_reference_fixtures(oracle, emu):
     texts = list(reference_fixtures.texts().values())
     assert len(texts) >= 240

@@ -34,7 +34,7 @@ class Stats(ctypes.Structure):
         "text_bytes", "n_modules", "n_tokens", "n_units", "n_result_words", "n_errors", "n_lex_errors", "n_sequential",
         "n_kernel_launches", "h2d_bytes", "d2h_bytes")] + [(n, ctypes.c_float) for n in (
             "h2d_ms", "kernel_ms", "d2h_ms", "lex_ms", "structure_ms", "decode_ms")] + [(n, ctypes.c_uint64) for n in (
-                "n_classes", "n_class_capacity", "n_untemplated", "n_signature_words", "n_signature_capacity")]
+                "n_classes", "n_class_capacity", "n_untemplated", "n_signature_words", "n_signature_capacity", "n_sequential_tokens")]
 
     def as_dict(self):
         return {n: getattr(self, n) for n, _ in self._fields_}

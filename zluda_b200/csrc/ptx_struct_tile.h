@@ -63,21 +63,41 @@ PTX_HD inline uint32_t sx_lowest(uint32_t x) {     // x != 0
 // leaves the upper half of every byte for a second mask:
 //   braces: scope-opening '{' (low halves) and scope-closing '}' (high halves);  parens: '(' and ')';
 //   marks: previous token is ';' or ':' (low halves) and directive keywords (high halves).
-// Threads of the other case keep the kinds in w[] and go token by token.
+// Threads of the other case go token by token and read the kinds again.
 struct SxThread {
     uint32_t tb, n_valid;
     uint32_t first;               // bit i: token tb - 3 + i is the first token of a module
     bool fast;
     uint32_t braces, parens, marks;
     uint32_t brace_before;        // the token in front of the thread's first is a scope brace
-    uint16_t w[SX_ITEMS + 3];     // slow case only: w[3 + k] is the kind of token tb + k, w[0..2] the three before
 };
+// token-by-token case: the kinds of the thread's tokens and the three in front, w[3 + k] = token tb + k
+struct SxWindow {
+    uint16_t w[SX_ITEMS + 3];
+};
+PTX_HD inline void sx_window(const PtxStructArgs& a, const SxThread& t, SxWindow& win) {
+    union { LtWord4 q[2]; uint16_t h[16]; } own;
+    own.q[0] = ((const LtWord4*)(a.kinds + t.tb))[0];
+    own.q[1] = ((const LtWord4*)(a.kinds + t.tb))[1];
+    union { unsigned long long q; uint16_t h[4]; } halo;
+    halo.q = t.tb ? *(const unsigned long long*)(a.kinds + t.tb - 4) : 0ull;
+    for (uint32_t k = 0; k < SX_ITEMS; k++) win.w[3 + k] = PTX_KL_KIND(own.h[k]);
+    for (uint32_t k = 0; k < 3; k++) win.w[k] = t.tb ? PTX_KL_KIND(halo.h[1 + k]) : (uint16_t)0;
+}
 constexpr uint32_t SX_LOW = 0x0F0F0F0Fu, SX_ONES = 0x01010101u;
 // spread position of token i, and the tokens of a spread mask moved one place up (token i's bit to token i + 1)
 PTX_HD inline uint32_t sx_pos(uint32_t i) { return 8u * (i >> 2) + (i & 3u); }
 PTX_HD inline uint32_t sx_up(uint32_t m) { return ((m & 0x07070707u) << 1) | ((m & 0x08080808u) << 5); }
 
-// does a module begin in the tile that starts at token tile_base, or in the three tokens in front of it
+// The tiles in which a module begins, or whose three tokens in front hold a module begin: module m marks them in a
+// word per tile (stride in words), ahead of the pass.
+PTX_HD inline void sx_mark_tiles(const PtxStructArgs& a, uint32_t m, uint32_t* marks, uint32_t stride) {
+    const uint32_t b = a.mtb[m];
+    if (b >= a.n_tokens) return;
+    marks[(size_t)(b / SX_TILE) * stride] = 1u;
+    if (b % SX_TILE >= SX_TILE - 3u && (uint64_t)(b / SX_TILE + 1u) * SX_TILE < a.n_tokens) marks[(size_t)(b / SX_TILE + 1u) * stride] = 1u;
+}
+// the same by a search of the module table
 PTX_HD inline bool sx_tile_has_first(const PtxStructArgs& a, uint32_t tile_base) {
     uint32_t lowest = tile_base >= 3 ? tile_base - 3 : 0;
     uint32_t lo = 0, hi = a.n_modules;
@@ -120,12 +140,7 @@ PTX_HD inline void sx_load(const PtxStructArgs& a, uint32_t tb, SxThread& t, con
     union { unsigned long long q; uint16_t h[4]; } halo;
     halo.q = tb ? *(const unsigned long long*)(a.kinds + tb - 4) : 0ull;
     t.fast = allow_fast && t.first == 0 && (uint64_t)tb + SX_ITEMS < a.n_tokens;
-    if (!t.fast) {
-#pragma unroll
-        for (uint32_t k = 0; k < SX_ITEMS; k++) t.w[3 + k] = PTX_KL_KIND(own.h[k]);
-        t.w[0] = tb ? PTX_KL_KIND(halo.h[1]) : 0; t.w[1] = tb ? PTX_KL_KIND(halo.h[2]) : 0; t.w[2] = tb ? PTX_KL_KIND(halo.h[3]) : 0;
-        return;
-    }
+    if (!t.fast) return;      // the token-by-token case reads the kinds where it needs them
     uint32_t F[4] = {0, 0, 0, 0};
 #pragma unroll
     for (uint32_t i = 0; i < 8; i++) {      // word i: tokens 2i and 2i + 1 -> byte i / 2 of words (i % 2) * 2 and + 1
@@ -153,36 +168,39 @@ PTX_HD inline void sx_load(const PtxStructArgs& a, uint32_t tb, SxThread& t, con
 }
 
 // scope delta of the token at window index x (x >= 3): see ptx_brace_class
-PTX_HD inline int sx_brace(const SxThread& t, uint32_t x) {
-    uint16_t k = t.w[x];
+PTX_HD inline int sx_brace(const SxWindow& win, const SxThread& t, uint32_t x) {
+    uint16_t k = win.w[x];
     if (k != T_LBRACE && k != T_RBRACE) return 0;
     bool first = (t.first >> x) & 1u;
-    uint16_t prev = first ? (uint16_t)0xFFFE : t.w[x - 1];
+    uint16_t prev = first ? (uint16_t)0xFFFE : win.w[x - 1];
     if (k == T_LBRACE) {
         bool section = false;
-        if (!first && !((t.first >> (x - 1)) & 1u) && t.tb + x >= 5) section = t.w[x - 2] == T_DOT_SECTION;
+        if (!first && !((t.first >> (x - 1)) & 1u) && t.tb + x >= 5) section = win.w[x - 2] == T_DOT_SECTION;
         return (!ptx_opens_operand(prev) && !section) ? 1 : 0;
     }
     return (prev == T_SEMI || prev == T_COLON || prev == T_LBRACE || prev == T_RBRACE) ? -1 : 0;
 }
 // the same for the token just in front of the thread's first (window index 2), whose own left context is w[0..1]
-PTX_HD inline int sx_brace_before(const SxThread& t) {
-    return t.tb ? sx_brace(t, 2) : 0;
+PTX_HD inline int sx_brace_before(const SxWindow& win, const SxThread& t) {
+    return t.tb ? sx_brace(win, t, 2) : 0;
 }
 
 // step 1: the thread's aggregate (flag = a module begins among its tokens; depths counted from the last such begin)
-PTX_HD inline PtxSeg3 sx_aggregate(const SxThread& t) {
+PTX_HD inline PtxSeg3 sx_aggregate(const PtxStructArgs& a, const SxThread& t) {
     if (t.fast)
         return PtxSeg3{(int32_t)sx_popc(t.braces & SX_LOW) - (int32_t)sx_popc(t.braces & ~SX_LOW),
                        (int32_t)sx_popc(t.parens & SX_LOW) - (int32_t)sx_popc(t.parens & ~SX_LOW), 0};
     PtxSeg3 v{0, 0, 0};
-#pragma unroll
-    for (uint32_t k = 0; k < SX_ITEMS; k++) {
-        if (k >= t.n_valid) break;
+    if (!t.n_valid) return v;
+    SxWindow win;
+    sx_window(a, t, win);
+#pragma unroll 1
+    for (uint32_t k = 0; k < t.n_valid; k++) {
         uint32_t x = 3 + k;
         if ((t.first >> x) & 1u) v = PtxSeg3{0, 0, 1};
-        v.scope += sx_brace(t, x);
-        v.paren += t.w[x] == T_LPAREN ? 1 : t.w[x] == T_RPAREN ? -1 : 0;
+        v.scope += sx_brace(win, t, x);
+        const uint16_t kk = win.w[x];
+        v.paren += kk == T_LPAREN ? 1 : kk == T_RPAREN ? -1 : 0;
     }
     return v;
 }
@@ -191,16 +209,52 @@ PTX_HD inline PtxSeg3 sx_aggregate(const SxThread& t) {
 // behind a module's last token goes to mod_final_scope.  The rule, for a token that does not begin a module: at the
 // top level (scope depth 0, outside parentheses) a directive keyword that does not continue a run of linking keywords;
 // inside a scope, the token after ';', ':' or a scope brace, and a scope brace itself.
-PTX_HD inline uint32_t sx_decide_slow(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before, uint16_t* codes);
-PTX_HD inline uint32_t sx_decide(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before) {
-    if (!t.fast) {
-        uint16_t codes[SX_ITEMS];
-        sx_decide_slow(a, t, before, codes);
-        uint32_t starts = 0;
-#pragma unroll
-        for (uint32_t k = 0; k < SX_ITEMS; k++) starts |= (codes[k] ? 1u : 0u) << sx_pos(k);
-        return starts;
+// Token by token from the kinds; with write set, the rows of the unit table are written as well (step 3).
+PTX_HD inline uint32_t sx_walk(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before, bool write, uint32_t units_before) {
+    int32_t sd = before.scope, pd = before.paren;
+    uint32_t starts = 0, u = units_before;
+    if (!t.n_valid) return 0;
+    SxWindow win;
+    sx_window(a, t, win);
+    int bc_prev = sx_brace_before(win, t);
+#pragma unroll 1
+    for (uint32_t k = 0; k < t.n_valid; k++) {
+        const uint32_t x = 3 + k, j = t.tb + k;
+        const int bc = sx_brace(win, t, x);
+        const uint16_t kk = win.w[x];
+        bool start, first = (t.first >> x) & 1u;
+        if (first) {
+            if (j) a.mod_final_scope[ptx_upper_bound_u32(a.mtb, a.n_modules, j - 1) - 1] = sd;
+            start = true;
+            sd = pd = 0;
+        } else if (sd <= 0) {
+            const uint16_t prev = win.w[x - 1];
+            start = sd == 0 && pd == 0 && ptx_is_directive_start(kk) && !(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak);
+        } else {
+            const uint16_t prev = win.w[x - 1];
+            start = prev == T_SEMI || prev == T_COLON || bc != 0 || bc_prev != 0;
+        }
+        if (start) {
+            starts |= 1u << sx_pos(k);
+            if (write) {
+                a.ustart[u] = j;
+                a.udepth[u] = (sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd) | (first ? 0x80000000u : 0u);
+                if (first) a.mub[ptx_upper_bound_u32(a.mtb, a.n_modules, j) - 1] = u;
+                u++;
+            }
+        }
+        sd += bc;
+        pd += kk == T_LPAREN ? 1 : kk == T_RPAREN ? -1 : 0;
+        bc_prev = bc;
+        if (j + 1 == a.n_tokens) {
+            a.mod_final_scope[ptx_upper_bound_u32(a.mtb, a.n_modules, j) - 1] = sd;
+            if (write) a.counters->n_units = u;
+        }
     }
+    return starts;
+}
+PTX_HD inline uint32_t sx_decide(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before) {
+    if (!t.fast) return sx_walk(a, t, before, false, 0);
     const uint32_t plus = t.braces & SX_LOW, minus = (t.braces >> 4) & SX_LOW;
     const uint32_t in_scope = (t.marks & SX_LOW) | plus | minus | sx_up(plus | minus) | t.brace_before;
     if (before.scope - (int32_t)sx_popc(minus) > 0) return in_scope;                        // inside a scope all the way
@@ -209,85 +263,35 @@ PTX_HD inline uint32_t sx_decide(const PtxStructArgs& a, const SxThread& t, PtxS
     // a bit of both: token by token
     int32_t sd = before.scope, pd = before.paren;
     uint32_t starts = 0;
-#pragma unroll
+#pragma unroll 1
     for (uint32_t k = 0; k < SX_ITEMS; k++) {
-        const uint32_t bit = 1u << sx_pos(k);
+        const uint32_t pos = sx_pos(k), bit = 1u << pos;
         if (sd > 0) {
             starts |= in_scope & bit;
         } else if (sd == 0 && pd == 0 && (dirs & bit)) {
             const uint16_t prev = PTX_KL_KIND(a.kinds[t.tb + k - 1]);       // fast threads have tb > 0
             if (!(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak)) starts |= bit;
         }
-        sd += (int32_t)((plus >> sx_pos(k)) & 1u) - (int32_t)((minus >> sx_pos(k)) & 1u);
-        pd += (int32_t)((t.parens >> sx_pos(k)) & 1u) - (int32_t)((t.parens >> (sx_pos(k) + 4u)) & 1u);
+        sd += (int32_t)((plus >> pos) & 1u) - (int32_t)((minus >> pos) & 1u);
+        pd += (int32_t)((t.parens >> pos) & 1u) - (int32_t)((t.parens >> (pos + 4u)) & 1u);
     }
     return starts;
 }
 
-// the same token by token from the kinds: the code of every token (0 = no unit starts here, else 1 + clamped scope
-// depth in front of it, bit 15 = first token of a module)
-PTX_HD inline uint32_t sx_decide_slow(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before, uint16_t* codes) {
-    int32_t sd = before.scope, pd = before.paren;
-    uint32_t count = 0;
-    int bc_prev = sx_brace_before(t);
-#pragma unroll
-    for (uint32_t k = 0; k < SX_ITEMS; k++) {
-        codes[k] = 0;
-        if (k >= t.n_valid) continue;
-        uint32_t x = 3 + k, j = t.tb + k;
-        int bc = sx_brace(t, x);
-        if ((t.first >> x) & 1u) {
-            if (j) a.mod_final_scope[ptx_upper_bound_u32(a.mtb, a.n_modules, j - 1) - 1] = sd;
-            codes[k] = (uint16_t)(1u | 0x8000u);
-            sd = pd = 0;
-        } else {
-            uint16_t kk = t.w[x], prev = t.w[x - 1];
-            bool start;
-            if (sd <= 0) {
-                // top level: a directive keyword outside parentheses that does not continue a run of linking keywords
-                start = sd == 0 && pd == 0 && ptx_is_directive_start(kk) && !(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak);
-            } else {
-                start = prev == T_SEMI || prev == T_COLON || bc != 0 || bc_prev != 0;
-            }
-            uint32_t clamped = sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
-            codes[k] = start ? (uint16_t)(1u + clamped) : (uint16_t)0;
-        }
-        count += codes[k] ? 1u : 0u;
-        sd += bc;
-        pd += t.w[x] == T_LPAREN ? 1 : t.w[x] == T_RPAREN ? -1 : 0;
-        bc_prev = bc;
-        if (j + 1 == a.n_tokens) a.mod_final_scope[ptx_upper_bound_u32(a.mtb, a.n_modules, j) - 1] = sd;
-    }
-    return count;
-}
-
 // step 3: with the number of unit starts in front of the thread's first token: the rows of the unit table
 PTX_HD inline void sx_write(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before, uint32_t starts, uint32_t units_before) {
-    uint32_t u = units_before;
-    if (t.fast) {
-        const uint32_t plus = t.braces & SX_LOW, minus = (t.braces >> 4) & SX_LOW;
-        while (starts) {
-            const uint32_t pos = sx_lowest(starts), below = (1u << pos) - 1u;
-            starts &= starts - 1u;
-            const int32_t sd = before.scope + (int32_t)sx_popc(plus & below) - (int32_t)sx_popc(minus & below);
-            a.ustart[u] = t.tb + (pos >> 3) * 4u + (pos & 3u);
-            a.udepth[u] = sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
-            u++;
-        }
+    if (!t.fast) {
+        if (t.n_valid) sx_walk(a, t, before, true, units_before);
         return;
     }
-    if (!t.n_valid) return;
-    uint16_t codes[SX_ITEMS];
-    sx_decide_slow(a, t, before, codes);
-#pragma unroll
-    for (uint32_t k = 0; k < SX_ITEMS; k++) {
-        uint32_t code = codes[k];
-        if (!code) continue;
-        uint32_t j = t.tb + k;
-        a.ustart[u] = j;
-        a.udepth[u] = ((code & 0x7FFFu) - 1u) | ((code & 0x8000u) ? 0x80000000u : 0u);
-        if (code & 0x8000u) a.mub[ptx_upper_bound_u32(a.mtb, a.n_modules, j) - 1] = u;
+    uint32_t u = units_before;
+    const uint32_t plus = t.braces & SX_LOW, minus = (t.braces >> 4) & SX_LOW;
+    while (starts) {
+        const uint32_t pos = sx_lowest(starts), below = (1u << pos) - 1u;
+        starts &= starts - 1u;
+        const int32_t sd = before.scope + (int32_t)sx_popc(plus & below) - (int32_t)sx_popc(minus & below);
+        a.ustart[u] = t.tb + (pos >> 3) * 4u + (pos & 3u);
+        a.udepth[u] = sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
         u++;
     }
-    if (t.tb + t.n_valid == a.n_tokens) a.counters->n_units = u;
 }

@@ -71,14 +71,17 @@ PTX_HD PTX_NOINLINE inline PtxUnitResult ptx_decode_unit(PtxDecoder& d, uint32_t
 // costs the reference 2^d times the work (it does not memoise) and appends as many errors.  After 4 * tokens + 1024
 // statement attempts the module is given up with the verdict ReferenceDiverges; this also bounds the running time of
 // the one thread that parses it.
-PTX_HD PTX_NOINLINE inline int ptx_decode_module_sequential(PtxDecoder& d, uint32_t tb, uint32_t base) {
+// With from_directive set, tb is the first token of a top-level directive instead: the module's header and the
+// directives in front of tb were parsed by the speculated units, which met one another up to there, so the sequential
+// parser would stand at tb in its directive loop with nothing but the errors so far behind it.
+PTX_HD PTX_NOINLINE inline int ptx_decode_module_sequential(PtxDecoder& d, uint32_t tb, uint32_t base, bool from_directive = false) {
     d.stmt_attempts = 0;
     d.stmt_budget = 4ull * (uint64_t)(d.te - tb) + 1024ull;
     d.diverged = false;
     d.pos = tb;
     d.unit_off = tb < d.te ? d.tk(tb).start : 0;
     uint32_t m;
-    if (!d.header()) {
+    if (!from_directive && !d.header()) {
         d.push(E_PARSER, 0, 0, 0);
         d.begin_record(&m);
         d.end_record(m, U_MODULE_FAIL);

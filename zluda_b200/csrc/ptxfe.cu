@@ -158,38 +158,60 @@ __global__ void __launch_bounds__(256) staged_kernel(size_t n, uint32_t* table, 
 
 // ---- one thread per item of a segmented range: a block takes 256 consecutive segments, whose items are contiguous,
 // and every thread finds the segment of its item by binary search over the block's offsets in shared memory
-// Two rounds: f(segment, item, global index) handles an item or returns true to put it off; the items put off are
-// collected and handled by g with full warps (work that only a few scattered items need: literal conversion).
+// Record emission (PtxEmitStep): a block takes 256 consecutive units, whose words are contiguous, loads what a word
+// needs of its unit into shared memory once, and then goes over the words with EMIT_ILP words per thread at a time:
+// all their reads are issued before the first of them is written, so that several chains of dependent loads (unit ->
+// template -> token) are in flight per thread.  The literals are collected and converted in a second round with the
+// warps full.
 #define SEG_DEFER_CAP 2048u
-template <class F, class G>
-__global__ void __launch_bounds__(256) segments2_kernel(uint32_t n_units, const PtxPair* off, F f, G g) {
+#define EMIT_ILP 4
+__global__ void __launch_bounds__(256, 6) emit_records_kernel(uint32_t n_units, const PtxPair* off, PtxEmitStep e) {
     __shared__ uint32_t so[257];
+    __shared__ PtxEmitUnit su[256];
     __shared__ uint32_t later[SEG_DEFER_CAP];
     __shared__ uint32_t n_later;
     const uint32_t u0 = blockIdx.x * 256;
     const uint32_t nu = n_units - u0 < 256u ? n_units - u0 : 256u;
     for (uint32_t k = threadIdx.x; k <= nu; k += 256) so[k] = off[u0 + k].a;
+    if (threadIdx.x < nu) su[threadIdx.x] = e.unit(u0 + threadIdx.x);
     if (threadIdx.x == 0) n_later = 0;
     __syncthreads();
     const uint32_t first = so[0], total = so[nu] - so[0];
-    for (uint32_t j = threadIdx.x; j < total; j += 256) {
-        uint32_t o = first + j;
-        uint32_t lo = 0, hi = nu;          // last k with so[k] <= o
-        while (hi - lo > 1) {
-            uint32_t mid = (lo + hi) >> 1;
-            if (so[mid] <= o) lo = mid; else hi = mid;
+    for (uint32_t j0 = threadIdx.x; j0 < total; j0 += 256 * EMIT_ILP) {
+        uint32_t x[EMIT_ILP], unit[EMIT_ILP];
+        int what[EMIT_ILP];
+#pragma unroll
+        for (int q = 0; q < EMIT_ILP; q++) {
+            const uint32_t j = j0 + q * 256;
+            what[q] = PtxEmitStep::NOTHING;
+            unit[q] = 0;
+            if (j >= total) continue;
+            const uint32_t o = first + j;
+            uint32_t lo = 0, hi = nu;          // last k with so[k] <= o
+            while (hi - lo > 1) {
+                uint32_t mid = (lo + hi) >> 1;
+                if (so[mid] <= o) lo = mid; else hi = mid;
+            }
+            unit[q] = lo;
+            what[q] = e.word(su[lo], (size_t)(u0 + lo), o - so[lo], x[q]);
         }
-        if (f((size_t)(u0 + lo), o - so[lo], o)) {
-            uint32_t slot = atomicAdd(&n_later, 1u);
-            if (slot < SEG_DEFER_CAP && j < (1u << 24)) later[slot] = j | (lo << 24);
-            else g((size_t)(u0 + lo), o - so[lo], o);
+#pragma unroll
+        for (int q = 0; q < EMIT_ILP; q++) {
+            const uint32_t j = j0 + q * 256;
+            if (what[q] == PtxEmitStep::WRITE) {
+                e.words[first + j] = x[q];
+            } else if (what[q] == PtxEmitStep::SECOND_ROUND) {
+                const uint32_t slot = atomicAdd(&n_later, 1u);
+                if (slot < SEG_DEFER_CAP && j < (1u << 24)) later[slot] = j | (unit[q] << 24);
+                else e.literal(su[unit[q]], first + j - so[unit[q]], first + j);
+            }
         }
     }
     __syncthreads();
     const uint32_t nl = n_later < SEG_DEFER_CAP ? n_later : SEG_DEFER_CAP;
     for (uint32_t x = threadIdx.x; x < nl; x += 256) {
         const uint32_t j = later[x] & 0xFFFFFFu, lo = later[x] >> 24, o = first + j;
-        g((size_t)(u0 + lo), o - so[lo], o);
+        e.literal(su[lo], o - so[lo], o);
     }
 }
 template <class F>
@@ -334,10 +356,16 @@ __global__ void __launch_bounds__(SCAN_THREADS) scan_apply_kernel(size_t n, Ld l
 // Waiting is bounded: a tile that waits too long sets the abort word, every other waiter sees it and leaves, and the
 // host reads struct_abort with the counters.
 struct StructDesc {
-    unsigned long long depth0, depth1, count, pad;
+    unsigned long long depth0, depth1, count;
+    uint32_t has_first, pad;      // has_first: set ahead of the pass (sx_mark_tiles)
 };
+__global__ void structure_mark_kernel(PtxStructArgs a, StructDesc* desc) {
+    uint32_t m = blockIdx.x * blockDim.x + threadIdx.x;
+    if (m < a.n_modules) sx_mark_tiles(a, m, &desc[0].has_first, (uint32_t)(sizeof(StructDesc) / 4));
+}
 constexpr unsigned long long SXD_AGG = 1ull << 62, SXD_PREFIX = 2ull << 62, SXD_STATE = 3ull << 62;
 constexpr uint32_t SX_WAIT_LIMIT = 1u << 22;
+constexpr int SX_DEPTH_PER_LANE = 1, SX_COUNT_PER_LANE = 1;     // tiles a lane of the look-back reads per trip to memory
 
 __device__ inline unsigned long long sx_ld(const unsigned long long* p) { return *(const volatile unsigned long long*)p; }
 __device__ inline void sx_st(unsigned long long* p, unsigned long long v) { *(volatile unsigned long long*)p = v; }
@@ -358,7 +386,7 @@ __device__ inline bool sx_read_depth(const StructDesc* d, uint32_t* ctl, unsigne
         }
         if ((spin & 63u) == 63u && *(volatile uint32_t*)&ctl[1]) return false;
         if (spin >= SX_WAIT_LIMIT) { atomicExch(&ctl[1], 1u); return false; }
-        __nanosleep(40);
+        __nanosleep(20);
     }
 }
 __device__ inline bool sx_read_count(const StructDesc* d, uint32_t* ctl, unsigned long long& state, uint32_t& v) {
@@ -367,14 +395,14 @@ __device__ inline bool sx_read_count(const StructDesc* d, uint32_t* ctl, unsigne
         if (a & SXD_STATE) { state = a & SXD_STATE; v = (uint32_t)a; return true; }
         if ((spin & 63u) == 63u && *(volatile uint32_t*)&ctl[1]) return false;
         if (spin >= SX_WAIT_LIMIT) { atomicExch(&ctl[1], 1u); return false; }
-        __nanosleep(40);
+        __nanosleep(20);
     }
 }
 
 __global__ void __launch_bounds__(SX_THREADS) structure_kernel(PtxStructArgs a, uint32_t n_tiles, StructDesc* desc, uint32_t* ctl) {
     __shared__ PtxSeg3 warp_depth[SX_THREADS / 32];
     __shared__ uint32_t warp_count[SX_THREADS / 32];
-    __shared__ uint32_t s_tile, s_units_before, s_ok, s_has_first;
+    __shared__ uint32_t s_tile, s_has_first, s_units_before, s_ok;
     __shared__ PtxSeg3 s_before;
     __shared__ uint8_t s_table[512];
     const int lane = threadIdx.x & 31;
@@ -383,22 +411,24 @@ __global__ void __launch_bounds__(SX_THREADS) structure_kernel(PtxStructArgs a, 
     for (;;) {
         __syncthreads();                                   // the shared words of the tile before are no longer read
         if (threadIdx.x == 0) {
-            const uint32_t tile = atomicAdd(&ctl[0], 1u);
-            s_tile = tile;
+            const uint32_t mine = atomicAdd(&ctl[0], 1u);
+            s_tile = mine;
             s_ok = *(volatile uint32_t*)&ctl[1] ? 0u : 1u;  // aborted: later tiles do nothing
-            s_has_first = tile < n_tiles && sx_tile_has_first(a, tile * SX_TILE) ? 1u : 0u;
+            s_has_first = mine < n_tiles ? desc[mine].has_first : 0u;
         }
         __syncthreads();
         const uint32_t tile = s_tile;
+        const bool has_first = s_has_first != 0;
         if (tile >= n_tiles) return;
-        if (!s_ok) {
-            if (threadIdx.x == 0) a.counters->struct_abort = 1;
-            return;
+        // the blocks take tiles more or less in turn: ask for the kinds of the tile one round ahead (whoever gets it)
+        if ((threadIdx.x & 3u) == 0 && (uint64_t)tile + gridDim.x < n_tiles) {
+            const uint16_t* ahead = a.kinds + ((size_t)tile + gridDim.x) * SX_TILE + threadIdx.x * SX_ITEMS;     // a 128-byte line
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(ahead));
         }
         SxThread t;
-        sx_load(a, tile * SX_TILE + threadIdx.x * SX_ITEMS, t, s_table, s_has_first != 0);
+        sx_load(a, tile * SX_TILE + threadIdx.x * SX_ITEMS, t, s_table, has_first);
         PtxSeg3 incl, excl;
-        block_scan(sx_aggregate(t), op, PtxSeg3{0, 0, 0}, warp_depth, incl, excl);
+        block_scan(sx_aggregate(a, t), op, PtxSeg3{0, 0, 0}, warp_depth, incl, excl);
         if (threadIdx.x == SX_THREADS - 1) s_before = incl;         // the tile's aggregate, for warp 0
         __syncthreads();
         if (threadIdx.x < 32) {
@@ -410,17 +440,33 @@ __global__ void __launch_bounds__(SX_THREADS) structure_kernel(PtxStructArgs a, 
                 if (lane == 0) sx_publish_depth(&desc[0], SXD_PREFIX, agg);
             } else {
                 if (lane == 0) sx_publish_depth(&desc[tile], SXD_AGG, agg);
-                // windows of 32 earlier tiles, nearest first; lane 0 holds the nearest tile of the window
+                // windows of 32 * SX_DEPTH_PER_LANE earlier tiles, nearest first; every lane takes consecutive tiles (its
+                // nearest first) and stops at one with a known prefix or a module begin (or in front of tile 0)
                 for (int64_t back = (int64_t)tile - 1; ok;) {
-                    int64_t mine = back - lane;
-                    unsigned long long state = SXD_PREFIX;
+                    const int64_t mine = back - (int64_t)lane * SX_DEPTH_PER_LANE;
+                    unsigned long long w0[SX_DEPTH_PER_LANE], w1[SX_DEPTH_PER_LANE];
+#pragma unroll
+                    for (int r = 0; r < SX_DEPTH_PER_LANE; r++) {       // all loads first: one trip to memory for the lot
+                        w0[r] = mine - r >= 0 ? sx_ld(&desc[mine - r].depth0) : 0ull;
+                        w1[r] = mine - r >= 0 ? sx_ld(&desc[mine - r].depth1) : 0ull;
+                    }
                     PtxSeg3 v{0, 0, 0};
-                    bool got = mine < 0 ? true : sx_read_depth(&desc[mine], ctl, state, v);
+                    bool done = false, got = true;
+#pragma unroll
+                    for (int r = 0; r < SX_DEPTH_PER_LANE; r++) {
+                        if (done || !got) continue;
+                        if (mine - r < 0) { done = true; continue; }
+                        unsigned long long state = w0[r] & SXD_STATE;
+                        PtxSeg3 x{(int32_t)(uint32_t)w0[r], (int32_t)(uint32_t)w1[r], (int32_t)((w0[r] >> 32) & 1u)};
+                        if (!state || state != (w1[r] & SXD_STATE)) got = sx_read_depth(&desc[mine - r], ctl, state, x);
+                        if (!got) continue;
+                        v = op(x, v);
+                        done = state == SXD_PREFIX || x.flag;
+                    }
                     if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
-                    // the chain ends at the nearest tile with a known prefix or a module begin (or before tile 0)
-                    unsigned ends = __ballot_sync(0xFFFFFFFFu, mine < 0 || state == SXD_PREFIX || v.flag);
+                    unsigned ends = __ballot_sync(0xFFFFFFFFu, done);
                     int last = ends ? __ffs(ends) - 1 : 31;
-                    if (lane > last || mine < 0) v = PtxSeg3{0, 0, 0};
+                    if (lane > last) v = PtxSeg3{0, 0, 0};
                     // ordered reduction: lane 0 ends up with op(v[last], ..., v[1], v[0])
 #pragma unroll
                     for (int d = 1; d < 32; d <<= 1) {
@@ -430,7 +476,7 @@ __global__ void __launch_bounds__(SX_THREADS) structure_kernel(PtxStructArgs a, 
                     v = shfl_words(v, 0);
                     before = op(v, before);
                     if (ends) break;
-                    back -= 32;
+                    back -= 32 * SX_DEPTH_PER_LANE;
                 }
                 if (ok && lane == 0) sx_publish_depth(&desc[tile], SXD_PREFIX, op(before, agg));
             }
@@ -457,17 +503,30 @@ __global__ void __launch_bounds__(SX_THREADS) structure_kernel(PtxStructArgs a, 
             } else {
                 if (lane == 0) sx_st(&desc[tile].count, SXD_AGG | agg);
                 for (int64_t back = (int64_t)tile - 1; ok;) {
-                    int64_t mine = back - lane;
-                    unsigned long long state = SXD_PREFIX;
+                    const int64_t mine = back - (int64_t)lane * SX_COUNT_PER_LANE;
+                    unsigned long long w[SX_COUNT_PER_LANE];
+#pragma unroll
+                    for (int r = 0; r < SX_COUNT_PER_LANE; r++) w[r] = mine - r >= 0 ? sx_ld(&desc[mine - r].count) : 0ull;
                     uint32_t v = 0;
-                    bool got = mine < 0 ? true : sx_read_count(&desc[mine], ctl, state, v);
+                    bool done = false, got = true;
+#pragma unroll
+                    for (int r = 0; r < SX_COUNT_PER_LANE; r++) {
+                        if (done || !got) continue;
+                        if (mine - r < 0) { done = true; continue; }
+                        unsigned long long state = w[r] & SXD_STATE;
+                        uint32_t x = (uint32_t)w[r];
+                        if (!state) got = sx_read_count(&desc[mine - r], ctl, state, x);
+                        if (!got) continue;
+                        v += x;
+                        done = state == SXD_PREFIX;
+                    }
                     if (!__all_sync(0xFFFFFFFFu, got)) { ok = false; break; }
-                    unsigned ends = __ballot_sync(0xFFFFFFFFu, mine < 0 || state == SXD_PREFIX);
+                    unsigned ends = __ballot_sync(0xFFFFFFFFu, done);
                     int last = ends ? __ffs(ends) - 1 : 31;
-                    if (lane > last || mine < 0) v = 0;
+                    if (lane > last) v = 0;
                     before += __reduce_add_sync(0xFFFFFFFFu, v);
                     if (ends) break;
-                    back -= 32;
+                    back -= 32 * SX_COUNT_PER_LANE;
                 }
                 if (ok && lane == 0) sx_st(&desc[tile].count, SXD_PREFIX | (uint32_t)(before + agg));
             }
@@ -735,10 +794,10 @@ struct CudaBackend {
         prof_end();
         ctx->launches++;
     }
-    template <class F, class G> void pf_segments2(const char* name, size_t n, const PtxPair* off, F f, G g) {
+    void emit_records(const char* name, size_t n, const PtxPair* off, const PtxEmitStep& e) {
         if (ctx->failed || n == 0) return;
         prof_begin(name);
-        segments2_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>((uint32_t)n, off, f, g);
+        emit_records_kernel<<<(unsigned)((n + 255) / 256), 256, 0, ctx->stream>>>((uint32_t)n, off, e);
         prof_end();
         ctx->launches++;
     }
@@ -805,7 +864,9 @@ struct CudaBackend {
         uint32_t* ctl = (uint32_t*)(desc + n_tiles);      // [0] next tile, [1] abort
         prof_begin(name);
         cudaMemsetAsync(desc, 0, sizeof(StructDesc) * n_tiles + 256, ctx->stream);
-        structure_kernel<<<resident_blocks((const void*)structure_kernel, 0, n_tiles), SX_THREADS, 0, ctx->stream>>>(a, (uint32_t)n_tiles, desc, ctl);
+        structure_mark_kernel<<<(a.n_modules + 255) / 256, 256, 0, ctx->stream>>>(a, desc);
+        const unsigned grid = resident_blocks((const void*)structure_kernel, 0, n_tiles);
+        structure_kernel<<<grid, SX_THREADS, 0, ctx->stream>>>(a, (uint32_t)n_tiles, desc, ctl);
         prof_end();
         ctx->launches++;
     }
@@ -1072,6 +1133,7 @@ int ptxfe_run(ptxfe_ctx* ctx, uint32_t mode) {
     s.n_lex_errors = ctx->counters.n_lexerrs;
     s.n_kernel_launches = ctx->launches;
     s.n_sequential = 0;
+    s.n_sequential_tokens = 0;
     s.n_classes = ctx->counters.n_classes;
     s.n_class_capacity = PTX_MAX_CLASSES;
     s.n_untemplated = ctx->counters.n_rest;
@@ -1135,9 +1197,10 @@ int ptxfe_fetch(ptxfe_ctx* ctx, ptxfe_batch** out) {
     CUDA_TRY(cudaEventElapsedTime(&ctx->stats.d2h_ms, ctx->ev[6], ctx->ev[7]));
     ctx->stats.d2h_bytes = wb + eb + lb + rb;
     ptxfe_batch* b = make_batch(ctx, n);
-    uint64_t seq = 0;
-    for (uint32_t m = 0; m < n; m++) seq += b->results[m].sequential;
+    uint64_t seq = 0, seq_tokens = 0;
+    for (uint32_t m = 0; m < n; m++) { seq += b->results[m].sequential; seq_tokens += b->results[m].seq_tokens; }
     ctx->stats.n_sequential = seq;
+    ctx->stats.n_sequential_tokens = seq_tokens;
     ctx->live = b;
     *out = b;
     return PTXFE_OK;
@@ -1330,13 +1393,14 @@ int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* 
 #undef DRAIN_TRY
     // ---- module results index the batch-wide host arrays
     PtxModuleResult* res = (PtxModuleResult*)ctx->h_results;
-    uint64_t seq = 0;
+    uint64_t seq = 0, seq_tokens = 0;
     for (size_t k = 0; k < ns; k++)
         for (uint32_t m = slices[k].m0; m < slices[k].m1; m++) {
             res[m].word_begin += (uint32_t)base_w[k]; res[m].word_end += (uint32_t)base_w[k];
             res[m].err_begin += (uint32_t)base_e[k]; res[m].err_end += (uint32_t)base_e[k];
             res[m].lexerr_begin += (uint32_t)base_l[k]; res[m].lexerr_end += (uint32_t)base_l[k];
             seq += res[m].sequential;
+            seq_tokens += res[m].seq_tokens;
         }
     // ---- statistics: busy time of each of the three streams
     cudaEventElapsedTime(&s.h2d_ms, ctx->ev[0], ctx->ev[1]);
@@ -1363,6 +1427,7 @@ int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* 
     s.d2h_bytes = words_done * 4 + errs_done * sizeof(PtxErrRec) + lexerrs_done * 8 + sizeof(PtxModuleResult) * (size_t)n;
     s.n_kernel_launches = ctx->launches;
     s.n_sequential = seq;
+    s.n_sequential_tokens = seq_tokens;
     collect_profile(ctx);
     ptxfe_batch* b = make_batch(ctx, n);
     ctx->live = b;

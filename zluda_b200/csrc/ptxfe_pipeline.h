@@ -26,7 +26,7 @@ struct PtxModuleResult {
     uint32_t sequential;   // 1 = parsed by the sequential path
     uint32_t status;       // sequential path: PtxUnitStatus | US_MODULE_FAILED
     uint32_t n_errors;     // parser errors raised (reserved slots that stayed unused not counted)
-    uint32_t pad;
+    uint32_t seq_tokens;   // tokens that went through the sequential path
 };
 
 // host view of one fetched batch (input of the dump)
@@ -329,7 +329,7 @@ struct SegDepthOp {
 //        afterwards the backend copies the first r.n staged words to table[r.unit * row_words ...]
 //   template <class F> void pf_segments(const char* name, size_t n, const PtxPair* off, F f);
 //        segment s owns the items [off[s].a, off[s + 1].a): f(s, i, off[s].a + i) for every s < n and every item i of s
-//   template <class F, class G> void pf_segments2(const char* name, size_t n, const PtxPair* off, F f, G g);
+//   void emit_records(const char* name, size_t n_units, const PtxPair* off, const PtxEmitStep& e);   C5, see PtxEmitStep
 //        the same in two rounds: an item for which f returns true is handled by g(s, i, off[s].a + i) afterwards, the
 //        items put off packed together (work that few scattered items need)
 //   PtxClassStore class_store(bool reset);   the batch's class store (device memory that outlives the arena), emptied if asked
@@ -469,7 +469,7 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         r.lexerr_begin = mod_lexerr_begin[m];
         r.lexerr_end = mod_lexerr_begin[m + 1];
         r.unit_begin = r.unit_end = r.word_begin = r.word_end = r.err_begin = r.err_end = 0;
-        r.sequential = r.status = r.n_errors = r.pad = 0;
+        r.sequential = r.status = r.n_errors = r.seq_tokens = 0;
         results[m] = r;
     });
 }
@@ -531,6 +531,65 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
     });
 }
 
+// C5 as a step object: one output word at a time.  unit() is what a word needs of its unit (loaded once per unit by
+// the backend); word() only reads and says what to do with the word, so that a backend can have several words in flight
+// per thread; literal() is the second round (one literal per call, written in place).
+struct PtxEmitUnit {
+    uint32_t tmpl, start, flag;
+};
+struct PtxEmitStep {
+    const uint8_t* uflag;
+    const uint32_t* utmpl;
+    const uint32_t* ustart;
+    const uint32_t* table;
+    PtxClassStore cs;
+    const PtxToken* tokens;
+    const uint8_t* text;
+    uint32_t* words;
+    enum { NOTHING = 0, WRITE = 1, SECOND_ROUND = 2 };
+    PTX_HD PtxEmitUnit unit(size_t u) const {
+        PtxEmitUnit e;
+        e.flag = uflag[u];
+        e.tmpl = e.flag == PTX_UNIT_TEMPLATED ? utmpl[u] : 0u;
+        e.start = ustart[u];
+        return e;
+    }
+    PTX_HD int word(const PtxEmitUnit& e, size_t u, uint32_t i, uint32_t& x) const {
+        if (e.flag == PTX_UNIT_STAGED) {
+            x = table[u * PTX_TMP_STRIDE + i];
+            return WRITE;
+        }
+        if (e.flag != PTX_UNIT_TEMPLATED) return NOTHING;
+        const size_t at = (size_t)e.tmpl * PTX_TMPL_WORDS + i;
+        x = cs.tmpl_words[at];
+        const uint32_t g = cs.tmpl_tags[at];
+        if (g) {
+            const uint32_t type = g >> 8;
+            if (type >= PTX_TAG_VAL_LO) {
+                if (!(type & 1u)) return SECOND_ROUND;      // low word
+                // high word: written by the low-word thread in front of it, unless it stands alone
+                if (i > 0 && cs.tmpl_tags[at - 1] == (uint16_t)(g - 0x100u)) return NOTHING;
+                return SECOND_ROUND;
+            }
+            const PtxToken t = tokens[e.start + (g & 0xFFu)];
+            x = type == PTX_TAG_START ? t.start : type == PTX_TAG_LEN ? (uint32_t)t.len : ((x & 0xFFu) | ((uint32_t)t.len << 8));
+        }
+        return WRITE;
+    }
+    // Literal values, one thread per literal with the warps full: the low-word thread also writes the high word when
+    // the template has it next (the two value words of an immediate)
+    PTX_HD void literal(const PtxEmitUnit& e, uint32_t i, uint32_t j) const {
+        const size_t at = (size_t)e.tmpl * PTX_TMPL_WORDS + i;
+        const uint32_t g = cs.tmpl_tags[at], type = g >> 8;
+        const PtxToken t = tokens[e.start + (g & 0xFFu)];
+        uint64_t v = ptx_literal_value(text, t.start, t.len, t.kind);
+        if (type >= PTX_TAG_NEG_LO) v = 0 - v;
+        if (type & 1u) { words[j] = (uint32_t)(v >> 32); return; }
+        words[j] = (uint32_t)v;
+        if (i + 1 < cs.info[e.tmpl].n_words && cs.tmpl_tags[at + 1] == (uint16_t)(g + 0x100u)) words[j + 1] = (uint32_t)(v >> 32);
+    }
+};
+
 // ------------------------------------------------------------------------------------------------ stage C: decode
 template <class BK>
 inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
@@ -562,6 +621,11 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     // C0: ordinal of the enclosing top-level unit
     bk.template scan<uint32_t>("scan_toplevel_ordinal", n_units, [=] PTX_HD(size_t u) { return (udepth[u] & 0x7FFFFFFFu) == 0 ? 1u : 0u; },
                                [=] PTX_HD(size_t u, uint32_t v) { udir[u] = v; }, AddOp(), 0u);
+    // ... and the unit that heads each top-level ordinal (a module's first unit, or a top-level directive's first)
+    uint32_t* top_unit = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
+    bk.pf("list_toplevel_units", n_units, [=] PTX_HD(size_t u) {
+        if ((udepth[u] & 0x7FFFFFFFu) == 0) top_unit[udir[u] - 1] = (uint32_t)u;
+    });
     // Very long top-level statements (arrays with huge initialisers) are listed for the bulk path
     PtxBulkInfo* bulk_info = (PtxBulkInfo*)bk.alloc(sizeof(PtxBulkInfo) * PTX_MAX_BULK);
     bk.pf("reset_bulk", 1, [=] PTX_HD(size_t) { counters->n_bulk = 0; });
@@ -943,38 +1007,53 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         }
         return ret;
     });
-    // C2: do consecutive units meet, and does every module return to depth 0?
+    // C2: do consecutive units meet, and does every module return to depth 0?  Where they do not, everything from
+    // the top-level directive that holds the first such place to the end of the module is parsed again by one thread
+    // with the reference's recovery rules; the directives in front of it keep their units.  (A module that does not
+    // return to depth 0 went wrong in or behind its last top-level unit: nothing behind an unclosed scope is one.)
+    // mod_bad[m] = 1 + the unit that heads the first bad directive, 0 = none
     bk.pf("chain_check", n_units, [=] PTX_HD(size_t u) {
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         if (mod_skip[m]) return;
         uint32_t next = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
         bool ok = ustatus[u] == US_OK && uend[u] == next;
         if (u + 1 == mub[m + 1]) ok = ok && mod_final_scope[m] == 0;
-        if (!ok) mod_bad[m] = 1;
+        if (ok) return;
+        const uint32_t head = top_unit[udir[u] - 1];
+#ifdef __CUDA_ARCH__
+        atomicMax(&mod_bad[m], 0xFFFFFFFFu - head);       // the smallest head wins
+#else
+        if (0xFFFFFFFFu - head > mod_bad[m]) mod_bad[m] = 0xFFFFFFFFu - head;
+#endif
     });
-    // C3: modules whose units do not meet are parsed sequentially by one thread each (count)
+    bk.pf("first_bad_directive", n_modules, [=] PTX_HD(size_t m) {
+        if (mod_bad[m]) mod_bad[m] = (0xFFFFFFFFu - mod_bad[m]) + 1u;
+    });
+    // C3: the sequential parse, one thread per such module (count)
     bk.pf("sequential_count", n_modules, [=] PTX_HD(size_t m) {
         if (!mod_bad[m]) return;
         counters->any_sequential = 1;
+        const uint32_t head = mod_bad[m] - 1u;
         PtxSink sink;
         PtxResolver res;
         PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
         d.bulk = bulk_table;
-        int st = ptx_decode_module_sequential(d, mtb[m], 0);
+        int st = ptx_decode_module_sequential(d, ustart[head], 0, head != mub[m]);
         PtxPair sz;
         sz.a = sink.peak;
         sz.b = sink.ne;
         mod_seq[m] = sz;
         mod_seq_status[m] = (uint32_t)st;
     });
-    // C4: sizes of sequential modules replace those of their units
+    // C4: its sizes replace those of the units it covers
     bk.pf("merge_sequential_sizes", n_units, [=] PTX_HD(size_t u) {
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
-        if (!mod_bad[m]) return;
+        if (!mod_bad[m] || u < mod_bad[m] - 1u) return;
         PtxPair z;
         z.a = z.b = 0;
-        usize[u + 1] = (u == mub[m]) ? mod_seq[m] : z;
-        uflag[u] = (u == mub[m]) ? 1 : 2;    // the module's first unit stands for the whole module in C6; the others write nothing
+        const bool head = u == mod_bad[m] - 1u;
+        usize[u + 1] = head ? mod_seq[m] : z;
+        uflag[u] = head ? 1 : 2;    // the head unit stands for the whole tail in C6; the others write nothing
     });
     bk.template scan<PtxPair>("scan_unit_sizes", (size_t)n_units + 1, [=] PTX_HD(size_t i) { return usize[i]; },
                               [=] PTX_HD(size_t i, PtxPair v) { usize[i] = v; }, PairAddOp(), PtxPair{0, 0});
@@ -992,41 +1071,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     // templated ones are instantiated from the class template and the unit's own tokens
     // Literal values are converted in a second round, one thread per literal with the warps full: the low-word thread
     // also writes the high word when the template has it next (the two value words of an immediate)
-    bk.pf_segments2(
-        "emit_records", n_units, usize,
-        [=] PTX_HD(size_t u, uint32_t i, uint32_t j) -> bool {
-            uint8_t fl = uflag[u];
-            if (fl == PTX_UNIT_STAGED) {
-                words[j] = table[u * PTX_TMP_STRIDE + i];
-                return false;
-            }
-            if (fl != PTX_UNIT_TEMPLATED) return false;
-            size_t at = (size_t)utmpl[u] * PTX_TMPL_WORDS + i;
-            uint32_t x = cs.tmpl_words[at], g = cs.tmpl_tags[at];
-            if (g) {
-                const uint32_t type = g >> 8;
-                if (type >= PTX_TAG_VAL_LO) {
-                    if (!(type & 1u)) return true;      // low word: second round
-                    // high word: written by the low-word thread in front of it, unless it stands alone
-                    if (i > 0 && cs.tmpl_tags[at - 1] == (uint16_t)(g - 0x100u)) return false;
-                    return true;
-                }
-                const PtxToken t = tokens[ustart[u] + (g & 0xFFu)];
-                x = type == PTX_TAG_START ? t.start : type == PTX_TAG_LEN ? (uint32_t)t.len : ((x & 0xFFu) | ((uint32_t)t.len << 8));
-            }
-            words[j] = x;
-            return false;
-        },
-        [=] PTX_HD(size_t u, uint32_t i, uint32_t j) {
-            size_t at = (size_t)utmpl[u] * PTX_TMPL_WORDS + i;
-            const uint32_t g = cs.tmpl_tags[at], type = g >> 8;
-            const PtxToken t = tokens[ustart[u] + (g & 0xFFu)];
-            uint64_t v = ptx_literal_value(text, t.start, t.len, t.kind);
-            if (type >= PTX_TAG_NEG_LO) v = 0 - v;
-            if (type & 1u) { words[j] = (uint32_t)(v >> 32); return; }
-            words[j] = (uint32_t)v;
-            if (i + 1 < cs.info[utmpl[u]].n_words && cs.tmpl_tags[at + 1] == (uint16_t)(g + 0x100u)) words[j + 1] = (uint32_t)(v >> 32);
-        });
+    bk.emit_records("emit_records", n_units, usize, PtxEmitStep{uflag, utmpl, ustart, table, cs, tokens, text, words});
     if (host_counters.n_flagged) {
         // function table for `call`
         uint32_t mask = 1;
@@ -1059,13 +1104,21 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         sink.errs = errs + usize[u].b;
         uint64_t text_end = layout[m].text_off + layout[m].text_len;
         if (mod_skip[m]) return;
-        if (mod_bad[m]) {
-            if (u != mub[m]) return;
+        if (mod_bad[m] && u >= mod_bad[m] - 1u) {
+            if (u != mod_bad[m] - 1u) return;
+            // functions declared in the tail are found through the records written so far, those in front of it
+            // through the table of the speculated function headers
             PtxResolver res;
             res.words = words;
+            res.entries = fn_entries;
+            res.slots = slots;
+            res.mask = mask;
+            res.unit_off = usize;
+            res.module = m;
+            res.my_dir_ord = udir[u];
             PtxDecoder d(text, tokens, mtb[m + 1], text_end, sink, res);
             d.bulk = bulk_table;
-            ptx_decode_module_sequential(d, mtb[m], usize[u].a);
+            ptx_decode_module_sequential(d, ustart[u], usize[u].a, u != mub[m]);
             if (sink.peak != usize[u + 1].a - usize[u].a || sink.ne != usize[u + 1].b - usize[u].b) counters->pad = (uint32_t)u + 1;
             sink.pad_to(usize[u + 1].a - usize[u].a);
             return;
@@ -1119,8 +1172,9 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         r.word_end = n_units ? usize[mub[m + 1]].a : 0;
         r.err_begin = n_units ? usize[mub[m]].b : 0;
         r.err_end = n_units ? usize[mub[m + 1]].b : 0;
-        r.sequential = mod_bad[m];
+        r.sequential = mod_bad[m] ? 1u : 0u;
         r.status = mod_seq_status[m];
+        r.seq_tokens = mod_bad[m] ? mtb[m + 1] - ustart[mod_bad[m] - 1u] : 0u;
         results[m] = r;
     });
     bk.download(&host_counters, counters, sizeof(PtxCounters));   // .pad != 0: unit (index + 1) whose two passes disagreed
