@@ -46,9 +46,14 @@ enum {
     PTXFE_MODULE_OK = 0,        /* checked: Ok(module); unchecked: a module was returned */
     PTXFE_MODULE_ERR = 1,       /* checked: Err(errors); unchecked: Module::empty() (ptx_parser/src/ast.rs:2008-2016) */
     PTXFE_MODULE_REF_PANICS = 2, /* input on which the reference unwraps an empty slice (lib.rs:939) */
-    PTXFE_MODULE_REF_DIVERGES = 3 /* damage below deeply nested blocks: the reference's statement recovery re-parses the
+    PTXFE_MODULE_REF_DIVERGES = 3, /* damage below deeply nested blocks: the reference's statement recovery re-parses the
                                      contents of every enclosing block and doubles its work per level (lib.rs:858-880,
                                      921-951); given up after 4 * tokens + 1024 statement attempts, no module, no errors */
+    PTXFE_MODULE_SEQ_REFUSED = 4   /* no counterpart in the reference.  A module whose structure is damaged is parsed with
+                                     the reference's recovery rules by ONE device thread from the top-level directive with
+                                     the first damage to its end (about a microsecond per token, twice).  A tail of more
+                                     than 2 Mi tokens (environment: PTXFE_SEQ_MAX_TOKENS) is refused instead of running
+                                     for minutes: no module, no errors.  Parse such a module on the CPU. */
 };
 
 typedef struct ptxfe_stats {

@@ -187,6 +187,7 @@ extern "C" {
 char* emu_parse(const char* const* texts, const uint64_t* lens, uint32_t n, uint32_t mode, uint64_t* out_len, uint64_t* stats) {
     HostBackend bk;
     PtxWork w;
+    if (const char* e = getenv("PTXFE_SEQ_MAX_TOKENS")) w.seq_max_tokens = (uint32_t)strtoul(e, nullptr, 10);
     std::vector<PtxModuleLayout> layout(n);
     std::vector<uint32_t> mcb(n + 1);
     uint64_t off = 0;

@@ -207,6 +207,21 @@ def test_damage_is_confined_to_the_tail(oracle, ctx):
     assert n_sequential >= 30
 
 
+def test_long_sequential_tail_is_refused(oracle, ctx, monkeypatch):
+    text, front = cases.confined_damage_cases()[1]
+    fine = cases.HEADER + ".global .u32 fine;\n"
+    monkeypatch.setenv("PTXFE_SEQ_MAX_TOKENS", "1000")
+    b = ctx.parse_batch([text, fine], 1)
+    assert b.dump(0) == "mode: unchecked\nstatus: SequentialPathRefused\nerrors: 0\n"
+    assert b.status(0) == 4 and b.error_count(0) == 0
+    assert b.dump(1) == oracle.parse(fine, 1)[1] and b.status(1) == 0
+    b.free()
+    monkeypatch.delenv("PTXFE_SEQ_MAX_TOKENS")
+    b = ctx.parse_batch([text], 1)
+    assert b.dump(0) == oracle.parse(text, 1)[1]
+    b.free()
+
+
 def test_large_truncated_module(oracle, ctx):
     """A 4 MB module cut off in the middle of its last function (what a dump of a crashed process looks like): only
     that function goes through the one-thread parser, and the module costs milliseconds, not seconds."""

@@ -205,6 +205,17 @@ def test_damage_is_confined_to_the_tail(oracle, emu):
     assert n_sequential >= 30
 
 
+def test_long_sequential_tail_is_refused(oracle, emu, monkeypatch):
+    """The one-thread parser does not take on a tail above its token limit: the module's verdict says so."""
+    text, front = cases.confined_damage_cases()[1]
+    monkeypatch.setenv("PTXFE_SEQ_MAX_TOKENS", "1000")
+    dumps, st = emu.parse([text, cases.HEADER + ".global .u32 fine;\n"], 1)
+    assert dumps[0] == "mode: unchecked\nstatus: SequentialPathRefused\nerrors: 0\n"
+    assert dumps[1] == oracle.parse(cases.HEADER + ".global .u32 fine;\n", 1)[1]
+    monkeypatch.setenv("PTXFE_SEQ_MAX_TOKENS", "100000")
+    assert emu.parse([text], 1)[0][0] == oracle.parse(text, 1)[1]
+
+
 def test_reference_fixtures(oracle, emu):
     texts = list(reference_fixtures.texts().values())
     assert len(texts) >= 240

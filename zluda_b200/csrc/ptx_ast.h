@@ -106,7 +106,7 @@ struct Error {
     bool lexer = false;
     uint64_t lex_start = 0;
 };
-enum { V_OK = 0, V_ERR, V_MODULE, V_EMPTY, V_ERRORS, V_PANICS, V_DIVERGES };
+enum { V_OK = 0, V_ERR, V_MODULE, V_EMPTY, V_ERRORS, V_PANICS, V_DIVERGES, V_REFUSED };
 struct Module {
     int verdict = V_ERR;
     bool have_module = false;       // the reference returns a module (checked: Ok; unchecked: not Module::empty())
@@ -346,8 +346,8 @@ inline void materialize(const PtxBatchView& v, uint32_t mi, Module* out) {
         e.lex_start = v.lexerrs[2 * (size_t)i] - base;
         m.errors.push_back(e);
     }
-    if (res.sequential && (res.status & US_MASK) == US_DIVERGE && !skip_parse) {
-        m.verdict = V_DIVERGES;
+    if (res.sequential && ((res.status & US_MASK) == US_DIVERGE || (res.status & US_MASK) == US_REFUSED) && !skip_parse) {
+        m.verdict = (res.status & US_MASK) == US_DIVERGE ? V_DIVERGES : V_REFUSED;
         m.errors.clear();
         return;
     }
@@ -664,9 +664,9 @@ inline std::string print(const PtxBatchView& v, uint32_t mi, const Module& m) {
     ptxdump::Out o;
     Printer p{o};
     ptxdump::Reader r(v, mi);
-    static const char* const verdicts[] = {"Ok", "Err", "Module", "Empty", "Errors", "ReferencePanics", "ReferenceDiverges"};
+    static const char* const verdicts[] = {"Ok", "Err", "Module", "Empty", "Errors", "ReferencePanics", "ReferenceDiverges", "SequentialPathRefused"};
     o.putf("mode: %s\nstatus: %s\n", v.mode == 0 ? "checked" : v.mode == 1 ? "unchecked" : "errors", verdicts[m.verdict]);
-    if (m.verdict == V_DIVERGES) { o.put("errors: 0\n"); return std::move(o.s); }
+    if (m.verdict == V_DIVERGES || m.verdict == V_REFUSED) { o.put("errors: 0\n"); return std::move(o.s); }
     if (m.have_module) {
         uint64_t kept = m.directives.size();
         o.putf("Module { ptx_version: (%u, %u), sm_version: %u, address_size: %u, invalid_directives: %llu, directives: %llu }\n", m.major, m.minor,

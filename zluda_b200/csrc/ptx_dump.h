@@ -489,8 +489,8 @@ inline std::string dump_module(const PtxBatchView& v, uint32_t m, int* status_ou
         else if (d.kind == U_FUNC || d.kind == U_MODVAR) kept++;
     }
     bool panicked = res.sequential && (res.status & US_MASK) == US_PANIC;
-    if (res.sequential && (res.status & US_MASK) == US_DIVERGE && !skip_parse) {
-        o.putf("mode: %s\nstatus: ReferenceDiverges\nerrors: 0\n", mode_name);
+    if (res.sequential && ((res.status & US_MASK) == US_DIVERGE || (res.status & US_MASK) == US_REFUSED) && !skip_parse) {
+        o.putf("mode: %s\nstatus: %s\nerrors: 0\n", mode_name, (res.status & US_MASK) == US_DIVERGE ? "ReferenceDiverges" : "SequentialPathRefused");
         if (status_out) *status_out = 1;
         if (hash_out) { o.fold(); *hash_out = o.h; }
         return std::move(o.s);

@@ -3,7 +3,10 @@
 #pragma once
 #include "ptx_decode.h"
 
-enum PtxUnitStatus { US_OK = 0, US_FAIL = 1, US_PANIC = 2, US_DIVERGE = 3 };
+enum PtxUnitStatus { US_OK = 0, US_FAIL = 1, US_PANIC = 2, US_DIVERGE = 3, US_REFUSED = 4 };
+// The sequential parser is one thread at about a microsecond per token and pass: a damaged tail longer than this is not
+// parsed at all and its module gets the verdict SequentialPathRefused (a bound on the running time of one launch).
+#define PTX_SEQ_MAX_TOKENS (2u << 20)
 #define US_MASK 0xFu
 #define US_MODULE_FAILED 0x10u     // sequential path: the module-level parse failed (a U_MODULE_FAIL record was written)
 

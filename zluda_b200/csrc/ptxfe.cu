@@ -1058,6 +1058,7 @@ static int run_pipeline(ptxfe_ctx* ctx, uint8_t* text, const PtxModuleLayout* la
     PtxWork& w = ctx->work;
     w = PtxWork();
     w.first_slice = first_slice;
+    if (const char* e = getenv("PTXFE_SEQ_MAX_TOKENS")) w.seq_max_tokens = (uint32_t)strtoul(e, nullptr, 10);
     w.text = text;
     w.n_modules = n;
     w.n_chunks = chunks;
@@ -1495,6 +1496,7 @@ int ptxfe_module_status(const ptxfe_batch* b, uint32_t i) {
     const uint32_t n_lex = r.lexerr_end - r.lexerr_begin;
     if (n_lex && b->mode != PTXFE_ERRORS_ONLY) return PTXFE_MODULE_ERR;      // not parsed (lib.rs:447-449, 487-489)
     if (r.sequential && (r.status & US_MASK) == US_DIVERGE) return PTXFE_MODULE_REF_DIVERGES;
+    if (r.sequential && (r.status & US_MASK) == US_REFUSED) return PTXFE_MODULE_SEQ_REFUSED;
     if (r.sequential && (r.status & US_MASK) == US_PANIC) return PTXFE_MODULE_REF_PANICS;
     if (b->mode == PTXFE_ERRORS_ONLY) return PTXFE_MODULE_ERR;               // no module is returned in this mode
     const bool parsed_ok = r.word_end > r.word_begin && !(r.status & US_MODULE_FAILED);
@@ -1508,7 +1510,7 @@ uint32_t ptxfe_module_error_count(const ptxfe_batch* b, uint32_t i) {
     const PtxModuleResult& r = b->results[i];
     const uint32_t n_lex = r.lexerr_end - r.lexerr_begin;
     if (n_lex && b->mode != PTXFE_ERRORS_ONLY) return n_lex;
-    if (r.sequential && (r.status & US_MASK) == US_DIVERGE) return 0;
+    if (r.sequential && ((r.status & US_MASK) == US_DIVERGE || (r.status & US_MASK) == US_REFUSED)) return 0;
     // a module without tokens: the implicit Parser error of the reference (the header does not parse)
     return n_lex + r.n_errors + (r.word_end == r.word_begin ? 1u : 0u);
 }

@@ -273,6 +273,7 @@ struct PtxWork {
     uint32_t* lexerrs = nullptr;           // [2 * n_lexerrs]
     uint32_t* mod_tok_begin = nullptr;     // [n_modules + 1]
     bool first_slice = true;               // the class store is emptied before the first slice of a batch
+    uint32_t seq_max_tokens = PTX_SEQ_MAX_TOKENS;   // longest tail the sequential parser takes on
     uint16_t* kinds = nullptr;             // [n_tokens] tokens[i].kind | min(tokens[i].len, 127) << 9
     int32_t* mod_final_scope = nullptr;    // [n_modules] scope depth behind the module's last token
     uint32_t* unit_start = nullptr;        // [n_units + 1]
@@ -606,6 +607,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     const uint32_t* mod_skip = w.mod_skip;
     PtxModuleResult* results = w.results;
     PtxCounters* counters = w.counters;
+    const uint32_t seq_max_tokens = w.seq_max_tokens;
     uint32_t* uend = w.unit_end = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
     uint32_t* udir = w.unit_dir = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
     PtxPair* usize = w.unit_size = (PtxPair*)bk.alloc(sizeof(PtxPair) * ((size_t)n_units + 2));
@@ -1034,6 +1036,10 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         if (!mod_bad[m]) return;
         counters->any_sequential = 1;
         const uint32_t head = mod_bad[m] - 1u;
+        if (mtb[m + 1] - ustart[head] > seq_max_tokens) {
+            mod_seq_status[m] = US_REFUSED;       // sizes stay 0: the module's verdict says so, nothing is parsed
+            return;
+        }
         PtxSink sink;
         PtxResolver res;
         PtxDecoder d(text, tokens, mtb[m + 1], layout[m].text_off + layout[m].text_len, sink, res);
@@ -1105,7 +1111,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         uint64_t text_end = layout[m].text_off + layout[m].text_len;
         if (mod_skip[m]) return;
         if (mod_bad[m] && u >= mod_bad[m] - 1u) {
-            if (u != mod_bad[m] - 1u) return;
+            if (u != mod_bad[m] - 1u || (mod_seq_status[m] & US_MASK) == US_REFUSED) return;
             // functions declared in the tail are found through the records written so far, those in front of it
             // through the table of the speculated function headers
             PtxResolver res;
