@@ -248,6 +248,17 @@ def confined_damage_cases(n_funcs=12, n_instr=60):
     return out
 
 
+STRAY_TOKENS = ["}", "(", ")", "foo", "foo bar baz;", ":", ",", ".entry", ".global", "12345", "mov.v2.u32 {%r1, %r2, %r3;"]
+
+
+def stray_token_modules(text, at_fraction=0.5):
+    """`text` (bytes) with one stray token on a line of its own at a line start near the given fraction: damage that
+    the speculated units recover from without the sequential parser ('{' is not among them: an unclosed scope changes
+    what everything behind it means, in the reference as well)."""
+    at = text.find(b"\n", int(at_fraction * len(text))) + 1
+    return [text[:at] + tok.encode() + b"\n" + text[at:] for tok in STRAY_TOKENS]
+
+
 def negative_decimal_side_file(n=1000):
     """Module-level scalars initialised with NEGATIVE decimal floats and integers: the reference has no rule for '-' in
     front of a float literal (ptx_parser/src/lib.rs:366-377), so every float directive must be rejected the same way,

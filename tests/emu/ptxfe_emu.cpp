@@ -123,18 +123,18 @@ struct HostBackend {
                 agg[t] = sx_aggregate(a, th[t]);
             });
             for (uint32_t t = 0; t < SX_THREADS; t++) { before[t] = run; run = op(run, agg[t]); }
-            phase([&](uint32_t t) { starts[t] = sx_decide(a, th[t], before[t]); });
+            phase([&](uint32_t t) { starts[t] = sx_decide(a, th[t], sx_depth(before[t])); });
             // the bitwise case against the token-by-token case, thread by thread
             for (uint32_t t = 0; t < SX_THREADS; t++) {
                 if (!th[t].fast) continue;
                 SxThread slow;
                 sx_load(a, th[t].tb, slow, table, true, false);
                 PtxSeg3 x = sx_aggregate(a, slow);
-                if (x.scope != agg[t].scope || x.paren != agg[t].paren || x.flag != agg[t].flag || sx_decide(a, slow, before[t]) != starts[t])
+                if (x.scope != agg[t].scope || sx_depth(x) != sx_depth(agg[t]) || x.flag != agg[t].flag || sx_decide(a, slow, sx_depth(before[t])) != starts[t])
                     fail("structure: the bitwise case and the token-by-token case disagree");
             }
             for (uint32_t t = 0; t < SX_THREADS; t++) { ubefore[t] = units; units += sx_popc(starts[t]); }
-            phase([&](uint32_t t) { sx_write(a, th[t], before[t], starts[t], ubefore[t]); });
+            phase([&](uint32_t t) { sx_write(a, th[t], sx_depth(before[t]), starts[t], ubefore[t]); });
         }
     }
     template <class F> void pf_staged(const char* name, size_t n, uint32_t* table, uint32_t row_words, F f) {

@@ -207,6 +207,21 @@ def test_damage_is_confined_to_the_tail(oracle, ctx):
     assert n_sequential >= 30
 
 
+def test_stray_tokens_in_a_large_module(oracle, ctx):
+    """One stray token in the middle of a function body of a 4 MB module: recovered by the speculated units, no
+    sequential parse, milliseconds."""
+    text = corpus.config1(n_modules=1, total_bytes=4 << 20)[0]
+    mods = cases.stray_token_modules(text)
+    b = ctx.parse_batch(mods, 1)
+    st = ctx.stats()
+    expect = oracle.dump_hashes(mods, 1)
+    assert [b.dump_hash(i) for i in range(len(mods))] == expect
+    assert all(b.error_count(i) >= 1 for i in range(len(mods)))
+    b.free()
+    assert st["n_sequential"] == 0, st
+    assert st["kernel_ms"] < 10.0 * len(mods), st
+
+
 def test_long_sequential_tail_is_refused(oracle, ctx, monkeypatch):
     text, front = cases.confined_damage_cases()[1]
     fine = cases.HEADER + ".global .u32 fine;\n"

@@ -205,6 +205,15 @@ def test_damage_is_confined_to_the_tail(oracle, emu):
     assert n_sequential >= 30
 
 
+def test_stray_tokens_need_no_sequential_parse(oracle, emu):
+    text = corpus.config1(n_modules=1, total_bytes=300000)[0]
+    for t in cases.stray_token_modules(text):
+        for mode in (0, 1):
+            dumps, st = emu.parse([t], mode)
+            assert dumps[0] == oracle.parse(t, mode)[1]
+            assert st["sequential"] == 0
+
+
 def test_long_sequential_tail_is_refused(oracle, emu, monkeypatch):
     """The one-thread parser does not take on a tail above its token limit: the module's verdict says so."""
     text, front = cases.confined_damage_cases()[1]

@@ -1,11 +1,21 @@
-// Stage B in one pass over the token kinds: scope / parenthesis depth (a segmented scan that restarts at every
-// module), the decision "a parse unit starts at this token", the numbering of the unit starts, and the unit table
-// (start token, depth in front of it, first unit of every module, scope depth behind every module's last token).
+// Stage B in one pass over the token kinds: scope depth (a segmented scan that restarts at every module), the decision
+// "a parse unit starts at this token", the numbering of the unit starts, and the unit table (start token, depth in
+// front of it, first unit of every module, scope depth behind every module's last token).
+//
+// Depth.  '{' that opens a scope counts +1, '}' that closes one counts -1 but never below 0: at the top level the
+// reference's directive recovery skips a '}' like any other token (lib.rs:590-607), so a stray '}' in a function body
+// ends the function early and must not throw off everything behind it.  "Add, but not below a floor" composes:
+// f(x) = max(x + a, b) with (a2, b2) after (a1, b1) = (a1 + a2, max(b1 + a2, b2)); that pair is what the scan carries
+// (PtxSeg3: scope = a, paren = b, flag = a module begins inside, everything in front is forgotten), and the depth
+// behind a prefix P of a module is max(P.scope, P.paren).
+//
+// Unit starts, for a token that does not begin a module:
+//   at depth 0: a directive keyword that does not continue a run of linking keywords and is not the state space of a
+//     `.ptr` parameter (lib.rs:973), and the token behind a scope-closing '}' (what follows a function; anything but a
+//     directive keyword there is skipped up to the next one by the directive's recovery);
+//   inside a scope: the token behind ';', ':' or a scope brace, and a scope brace itself.
 //
 // The work is cut into tiles of SX_TILE tokens; a tile is SX_THREADS threads with SX_ITEMS consecutive tokens each.
-// Everything a thread needs of its tokens sits in registers: the 16 kinds, the three kinds in front of them (a brace is
-// classified by two tokens of left context, and a unit start looks at the class of the token before it), and one bit
-// per token for "first token of a module" (found by a binary search of the module table, not stored per token).
 // Per tile: thread aggregates -> ordered scan over the tile's threads -> the prefix of the tiles before (the backend's
 // business: a look-back chain on the device, a running value in the host emulation) -> the start decisions -> their
 // count, scanned the same way -> the unit table rows.  The functions here are the per-thread bodies of those steps.
@@ -26,15 +36,32 @@ struct PtxStructArgs {
     PtxCounters* counters;        // out: n_units
 };
 
+// the scan's operator and what a prefix says about the depth
+struct SegDepthOp {
+    PTX_HD PtxSeg3 operator()(PtxSeg3 x, PtxSeg3 y) const {
+        if (y.flag) return y;
+        PtxSeg3 r;
+        r.scope = x.scope + y.scope;
+        r.paren = x.paren + y.scope > y.paren ? x.paren + y.scope : y.paren;
+        r.flag = x.flag;
+        return r;
+    }
+};
+PTX_HD inline int32_t sx_depth(PtxSeg3 p) { return p.scope > p.paren ? p.scope : p.paren; }
+// one token: delta d (+1, 0, -1) applied to the pair
+PTX_HD inline void sx_step(PtxSeg3& v, int d) {
+    v.scope += d;
+    v.paren += d;
+    if (v.paren < 0) v.paren = 0;
+}
+
 // ---- flags of a token kind, one byte: what the structure pass wants to know of a token
-enum : uint32_t { SXF_L = 1, SXF_R = 2, SXF_OPENS = 4, SXF_LP = 8, SXF_RP = 16, SXF_S = 32, SXF_DIR = 64, SXF_SECTION = 128 };
+enum : uint32_t { SXF_L = 1, SXF_R = 2, SXF_OPENS = 4, SXF_S = 32, SXF_DIR = 64, SXF_SECTION = 128 };
 PTX_HD inline uint32_t sx_flags(uint32_t k) {
     uint32_t f = 0;
     if (k == T_LBRACE) f |= SXF_L;
     if (k == T_RBRACE) f |= SXF_R;
     if (ptx_opens_operand((uint16_t)k)) f |= SXF_OPENS;
-    if (k == T_LPAREN) f |= SXF_LP;
-    if (k == T_RPAREN) f |= SXF_RP;
     if (k == T_SEMI || k == T_COLON) f |= SXF_S;
     if (ptx_is_directive_start((uint16_t)k)) f |= SXF_DIR;
     if (k == T_DOT_SECTION) f |= SXF_SECTION;
@@ -61,15 +88,15 @@ PTX_HD inline uint32_t sx_lowest(uint32_t x) {     // x != 0
 // and four tokens are judged by one bitwise operation.  One-bit-per-token results are kept as "spread" masks: token i
 // at bit 8 * (i / 4) + i % 4, which keeps the tokens in order (so "the tokens before i" is a mask of lower bits) and
 // leaves the upper half of every byte for a second mask:
-//   braces: scope-opening '{' (low halves) and scope-closing '}' (high halves);  parens: '(' and ')';
+//   braces: scope-opening '{' (low halves) and scope-closing '}' (high halves);
 //   marks: previous token is ';' or ':' (low halves) and directive keywords (high halves).
 // Threads of the other case go token by token and read the kinds again.
 struct SxThread {
     uint32_t tb, n_valid;
     uint32_t first;               // bit i: token tb - 3 + i is the first token of a module
     bool fast;
-    uint32_t braces, parens, marks;
-    uint32_t brace_before;        // the token in front of the thread's first is a scope brace
+    uint32_t braces, marks;
+    uint32_t brace_before;        // the token in front of the thread's first: bit 0 = a scope brace, bit 1 = a closing one
 };
 // token-by-token case: the kinds of the thread's tokens and the three in front, w[3 + k] = token tb + k
 struct SxWindow {
@@ -116,7 +143,7 @@ PTX_HD inline void sx_load(const PtxStructArgs& a, uint32_t tb, SxThread& t, con
     t.n_valid = tb >= a.n_tokens ? 0u : (a.n_tokens - tb < SX_ITEMS ? a.n_tokens - tb : SX_ITEMS);
     t.first = 0;
     t.fast = false;
-    t.braces = t.parens = t.marks = t.brace_before = 0;
+    t.braces = t.marks = t.brace_before = 0;
     if (!t.n_valid) return;
     if (has_first) {
         // module begins inside [tb - 3, tb + 16)
@@ -152,19 +179,18 @@ PTX_HD inline void sx_load(const PtxStructArgs& a, uint32_t tb, SxThread& t, con
     const uint32_t h1 = table[PTX_KL_KIND(halo.h[1])], h2 = table[PTX_KL_KIND(halo.h[2])], h3 = table[PTX_KL_KIND(halo.h[3])];
     const uint32_t P1[4] = {(F[3] << 8) | h3, F[0], F[1], F[2]};          // the token before
     const uint32_t P2[4] = {(F[2] << 8) | h2, P1[0], F[0], F[1]};         // the token two before
-    uint32_t braces = 0, parens = 0, marks = 0;
+    uint32_t braces = 0, marks = 0;
 #pragma unroll
     for (uint32_t r = 0; r < 4; r++) {
         const uint32_t f = F[r], p1 = P1[r], p2 = P2[r];
         const uint32_t plus = f & ~(p1 >> 2) & ~(p2 >> 7) & SX_ONES;                   // '{' not after an operand opener or .section x
         const uint32_t minus = (f >> 1) & (p1 | (p1 >> 1) | (p1 >> 5)) & SX_ONES;      // '}' after ';' ':' '{' '}'
         braces |= (plus << r) | (minus << (4u + r));
-        parens |= (((f >> 3) & SX_ONES) << r) | (((f >> 4) & SX_ONES) << (4u + r));
         marks |= (((p1 >> 5) & SX_ONES) << r) | (((f >> 6) & SX_ONES) << (4u + r));
     }
-    t.braces = braces; t.parens = parens; t.marks = marks;
+    t.braces = braces; t.marks = marks;
     const uint32_t plus_h = h3 & ~(h2 >> 2) & ~(h1 >> 7) & 1u, minus_h = (h3 >> 1) & (h2 | (h2 >> 1) | (h2 >> 5)) & 1u;
-    t.brace_before = plus_h | minus_h;
+    t.brace_before = plus_h | minus_h | (minus_h << 1);
 }
 
 // scope delta of the token at window index x (x >= 3): see ptx_brace_class
@@ -185,12 +211,16 @@ PTX_HD inline int sx_brace_before(const SxWindow& win, const SxThread& t) {
     return t.tb ? sx_brace(win, t, 2) : 0;
 }
 
-// step 1: the thread's aggregate (flag = a module begins among its tokens; depths counted from the last such begin)
+// step 1: the thread's aggregate (flag = a module begins among its tokens)
 PTX_HD inline PtxSeg3 sx_aggregate(const PtxStructArgs& a, const SxThread& t) {
-    if (t.fast)
-        return PtxSeg3{(int32_t)sx_popc(t.braces & SX_LOW) - (int32_t)sx_popc(t.braces & ~SX_LOW),
-                       (int32_t)sx_popc(t.parens & SX_LOW) - (int32_t)sx_popc(t.parens & ~SX_LOW), 0};
     PtxSeg3 v{0, 0, 0};
+    if (t.fast) {
+        const uint32_t plus = t.braces & SX_LOW, minus = (t.braces >> 4) & SX_LOW;
+        if (!minus) return PtxSeg3{(int32_t)sx_popc(plus), 0, 0};
+#pragma unroll 1
+        for (uint32_t k = 0; k < SX_ITEMS; k++) sx_step(v, (int)((plus >> sx_pos(k)) & 1u) - (int)((minus >> sx_pos(k)) & 1u));
+        return v;
+    }
     if (!t.n_valid) return v;
     SxWindow win;
     sx_window(a, t, win);
@@ -198,20 +228,20 @@ PTX_HD inline PtxSeg3 sx_aggregate(const PtxStructArgs& a, const SxThread& t) {
     for (uint32_t k = 0; k < t.n_valid; k++) {
         uint32_t x = 3 + k;
         if ((t.first >> x) & 1u) v = PtxSeg3{0, 0, 1};
-        v.scope += sx_brace(win, t, x);
-        const uint16_t kk = win.w[x];
-        v.paren += kk == T_LPAREN ? 1 : kk == T_RPAREN ? -1 : 0;
+        sx_step(v, sx_brace(win, t, x));
     }
     return v;
 }
 
-// step 2: with the depths in front of the thread's first token: where units start, as a spread mask; the scope depth
-// behind a module's last token goes to mod_final_scope.  The rule, for a token that does not begin a module: at the
-// top level (scope depth 0, outside parentheses) a directive keyword that does not continue a run of linking keywords;
-// inside a scope, the token after ';', ':' or a scope brace, and a scope brace itself.
+PTX_HD inline bool sx_continues(uint16_t prev) {      // a directive keyword behind one of these is no start
+    return prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak || prev == T_DOT_PTR;
+}
+
+// step 2: with the depth in front of the thread's first token: where units start, as a spread mask; the scope depth
+// behind a module's last token goes to mod_final_scope.
 // Token by token from the kinds; with write set, the rows of the unit table are written as well (step 3).
-PTX_HD inline uint32_t sx_walk(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before, bool write, uint32_t units_before) {
-    int32_t sd = before.scope, pd = before.paren;
+PTX_HD inline uint32_t sx_walk(const PtxStructArgs& a, const SxThread& t, int32_t depth, bool write, uint32_t units_before) {
+    int32_t sd = depth;
     uint32_t starts = 0, u = units_before;
     if (!t.n_valid) return 0;
     SxWindow win;
@@ -226,10 +256,9 @@ PTX_HD inline uint32_t sx_walk(const PtxStructArgs& a, const SxThread& t, PtxSeg
         if (first) {
             if (j) a.mod_final_scope[ptx_upper_bound_u32(a.mtb, a.n_modules, j - 1) - 1] = sd;
             start = true;
-            sd = pd = 0;
-        } else if (sd <= 0) {
-            const uint16_t prev = win.w[x - 1];
-            start = sd == 0 && pd == 0 && ptx_is_directive_start(kk) && !(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak);
+            sd = 0;
+        } else if (sd == 0) {
+            start = (ptx_is_directive_start(kk) && !sx_continues(win.w[x - 1])) || bc_prev < 0;
         } else {
             const uint16_t prev = win.w[x - 1];
             start = prev == T_SEMI || prev == T_COLON || bc != 0 || bc_prev != 0;
@@ -238,13 +267,13 @@ PTX_HD inline uint32_t sx_walk(const PtxStructArgs& a, const SxThread& t, PtxSeg
             starts |= 1u << sx_pos(k);
             if (write) {
                 a.ustart[u] = j;
-                a.udepth[u] = (sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd) | (first ? 0x80000000u : 0u);
+                a.udepth[u] = (sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd) | (first ? 0x80000000u : 0u);
                 if (first) a.mub[ptx_upper_bound_u32(a.mtb, a.n_modules, j) - 1] = u;
                 u++;
             }
         }
         sd += bc;
-        pd += kk == T_LPAREN ? 1 : kk == T_RPAREN ? -1 : 0;
+        if (sd < 0) sd = 0;
         bc_prev = bc;
         if (j + 1 == a.n_tokens) {
             a.mod_final_scope[ptx_upper_bound_u32(a.mtb, a.n_modules, j) - 1] = sd;
@@ -253,45 +282,71 @@ PTX_HD inline uint32_t sx_walk(const PtxStructArgs& a, const SxThread& t, PtxSeg
     }
     return starts;
 }
-PTX_HD inline uint32_t sx_decide(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before) {
-    if (!t.fast) return sx_walk(a, t, before, false, 0);
+PTX_HD inline uint32_t sx_decide(const PtxStructArgs& a, const SxThread& t, int32_t depth) {
+    if (!t.fast) return sx_walk(a, t, depth, false, 0);
     const uint32_t plus = t.braces & SX_LOW, minus = (t.braces >> 4) & SX_LOW;
-    const uint32_t in_scope = (t.marks & SX_LOW) | plus | minus | sx_up(plus | minus) | t.brace_before;
-    if (before.scope - (int32_t)sx_popc(minus) > 0) return in_scope;                        // inside a scope all the way
-    const uint32_t dirs = (t.marks >> 4) & SX_LOW;
-    if (before.scope <= 0 && !plus && !dirs) return 0;                                     // top level all the way, no directive keyword
+    const uint32_t in_scope = (t.marks & SX_LOW) | plus | minus | sx_up(plus | minus) | (t.brace_before & 1u);
+    if (depth - (int32_t)sx_popc(minus) > 0) return in_scope;                              // inside a scope all the way
+    uint32_t dirs = (t.marks >> 4) & SX_LOW;
+    const uint32_t behind_close = sx_up(minus) | (t.brace_before >> 1);
+    if (depth == 0 && !plus) {                                                             // top level all the way
+        uint32_t starts = behind_close;
+        while (dirs) {
+            const uint32_t pos = sx_lowest(dirs);
+            dirs &= dirs - 1u;
+            const uint32_t k = (pos >> 3) * 4u + (pos & 3u);
+            if (!sx_continues(PTX_KL_KIND(a.kinds[t.tb + k - 1]))) starts |= 1u << pos;     // fast threads have tb > 0
+        }
+        return starts;
+    }
     // a bit of both: token by token
-    int32_t sd = before.scope, pd = before.paren;
+    int32_t sd = depth;
     uint32_t starts = 0;
 #pragma unroll 1
     for (uint32_t k = 0; k < SX_ITEMS; k++) {
         const uint32_t pos = sx_pos(k), bit = 1u << pos;
         if (sd > 0) {
             starts |= in_scope & bit;
-        } else if (sd == 0 && pd == 0 && (dirs & bit)) {
-            const uint16_t prev = PTX_KL_KIND(a.kinds[t.tb + k - 1]);       // fast threads have tb > 0
-            if (!(prev == T_DOT_EXTERN || prev == T_DOT_VISIBLE || prev == T_MOD_weak)) starts |= bit;
+        } else {
+            starts |= behind_close & bit;
+            if ((dirs & bit) && !sx_continues(PTX_KL_KIND(a.kinds[t.tb + k - 1]))) starts |= bit;
         }
         sd += (int32_t)((plus >> pos) & 1u) - (int32_t)((minus >> pos) & 1u);
-        pd += (int32_t)((t.parens >> pos) & 1u) - (int32_t)((t.parens >> (pos + 4u)) & 1u);
+        if (sd < 0) sd = 0;
     }
     return starts;
 }
 
 // step 3: with the number of unit starts in front of the thread's first token: the rows of the unit table
-PTX_HD inline void sx_write(const PtxStructArgs& a, const SxThread& t, PtxSeg3 before, uint32_t starts, uint32_t units_before) {
+PTX_HD inline void sx_write(const PtxStructArgs& a, const SxThread& t, int32_t depth, uint32_t starts, uint32_t units_before) {
     if (!t.fast) {
-        if (t.n_valid) sx_walk(a, t, before, true, units_before);
+        if (t.n_valid) sx_walk(a, t, depth, true, units_before);
         return;
     }
     uint32_t u = units_before;
     const uint32_t plus = t.braces & SX_LOW, minus = (t.braces >> 4) & SX_LOW;
-    while (starts) {
-        const uint32_t pos = sx_lowest(starts), below = (1u << pos) - 1u;
-        starts &= starts - 1u;
-        const int32_t sd = before.scope + (int32_t)sx_popc(plus & below) - (int32_t)sx_popc(minus & below);
-        a.ustart[u] = t.tb + (pos >> 3) * 4u + (pos & 3u);
-        a.udepth[u] = sd < 0 ? 0u : sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
-        u++;
+    if (depth - (int32_t)sx_popc(minus) >= 0) {
+        // the depth never meets its floor: plain sums
+        while (starts) {
+            const uint32_t pos = sx_lowest(starts), below = (1u << pos) - 1u;
+            starts &= starts - 1u;
+            const int32_t sd = depth + (int32_t)sx_popc(plus & below) - (int32_t)sx_popc(minus & below);
+            a.ustart[u] = t.tb + (pos >> 3) * 4u + (pos & 3u);
+            a.udepth[u] = sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
+            u++;
+        }
+        return;
+    }
+    int32_t sd = depth;
+#pragma unroll 1
+    for (uint32_t k = 0; k < SX_ITEMS; k++) {
+        const uint32_t pos = sx_pos(k);
+        if ((starts >> pos) & 1u) {
+            a.ustart[u] = t.tb + k;
+            a.udepth[u] = sd > 0x7FF0 ? 0x7FF0u : (uint32_t)sd;
+            u++;
+        }
+        sd += (int32_t)((plus >> pos) & 1u) - (int32_t)((minus >> pos) & 1u);
+        if (sd < 0) sd = 0;
     }
 }

@@ -487,7 +487,7 @@ __global__ void __launch_bounds__(SX_THREADS) structure_kernel(PtxStructArgs a, 
             if (threadIdx.x == 0) a.counters->struct_abort = 1;
             return;
         }
-        const PtxSeg3 before = op(s_before, excl);
+        const int32_t before = sx_depth(op(s_before, excl));
         const uint32_t starts = sx_decide(a, t, before);
         uint32_t cincl, cexcl;
         block_scan((uint32_t)__popc(starts), AddOp(), 0u, warp_count, cincl, cexcl);

@@ -305,17 +305,6 @@ struct PairAddOp {
 struct AddOp {
     PTX_HD uint32_t operator()(uint32_t a, uint32_t b) const { return a + b; }
 };
-struct SegDepthOp {
-    PTX_HD PtxSeg3 operator()(PtxSeg3 x, PtxSeg3 y) const {
-        if (y.flag) return y;
-        PtxSeg3 r;
-        r.scope = x.scope + y.scope;
-        r.paren = x.paren + y.paren;
-        r.flag = x.flag;
-        return r;
-    }
-};
-
 // Backend concept:
 //   template <class F> void pf(const char* name, size_t n, F f);                f(i) for i in [0, n)
 //   template <class T, class Op, class Ld, class St> void scan(const char* name, size_t n, Ld ld, St st, Op op, T identity);
