@@ -39,9 +39,8 @@ UNIT = "GB/s"
 
 
 # (dram__bytes_read.sum + dram__bytes_write.sum) / text bytes, from the ncu captures summarised under profiles/
-NCU_DRAM_BYTES_PER_TEXT_BYTE = {      # from the ncu launch list summarised under profiles/ (64 MiB instance)
-    "lex_tokens": 4.59, "lex_compact_classify": 6.28, "scan_depth": 1.76, "apply_templates": 3.04, "unit_class_key": 2.67,
-    "emit_records": 3.62, "lex_context_vectors": 1.00,
+NCU_DRAM_BYTES_PER_TEXT_BYTE = {      # from the ncu captures summarised under profiles/ (512 MiB instance of the workload)
+    "lex_emit": 4.74, "lex_mark": 1.31, "structure": 0.74, "lex_context_vectors": 1.04, "emit_records": 4.48,
 }
 
 
@@ -329,7 +328,7 @@ def main():
     U = stats["n_units"]
     algo = {   # algorithmic bytes per launch: text read once, tokens / records read or written once
         "lex_context_vectors": N, "lex_mark": N + N // 4, "lex_emit": N + N // 4 + 10 * T,
-        "scan_depth": 8 * T, "scan_unit_index": 4 * T + 8 * U,
+        "structure": 2 * T + 8 * U,
         "unit_shape_key": 2 * T + 10 * U, "apply_templates": 2 * T + 16 * U, "class_insert": 12 * U,
         "emit_records": 4 * W + 9 * U, "decode_units": N + 8 * T + 4 * W, "decode_emit_flagged": 5 * U,
     }
@@ -340,15 +339,15 @@ def main():
         ab = algo.get(top)
         ach = ab / (ms / 1e3) / 1e9 if ab else None
         # DRAM traffic per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture of the same kernel on a
-        # 64 MiB instance of this workload (profiles/), scaled by text bytes (traffic grows in proportion to the text)
+        # 512 MiB instance of this workload (profiles/), scaled by text bytes (traffic grows in proportion to the text)
         tpb = NCU_DRAM_BYTES_PER_TEXT_BYTE.get(top)
         roof = {"kernel": top, "bound": "hbm", "achieved": ach, "peak": peak, "peak_kind": peak_kind, "unit": "GB/s",
                 "frac": ach / peak if ach else None, "traffic": tpb * N if tpb else None, "ms_per_launch": ms, "algorithmic_bytes": ab,
                 "lexer_segmenter": None}
         lex_ms = sum(prof.get(k, 0.0) for k in ("lex_context_vectors", "scan_context", "lex_tile_modules", "lex_mark", "lex_serial_modules",
                                                   "scan_token_counts", "set_token_total", "lex_emit", "module_token_ranges",
-                                                  "module_results_init", "mark_module_first", "scan_depth", "reset_unit_total",
-                                                  "scan_unit_index", "module_unit_ranges", "module_unit_ranges_fill")) / a.steps
+                                                  "module_results_init", "mark_module_skip", "structure", "reset_unit_total",
+                                                  "module_unit_ranges", "module_unit_ranges_fill")) / a.steps
         # whole front end: text read once, records written once (N + O) over the kernel time of a step
         a_fe = N + 4 * W
         fe_ms = kernel_ms / a.steps

@@ -486,6 +486,16 @@ PTX_HD inline bool ptx_is_numeric_kind(uint16_t k) {
     static_assert(T_F32HEX == 18 && T_DECIMAL == 22, "the five numeric literal kinds are consecutive");
     return (uint32_t)(k - T_F32HEX) <= (uint32_t)(T_DECIMAL - T_F32HEX);
 }
+// does v * radix + d exceed 64 bits (no division: the radix is not known at compile time)
+PTX_HD inline bool ptx_mul_add_overflows(uint64_t v, uint32_t radix, uint32_t d) {
+#ifdef __CUDA_ARCH__
+    const uint64_t lo = v * radix;
+    return __umul64hi(v, (uint64_t)radix) != 0 || lo + d < lo;
+#else
+    uint64_t lo, sum;
+    return __builtin_mul_overflow(v, (uint64_t)radix, &lo) || __builtin_add_overflow(lo, (uint64_t)d, &sum);
+#endif
+}
 // Magnitude (DECIMAL, HEX: radix 8 / 10 / 16 by prefix, 'U' stripped) or bit pattern (F32HEX, F64HEX) of a literal of
 // `len` < 65535 bytes, and its code.  T_F64 (decimal floating point) has code 0 and is converted elsewhere.
 PTX_HD inline uint32_t ptx_literal_scan(const uint8_t* s, uint32_t len, uint16_t kind, uint64_t* mag) {
@@ -501,13 +511,15 @@ PTX_HD inline uint32_t ptx_literal_scan(const uint8_t* s, uint32_t len, uint16_t
     }
     if (i >= len) return code | PTX_LC_ERR;
     uint64_t v = 0;
+    // 16 hexadecimal, 19 decimal or 21 octal digits cannot overflow 64 bits; longer ones are checked digit by digit
+    const bool checked = len - i > (radix == 16 ? 16u : radix == 10 ? 19u : 21u);
     for (; i < len; i++) {
         uint32_t ch = s[i], d;
         if (ch - '0' < 10u) d = ch - '0';
         else if ((ch | 32u) - 'a' < 26u) d = (ch | 32u) - 'a' + 10;
         else return code | PTX_LC_ERR;
         if (d >= radix) return code | PTX_LC_ERR;
-        if (v > (~0ull - d) / radix) return code | PTX_LC_ERR;
+        if (checked && ptx_mul_add_overflows(v, radix, d)) return code | PTX_LC_ERR;
         v = v * radix + d;
     }
     *mag = v;
