@@ -150,6 +150,49 @@ PTX_HD PTX_NOINLINE inline uint32_t lx_colon_literal(const uint8_t* s, uint64_t 
     return 0;
 }
 
+// The number rules: the token at p, whose first byte is a digit.  `s` is anything that can be indexed by byte offset (a
+// pointer into the text, or a reader of a copy of it).
+template <class S>
+PTX_HD inline uint16_t lx_number(const S& s, uint64_t p, uint64_t n, uint32_t* len) {
+    const unsigned c = s[p];
+    {
+        if (c == '0' && p + 1 < n) {
+            unsigned d = s[p + 1] | 32u;
+            if (d == 'x') {
+                uint64_t q = p + 2;
+                while (q < n && lx_alnum(s[q])) q++;
+                if (q > p + 2) { *len = (uint32_t)(q - p); return T_HEX; }
+            } else if (d == 'f' || d == 'd') {
+                uint64_t need = d == 'f' ? 8 : 16;
+                uint64_t q = p + 2;
+                while (q < n && q < p + 2 + need && lx_alnum(s[q])) q++;
+                if (q == p + 2 + need) { *len = (uint32_t)(q - p); return d == 'f' ? T_F32HEX : T_F64HEX; }
+            }
+        }
+        uint64_t q = p + 1;
+        while (q < n && lx_digit(s[q])) q++;
+        if (q + 1 < n && s[q] == '.' && lx_digit(s[q + 1])) {
+            uint64_t r = q + 1;
+            while (r < n && lx_digit(s[r])) r++;
+            if (r < n && (s[r] | 32u) == 'e') {
+                uint64_t e = r + 1;
+                if (e < n && (s[e] == '-' || s[e] == '+')) e++;
+                if (e < n && lx_digit(s[e])) {
+                    while (e < n && lx_digit(s[e])) e++;
+                    r = e;
+                }
+            }
+            *len = (uint32_t)(r - p);
+            return T_F64;
+        }
+        if (q < n && s[q] == 'U') q++;
+        *len = (uint32_t)(q - p);
+        return T_DECIMAL;
+    }
+    *len = 1;
+    return T_ERROR;
+}
+
 // Longest token at p (p < n; text[p] is not whitespace, '/', or '"').  Returns its kind; *len = its length.
 // T_ERROR: no rule matches here (*len = 1).
 PTX_HD PTX_NOINLINE inline uint16_t lx_one(const uint8_t* s, uint64_t p, uint64_t n, uint32_t* len) {
@@ -221,40 +264,7 @@ PTX_HD PTX_NOINLINE inline uint16_t lx_one(const uint8_t* s, uint64_t p, uint64_
         *len = 1;
         return T_DOT;
     }
-    if (lx_digit(c)) {
-        if (c == '0' && p + 1 < n) {
-            unsigned d = s[p + 1] | 32u;
-            if (d == 'x') {
-                uint64_t q = p + 2;
-                while (q < n && lx_alnum(s[q])) q++;
-                if (q > p + 2) { *len = (uint32_t)(q - p); return T_HEX; }
-            } else if (d == 'f' || d == 'd') {
-                uint64_t need = d == 'f' ? 8 : 16;
-                uint64_t q = p + 2;
-                while (q < n && q < p + 2 + need && lx_alnum(s[q])) q++;
-                if (q == p + 2 + need) { *len = (uint32_t)(q - p); return d == 'f' ? T_F32HEX : T_F64HEX; }
-            }
-        }
-        uint64_t q = p + 1;
-        while (q < n && lx_digit(s[q])) q++;
-        if (q + 1 < n && s[q] == '.' && lx_digit(s[q + 1])) {
-            uint64_t r = q + 1;
-            while (r < n && lx_digit(s[r])) r++;
-            if (r < n && (s[r] | 32u) == 'e') {
-                uint64_t e = r + 1;
-                if (e < n && (s[e] == '-' || s[e] == '+')) e++;
-                if (e < n && lx_digit(s[e])) {
-                    while (e < n && lx_digit(s[e])) e++;
-                    r = e;
-                }
-            }
-            *len = (uint32_t)(r - p);
-            return T_F64;
-        }
-        if (q < n && s[q] == 'U') q++;
-        *len = (uint32_t)(q - p);
-        return T_DECIMAL;
-    }
+    if (lx_digit(c)) return lx_number(s, p, n, len);
     *len = 1;
     return T_ERROR;
 }
@@ -498,7 +508,8 @@ PTX_HD inline bool ptx_mul_add_overflows(uint64_t v, uint32_t radix, uint32_t d)
 }
 // Magnitude (DECIMAL, HEX: radix 8 / 10 / 16 by prefix, 'U' stripped) or bit pattern (F32HEX, F64HEX) of a literal of
 // `len` < 65535 bytes, and its code.  T_F64 (decimal floating point) has code 0 and is converted elsewhere.
-PTX_HD inline uint32_t ptx_literal_scan(const uint8_t* s, uint32_t len, uint16_t kind, uint64_t* mag) {
+template <class S>
+PTX_HD inline uint32_t ptx_literal_scan(const S& s, uint32_t len, uint16_t kind, uint64_t* mag) {
     *mag = 0;
     if (kind == T_F64) return 0;
     uint32_t code = 0, i = 0, radix = 16;

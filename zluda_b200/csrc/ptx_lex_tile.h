@@ -582,6 +582,34 @@ PTX_HD inline void lt_emit_exact(const PtxLexTileArgs& a, uint32_t j, uint32_t p
     }
     lt_put_token(a, j, pos, len, k);
 }
+// The tile's text in shared memory as something to index by byte offset
+struct LtTileBytes {
+    const PtxLexEmitShared* sh;
+    uint32_t base;                       // offset inside the tile that index 0 stands for
+    PTX_HD unsigned operator[](uint64_t i) const { return lt_tb(*sh, base + (uint32_t)i); }
+};
+// Numbers are most of what the exact rules see: the number rules and the literal code straight from the tile in shared
+// memory, unless the number, or what the rules look at behind it (three bytes: an exponent's 'e', sign and first digit;
+// eighteen for the shortest reading of what may be a hexadecimal float), may lie behind the tile (then, as everything else, through lt_emit_exact)
+PTX_HD inline void lt_emit_exact_tile(const PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile_base, uint32_t j, uint32_t off, uint32_t me) {
+    const bool module_ends_here = me - tile_base <= LT_BYTES;
+    const uint32_t end = module_ends_here ? me - tile_base : LT_BYTES;
+    if (off < end && lx_digit(lt_tb(sh, off))) {
+        const LtTileBytes bytes{&sh, 0};
+        uint32_t len;
+        const uint16_t k = lx_number(bytes, off, end, &len);
+        if (module_ends_here || off + (len > 18u ? len : 18u) + 3u <= end) {
+            PtxTokenWord t;
+            t.x = tile_base + off;
+            t.y = len | ((uint32_t)k << 16);                  // a length inside a tile
+            ((PtxTokenWord*)a.tokens)[j] = t;
+            uint64_t mag;
+            a.kinds[j] = (uint16_t)(k | (ptx_literal_scan(LtTileBytes{&sh, off}, len, k, &mag) << 9));
+            return;
+        }
+    }
+    lt_emit_exact(a, j, tile_base + off, me);
+}
 PTX_HD inline uint32_t lt_window_rank(const PtxLexEmitShared& sh, uint32_t w) {
     uint32_t rank = sh.chunk_rank[w >> 2];
     for (uint32_t v = w & ~3u; v < w; v++) {
@@ -690,7 +718,7 @@ PTX_HD inline void lt_emit_second(PtxLexEmitShared& sh, const PtxLexTileArgs& a,
     const uint32_t n_exact = sh.n_exact < LT_EXACT_CAP ? sh.n_exact : LT_EXACT_CAP;
     for (uint32_t x = tid; x < n_exact; x += nt) {
         const uint32_t off = sh.exact[x] & 0x1FFFu, rank = sh.exact[x] >> 13;
-        lt_emit_exact(a, j0 + rank, tile_base + off, sh.chunk_me[off >> 7]);
+        lt_emit_exact_tile(sh, a, tile_base, j0 + rank, off, sh.chunk_me[off >> 7]);
     }
 }
 

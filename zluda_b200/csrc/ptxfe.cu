@@ -177,27 +177,58 @@ __global__ void __launch_bounds__(256, 6) emit_records_kernel(uint32_t n_units, 
     if (threadIdx.x == 0) n_later = 0;
     __syncthreads();
     const uint32_t first = so[0], total = so[nu] - so[0];
-    for (uint32_t j0 = threadIdx.x; j0 < total; j0 += 256 * EMIT_ILP) {
+    // Every warp takes a contiguous eighth of the block's words, 32 at a time.  The unit of a word: `ua` is the unit of
+    // the window's first word; the lanes read the next 32 unit offsets, those inside the window mark their place in a
+    // 32-bit mask, and a lane's unit is ua + the number of marks at or below it.  (Units without words put two marks on
+    // one place: such a window searches, as does the first of a warp.)
+    const uint32_t lane = threadIdx.x & 31u, warp = threadIdx.x >> 5;
+    const uint32_t per_warp = ((total + 255u) / 256u) * 32u;
+    const uint32_t wbeg = warp * per_warp, wend = wbeg + per_warp < total ? wbeg + per_warp : total;
+    uint32_t ua = 0;
+    if (wbeg < wend) {
+        const uint32_t o = first + wbeg;
+        uint32_t lo = 0, hi = nu;              // last k with so[k] <= o
+        while (hi - lo > 1) {
+            uint32_t mid = (lo + hi) >> 1;
+            if (so[mid] <= o) lo = mid; else hi = mid;
+        }
+        ua = lo;
+    }
+    for (uint32_t jb = wbeg; jb < wend; jb += 32 * EMIT_ILP) {
         uint32_t x[EMIT_ILP], unit[EMIT_ILP];
         int what[EMIT_ILP];
 #pragma unroll
         for (int q = 0; q < EMIT_ILP; q++) {
-            const uint32_t j = j0 + q * 256;
+            const uint32_t j0 = jb + q * 32, j = j0 + lane;       // j0 is the same for the whole warp
             what[q] = PtxEmitStep::NOTHING;
             unit[q] = 0;
-            if (j >= total) continue;
-            const uint32_t o = first + j;
-            uint32_t lo = 0, hi = nu;          // last k with so[k] <= o
-            while (hi - lo > 1) {
-                uint32_t mid = (lo + hi) >> 1;
-                if (so[mid] <= o) lo = mid; else hi = mid;
+            if (j0 >= wend) continue;
+            const uint32_t o0 = first + j0, o = o0 + lane;
+            while (ua + 1 < nu && so[ua + 1] <= o0) ua++;        // the unit of the window's first word (a step or none)
+            const uint32_t k = ua + 1 + lane;
+            const uint32_t rel = k <= nu ? so[k] - o0 : 0xFFFFFFFFu;
+            const bool inside = rel < 32u;
+            const uint32_t n_in = (uint32_t)__popc(__ballot_sync(0xFFFFFFFFu, inside));
+            const uint32_t marks = __reduce_or_sync(0xFFFFFFFFu, inside ? 1u << rel : 0u);
+            uint32_t lo;
+            if ((uint32_t)__popc(marks) == n_in) {
+                lo = ua + (uint32_t)__popc(marks & (0xFFFFFFFFu >> (31u - lane)));
+            } else {
+                uint32_t hi = nu;
+                lo = ua;
+                while (hi - lo > 1) {
+                    uint32_t mid = (lo + hi) >> 1;
+                    if (so[mid] <= o) lo = mid; else hi = mid;
+                }
             }
+            ua = ua + n_in < nu - 1u ? ua + n_in : nu - 1u;     // the marks are all in front of the next window
+            if (j >= wend) continue;
             unit[q] = lo;
             what[q] = e.word(su[lo], (size_t)(u0 + lo), o - so[lo], x[q]);
         }
 #pragma unroll
         for (int q = 0; q < EMIT_ILP; q++) {
-            const uint32_t j = j0 + q * 256;
+            const uint32_t j = jb + q * 32 + lane;
             if (what[q] == PtxEmitStep::WRITE) {
                 e.words[first + j] = x[q];
             } else if (what[q] == PtxEmitStep::SECOND_ROUND) {
