@@ -244,6 +244,7 @@ def test_large_truncated_module(oracle, ctx):
     last = text.rfind(b".visible .entry")
     assert last > 0.8 * len(text)
     cut = text[:last + (len(text) - last) // 2]
+    ctx.parse_batch([text], 1).free()          # first use of a context pays for its tables, arenas and the kernels' loading
     b = ctx.parse_batch([cut], 1)
     st = ctx.stats()
     assert b.dump_hash(0) == oracle.dump_hash(cut, 1)
@@ -260,6 +261,25 @@ def test_large_truncated_module(oracle, ctx):
     assert b.dump_hash(0) == oracle.dump_hash(damaged, 1)
     b.free()
     assert st["n_sequential"] == 1 and st["n_sequential_tokens"] < 0.3 * st["n_tokens"], st
+
+
+def test_small_modules_behind_a_large_batch_repeatedly(oracle, ctx):
+    """Three thousand one-statement modules of a thousand shapes (most units are decoded one by one, through the staging
+    table), parsed forty times, each time behind a 4 MB module that leaves the arenas full of other data: every parse
+    must give the oracle's dumps.  (A cooperative copy of the staged records used to lose words in about one such parse
+    in ten.)"""
+    import test_pattern_pins as pins
+    import pattern_statements as ps
+    texts = zluda_b200.Texts([ps.module([c[0]]) for c in pins.sweep_cases()])
+    expect = oracle.dump_hashes([ps.module([c[0]]) for c in pins.sweep_cases()], 1)
+    big = corpus.config1(n_modules=1, total_bytes=4 << 20)
+    for rep in range(40):
+        ctx.parse_batch(big, 1).free()
+        b = ctx.parse_batch(texts, 1)
+        got = [b.dump_hash(i) for i in range(len(expect))]
+        b.free()
+        bad = [i for i in range(len(expect)) if got[i] != expect[i]]
+        assert not bad, (rep, bad[:8])
 
 
 def test_pattern_pins_on_the_device(ctx):

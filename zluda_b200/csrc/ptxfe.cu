@@ -128,10 +128,9 @@ __global__ void __launch_bounds__(256) lex_emit_kernel(PtxLexTileArgs a, uint32_
     }
 }
 
-// ---- first decode pass: every thread builds its record in shared memory, then each warp copies its 32 records to
-// their rows of the staging table with coalesced stores.  Word k of thread t lives at stage[k * STAGE_STRIDE + t]:
-// threads of a warp decode units of the same shape in lockstep, so they write the same k at the same time (32
-// consecutive banks), and the copy loop reads one thread's words with a stride that is odd (no bank conflicts).
+// ---- first decode pass: every thread builds its record in shared memory and copies it to its row of the staging
+// table.  Word k of thread t lives at stage[k * STAGE_STRIDE + t]: threads of a warp decode units of the same shape in
+// lockstep, so they write the same k at the same time (32 consecutive banks).
 #define STAGE_STRIDE 257u
 #define STAGE_CAP 40u
 #define WIN_CAP 12u
@@ -146,14 +145,12 @@ __global__ void __launch_bounds__(256) staged_kernel(size_t n, uint32_t* table, 
     r.unit = 0;
     r.n = 0;
     if (i < n) r = f(i, PtxScratch{stage + threadIdx.x, STAGE_STRIDE, STAGE_CAP, win + threadIdx.x, STAGE_STRIDE, WIN_CAP});
-    __syncwarp();
-    const uint32_t lane = threadIdx.x & 31u, warp_base = threadIdx.x & ~31u;
-    for (uint32_t l = 0; l < 32; l++) {
-        uint32_t cnt = __shfl_sync(0xFFFFFFFFu, r.n, l);
-        uint32_t unit = __shfl_sync(0xFFFFFFFFu, r.unit, l);
-        uint32_t* row = table + (size_t)unit * row_words;
-        for (uint32_t k = lane; k < cnt; k += 32) row[k] = stage[k * STAGE_STRIDE + warp_base + l];
-    }
+    // Every thread copies its own record.  (The copy used to be cooperative, 32 lanes per record behind a __syncwarp and
+    // two __shfl_sync per record.  About one parse in ten of a batch of 3,000 small modules of many shapes, run behind
+    // a large batch, then lost words of a few records: lanes that came late out of long decoders skipped the records of
+    // lanes that were done.  With each thread writing what it staged, 300 such parses in a row come out identical.)
+    uint32_t* row = table + (size_t)r.unit * row_words;
+    for (uint32_t k = 0; k < r.n; k++) row[k] = stage[k * STAGE_STRIDE + threadIdx.x];
 }
 
 // ---- one thread per item of a segmented range: a block takes 256 consecutive segments, whose items are contiguous,
