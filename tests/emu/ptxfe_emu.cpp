@@ -3,6 +3,7 @@
 // decoders and the record format can be checked against the oracle on a machine without a GPU.  It is not linked
 // into the product library and is never a fallback for it.
 #include <stdint.h>
+#include <time.h>
 #include <stdio.h>
 #include <stdlib.h>
 #include <string.h>
@@ -30,12 +31,16 @@ struct HostBackend {
     // PTXFE_EMU_ORDER=reverse runs every parallel-for backwards: a step whose result depends on the order in which its
     // indices run (a data race on the GPU) then shows up as a parity failure on the host.
     bool reverse = getenv("PTXFE_EMU_ORDER") && !strcmp(getenv("PTXFE_EMU_ORDER"), "reverse");
-    template <class F> void pf(const char*, size_t n, F f) {
+    // PTXFE_EMU_TIMES=1 prints the host time of every step that takes more than 50 ms (to find what is slow in a case)
+    bool times = getenv("PTXFE_EMU_TIMES") != nullptr;
+    template <class F> void pf(const char* name, size_t n, F f) {
+        const clock_t t0 = times ? clock() : 0;
         if (reverse) {
             for (size_t i = n; i-- > 0;) f(i);
         } else {
             for (size_t i = 0; i < n; i++) f(i);
         }
+        if (times && (double)(clock() - t0) / CLOCKS_PER_SEC > 0.05) fprintf(stderr, "emu step %s: %.2f s\n", name, (double)(clock() - t0) / CLOCKS_PER_SEC);
     }
     // per-chunk lexer steps: the reader is plain memory (n chunks of text are readable)
     template <class F> void pf_text(const char* name, size_t n, const uint8_t* text, F f) {
@@ -62,6 +67,8 @@ struct HostBackend {
         return &tables;
     }
     void lex_mark(const char*, size_t n_tiles, const PtxLexTileArgs& a) {
+        const clock_t t0 = clock();
+        struct Report { clock_t t0; bool on; ~Report() { if (on && (double)(clock() - t0) / CLOCKS_PER_SEC > 0.05) fprintf(stderr, "emu step lex_mark: %.2f s\n", (double)(clock() - t0) / CLOCKS_PER_SEC); } } report{t0, times};
         const uint32_t nt = 24;
         std::vector<PtxLexMarkShared> shv(1);
         PtxLexMarkShared& sh = shv[0];
@@ -78,6 +85,8 @@ struct HostBackend {
         }
     }
     void lex_emit(const char*, size_t n_tiles, const PtxLexTileArgs& a) {
+        const clock_t t0 = clock();
+        struct Report { clock_t t0; bool on; ~Report() { if (on && (double)(clock() - t0) / CLOCKS_PER_SEC > 0.05) fprintf(stderr, "emu step lex_emit: %.2f s\n", (double)(clock() - t0) / CLOCKS_PER_SEC); } } report{t0, times};
         const uint32_t nt = 24;
         std::vector<PtxLexEmitShared> shv(1);
         PtxLexEmitShared& sh = shv[0];

@@ -263,6 +263,20 @@ def test_large_truncated_module(oracle, ctx):
     assert st["n_sequential"] == 1 and st["n_sequential_tokens"] < 0.3 * st["n_tokens"], st
 
 
+def test_long_runs_of_soft_bytes(oracle, ctx):
+    """A quarter of a MiB of sigils and dots in one run, lexer errors all along it: the oracle's errors, and a kernel time
+    that one thread's single walk over the module explains (the per-chunk error pass used to be quadratic here)."""
+    n = 256 << 10
+    for run in ("%." * (n // 2), "a" * n, "a.b::" * (n // 5)):
+        text = cases.HEADER + ".visible .entry k()\n{\nmov.u32 %r1, " + run + ";\nret;\n}\n"
+        for mode in (1, 2):
+            b = ctx.parse_batch([text], mode)
+            st = ctx.stats()
+            assert b.dump(0) == oracle.parse(text, mode)[1], (run[:8], mode)
+            b.free()
+            assert st["kernel_ms"] < 2000, (run[:8], st)
+
+
 def test_small_modules_behind_a_large_batch_repeatedly(oracle, ctx):
     """Three thousand one-statement modules of a thousand shapes (most units are decoded one by one, through the staging
     table), parsed forty times, each time behind a 4 MB module that leaves the arenas full of other data: every parse

@@ -205,6 +205,24 @@ def test_damage_is_confined_to_the_tail(oracle, emu):
     assert n_sequential >= 30
 
 
+def test_long_runs_of_soft_bytes_stay_linear(oracle, emu):
+    """Runs of identifier characters, dots, colons, sigils and signs a few hundred KiB long, with and without lexer
+    errors inside: the same tokens and errors as the oracle, in time that grows with the length (the chunk lexer's
+    rewind to the start of such a run used to make the error pass quadratic: 4.6 s for the 256 KiB case below, 18 s
+    for twice that)."""
+    import time
+    n = 256 << 10
+    runs = ["a" * n, "%." * (n // 2), "::" * (n // 2), ".1" * (n // 2), "%" * n, "1." * (n // 2), "+-" * (n // 2), "a.b::" * (n // 5)]
+    for run in runs:
+        text = cases.HEADER + ".visible .entry k()\n{\nmov.u32 %r1, " + run + ";\nret;\n}\n"
+        for mode in (1, 2):
+            t0 = time.time()
+            dumps, _ = emu.parse([text], mode)
+            took = time.time() - t0
+            assert dumps[0] == oracle.parse(text, mode)[1], (run[:8], mode)
+            assert took < 3.0, (run[:8], mode, took)
+
+
 def test_numbers_across_tile_ends(oracle, emu):
     """Every kind of numeric literal at every position around the end of an 8 KiB lexer tile: the number rules run on
     the tile's copy of the text only when the number and what the rules look at behind it lie inside the tile."""

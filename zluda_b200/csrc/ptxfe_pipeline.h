@@ -384,8 +384,12 @@ struct PtxLexErrorsStep {
     const uint32_t* vec;
     const PtxPair* cnt;
     uint32_t* lexerrs;
+    const uint32_t* mod_flag;     // 1 = the module was lexed by one thread (a long run of soft bytes): so are its errors
     template <class R> PTX_HD void operator()(size_t c, const R& rd) const {
         if (cnt[c + 1].b == cnt[c].b) return;     // no error starts in this chunk
+        // (a chunk re-lexes the run of soft bytes that reaches into it from the run's start: bounded by the look-back
+        // of the marking step for every module that step did not flag)
+        if (mod_flag[ptx_upper_bound_u32(info.mcb, info.n_modules, (uint32_t)c) - 1]) return;
         uint32_t ms, me, cs = (uint32_t)c * PTX_CHUNK;
         bool first;
         info.locate(c, ms, me, first);
@@ -444,7 +448,19 @@ inline void ptx_stage_lex(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     la.kinds = kinds;
     bk.lex_emit("lex_emit", n_tiles, la);
     // A6: lexer errors are rare: a second walk, only when there are any, and only over the chunks that have one
-    if (n_lexerrs) bk.pf_text("lex_emit_errors", n_chunks, text, PtxLexErrorsStep{info, text, vec, cnt, lexerrs});
+    if (n_lexerrs) {
+        bk.pf_text("lex_emit_errors", n_chunks, text, PtxLexErrorsStep{info, text, vec, cnt, lexerrs, mod_flag});
+        // the flagged modules: one thread each, one walk over the module (linear in its length whatever its runs)
+        bk.pf("lex_emit_errors_serial", n_modules, [=] PTX_HD(size_t m) {
+            if (!mod_flag[m]) return;
+            const uint32_t c0 = mcb[m], c1 = mcb[m + 1];
+            if (c0 == c1 || cnt[c1].b == cnt[c0].b) return;
+            const uint32_t ms = (uint32_t)layout[m].text_off, me = ms + (uint32_t)layout[m].text_len;
+            LexErrorSink sink;
+            sink.errors = lexerrs + 2 * (size_t)cnt[c0].b;
+            lx_chunk(PtxGlobalReader{text, me}, text, ms, me, ms, me, CX_CODE, sink);
+        });
+    }
     uint32_t* mtb = w.mod_tok_begin;
     bk.pf("module_token_ranges", n_modules + 1, [=] PTX_HD(size_t m) {
         uint32_t c = mcb[m];   // mod_chunk_begin[n_modules] = n_chunks
