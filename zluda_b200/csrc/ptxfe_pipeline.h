@@ -689,8 +689,11 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         uint32_t h = (uint32_t)(key ^ (key >> 29)) & (PTX_CLASS_SLOTS - 1);
         for (int probe = 0; probe < 64; probe++) {
 #ifdef __CUDA_ARCH__
-            // most units find their class already there: look before competing for the slot
-            unsigned long long old = *(volatile unsigned long long*)&cs.keys[h];
+            // most units find their class already there: look before competing for the slot, and look through the
+            // SM's own cache first (a batch has few classes: every SM asking L2 for the same few lines is what this
+            // step otherwise waits for; a stale empty slot only sends the thread on to the exact look)
+            unsigned long long old = __ldca(&cs.keys[h]);
+            if (old != key) old = *(volatile unsigned long long*)&cs.keys[h];
             if (old == 0) old = atomicCAS(&cs.keys[h], 0ull, key);
 #else
             unsigned long long old = cs.keys[h];
@@ -1020,6 +1023,11 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     // return to depth 0 went wrong in or behind its last top-level unit: nothing behind an unclosed scope is one.)
     // mod_bad[m] = 1 + the unit that heads the first bad directive, 0 = none
     bk.pf("chain_check", n_units, [=] PTX_HD(size_t u) {
+        // units lie back to back over the whole batch, and a module's first unit says so in its depth word: the common
+        // case (the unit meets the next one, which is in the same module) needs no module look-up
+        const bool last_of_module = u + 1 == n_units || (udepth[u + 1] >> 31) != 0;
+        const uint32_t next_start = u + 1 < n_units ? ustart[u + 1] : n_tokens;
+        if (!last_of_module && ustatus[u] == US_OK && uend[u] == next_start) return;
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         if (mod_skip[m]) return;
         uint32_t next = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
@@ -1058,6 +1066,7 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     });
     // C4: its sizes replace those of the units it covers
     bk.pf("merge_sequential_sizes", n_units, [=] PTX_HD(size_t u) {
+        if (!counters->any_sequential) return;       // no module of this slice needs the sequential parser
         uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         if (!mod_bad[m] || u < mod_bad[m] - 1u) return;
         PtxPair z;
