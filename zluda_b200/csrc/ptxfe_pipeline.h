@@ -248,6 +248,7 @@ struct PtxCounters {
     uint32_t n_classes;         // statement classes met so far in this batch (all slices)
     uint32_t n_sig_words;       // words of the signature pool in use
     uint32_t struct_abort;      // the structure pass ran into its wait limit (its results are void)
+    uint32_t n_skipped;         // modules with tokens that are not parsed (a lexer error, and not the errors-only mode)
 };
 
 PTX_HD inline uint32_t ptx_upper_bound_u32(const uint32_t* a, uint32_t n, uint32_t x) {
@@ -505,11 +506,19 @@ inline void ptx_stage_structure(BK& bk, PtxWork& w, PtxCounters& host_counters, 
     PtxCounters* counters = w.counters;
     uint32_t* mod_skip = w.mod_skip = (uint32_t*)bk.alloc(sizeof(uint32_t) * (n_modules + 1));
     bk.zero(mod_final_scope, sizeof(int32_t) * (n_modules + 1));
+    bk.pf("reset_skipped", 1, [=] PTX_HD(size_t) { counters->n_skipped = 0; });
     // B0: a module with a lex error is not parsed unless only its errors
     // are wanted (lib.rs:392-411 vs 447-449, 487-489)
     bk.pf("mark_module_skip", n_modules, [=] PTX_HD(size_t m) {
         bool lexerr = results[m].lexerr_end > results[m].lexerr_begin;
         mod_skip[m] = (mtb[m] == mtb[m + 1] || (lexerr && mode != 2)) ? 1u : 0u;
+        if (mtb[m] != mtb[m + 1] && lexerr && mode != 2) {
+#ifdef __CUDA_ARCH__
+            atomicAdd(&counters->n_skipped, 1u);
+#else
+            counters->n_skipped++;
+#endif
+        }
     });
     // B1: one pass over the token kinds: (scope, paren) depth restarting at every module, the unit starts, their
     // numbering and the unit table (at most one unit per token); nothing per token is kept of it
@@ -665,11 +674,13 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
     uint32_t* order = (uint32_t*)bk.alloc(sizeof(uint32_t) * ((size_t)n_units + 1));
     uint64_t* ckey_of = (uint64_t*)bk.alloc(sizeof(uint64_t) * ((size_t)n_units + 1));
     bk.pf("unit_class_key", n_units, [=] PTX_HD(size_t u) {
-        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
+        // units lie back to back over the whole batch: a unit ends where the next one starts.  The unit's module is looked
+        // up only when some module of the slice is not parsed at all (a lexer error outside the errors-only mode)
         uint32_t start = ustart[u];
-        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        uint32_t end = u + 1 < n_units ? ustart[u + 1] : n_tokens;
         uint32_t dp = udepth[u];
-        ckey_of[u] = mod_skip[m] ? 0 : ptx_class_key(text, tokens, kinds, start, end, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
+        const bool skipped = counters->n_skipped != 0 && mod_skip[ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1] != 0;
+        ckey_of[u] = skipped ? 0 : ptx_class_key(text, tokens, kinds, start, end, dp & 0x7FFFFFFFu, (dp >> 31) != 0);
     });
 
     // T1: class table (open addressing on the 64-bit key), shared by the slices of a batch; the thread that inserts
@@ -777,9 +788,8 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         if (id == PTX_ABSENT) { rest(); return; }
         const PtxTemplateInfo ti = cs.info[id];
         if (!ti.ok) { rest(); return; }
-        uint32_t m = ptx_upper_bound_u32(mub, n_modules, (uint32_t)u) - 1;
         uint32_t start = ustart[u];
-        uint32_t end = (u + 1 < mub[m + 1]) ? ustart[u + 1] : mtb[m + 1];
+        uint32_t end = u + 1 < n_units ? ustart[u + 1] : n_tokens;
         uint32_t dp = udepth[u];
         uint32_t depth1 = (dp & 0x7FFFFFFFu) == 1 ? 1u : 0u;
         if (end - start != ti.n_tokens || !ptx_signature_matches(cs.sig_pool + cs.sig_off[id], text, tokens, kinds, start, ti.n_tokens, depth1)) { rest(); return; }
