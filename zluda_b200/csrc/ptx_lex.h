@@ -82,26 +82,39 @@ PTX_HD inline bool cx_word_has(uint32_t w, uint32_t byte) {
 }
 // transition vector of text[begin, end); begin is a multiple of 4.  `rd` is a text reader (see PtxGlobalReader).
 // Four bytes at a time: a word without '/', '*' and '"' acts as one map (the newline map if it holds a newline, else
-// the map of an ordinary byte: both are idempotent and the newline map absorbs the other), so only words inside or
-// next to comments and strings are walked byte by byte.
+// the map of an ordinary byte: both are idempotent and the newline map absorbs the other, in either order), so only
+// words inside or next to comments and strings are walked byte by byte, and a run of the others costs one map.
 template <class R>
 PTX_HD inline uint32_t cx_chunk_vector(const R& rd, uint32_t begin, uint32_t end) {
     uint32_t s0 = 0, s1 = 1, s2 = 2, s3 = 3, s4 = 4, s5 = 5;
+    // a run of words without '/', '*' and '"' is applied as ONE map when it ends: the newline map if any of its words
+    // holds a newline, else the map of an ordinary byte
+    bool run = false, run_newline = false;
     for (uint32_t p = begin; p < end; p += 4) {
         uint32_t wd = rd.word(p);
         uint32_t nb = end - p < 4u ? end - p : 4u;
         if (nb < 4) wd &= (1u << (8 * nb)) - 1u;          // bytes past the end read as NUL: ordinary bytes
         if (cx_word_has(wd, '/') || cx_word_has(wd, '*') || cx_word_has(wd, '"')) {
+            if (run) {
+                const uint32_t v = run_newline ? cx_byte_vector('\n') : cx_byte_vector('a');
+                s0 = (v >> (4 * s0)) & 7u; s1 = (v >> (4 * s1)) & 7u; s2 = (v >> (4 * s2)) & 7u;
+                s3 = (v >> (4 * s3)) & 7u; s4 = (v >> (4 * s4)) & 7u; s5 = (v >> (4 * s5)) & 7u;
+                run = run_newline = false;
+            }
             for (uint32_t k = 0; k < nb; k++) {
                 uint32_t v = cx_byte_vector((wd >> (8 * k)) & 0xFFu);
                 s0 = (v >> (4 * s0)) & 7u; s1 = (v >> (4 * s1)) & 7u; s2 = (v >> (4 * s2)) & 7u;
                 s3 = (v >> (4 * s3)) & 7u; s4 = (v >> (4 * s4)) & 7u; s5 = (v >> (4 * s5)) & 7u;
             }
         } else {
-            uint32_t v = (cx_word_has(wd, '\n') || cx_word_has(wd, '\r')) ? cx_byte_vector('\n') : cx_byte_vector('a');
-            s0 = (v >> (4 * s0)) & 7u; s1 = (v >> (4 * s1)) & 7u; s2 = (v >> (4 * s2)) & 7u;
-            s3 = (v >> (4 * s3)) & 7u; s4 = (v >> (4 * s4)) & 7u; s5 = (v >> (4 * s5)) & 7u;
+            run = true;
+            run_newline |= cx_word_has(wd, '\n') || cx_word_has(wd, '\r');
         }
+    }
+    if (run) {
+        const uint32_t v = run_newline ? cx_byte_vector('\n') : cx_byte_vector('a');
+        s0 = (v >> (4 * s0)) & 7u; s1 = (v >> (4 * s1)) & 7u; s2 = (v >> (4 * s2)) & 7u;
+        s3 = (v >> (4 * s3)) & 7u; s4 = (v >> (4 * s4)) & 7u; s5 = (v >> (4 * s5)) & 7u;
     }
     return s0 | (s1 << 4) | (s2 << 8) | (s3 << 12) | (s4 << 16) | (s5 << 20);
 }
