@@ -86,7 +86,7 @@ const char* ptxfe_status_str(int status);
  * their neighbours; text offsets in a module's records are relative to its slice: subtract the `text_base` that
  * ptxfe_module_records reports.  In ptxfe_stats, h2d_ms / kernel_ms / d2h_ms are then the busy times of the three
  * streams, which overlap.  Environment: PTXFE_SLICE_BYTES forces one slice size, PTXFE_SLICE_DIV the divisor that
- * sizes the middle slices (default 6), PTXFE_TRACE=1 prints the slices' device timeline to stderr. */
+ * sizes the middle slices (default 8), PTXFE_TRACE=1 prints the slices' device timeline to stderr. */
 int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* lens, uint32_t n, uint32_t mode,
                       ptxfe_batch** out);
 

@@ -1257,7 +1257,7 @@ int ptxfe_parse_batch(ptxfe_ctx* ctx, const char* const* texts, const uint64_t* 
     // between (every slice costs a few host synchronisations and ~70 launches).  PTXFE_SLICE_BYTES forces one size.
     uint64_t grand_total = 0;
     for (uint32_t m = 0; m < n; m++) grand_total += lens[m];
-    uint64_t edge = (uint64_t)32 << 20, div = 6;
+    uint64_t edge = (uint64_t)32 << 20, div = 8;
     if (const char* e = getenv("PTXFE_SLICE_DIV")) { uint64_t v = strtoull(e, nullptr, 10); if (v) div = v; }
     uint64_t middle = grand_total / div;
     if (middle < ((uint64_t)64 << 20)) middle = (uint64_t)64 << 20;
