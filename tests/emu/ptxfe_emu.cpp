@@ -87,7 +87,7 @@ struct HostBackend {
     void lex_emit(const char*, size_t n_tiles, const PtxLexTileArgs& a) {
         const clock_t t0 = clock();
         struct Report { clock_t t0; bool on; ~Report() { if (on && (double)(clock() - t0) / CLOCKS_PER_SEC > 0.05) fprintf(stderr, "emu step lex_emit: %.2f s\n", (double)(clock() - t0) / CLOCKS_PER_SEC); } } report{t0, times};
-        const uint32_t nt = 24;
+        const uint32_t nt = 256;     // the device's block size: the init phase then holds its text words the same way
         std::vector<PtxLexEmitShared> shv(1);
         PtxLexEmitShared& sh = shv[0];
         auto phase = [&](auto f) {
@@ -96,9 +96,12 @@ struct HostBackend {
         phase([&](uint32_t t) { lt_emit_tables(sh, a, t, nt); });
         for (size_t tile = 0; tile < n_tiles; tile++) {
             phase([&](uint32_t t) { lt_emit_init(sh, a, (uint32_t)tile, t, nt); });
-            phase([&](uint32_t t) { lt_emit_first(sh, a, (uint32_t)tile, t, nt); });
-            phase([&](uint32_t t) { lt_emit_keywords(sh, a, (uint32_t)tile, t, nt); });
-            phase([&](uint32_t t) { lt_emit_second(sh, a, (uint32_t)tile, t, nt); });
+            for (uint32_t pass = 0, passes = lt_emit_passes(sh); pass < passes; pass++) {
+                phase([&](uint32_t t) { lt_emit_list(sh, pass, t, nt); });
+                phase([&](uint32_t t) { lt_emit_first(sh, a, (uint32_t)tile, pass, t, nt); });
+                phase([&](uint32_t t) { lt_emit_keywords(sh, a, (uint32_t)tile, pass, t, nt); });
+                phase([&](uint32_t t) { lt_emit_second(sh, a, (uint32_t)tile, pass, t, nt); });
+            }
         }
     }
     // stage B: the per-thread bodies of the device kernel, tile after tile; the prefix of the earlier tiles is a running

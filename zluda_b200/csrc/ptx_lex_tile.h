@@ -20,10 +20,11 @@
 //   Chunks that contain a comment or string character (/ * ") or start inside a comment or string take the proven
 //   byte-serial walk (lx_chunk), one thread per chunk.  Every writer of the second round sets bits to the true lexing,
 //   so where two of them meet they agree.
-// Step 2, lex_emit: one thread per token (the set bits, enumerated per 32-byte window) finds the token's length and
-//   kind - punctuation and sigil-led words at once, words that may spell a keyword through the 8-byte keyword table,
-//   numbers through lx_one - and writes the 8-byte token and the kinds entry to their final place
-//   (chunk base from the scanned per-chunk counts + rank inside the chunk).
+// Step 2, lex_emit: the set bits are first listed (one thread per 32-byte window writes the tile offsets of its tokens
+//   to their ranks in shared memory); then one thread per TOKEN finds the token's length and kind - punctuation and
+//   sigil-led words at once, words that may spell a keyword through the 8-byte keyword table, numbers through the
+//   exact rules - and writes the 8-byte token and the kinds entry to their final place (tile base from the scanned
+//   per-chunk counts + rank inside the tile): the threads of a warp hold consecutive tokens and write consecutive entries.
 #pragma once
 #include "ptx_lex.h"
 
@@ -33,7 +34,9 @@
 #define LT_WORDS (LT_BYTES / 32u)
 #define LT_TRIG_CAP 1536u          // triggers per tile; a tile with more is lexed chunk by chunk by the serial walk
 #define LT_BACK_CAP 2048u          // longest look-back over a run of soft bytes; beyond it the module is lexed by one thread
-#define LT_EXACT_CAP 2048u         // tokens of a tile the emit step leaves to its second round (more are settled on the spot)
+#define LT_TOK_CAP 3072u           // tokens the emit step lists at a time; a tile with more goes in passes of LT_TOK_CAP / PTX_CHUNK chunks
+#define LT_EXACT_CAP 2048u         // tokens of a pass the emit step leaves to its second round (more are settled on the spot)
+#define LT_KW_CAP 2048u            // keyword candidates of a pass listed for the keyword round (more are looked up on the spot)
 
 enum { TC_WS = 0, TC_ALPHA = 1, TC_DIGIT = 2, TC_SIGIL = 3, TC_PCT = 4, TC_DOT = 5, TC_COLON = 6, TC_PM = 7, TC_PUNCT = 8, TC_SPECIAL = 9, TC_BAD = 10 };
 enum { LP_START = 1, LP_ERR = 2, LP_WORD = 4, LP_T1 = 8, LP_T2 = 16, LP_T3 = 32, LP_SPECIAL = 64 };
@@ -466,10 +469,11 @@ struct PtxLexEmitShared {
     uint16_t first[256];
     PtxKw8Entry kw[PTX_KW8_SIZE];       // the keyword table
     uint32_t bits[LT_WORDS], word[LT_WORDS + 2];
-    uint32_t kwbits[LT_WORDS];          // first round -> keyword round: the tokens that may spell a keyword
     uint32_t chunk_me[LT_CHUNKS], chunk_rank[LT_CHUNKS + 1];     // rank of the chunk's first token inside the tile
-    uint32_t exact[LT_EXACT_CAP];       // tokens left to the second round: tile offset | rank in the tile << 13
-    uint32_t n_exact;
+    uint16_t tokoff[LT_TOK_CAP];        // tile offset of token r of the pass
+    uint16_t exact[LT_EXACT_CAP];       // tokens left to the second round, by their rank in the pass
+    uint16_t kwlist[LT_KW_CAP];         // first round -> keyword round: the tokens that may spell a keyword, likewise
+    uint32_t n_exact, n_kw;
     // The tile's text, one spare word behind every 32 bytes: the threads of a warp work on consecutive 32-byte windows,
     // and with a stride of nine words instead of eight their byte reads fall into different banks.
     uint32_t text[LT_BYTES / 4 + LT_WORDS + 16];
@@ -486,8 +490,24 @@ PTX_HD inline void lt_emit_tables(PtxLexEmitShared& sh, const PtxLexTileArgs& a,
     }
     for (uint32_t i = tid; i < PTX_KW8_SIZE; i += nt) sh.kw[i] = ptx_kw8_table[i];
 }
+#define LT_TEXT_LOADS 8u              // text words a thread of a 256-thread block holds in registers during the init phase
 PTX_HD inline void lt_emit_init(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
     const uint32_t c0 = tile * LT_CHUNKS;
+    const uint32_t n_words = (c0 + LT_CHUNKS <= a.n_chunks ? LT_CHUNKS : a.n_chunks - c0) * (PTX_CHUNK / 4);
+    const uint32_t* src = (const uint32_t*)(a.text + (size_t)tile * LT_BYTES);
+    // The text loads go out first and land in registers: the look-ups below (three dependent loads per chunk) then
+    // run under their latency instead of after it.
+    const bool held = nt * LT_TEXT_LOADS >= LT_BYTES / 4;
+    uint32_t tx[LT_TEXT_LOADS];
+    if (held) {
+#ifdef __CUDA_ARCH__
+#pragma unroll
+#endif
+        for (uint32_t j = 0; j < LT_TEXT_LOADS; j++) {
+            const uint32_t i = tid + j * nt;
+            tx[j] = i < n_words ? src[i] : 0u;
+        }
+    }
     for (uint32_t w = tid; w < LT_WORDS + 2; w += nt) {
         const bool in = w < LT_WORDS && c0 + (w >> 2) < a.n_chunks;
         if (w < LT_WORDS) sh.bits[w] = in ? a.start_bits[(size_t)tile * LT_WORDS + w] : 0u;
@@ -503,10 +523,18 @@ PTX_HD inline void lt_emit_init(PtxLexEmitShared& sh, const PtxLexTileArgs& a, u
             sh.chunk_me[k] = me;
         }
     }
-    const uint32_t n_words = (c0 + LT_CHUNKS <= a.n_chunks ? LT_CHUNKS : a.n_chunks - c0) * (PTX_CHUNK / 4);
-    const uint32_t* src = (const uint32_t*)(a.text + (size_t)tile * LT_BYTES);
-    for (uint32_t i = tid; i < LT_BYTES / 4 + 12; i += nt) sh.text[i + (i >> 3)] = i < n_words ? src[i] : 0u;
-    if (tid == 0) sh.n_exact = 0;
+    if (held) {
+#ifdef __CUDA_ARCH__
+#pragma unroll
+#endif
+        for (uint32_t j = 0; j < LT_TEXT_LOADS; j++) {
+            const uint32_t i = tid + j * nt;
+            if (i < LT_BYTES / 4) sh.text[i + (i >> 3)] = tx[j];
+        }
+        for (uint32_t i = LT_BYTES / 4 + tid; i < LT_BYTES / 4 + 12; i += nt) sh.text[i + (i >> 3)] = 0u;
+    } else {
+        for (uint32_t i = tid; i < LT_BYTES / 4 + 12; i += nt) sh.text[i + (i >> 3)] = i < n_words ? src[i] : 0u;
+    }
 }
 // length of the run of word characters that starts at tile offset o (at most 32; the bits behind the tile are zero)
 PTX_HD inline uint32_t lt_word_run(const PtxLexEmitShared& sh, uint32_t o) {
@@ -621,104 +649,143 @@ PTX_HD inline uint32_t lt_window_rank(const PtxLexEmitShared& sh, uint32_t w) {
     }
     return rank;
 }
-// First round: one thread per 32-byte window walks its set bits in order, the same few steps for every token: first
-// byte, length from the word-character bits, kind by the first byte.  Every token but the numbers, strings and the
-// unusual (second round: exact rules) is written here; words that may spell a keyword are written as plain words and
-// marked for the keyword round, so that no thread looks up a keyword while its neighbours wait.
-// one token of the first round: returns its bit for the keyword round (0: not a keyword candidate)
-PTX_HD inline uint32_t lt_emit_one(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile_base, uint32_t j, uint32_t rank, uint32_t w, uint32_t bit) {
-    // straight-line on purpose (bitwise logic, no short-circuit): the tokens of a warp's 32 windows are of all sorts, and
-    // every branch taken by some of them would be paid by all
-    const uint32_t off = w * 32u + bit;
-    const uint32_t f = sh.first[lt_tb(sh, off)];
-    const uint32_t dc = sh.cls[lt_tb(sh, off + 1)];        // the bytes behind the tile read as 0: no word characters
-    const uint32_t run = lt_word_run(sh, off + 1);
-    const uint32_t e = off + 1 + run;
-    const uint32_t colons = (uint32_t)(lt_tb(sh, e) == ':') & (uint32_t)(lt_tb(sh, e + 1) == ':');
-    const uint32_t isdot = (f >> 12) & 1u;                                                // FK_DOT
-    const uint32_t dotword = isdot & ((uint32_t)(dc == TC_ALPHA) | (uint32_t)(dc == TC_SIGIL));
-    const uint32_t word = ((f >> 9) & 1u) | dotword;                                        // FK_WORD
-    const uint32_t len = 1u + (word ? run : 0u);
-    const uint32_t kind = dotword ? (uint32_t)T_DOTIDENT : (f & 0x1FFu);
-    const uint32_t kw = ((f >> 10) & 1u) | dotword;                                         // FK_KW
-    // exact rules: numbers, strings, the unusual; a dot in front of a digit or '%'; a lone sigil behind a dot or "::"
-    // behind a dot-word; a long word, or one that may go on behind the tile
-    const uint32_t exact = ((f >> 11) & 1u) |
-                           (isdot & ((uint32_t)(dc == TC_DIGIT) | (uint32_t)(dc == TC_PCT) | (uint32_t)(off + 1 >= LT_BYTES))) |
-                           (dotword & (((uint32_t)(dc == TC_SIGIL) & (uint32_t)(run == 1u)) | colons | (uint32_t)(e + 1 >= LT_BYTES))) |
-                           (word & ((uint32_t)(run >= 32u) | (uint32_t)(off + len >= LT_BYTES)));
-    if (exact) {
-        const uint32_t slot = LT_ATOMIC_ADD(&sh.n_exact, 1u);
-        if (slot < LT_EXACT_CAP) sh.exact[slot] = off | (rank << 13);
-        else lt_emit_exact(a, j, tile_base + off, sh.chunk_me[off >> 7]);       // no room in the list (a tile of numbers)
-        return 0;
-    }
-    lt_put_plain(a, j, tile_base + off, len, kind);
-    return (kw & (uint32_t)(len <= PTX_KW_MAXLEN)) << bit;
+// A tile is emitted in passes: one, if its tokens fit the list; else chunk ranges that always fit (a chunk holds at
+// most PTX_CHUNK tokens).  Every thread of the block computes the same ranges.
+struct LtPass {
+    uint32_t c_a, c_b;        // chunks [c_a, c_b) of the tile
+    uint32_t base, n;         // rank in the tile of the pass's first token; tokens in the pass
+};
+PTX_HD inline uint32_t lt_emit_passes(const PtxLexEmitShared& sh) {
+    const uint32_t per = LT_TOK_CAP / PTX_CHUNK;
+    return sh.chunk_rank[LT_CHUNKS] <= LT_TOK_CAP ? 1u : (LT_CHUNKS + per - 1) / per;
 }
-PTX_HD inline void lt_emit_first(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
-    const uint32_t tile_base = tile * LT_BYTES;
-    const uint32_t j0 = a.cnt[tile * LT_CHUNKS].a;
-    for (uint32_t w = tid; w < LT_WORDS; w += nt) {
-        uint32_t bits = sh.bits[w], kwb = 0;
-        uint32_t rank = bits ? lt_window_rank(sh, w) : 0u;
-        // two tokens per turn: their steps do not depend on one another and overlap
+PTX_HD inline LtPass lt_emit_pass(const PtxLexEmitShared& sh, uint32_t pass) {
+    LtPass p;
+    if (sh.chunk_rank[LT_CHUNKS] <= LT_TOK_CAP) {
+        p.c_a = 0;
+        p.c_b = LT_CHUNKS;
+    } else {
+        const uint32_t per = LT_TOK_CAP / PTX_CHUNK;
+        p.c_a = pass * per;
+        p.c_b = p.c_a + per < LT_CHUNKS ? p.c_a + per : LT_CHUNKS;
+    }
+    p.base = sh.chunk_rank[p.c_a];
+    p.n = sh.chunk_rank[p.c_b] - p.base;
+    return p;
+}
+// a slot in a list of the block for every caller with `want` set; on the device all 32 lanes of the warp call it
+// together and the warp takes its slots with one atomic operation
+PTX_HD inline uint32_t lt_list_slot(uint32_t* counter, bool want) {
+#ifdef __CUDA_ARCH__
+    const uint32_t m = __ballot_sync(0xFFFFFFFFu, want);
+    if (!m) return 0;
+    const uint32_t lane = threadIdx.x & 31u;
+    uint32_t base = 0;
+    if (lane == (uint32_t)(__ffs(m) - 1)) base = atomicAdd(counter, (uint32_t)__popc(m));
+    base = __shfl_sync(0xFFFFFFFFu, base, __ffs(m) - 1);
+    return base + (uint32_t)__popc(m & ((1u << lane) - 1u));
+#else
+    return want ? (*counter)++ : 0u;
+#endif
+}
+// Listing: one thread per 32-byte window of the pass writes the tile offsets of its tokens to their ranks
+PTX_HD inline void lt_emit_list(PtxLexEmitShared& sh, uint32_t pass, uint32_t tid, uint32_t nt) {
+    const LtPass p = lt_emit_pass(sh, pass);
+    for (uint32_t w = p.c_a * 4u + tid; w < p.c_b * 4u; w += nt) {
+        uint32_t bits = sh.bits[w];
+        if (!bits) continue;
+        uint32_t r = lt_window_rank(sh, w) - p.base;
         while (bits) {
 #ifdef __CUDA_ARCH__
-            const uint32_t b0 = (uint32_t)(__ffs(bits) - 1);
+            const uint32_t b = (uint32_t)(__ffs(bits) - 1);
 #else
-            const uint32_t b0 = (uint32_t)__builtin_ctz(bits);
+            const uint32_t b = (uint32_t)__builtin_ctz(bits);
 #endif
             bits &= bits - 1;
-            const uint32_t more = bits;
-#ifdef __CUDA_ARCH__
-            const uint32_t b1 = more ? (uint32_t)(__ffs(more) - 1) : b0;
-#else
-            const uint32_t b1 = more ? (uint32_t)__builtin_ctz(more) : b0;
-#endif
-            bits &= bits - 1;       // 0 stays 0
-            const uint32_t k0 = lt_emit_one(sh, a, tile_base, j0 + rank, rank, w, b0);
-            uint32_t k1 = 0;
-            if (more) k1 = lt_emit_one(sh, a, tile_base, j0 + rank + 1, rank + 1, w, b1);
-            kwb |= k0 | k1;
-            rank += more ? 2u : 1u;
+            sh.tokoff[r++] = (uint16_t)(w * 32u + b);
         }
-        sh.kwbits[w] = kwb;
     }
+    if (tid == 0) sh.n_exact = sh.n_kw = 0;
 }
-// keyword round: the marked words through the keyword table; a word that spells one gets that kind
-PTX_HD inline void lt_emit_keywords(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
+// First round: one thread per token, the same few steps for every token: first byte, length from the word-character
+// bits, kind by the first byte.  Every token but the numbers, strings and the unusual (second round: exact rules) is
+// written here; words that may spell a keyword are written as plain words and listed for the keyword round, so that
+// no thread looks up a keyword while its neighbours wait.  Every thread of the block makes the same number of turns.
+PTX_HD inline void lt_emit_first(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t pass, uint32_t tid, uint32_t nt) {
+    const uint32_t tile_base = tile * LT_BYTES;
     const uint32_t j0 = a.cnt[tile * LT_CHUNKS].a;
-    for (uint32_t w = tid; w < LT_WORDS; w += nt) {
-        uint32_t kwb = sh.kwbits[w];
-        if (!kwb) continue;
-        const uint32_t all = sh.bits[w], rank0 = lt_window_rank(sh, w);
-        while (kwb) {
-#ifdef __CUDA_ARCH__
-            const uint32_t bit = (uint32_t)(__ffs(kwb) - 1);
-            const uint32_t rank = rank0 + (uint32_t)__popc(all & ((1u << bit) - 1u));
-#else
-            const uint32_t bit = (uint32_t)__builtin_ctz(kwb);
-            const uint32_t rank = rank0 + (uint32_t)__builtin_popcount(all & ((1u << bit) - 1u));
-#endif
-            kwb &= kwb - 1;
-            const uint32_t off = w * 32u + bit;
-            const uint32_t len = 1 + lt_word_run(sh, off + 1);
-            const uint32_t k = lt_keyword8(sh, off, len);
-            if (k != T_ERROR) {
-                a.tokens[j0 + rank].kind = (uint16_t)k;
-                a.kinds[j0 + rank] = (uint16_t)(k | (len << 9));      // a keyword is at most 20 bytes long
+    const LtPass p = lt_emit_pass(sh, pass);
+    for (uint32_t r0 = 0; r0 < p.n; r0 += nt) {
+        const uint32_t r = r0 + tid;
+        const bool valid = r < p.n;
+        // straight-line on purpose (bitwise logic, no short-circuit): the tokens of a warp are of all sorts, and every
+        // branch taken by some of them would be paid by all
+        const uint32_t off = valid ? sh.tokoff[r] : 0u;
+        const uint32_t f = sh.first[lt_tb(sh, off)];
+        const uint32_t dc = sh.cls[lt_tb(sh, off + 1)];        // the bytes behind the tile read as 0: no word characters
+        const uint32_t run = lt_word_run(sh, off + 1);
+        const uint32_t e = off + 1 + run;
+        const uint32_t colons = (uint32_t)(lt_tb(sh, e) == ':') & (uint32_t)(lt_tb(sh, e + 1) == ':');
+        const uint32_t isdot = (f >> 12) & 1u;                                                // FK_DOT
+        const uint32_t dotword = isdot & ((uint32_t)(dc == TC_ALPHA) | (uint32_t)(dc == TC_SIGIL));
+        const uint32_t word = ((f >> 9) & 1u) | dotword;                                        // FK_WORD
+        const uint32_t len = 1u + (word ? run : 0u);
+        const uint32_t kind = dotword ? (uint32_t)T_DOTIDENT : (f & 0x1FFu);
+        const uint32_t kw = ((f >> 10) & 1u) | dotword;                                         // FK_KW
+        // exact rules: numbers, strings, the unusual; a dot in front of a digit or '%'; a lone sigil behind a dot or "::"
+        // behind a dot-word; a long word, or one that may go on behind the tile
+        const uint32_t exact = ((f >> 11) & 1u) |
+                               (isdot & ((uint32_t)(dc == TC_DIGIT) | (uint32_t)(dc == TC_PCT) | (uint32_t)(off + 1 >= LT_BYTES))) |
+                               (dotword & (((uint32_t)(dc == TC_SIGIL) & (uint32_t)(run == 1u)) | colons | (uint32_t)(e + 1 >= LT_BYTES))) |
+                               (word & ((uint32_t)(run >= 32u) | (uint32_t)(off + len >= LT_BYTES)));
+        const bool want_exact = valid && exact;
+        const bool want_kw = valid && !exact && kw && len <= PTX_KW_MAXLEN;
+        const uint32_t slot_e = lt_list_slot(&sh.n_exact, want_exact);
+        const uint32_t slot_k = lt_list_slot(&sh.n_kw, want_kw);
+        if (!valid) continue;
+        const uint32_t j = j0 + p.base + r;
+        if (exact) {
+            if (slot_e < LT_EXACT_CAP) sh.exact[slot_e] = (uint16_t)r;
+            else lt_emit_exact_tile(sh, a, tile_base, j, off, sh.chunk_me[off >> 7]);       // no room in the list (a tile of numbers)
+            continue;
+        }
+        lt_put_plain(a, j, tile_base + off, len, kind);
+        if (want_kw) {
+            if (slot_k < LT_KW_CAP) sh.kwlist[slot_k] = (uint16_t)r;
+            else {
+                const uint32_t k = lt_keyword8(sh, off, len);
+                if (k != T_ERROR) {
+                    a.tokens[j].kind = (uint16_t)k;
+                    a.kinds[j] = (uint16_t)(k | (len << 9));
+                }
             }
         }
     }
 }
+// keyword round: the listed words through the keyword table; a word that spells one gets that kind
+PTX_HD inline void lt_emit_keywords(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t pass, uint32_t tid, uint32_t nt) {
+    const uint32_t j0 = a.cnt[tile * LT_CHUNKS].a;
+    const LtPass p = lt_emit_pass(sh, pass);
+    const uint32_t n_kw = sh.n_kw < LT_KW_CAP ? sh.n_kw : LT_KW_CAP;
+    for (uint32_t x = tid; x < n_kw; x += nt) {
+        const uint32_t r = sh.kwlist[x], off = sh.tokoff[r];
+        const uint32_t len = 1 + lt_word_run(sh, off + 1);
+        const uint32_t k = lt_keyword8(sh, off, len);
+        if (k != T_ERROR) {
+            const uint32_t j = j0 + p.base + r;
+            a.tokens[j].kind = (uint16_t)k;
+            a.kinds[j] = (uint16_t)(k | (len << 9));      // a keyword is at most 20 bytes long
+        }
+    }
+}
 // second round: the exact rules, one thread per token left over
-PTX_HD inline void lt_emit_second(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
+PTX_HD inline void lt_emit_second(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t pass, uint32_t tid, uint32_t nt) {
     const uint32_t tile_base = tile * LT_BYTES, j0 = a.cnt[tile * LT_CHUNKS].a;
+    const LtPass p = lt_emit_pass(sh, pass);
     const uint32_t n_exact = sh.n_exact < LT_EXACT_CAP ? sh.n_exact : LT_EXACT_CAP;
     for (uint32_t x = tid; x < n_exact; x += nt) {
-        const uint32_t off = sh.exact[x] & 0x1FFFu, rank = sh.exact[x] >> 13;
-        lt_emit_exact_tile(sh, a, tile_base, j0 + rank, off, sh.chunk_me[off >> 7]);
+        const uint32_t r = sh.exact[x], off = sh.tokoff[r];
+        lt_emit_exact_tile(sh, a, tile_base, j0 + p.base + r, off, sh.chunk_me[off >> 7]);
     }
 }
 

@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(256, 6) lex_mark_kernel(PtxLexTileArgs a, uint
         lt_mark_finish(sh, a, tile, tid, 256);
     }
 }
-__global__ void __launch_bounds__(256) lex_emit_kernel(PtxLexTileArgs a, uint32_t n_tiles) {
+__global__ void __launch_bounds__(256, 5) lex_emit_kernel(PtxLexTileArgs a, uint32_t n_tiles) {
     extern __shared__ __align__(16) unsigned char lex_emit_smem[];
     PtxLexEmitShared& sh = *(PtxLexEmitShared*)lex_emit_smem;
     const uint32_t tid = threadIdx.x;
@@ -121,10 +121,16 @@ __global__ void __launch_bounds__(256) lex_emit_kernel(PtxLexTileArgs a, uint32_
         __syncthreads();
         lt_emit_init(sh, a, tile, tid, 256);
         __syncthreads();
-        lt_emit_first(sh, a, tile, tid, 256);
-        __syncthreads();
-        lt_emit_keywords(sh, a, tile, tid, 256);
-        lt_emit_second(sh, a, tile, tid, 256);
+        const uint32_t passes = lt_emit_passes(sh);
+        for (uint32_t pass = 0; pass < passes; pass++) {
+            if (pass) __syncthreads();
+            lt_emit_list(sh, pass, tid, 256);
+            __syncthreads();
+            lt_emit_first(sh, a, tile, pass, tid, 256);
+            __syncthreads();
+            lt_emit_keywords(sh, a, tile, pass, tid, 256);
+            lt_emit_second(sh, a, tile, pass, tid, 256);
+        }
     }
 }
 
