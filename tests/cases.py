@@ -277,3 +277,16 @@ def negative_decimal_side_file(n=1000):
         else:
             lines.append(".global .f64 c%d = %.17g;" % (i, rng.random()))
     return HEADER + "\n".join(lines) + "\n.visible .entry k()\n{\nret;\n}\n"
+
+
+def dense_token_texts():
+    """Texts with more tokens per 8 KiB lexer tile than the emit step lists at a time (3,072), and tiles whose tokens are
+    nearly all numbers or nearly all keyword candidates (more than the 2,048 either list of a pass holds)."""
+    import random
+    rng = random.Random(11)
+    texts = ["1," * 20000, ";" * 30000, "12 " * 12000, "ab " * 12000, "add mov " * 6000, ".f32.u8 " * 5000, "0x1F 1.5 " * 5000,
+             "{%r1,%r2}," * 4000, "a+1," * 9000]
+    pieces = [",", ";", "1", "a", ".x", "%r", "+", "-", "[", "]", "0f3F800000", "ld", "st", " ", "\n", "12U", ".5", "::", "@!p"]
+    for _ in range(6):
+        texts.append("".join(rng.choice(pieces) for _ in range(30000)))
+    return texts

@@ -112,6 +112,12 @@ def test_lexer_tokens(oracle, ctx):
         assert oracle.lex(text) == ctx.lex(text), pad
 
 
+def test_dense_tiles_lex_like_the_oracle(oracle, ctx):
+    """Tiles that the emit step takes in several passes, and tiles that overflow its lists of numbers and keyword candidates."""
+    for text in cases.dense_token_texts():
+        assert oracle.lex(text) == ctx.lex(text), text[:40]
+
+
 def test_corpora(oracle, ctx):
     sets = {
         "config0": corpus.config0(n_kernels=8, n_instr=2000),

@@ -157,6 +157,15 @@ def test_lexer_tokens_match_oracle(oracle, emu):
         assert oracle.lex(text) == emu.lex(text)
 
 
+def test_dense_tiles_lex_like_the_oracle(oracle, emu):
+    """Tiles that the emit step takes in several passes, and tiles that overflow its lists of numbers and keyword candidates."""
+    for text in cases.dense_token_texts():
+        ot, oe = oracle.lex(text)
+        et, ee = emu.lex(text)
+        assert ot == et, text[:40]
+        assert oe == ee, text[:40]
+
+
 def test_corpora_small(oracle, emu):
     sets = {
         "config0": corpus.config0(n_kernels=3, n_instr=400),
