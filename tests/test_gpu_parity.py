@@ -100,7 +100,8 @@ def test_lexer_tokens(oracle, ctx):
     rng = random.Random(7)
     pieces = ["add", ".f32", "%r1", ",", ";", " ", "\n", "// c\n", "/* x */", "/*", "*/", "\"s\"", "\"", "0f3F800000", "0x1F", "1.5e-3",
               "1.5e", ".5", "12U", ".L2::cache_hint", ".shared::cta", ".shared::", "::", ":", "+", "-", "{", "}", "[", "]", "#", "$L_1",
-              "%", ".", ".1d", "WARP_SZ", "0d3FF0000000000000", "abc" * 60, "/", "*", "é", "a.b", "1e5", "0xU"]
+              "%", ".", ".1d", "WARP_SZ", "0d3FF0000000000000", "abc" * 60, "/", "*", "é", "a.b", "1e5", "0xU",
+              "0x1F_a", "0f3F800000U", "0f3F80000_", "12Ua", "00x1F", "0x" + "A" * 20, "0x" + "b" * 16, "5U", "0F3f800000", "0d3FF000000000000", "0x1$"]
     for trial in range(60):
         text = "".join(rng.choice(pieces) for _ in range(rng.randrange(1, 120)))
         ot, oe = oracle.lex(text)

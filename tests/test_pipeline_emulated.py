@@ -138,7 +138,8 @@ def test_lexer_tokens_match_oracle(oracle, emu):
     pieces = ["add", ".f32", "%r1", ",", ";", " ", "\n", "\t", "// c\n", "/* x */", "/*", "*/", "\"s\"", "\"", "0f3F800000", "0x1F",
               "1.5e-3", "1.5e", ".5", "12U", ".L2::cache_hint", ".shared::cta", ".shared::", ".param::funcx", "::", ":", "+", "-", "{",
               "}", "[", "]", "(", ")", "<", ">", "=", "@", "!", "|", "#", "~", "$L_1", "_a", "%", "$", ".", "..", ".1d", ".2dx", "WARP_SZ",
-              "0d3FF0000000000000", "0f123", "abc" * 60, "/", "*", "é", "\r\n", "a.b", "a:b", "1e5", "0X", "0xU", "09"]
+              "0d3FF0000000000000", "0f123", "abc" * 60, "/", "*", "é", "\r\n", "a.b", "a:b", "1e5", "0X", "0xU", "09",
+              "0x1F_a", "0f3F800000U", "0f3F80000_", "12Ua", "00x1F", "0x" + "A" * 20, "0x" + "b" * 16, "5U", "0F3f800000", "0D3FF0000000000000", "0d3FF000000000000", "0x1$"]
     for trial in range(300):
         n = rng.randrange(1, 80)
         text = "".join(rng.choice(pieces) for _ in range(n))

@@ -362,6 +362,29 @@ PTX_HD inline void lt_mark_special(PtxLexMarkShared& sh, const PtxLexTileArgs& a
     }
 }
 
+// A word character behind a number (the trigger at `pos`) whose token, by the number rules (lx_number), ends where the
+// run of word characters ends - 0x1F, 0f3F800000, 0d and sixteen, 12U, with no word character behind them: the first
+// round took the whole run for one token that starts at the number's first digit, which is the true lexing, and what
+// follows starts afresh.  Nothing to settle; other triggers of the same run of soft bytes look after themselves.
+PTX_HD inline bool lt_trigger_benign(const uint8_t* text, uint32_t pos, uint32_t ms, uint32_t me) {
+    if (pos <= ms || pos >= me) return false;
+    const unsigned c = text[pos];
+    if (lx_digit(c)) return false;              // the other kind of trigger: a digit behind a dot
+    if (c == 'U') return pos + 1 >= me || !lx_identc(text[pos + 1]);
+    const unsigned d = c | 32u;
+    if (d != 'x' && d != 'f' && d != 'd') return false;
+    if (text[pos - 1] != '0' || (pos - 1 > ms && lx_digit(text[pos - 2]))) return false;      // the number is a single 0
+    uint32_t q = pos + 1;
+    if (d == 'x') {
+        while (q < me && q < pos + 18u && lx_alnum(text[q])) q++;
+        if (q == pos + 1 || q == pos + 18u) return false;       // no digit, or longer than looked at here
+    } else {
+        const uint32_t need = d == 'f' ? 8u : 16u;
+        while (q < me && q < pos + 1 + need && lx_alnum(text[q])) q++;
+        if (q != pos + 1 + need) return false;
+    }
+    return q >= me || !lx_identc(text[q]);
+}
 // ---- phase 2b: one thread per trigger, and one for the run of soft bytes that enters the tile
 PTX_HD inline void lt_mark_triggers(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
     const uint32_t tile_base = tile * LT_BYTES;
@@ -387,6 +410,7 @@ PTX_HD inline void lt_mark_triggers(PtxLexMarkShared& sh, const PtxLexTileArgs& 
         const uint32_t k = at >> 7;
         if (sh.chunk_special[k]) continue;        // lexed by the serial walk
         const uint32_t ms = sh.chunk_ms[k], me = sh.chunk_me[k];
+        if (kind == LP_T1 && off < LT_BYTES && lt_trigger_benign(a.text, pos, ms, me)) continue;
         if (kind & (LP_T1 | LP_T3)) {
             // the run of soft bytes around the trigger is lexed from its first byte, which is a token start (several
             // triggers in one run do the same work and write the same bits)
