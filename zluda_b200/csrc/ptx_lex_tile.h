@@ -133,6 +133,9 @@ struct PtxLexTables {
     uint8_t cls[256];
     uint16_t step[TS_COUNT * 16];
     uint16_t first[256];       // emit step: what a token's first byte says about it (FK_* flags)
+    // class and transition in one look-up: row `state` (1 KiB), entry `byte`: the flags of step[] in the low byte, the
+    // byte offset of the next state's row above it
+    uint32_t step2[TS_COUNT * 256];
 };
 
 #ifdef __CUDA_ARCH__
@@ -164,6 +167,7 @@ struct PtxLexTileArgs {
 struct PtxLexMarkShared {
     uint8_t cls[256];
     uint16_t step[TS_COUNT * 16];
+    uint32_t step2[TS_COUNT * 256];
     uint32_t start[LT_WORDS], err[LT_WORDS], word[LT_WORDS];
     uint32_t chunk_ms[LT_CHUNKS], chunk_me[LT_CHUNKS];
     uint8_t chunk_cx[LT_CHUNKS], chunk_special[LT_CHUNKS];
@@ -185,6 +189,7 @@ PTX_HD inline void lt_locate(const PtxLexTileArgs& a, uint32_t tile, uint32_t c,
 PTX_HD inline void lt_mark_tables(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tid, uint32_t nt) {
     for (uint32_t i = tid; i < 256; i += nt) sh.cls[i] = a.tables->cls[i];
     for (uint32_t i = tid; i < TS_COUNT * 16; i += nt) sh.step[i] = a.tables->step[i];
+    for (uint32_t i = tid; i < TS_COUNT * 256; i += nt) sh.step2[i] = a.tables->step2[i];
 }
 PTX_HD inline void lt_mark_init(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
     for (uint32_t k = tid; k < LT_CHUNKS; k += nt) {
@@ -228,21 +233,33 @@ PTX_HD inline void lt_mark_simple(PtxLexMarkShared& sh, const PtxLexTileArgs& a,
             const uint32_t n = me - pos0 < 32u ? me - pos0 : 32u;
             uint32_t st4 = st << 4;      // the table entries carry the next state shifted the same way
             if (n == 32u) {
+                // one look-up per byte: the entry holds the flags and where the next state's row begins; the start and
+                // word bits are shifted in from the top, errors and triggers are rare and handled aside
+                const uint8_t* rows = (const uint8_t*)sh.step2;
+                uint32_t row = st * 1024u;
 #pragma unroll
                 for (uint32_t i = 0; i < 32; i++) {
                     const uint32_t wd = i < 4 ? lo.x : i < 8 ? lo.y : i < 12 ? lo.z : i < 16 ? lo.w : i < 20 ? hi.x : i < 24 ? hi.y : i < 28 ? hi.z : hi.w;
                     const uint32_t ch = (wd >> (8u * (i & 3u))) & 0xFFu;
-                    const uint32_t e = sh.step[st4 | sh.cls[ch]];
-                    sm |= (e & 1u) << i;
-                    em |= ((e >> 1) & 1u) << i;
-                    wm |= ((e >> 2) & 1u) << i;
+                    const uint32_t e = *(const uint32_t*)(rows + row + ch * 4u);
+#ifdef __CUDA_ARCH__
+                    sm = __funnelshift_r(sm, e, 1);
+                    wm = __funnelshift_r(wm, e >> 2, 1);
+#else
+                    sm = (sm >> 1) | (e << 31);
+                    wm = (wm >> 1) | ((e >> 2) << 31);
+#endif
                     any |= e;
-                    if (e & (LP_T1 | LP_T2 | LP_T3)) {
-                        uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
-                        if (slot < LT_TRIG_CAP) sh.trig[slot] = (win * 32u + i) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
+                    if (e & (LP_ERR | LP_T1 | LP_T2 | LP_T3)) {
+                        em |= ((e >> 1) & 1u) << i;
+                        if (e & (LP_T1 | LP_T2 | LP_T3)) {
+                            uint32_t slot = LT_ATOMIC_ADD(&sh.n_trig, 1u);
+                            if (slot < LT_TRIG_CAP) sh.trig[slot] = (win * 32u + i) | ((e & (LP_T1 | LP_T2 | LP_T3)) << 16);
+                        }
                     }
-                    st4 = e >> 8;
+                    row = e >> 8;
                 }
+                st4 = (row >> 10) << 4;
             } else {
                 for (uint32_t i = 0; i < n; i++) {
                     const uint32_t e = sh.step[st4 | sh.cls[a.text[pos0 + i]]];
@@ -828,4 +845,8 @@ PTX_HD inline void lt_fill_tables(PtxLexTables* t, uint32_t tid, uint32_t nt) {
         t->first[i] = (uint16_t)f;
     }
     for (uint32_t i = tid; i < TS_COUNT * 16; i += nt) t->step[i] = (uint16_t)lt_step(i >> 4, i & 15u);
+    for (uint32_t i = tid; i < TS_COUNT * 256; i += nt) {
+        const uint32_t e = lt_step(i >> 8, lt_class(i & 255u));
+        t->step2[i] = (e & 0xFFu) | (((e >> 12) * 1024u) << 8);
+    }
 }
