@@ -76,8 +76,8 @@ struct HostBackend {
             if (reverse) { for (uint32_t t = nt; t-- > 0;) f(t); } else { for (uint32_t t = 0; t < nt; t++) f(t); }
         };
         phase([&](uint32_t t) { lt_mark_tables(sh, a, t, nt); });
+        phase([&](uint32_t t) { lt_mark_reset(sh, t, nt); });
         for (size_t tile = 0; tile < n_tiles; tile++) {
-            phase([&](uint32_t t) { lt_mark_init(sh, a, (uint32_t)tile, t, nt); });
             phase([&](uint32_t t) { lt_mark_simple(sh, a, (uint32_t)tile, t, nt); });
             phase([&](uint32_t t) { lt_mark_special(sh, a, (uint32_t)tile, t, nt); });
             phase([&](uint32_t t) { lt_mark_triggers(sh, a, (uint32_t)tile, t, nt); });

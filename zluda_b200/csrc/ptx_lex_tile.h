@@ -191,20 +191,11 @@ PTX_HD inline void lt_mark_tables(PtxLexMarkShared& sh, const PtxLexTileArgs& a,
     for (uint32_t i = tid; i < TS_COUNT * 16; i += nt) sh.step[i] = a.tables->step[i];
     for (uint32_t i = tid; i < TS_COUNT * 256; i += nt) sh.step2[i] = a.tables->step2[i];
 }
-PTX_HD inline void lt_mark_init(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
+// per-tile state that the first phase adds to: cleared before the first tile and by the last phase of every tile
+PTX_HD inline void lt_mark_reset(PtxLexMarkShared& sh, uint32_t tid, uint32_t nt) {
     for (uint32_t k = tid; k < LT_CHUNKS; k += nt) {
-        uint32_t c = tile * LT_CHUNKS + k;
         sh.chunk_special[k] = 0;
         sh.chunk_errs[k] = 0;
-        if (c >= a.n_chunks) { sh.chunk_ms[k] = sh.chunk_me[k] = 0; sh.chunk_cx[k] = CX_CODE; continue; }
-        uint32_t ms, me;
-        bool first;
-        lt_locate(a, tile, c, &ms, &me, &first);
-        sh.chunk_ms[k] = ms;
-        sh.chunk_me[k] = me;
-        int cx = first ? CX_CODE : (int)(a.vec[c - 1] & 7u);
-        sh.chunk_cx[k] = (uint8_t)cx;
-        if (cx != CX_CODE) sh.chunk_special[k] = 1;
     }
     if (tid == 0) sh.n_trig = 0;
 }
@@ -214,16 +205,32 @@ PTX_HD inline void lt_fill_tables(PtxLexTables* t, uint32_t tid, uint32_t nt);
 struct alignas(16) LtWord4 {
     uint32_t x, y, z, w;
 };
-// ---- phase 1: 32 bytes per thread through the two tables; the thread owns one word of each bit map
+// ---- phase 1: chunk geometry, and 32 bytes per thread through the tables; the thread owns one word of each bit map
 PTX_HD inline void lt_mark_simple(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
     for (uint32_t win = tid; win < LT_WORDS; win += nt) {
         const uint32_t k = win >> 2, c = tile * LT_CHUNKS + k;
         uint32_t sm = 0, em = 0, wm = 0, any = 0;
-        const uint32_t ms = sh.chunk_ms[k], me = sh.chunk_me[k];
         const uint32_t pos0 = c * PTX_CHUNK + (win & 3u) * 32u;
-        if (c < a.n_chunks && pos0 < me) {
+        // the window's text is asked for first; the chunk's module bounds and entry context (dependent look-ups, the
+        // same for the four windows of a chunk) arrive while it is on its way
+        LtWord4 lo = {0, 0, 0, 0}, hi = {0, 0, 0, 0};
+        uint32_t ms = 0, me = 0;
+        int cx = CX_CODE;
+        if (c < a.n_chunks) {
             const LtWord4* w = (const LtWord4*)(a.text + pos0);
-            const LtWord4 lo = w[0], hi = w[1];
+            lo = w[0];
+            hi = w[1];
+            bool first;
+            lt_locate(a, tile, c, &ms, &me, &first);
+            if (!first) cx = (int)(a.vec[c - 1] & 7u);
+        }
+        if ((win & 3u) == 0) {
+            sh.chunk_ms[k] = ms;
+            sh.chunk_me[k] = me;
+            sh.chunk_cx[k] = (uint8_t)cx;
+        }
+        if (cx != CX_CODE) sh.chunk_special[k] = 1;
+        if (c < a.n_chunks && pos0 < me) {
             uint32_t st = TS_OTHER;
             if (pos0 > ms && !lt_state_before(sh.cls, a.text, pos0, ms, &st)) {
                 // the module goes to the one-thread path, which rewrites its token starts; the word bits below stay valid
@@ -444,6 +451,10 @@ PTX_HD inline void lt_mark_triggers(PtxLexMarkShared& sh, const PtxLexTileArgs& 
 PTX_HD inline void lt_mark_finish(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
     for (uint32_t k = tid; k < LT_CHUNKS; k += nt) {
         const uint32_t c = tile * LT_CHUNKS + k;
+        const bool special = sh.chunk_special[k];
+        const uint32_t serial_errs = sh.chunk_errs[k];
+        sh.chunk_special[k] = 0;         // for the next tile (lt_mark_reset)
+        sh.chunk_errs[k] = 0;
         if (c >= a.n_chunks) continue;
         uint32_t ntok = 0, nerr = 0;
         for (uint32_t w = 0; w < 4; w++) {
@@ -457,7 +468,7 @@ PTX_HD inline void lt_mark_finish(PtxLexMarkShared& sh, const PtxLexTileArgs& a,
         }
         PtxPair p;
         p.a = ntok;
-        p.b = sh.chunk_special[k] ? sh.chunk_errs[k] : nerr;
+        p.b = special ? serial_errs : nerr;
         a.cnt[c + 1] = p;
         if (c == 0) { PtxPair z; z.a = z.b = 0; a.cnt[0] = z; }
     }
@@ -466,6 +477,7 @@ PTX_HD inline void lt_mark_finish(PtxLexMarkShared& sh, const PtxLexTileArgs& a,
             a.start_bits[(size_t)tile * LT_WORDS + w] = sh.start[w];
             a.word_bits[(size_t)tile * LT_WORDS + w] = sh.word[w];
         }
+    if (tid == 0) sh.n_trig = 0;
 }
 
 // ---- modules whose soft runs outgrew the look-back: one thread lexes the whole module and rewrites its bits and counts

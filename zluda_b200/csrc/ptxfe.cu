@@ -99,9 +99,8 @@ __global__ void __launch_bounds__(256, 6) lex_mark_kernel(PtxLexTileArgs a, uint
     __shared__ PtxLexMarkShared sh;
     const uint32_t tid = threadIdx.x;
     lt_mark_tables(sh, a, tid, 256);
+    lt_mark_reset(sh, tid, 256);
     for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
-        __syncthreads();
-        lt_mark_init(sh, a, tile, tid, 256);
         __syncthreads();
         lt_mark_simple(sh, a, tile, tid, 256);
         __syncthreads();
