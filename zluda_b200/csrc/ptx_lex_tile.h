@@ -329,13 +329,17 @@ PTX_HD inline void lt_chain(PtxLexMarkShared& sh, const uint8_t* text, uint32_t 
         pos += len;
     }
 }
+// The helpers of the trigger phase go through the class and transition tables in shared memory: a few threads of a
+// tile run them while the others wait, so they are kept short (the arithmetic forms lt_class / lt_step cost more in
+// instruction fetches than in execution there).
+PTX_HD inline bool lt_soft_class(uint32_t cls) { return (0xFEu >> cls) & 1u; }       // TC_ALPHA .. TC_PM: what lx_soft accepts
 // does the run of soft bytes [q, end), which begins at a token start, hold a T1 or T3 trigger?
-PTX_HD inline bool lt_run_has_trigger(const uint8_t* text, uint32_t q, uint32_t end) {
-    uint32_t st = TS_OTHER;
+PTX_HD inline bool lt_run_has_trigger(const PtxLexMarkShared& sh, const uint8_t* text, uint32_t q, uint32_t end) {
+    uint32_t st4 = (uint32_t)TS_OTHER << 4;
     for (uint32_t j = q; j < end; j++) {
-        const uint32_t e = lt_step(st, lt_class(text[j]));
+        const uint32_t e = sh.step[st4 | sh.cls[text[j]]];
         if (e & (LP_T1 | LP_T3)) return true;
-        st = e >> 12;
+        st4 = e >> 8;
     }
     return false;
 }
@@ -390,24 +394,22 @@ PTX_HD inline void lt_mark_special(PtxLexMarkShared& sh, const PtxLexTileArgs& a
 // run of word characters ends - 0x1F, 0f3F800000, 0d and sixteen, 12U, with no word character behind them: the first
 // round took the whole run for one token that starts at the number's first digit, which is the true lexing, and what
 // follows starts afresh.  Nothing to settle; other triggers of the same run of soft bytes look after themselves.
-PTX_HD inline bool lt_trigger_benign(const uint8_t* text, uint32_t pos, uint32_t ms, uint32_t me) {
+PTX_HD inline bool lt_trigger_benign(const PtxLexMarkShared& sh, const uint8_t* text, uint32_t pos, uint32_t ms, uint32_t me) {
     if (pos <= ms || pos >= me) return false;
     const unsigned c = text[pos];
-    if (lx_digit(c)) return false;              // the other kind of trigger: a digit behind a dot
-    if (c == 'U') return pos + 1 >= me || !lx_identc(text[pos + 1]);
+    if (sh.cls[c] == TC_DIGIT) return false;     // the other kind of trigger: a digit behind a dot
+    if (c == 'U') return pos + 1 >= me || !lt_word(sh.cls[text[pos + 1]]);
     const unsigned d = c | 32u;
     if (d != 'x' && d != 'f' && d != 'd') return false;
-    if (text[pos - 1] != '0' || (pos - 1 > ms && lx_digit(text[pos - 2]))) return false;      // the number is a single 0
+    if (text[pos - 1] != '0' || (pos - 1 > ms && sh.cls[text[pos - 2]] == TC_DIGIT)) return false;      // the number is a single 0
+    const uint32_t stop = d == 'x' ? pos + 18u : d == 'f' ? pos + 9u : pos + 17u;
     uint32_t q = pos + 1;
-    if (d == 'x') {
-        while (q < me && q < pos + 18u && lx_alnum(text[q])) q++;
-        if (q == pos + 1 || q == pos + 18u) return false;       // no digit, or longer than looked at here
-    } else {
-        const uint32_t need = d == 'f' ? 8u : 16u;
-        while (q < me && q < pos + 1 + need && lx_alnum(text[q])) q++;
-        if (q != pos + 1 + need) return false;
+    for (; q < me && q < stop; q++) {
+        const uint32_t cc = sh.cls[text[q]];
+        if (cc != TC_ALPHA && cc != TC_DIGIT) break;
     }
-    return q >= me || !lx_identc(text[q]);
+    if (d == 'x' ? (q == pos + 1 || q == stop) : q != stop) return false;      // hex: a digit, and no longer than looked at here
+    return q >= me || !lt_word(sh.cls[text[q]]);
 }
 // ---- phase 2b: one thread per trigger, and one for the run of soft bytes that enters the tile
 PTX_HD inline void lt_mark_triggers(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
@@ -419,12 +421,12 @@ PTX_HD inline void lt_mark_triggers(PtxLexMarkShared& sh, const PtxLexTileArgs& 
             const uint32_t c = tile * LT_CHUNKS;
             if (c >= a.n_chunks || sh.chunk_special[0]) continue;
             const uint32_t ms = sh.chunk_ms[0], me = sh.chunk_me[0];
-            if (tile_base >= me || tile_base <= ms || !lx_soft(a.text[tile_base]) || !lx_soft(a.text[tile_base - 1])) continue;
+            if (tile_base >= me || tile_base <= ms || !lt_soft_class(sh.cls[a.text[tile_base]]) || !lt_soft_class(sh.cls[a.text[tile_base - 1]])) continue;
             uint32_t q = tile_base - 1;
-            while (q > ms && tile_base - q <= LT_BACK_CAP && lx_soft(a.text[q - 1])) q--;
+            while (q > ms && tile_base - q <= LT_BACK_CAP && lt_soft_class(sh.cls[a.text[q - 1]])) q--;
             if (tile_base - q > LT_BACK_CAP) { a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, c) - 1] = 1; continue; }
             // one byte past the tile's first: a trigger there (a digit behind a dot, the second colon) looks back into the run
-            if (lt_run_has_trigger(a.text, q, tile_base + 1 < me ? tile_base + 1 : me)) lt_chain(sh, a.text, tile_base, q, me);
+            if (lt_run_has_trigger(sh, a.text, q, tile_base + 1 < me ? tile_base + 1 : me)) lt_chain(sh, a.text, tile_base, q, me);
             continue;
         }
         const uint32_t off = sh.trig[t] & 0xFFFFu, kind = sh.trig[t] >> 16;
@@ -434,12 +436,12 @@ PTX_HD inline void lt_mark_triggers(PtxLexMarkShared& sh, const PtxLexTileArgs& 
         const uint32_t k = at >> 7;
         if (sh.chunk_special[k]) continue;        // lexed by the serial walk
         const uint32_t ms = sh.chunk_ms[k], me = sh.chunk_me[k];
-        if (kind == LP_T1 && off < LT_BYTES && lt_trigger_benign(a.text, pos, ms, me)) continue;
+        if (kind == LP_T1 && off < LT_BYTES && lt_trigger_benign(sh, a.text, pos, ms, me)) continue;
         if (kind & (LP_T1 | LP_T3)) {
             // the run of soft bytes around the trigger is lexed from its first byte, which is a token start (several
             // triggers in one run do the same work and write the same bits)
             uint32_t j = pos < me ? pos : me - 1;
-            while (j > ms && pos - j <= LT_BACK_CAP && lx_soft(a.text[j - 1])) j--;
+            while (j > ms && pos - j <= LT_BACK_CAP && lt_soft_class(sh.cls[a.text[j - 1]])) j--;
             if (pos - j > LT_BACK_CAP) { a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, tile * LT_CHUNKS + k) - 1] = 1; continue; }
             lt_chain(sh, a.text, tile_base, j, me);
         }
