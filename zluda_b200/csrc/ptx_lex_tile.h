@@ -415,20 +415,21 @@ PTX_HD inline bool lt_trigger_benign(const PtxLexMarkShared& sh, const uint8_t* 
 PTX_HD inline void lt_mark_triggers(PtxLexMarkShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t tid, uint32_t nt) {
     const uint32_t tile_base = tile * LT_BYTES;
     const uint32_t n_trig = sh.n_trig > LT_TRIG_CAP ? 0u : sh.n_trig;
-    for (uint32_t t = tid; t < n_trig + 1; t += nt) {
-        if (t == n_trig) {
-            // a run of soft bytes that begins in front of the tile may hold a number or a "::" literal: lex it from its start
-            const uint32_t c = tile * LT_CHUNKS;
-            if (c >= a.n_chunks || sh.chunk_special[0]) continue;
-            const uint32_t ms = sh.chunk_ms[0], me = sh.chunk_me[0];
-            if (tile_base >= me || tile_base <= ms || !lt_soft_class(sh.cls[a.text[tile_base]]) || !lt_soft_class(sh.cls[a.text[tile_base - 1]])) continue;
+    // the block's last thread: a run of soft bytes that begins in front of the tile may hold a number or a "::" literal;
+    // it is lexed from its start (the triggers go to the first threads: on the device another warp, at the same time)
+    if (tid == nt - 1) {
+        const uint32_t c = tile * LT_CHUNKS;
+        const uint32_t ms = sh.chunk_ms[0], me = sh.chunk_me[0];
+        if (c < a.n_chunks && !sh.chunk_special[0] && tile_base < me && tile_base > ms && lt_soft_class(sh.cls[a.text[tile_base]]) &&
+            lt_soft_class(sh.cls[a.text[tile_base - 1]])) {
             uint32_t q = tile_base - 1;
             while (q > ms && tile_base - q <= LT_BACK_CAP && lt_soft_class(sh.cls[a.text[q - 1]])) q--;
-            if (tile_base - q > LT_BACK_CAP) { a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, c) - 1] = 1; continue; }
+            if (tile_base - q > LT_BACK_CAP) a.mod_flag[ptx_upper_bound_u32(a.info.mcb, a.info.n_modules, c) - 1] = 1;
             // one byte past the tile's first: a trigger there (a digit behind a dot, the second colon) looks back into the run
-            if (lt_run_has_trigger(sh, a.text, q, tile_base + 1 < me ? tile_base + 1 : me)) lt_chain(sh, a.text, tile_base, q, me);
-            continue;
+            else if (lt_run_has_trigger(sh, a.text, q, tile_base + 1 < me ? tile_base + 1 : me)) lt_chain(sh, a.text, tile_base, q, me);
         }
+    }
+    for (uint32_t t = tid; t < n_trig; t += nt) {
         const uint32_t off = sh.trig[t] & 0xFFFFu, kind = sh.trig[t] >> 16;
         const uint32_t pos = tile_base + off;
         // T1 sits on its digit; T2 and T3 sit one byte behind the sigil / the first colon they are about
