@@ -529,14 +529,14 @@ struct PtxLexEmitShared {
     uint16_t tokoff[LT_TOK_CAP];        // tile offset of token r of the pass
     uint16_t exact[LT_EXACT_CAP];       // tokens left to the second round, by their rank in the pass
     uint16_t kwlist[LT_KW_CAP];         // first round -> keyword round: the tokens that may spell a keyword, likewise
-    uint32_t n_exact, n_kw;
-    // The tile's text, one spare word behind every 32 bytes: the threads of a warp work on consecutive 32-byte windows,
-    // and with a stride of nine words instead of eight their byte reads fall into different banks.
-    uint32_t text[LT_BYTES / 4 + LT_WORDS + 16];
+    uint32_t n_listed;                  // entries of exact[] << 16 | entries of kwlist[]
+    // The tile's text and twelve words of zeros behind it.  The threads of a warp work on consecutive tokens: their byte
+    // reads fall into a stretch of a hundred bytes or so, different banks without further ado.
+    uint32_t text[LT_BYTES / 4 + 12];
 };
-// byte `o` of the tile (o may run a few bytes past the tile: zeros), and text word `i`, in the skewed layout
-PTX_HD inline unsigned lt_tb(const PtxLexEmitShared& sh, uint32_t o) { return ((const uint8_t*)sh.text)[o + ((o >> 5) << 2)]; }
-PTX_HD inline uint32_t lt_tw(const PtxLexEmitShared& sh, uint32_t i) { return sh.text[i + (i >> 3)]; }
+// byte `o` of the tile (o may run a few bytes past the tile: zeros), and text word `i`
+PTX_HD inline unsigned lt_tb(const PtxLexEmitShared& sh, uint32_t o) { return ((const uint8_t*)sh.text)[o]; }
+PTX_HD inline uint32_t lt_tw(const PtxLexEmitShared& sh, uint32_t i) { return sh.text[i]; }
 
 // once per block: the constant tables
 PTX_HD inline void lt_emit_tables(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tid, uint32_t nt) {
@@ -585,11 +585,11 @@ PTX_HD inline void lt_emit_init(PtxLexEmitShared& sh, const PtxLexTileArgs& a, u
 #endif
         for (uint32_t j = 0; j < LT_TEXT_LOADS; j++) {
             const uint32_t i = tid + j * nt;
-            if (i < LT_BYTES / 4) sh.text[i + (i >> 3)] = tx[j];
+            if (i < LT_BYTES / 4) sh.text[i] = tx[j];
         }
-        for (uint32_t i = LT_BYTES / 4 + tid; i < LT_BYTES / 4 + 12; i += nt) sh.text[i + (i >> 3)] = 0u;
+        for (uint32_t i = LT_BYTES / 4 + tid; i < LT_BYTES / 4 + 12; i += nt) sh.text[i] = 0u;
     } else {
-        for (uint32_t i = tid; i < LT_BYTES / 4 + 12; i += nt) sh.text[i + (i >> 3)] = i < n_words ? src[i] : 0u;
+        for (uint32_t i = tid; i < LT_BYTES / 4 + 12; i += nt) sh.text[i] = i < n_words ? src[i] : 0u;
     }
 }
 // length of the run of word characters that starts at tile offset o (at most 32; the bits behind the tile are zero)
@@ -729,19 +729,24 @@ PTX_HD inline LtPass lt_emit_pass(const PtxLexEmitShared& sh, uint32_t pass) {
     p.n = sh.chunk_rank[p.c_b] - p.base;
     return p;
 }
-// a slot in a list of the block for every caller with `want` set; on the device all 32 lanes of the warp call it
-// together and the warp takes its slots with one atomic operation
-PTX_HD inline uint32_t lt_list_slot(uint32_t* counter, bool want) {
+// Slots in the two lists of the block (numbers and their like; keyword candidates) for every caller that wants one;
+// the counter holds both lengths (the first list's in the high half).  On the device all 32 lanes of the warp call it
+// together and the warp takes its slots with one atomic operation.
+PTX_HD inline void lt_list_slots(uint32_t* counter, bool want_exact, bool want_kw, uint32_t* slot_exact, uint32_t* slot_kw) {
 #ifdef __CUDA_ARCH__
-    const uint32_t m = __ballot_sync(0xFFFFFFFFu, want);
-    if (!m) return 0;
+    const uint32_t me = __ballot_sync(0xFFFFFFFFu, want_exact), mk = __ballot_sync(0xFFFFFFFFu, want_kw);
+    if (!(me | mk)) return;
     const uint32_t lane = threadIdx.x & 31u;
     uint32_t base = 0;
-    if (lane == (uint32_t)(__ffs(m) - 1)) base = atomicAdd(counter, (uint32_t)__popc(m));
-    base = __shfl_sync(0xFFFFFFFFu, base, __ffs(m) - 1);
-    return base + (uint32_t)__popc(m & ((1u << lane) - 1u));
+    if (lane == 0) base = atomicAdd(counter, ((uint32_t)__popc(me) << 16) | (uint32_t)__popc(mk));
+    base = __shfl_sync(0xFFFFFFFFu, base, 0);
+    const uint32_t below = (1u << lane) - 1u;
+    *slot_exact = (base >> 16) + (uint32_t)__popc(me & below);
+    *slot_kw = (base & 0xFFFFu) + (uint32_t)__popc(mk & below);
 #else
-    return want ? (*counter)++ : 0u;
+    *slot_exact = *counter >> 16;
+    *slot_kw = *counter & 0xFFFFu;
+    *counter += ((uint32_t)want_exact << 16) | (uint32_t)want_kw;
 #endif
 }
 // Listing: one thread per 32-byte window of the pass writes the tile offsets of its tokens to their ranks
@@ -761,7 +766,7 @@ PTX_HD inline void lt_emit_list(PtxLexEmitShared& sh, uint32_t pass, uint32_t ti
             sh.tokoff[r++] = (uint16_t)(w * 32u + b);
         }
     }
-    if (tid == 0) sh.n_exact = sh.n_kw = 0;
+    if (tid == 0) sh.n_listed = 0;
 }
 // First round: one thread per token, the same few steps for every token: first byte, length from the word-character
 // bits, kind by the first byte.  Every token but the numbers, strings and the unusual (second round: exact rules) is
@@ -796,8 +801,8 @@ PTX_HD inline void lt_emit_first(PtxLexEmitShared& sh, const PtxLexTileArgs& a, 
                                (word & ((uint32_t)(run >= 32u) | (uint32_t)(off + len >= LT_BYTES)));
         const bool want_exact = valid && exact;
         const bool want_kw = valid && !exact && kw && len <= PTX_KW_MAXLEN;
-        const uint32_t slot_e = lt_list_slot(&sh.n_exact, want_exact);
-        const uint32_t slot_k = lt_list_slot(&sh.n_kw, want_kw);
+        uint32_t slot_e = 0, slot_k = 0;
+        lt_list_slots(&sh.n_listed, want_exact, want_kw, &slot_e, &slot_k);
         if (!valid) continue;
         const uint32_t j = j0 + p.base + r;
         if (exact) {
@@ -822,7 +827,7 @@ PTX_HD inline void lt_emit_first(PtxLexEmitShared& sh, const PtxLexTileArgs& a, 
 PTX_HD inline void lt_emit_keywords(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t pass, uint32_t tid, uint32_t nt) {
     const uint32_t j0 = a.cnt[tile * LT_CHUNKS].a;
     const LtPass p = lt_emit_pass(sh, pass);
-    const uint32_t n_kw = sh.n_kw < LT_KW_CAP ? sh.n_kw : LT_KW_CAP;
+    const uint32_t listed = sh.n_listed & 0xFFFFu, n_kw = listed < LT_KW_CAP ? listed : LT_KW_CAP;
     for (uint32_t x = tid; x < n_kw; x += nt) {
         const uint32_t r = sh.kwlist[x], off = sh.tokoff[r];
         const uint32_t len = 1 + lt_word_run(sh, off + 1);
@@ -838,7 +843,7 @@ PTX_HD inline void lt_emit_keywords(PtxLexEmitShared& sh, const PtxLexTileArgs& 
 PTX_HD inline void lt_emit_second(PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile, uint32_t pass, uint32_t tid, uint32_t nt) {
     const uint32_t tile_base = tile * LT_BYTES, j0 = a.cnt[tile * LT_CHUNKS].a;
     const LtPass p = lt_emit_pass(sh, pass);
-    const uint32_t n_exact = sh.n_exact < LT_EXACT_CAP ? sh.n_exact : LT_EXACT_CAP;
+    const uint32_t listed = sh.n_listed >> 16, n_exact = listed < LT_EXACT_CAP ? listed : LT_EXACT_CAP;
     for (uint32_t x = tid; x < n_exact; x += nt) {
         const uint32_t r = sh.exact[x], off = sh.tokoff[r];
         lt_emit_exact_tile(sh, a, tile_base, j0 + p.base + r, off, sh.chunk_me[off >> 7]);
