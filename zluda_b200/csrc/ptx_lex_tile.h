@@ -678,6 +678,41 @@ struct LtTileBytes {
 PTX_HD inline void lt_emit_exact_tile(const PtxLexEmitShared& sh, const PtxLexTileArgs& a, uint32_t tile_base, uint32_t j, uint32_t off, uint32_t me) {
     const bool module_ends_here = me - tile_base <= LT_BYTES;
     const uint32_t end = module_ends_here ? me - tile_base : LT_BYTES;
+    // Most numbers are a few decimal digits or a 0f float: short straight-line code for those (the threads of a warp hold
+    // numbers of all sorts, and the general rules below are long).  Up to nine decimal digits with no '.', 'U' or tenth
+    // digit behind them are a DECIMAL below 2^31 (literal code 0: lx_number, ptx_literal_scan); a lone 0 likewise; 0f and
+    // eight hexadecimal digits are an F32HEX with code 0.  Everything else, and anything near the end of the tile or the
+    // module, takes the general rules.
+    if (off + 12u <= end) {
+        const unsigned c0 = lt_tb(sh, off);
+        uint32_t len = 0, kind = T_DECIMAL;
+        if (c0 - '1' < 9u) {
+            uint32_t q = off + 1;
+            while (q < off + 9u && lt_tb(sh, q) - '0' < 10u) q++;
+            const unsigned c = lt_tb(sh, q);
+            if (c - '0' >= 10u && c != '.' && c != 'U') len = q - off;
+        } else if (c0 == '0') {
+            const unsigned c = lt_tb(sh, off + 1), d = c | 32u;
+            if (d == 'f') {
+                uint32_t hex = 1;
+                for (uint32_t i = 2; i < 10; i++) {
+                    const unsigned ch = lt_tb(sh, off + i);
+                    hex &= (uint32_t)(ch - '0' < 10u) | (uint32_t)((ch | 32u) - 'a' < 6u);
+                }
+                if (hex) { len = 10; kind = T_F32HEX; }
+            } else if (c - '0' >= 10u && c != '.' && c != 'U' && d != 'x' && d != 'd') {
+                len = 1;
+            }
+        }
+        if (len) {
+            PtxTokenWord t;
+            t.x = tile_base + off;
+            t.y = len | (kind << 16);
+            ((PtxTokenWord*)a.tokens)[j] = t;
+            a.kinds[j] = (uint16_t)kind;
+            return;
+        }
+    }
     if (off < end && lx_digit(lt_tb(sh, off))) {
         const LtTileBytes bytes{&sh, 0};
         uint32_t len;
