@@ -290,3 +290,25 @@ def dense_token_texts():
     for _ in range(6):
         texts.append("".join(rng.choice(pieces) for _ in range(30000)))
     return texts
+
+
+def numbers_across_tile_ends():
+    """One module per probe and shift: a `mov` whose immediate is the probe, placed so that the probe slides across the
+    end of the first 8 KiB lexer tile (the module has to begin where a tile begins: parse it alone)."""
+    probes = ["123456789.12345678e-05", "1.5e+3", "1.5e", "7.25", "0d3FF0000000000000", "0f3F800000", "0f3F80000", "0x1F2e3D4cU", "4294967295U",
+              "18446744073709551615", "18446744073709551616", "017", "09", "0", "5", "123456789", "1234567890", "2147483648", "999999999U",
+              "0f3F80000G", "0F3f80000a", "12.", "00", "0x", "0d1"]
+    head = HEADER + ".visible .entry k()\n{\n.reg .f64 %fd<4>;\n"
+    texts = []
+    for probe in probes:
+        for shift in range(0, 24):
+            stmt = "mov.f64 %%fd1, %s;\n" % probe
+            # filler statements up to the tile end, then the probe shifted across it
+            target = 8192 - len("mov.f64 %fd1, ") - len(probe) + shift
+            body, filler = "", "add.s32 %r1, %r2, 3;\n"
+            while len(head) + len(body) + len(filler) < target - 40:
+                body += filler
+            pad = target - len(head) - len(body)
+            body += "/*" + "x" * max(0, pad - 5) + "*/\n" if pad >= 5 else " " * max(0, pad)
+            texts.append(head + body + stmt + "ret;\n}\n")
+    return texts

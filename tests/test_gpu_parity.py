@@ -119,6 +119,15 @@ def test_dense_tiles_lex_like_the_oracle(oracle, ctx):
         assert oracle.lex(text) == ctx.lex(text), text[:40]
 
 
+def test_numbers_across_tile_ends(oracle, ctx):
+    """Every kind of numeric literal at every position around the end of an 8 KiB lexer tile."""
+    for t in cases.numbers_across_tile_ends():          # one module per batch: the module begins where a tile begins
+        b = ctx.parse_batch([t], 1)
+        dump = b.dump(0)
+        b.free()
+        assert dump == oracle.parse(t, 1)[1], t[-80:]
+
+
 def test_corpora(oracle, ctx):
     sets = {
         "config0": corpus.config0(n_kernels=8, n_instr=2000),

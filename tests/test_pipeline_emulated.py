@@ -236,22 +236,7 @@ def test_long_runs_of_soft_bytes_stay_linear(oracle, emu):
 def test_numbers_across_tile_ends(oracle, emu):
     """Every kind of numeric literal at every position around the end of an 8 KiB lexer tile: the number rules run on
     the tile's copy of the text only when the number and what the rules look at behind it lie inside the tile."""
-    probes = ["123456789.12345678e-05", "1.5e+3", "1.5e", "7.25", "0d3FF0000000000000", "0f3F800000", "0f3F80000", "0x1F2e3D4cU", "4294967295U",
-              "18446744073709551615", "18446744073709551616", "017", "09", "0"]
-    head = cases.HEADER + ".visible .entry k()\n{\n.reg .f64 %fd<4>;\n"
-    texts = []
-    for probe in probes:
-        for shift in range(0, 24):
-            stmt = "mov.f64 %%fd1, %s;\n" % probe
-            # filler statements up to the tile end, then the probe shifted across it
-            target = 8192 - len("mov.f64 %fd1, ") - len(probe) + shift
-            body, filler = "", "add.s32 %r1, %r2, 3;\n"
-            while len(head) + len(body) + len(filler) < target - 40:
-                body += filler
-            pad = target - len(head) - len(body)
-            body += "/*" + "x" * max(0, pad - 5) + "*/\n" if pad >= 5 else " " * max(0, pad)
-            texts.append(head + body + stmt + "ret;\n}\n")
-    for t in texts:          # one module per batch: the module begins where a tile begins
+    for t in cases.numbers_across_tile_ends():          # one module per batch: the module begins where a tile begins
         assert emu.parse([t], 1)[0][0] == oracle.parse(t, 1)[1], t[-80:]
 
 
