@@ -730,7 +730,10 @@ inline void ptx_stage_decode(BK& bk, PtxWork& w, PtxCounters& host_counters) {
         }
     });
     // T2: decode the representatives of the classes this slice added, with tagged output, and spell out their signature
-    bk.pf("decode_representatives", PTX_MAX_CLASSES, [=] PTX_HD(size_t k) {
+    // (thread i takes new class (i / 32) + (i % 32) * (PTX_MAX_CLASSES / 32): the first 8,192 new classes go to lane 0 of
+    // a warp each.  Representatives are statements of different shapes; 32 of them in one warp ran one after the other.)
+    bk.pf("decode_representatives", PTX_MAX_CLASSES, [=] PTX_HD(size_t i) {
+        const size_t k = (i >> 5) + (i & 31u) * (PTX_MAX_CLASSES / 32u);
         size_t id = (size_t)cs.state[2] + k;
         if (id >= cs.state[0] || id >= PTX_MAX_CLASSES) return;
         uint32_t u = cs.rep_unit[id];
