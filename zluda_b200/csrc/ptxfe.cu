@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(256) lex_tile_kernel(uint32_t n_chunks, const 
 // ---- the two block-cooperative lexer steps (ptx_lex_tile.h): one block per tile, a barrier between the phases
 __global__ void lex_fill_tables_kernel(PtxLexTables* t) { lt_fill_tables(t, threadIdx.x, blockDim.x); }
 // Persistent blocks: the tables are loaded once, then the block takes every gridDim.x-th tile.
-__global__ void __launch_bounds__(256, 6) lex_mark_kernel(PtxLexTileArgs a, uint32_t n_tiles) {
+__global__ void __launch_bounds__(256, 8) lex_mark_kernel(PtxLexTileArgs a, uint32_t n_tiles) {
     __shared__ PtxLexMarkShared sh;
     const uint32_t tid = threadIdx.x;
     lt_mark_tables(sh, a, tid, 256);
