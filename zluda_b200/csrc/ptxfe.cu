@@ -104,6 +104,9 @@ __global__ void __launch_bounds__(256, 8) lex_mark_kernel(PtxLexTileArgs a, uint
         __syncthreads();
         lt_mark_simple(sh, a, tile, tid, 256);
         __syncthreads();
+        // ask for the text of the block's next tile while the rest of this one is settled
+        if (tid < LT_BYTES / 128u && (uint64_t)tile + gridDim.x + 1 < n_tiles)       // a whole tile
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(a.text + ((size_t)tile + gridDim.x) * LT_BYTES + tid * 128u));
         lt_mark_special(sh, a, tile, tid, 256);
         __syncthreads();
         lt_mark_triggers(sh, a, tile, tid, 256);
@@ -120,6 +123,13 @@ __global__ void __launch_bounds__(256, 5) lex_emit_kernel(PtxLexTileArgs a, uint
         __syncthreads();
         lt_emit_init(sh, a, tile, tid, 256);
         __syncthreads();
+        // ask for the block's next tile (text, start bits, word bits) while this one is worked on
+        if ((uint64_t)tile + gridDim.x + 1 < n_tiles) {     // a whole tile: every line asked for lies inside the arrays
+            const size_t next = (size_t)tile + gridDim.x;
+            if (tid < LT_BYTES / 128u) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.text + next * LT_BYTES + tid * 128u));
+            else if (tid < LT_BYTES / 128u + 8u) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.start_bits + next * LT_WORDS + (tid - LT_BYTES / 128u) * 32u));
+            else if (tid < LT_BYTES / 128u + 16u) asm volatile("prefetch.global.L2 [%0];" ::"l"(a.word_bits + next * LT_WORDS + (tid - LT_BYTES / 128u - 8u) * 32u));
+        }
         const uint32_t passes = lt_emit_passes(sh);
         for (uint32_t pass = 0; pass < passes; pass++) {
             if (pass) __syncthreads();
