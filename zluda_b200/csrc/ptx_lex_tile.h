@@ -879,7 +879,9 @@ PTX_HD inline void lt_emit_second(PtxLexEmitShared& sh, const PtxLexTileArgs& a,
     const uint32_t tile_base = tile * LT_BYTES, j0 = a.cnt[tile * LT_CHUNKS].a;
     const LtPass p = lt_emit_pass(sh, pass);
     const uint32_t listed = sh.n_listed >> 16, n_exact = listed < LT_EXACT_CAP ? listed : LT_EXACT_CAP;
-    for (uint32_t x = tid; x < n_exact; x += nt) {
+    // from the block's last thread down: the keyword round, which runs just before without a barrier, leaves its last,
+    // partly filled turn to the first threads
+    for (uint32_t x = nt - 1 - tid; x < n_exact; x += nt) {
         const uint32_t r = sh.exact[x], off = sh.tokoff[r];
         lt_emit_exact_tile(sh, a, tile_base, j0 + p.base + r, off, sh.chunk_me[off >> 7]);
     }
