@@ -40,7 +40,7 @@ UNIT = "GB/s"
 
 # (dram__bytes_read.sum + dram__bytes_write.sum) / text bytes, from the ncu captures summarised under profiles/
 NCU_DRAM_BYTES_PER_TEXT_BYTE = {      # from the ncu captures summarised under profiles/ (512 MiB instance of the workload)
-    "lex_emit": 4.23, "lex_mark": 1.31, "structure": 0.74, "lex_context_vectors": 1.03, "emit_records": 4.48,
+    "lex_emit": 4.20, "lex_mark": 1.32, "structure": 0.74, "lex_context_vectors": 1.03, "emit_records": 4.48,
 }
 
 
